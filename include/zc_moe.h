@@ -1,0 +1,184 @@
+/* zc_moe.h — C ABI of the B200 (sm_100a) Mixture-of-Experts layer.
+ *
+ * This is the boundary a ZeroCool-style engine binds instead of its Metal operator calls for the MoE
+ * layer. The reference has no FFI layer of its own: the layer is `Buf Model::moe(const Buf& x, int layer,
+ * uint32_t tokens, const std::atomic<bool>* cancel, const Buf& predict)` (include/engine/model.hpp:156,
+ * src/engine/model.cpp:431-557) built from `class Metal` operators (include/engine/metal.hpp:101-119).
+ * Each entry point below names the reference interface it replaces.
+ *
+ * Conventions
+ *  - Plain C, no exceptions: every call returns ZC_OK or a negative code; zc_moe_last_error() gives the
+ *    text the reference would have thrown (invalid_argument -> ZC_EINVAL, out_of_range -> ZC_ERANGE,
+ *    runtime_error -> ZC_EEXEC).
+ *  - The handle owns the HBM-resident expert records and all scratch. x / out belong to the caller.
+ *  - Calls taking a stream are stream-ordered and do not block the host. `stream` is a cudaStream_t
+ *    passed as void* (NULL = the legacy default stream).
+ *  - One host thread drives a handle at a time (the reference's single-coordinator rule,
+ *    include/engine/metal.hpp:45-47).
+ *  - All arguments are validated on the host before anything is launched. Conditions only the device
+ *    can see (a token whose router scores select fewer than top_k experts) set a status word read by
+ *    zc_moe_status(), like the reference's sparse_status_ (src/engine/model.cpp:118-120).
+ *  - There is no CPU fallback: without a CUDA device zc_moe_create fails with ZC_EEXEC.
+ */
+#ifndef ZC_MOE_H
+#define ZC_MOE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZC_OK          0
+#define ZC_EINVAL     -1   /* std::invalid_argument in the reference */
+#define ZC_ERANGE     -2   /* std::out_of_range */
+#define ZC_EEXEC      -3   /* std::runtime_error ("Metal execution: ..." / CUDA error) */
+#define ZC_ECANCELLED -4   /* "generation cancelled", src/engine/model.cpp:15 */
+#define ZC_ENOMEM     -5
+
+/* Element types. Numbering follows Resident::dtype (src/engine/metal.mm:1100-1102). */
+#define ZC_BF16 0
+#define ZC_F32  1
+#define ZC_F16  2
+
+/* Arithmetic contract.
+ * ZC_ARITH_FP32:      fp32 accumulation everywhere, no intermediate rounding.
+ * ZC_ARITH_REFERENCE: every BF16 rounding boundary of kernels/metal/qwen.metal (gate/up, activation,
+ *                     down, combine) and the BF16 sum-of-four that multiplies the Q4 bias (:46-62). */
+#define ZC_ARITH_FP32      0
+#define ZC_ARITH_REFERENCE 1
+
+/* Bits of the device status word. */
+#define ZC_STATUS_INVALID_ROUTE 1u   /* "invalid router output", src/engine/model.cpp:459 */
+
+typedef struct zc_moe zc_moe;
+
+/* Layer geometry and formats. The reference fixes these at compile time
+ * (include/engine/storage.hpp:26-34: hidden 2560, ffn 640, 512 experts, top-10, Q4 group 64, BF16
+ * metadata); here they are parameters. Expert record layout: see zc_moe_load_layer. */
+typedef struct zc_moe_desc {
+    uint32_t hidden;         /* H, multiple of 64 */
+    uint32_t ffn;            /* F, expert intermediate width, multiple of 64 */
+    uint32_t experts;        /* E, routed experts seen by the router (multiple of 32, <= 1024) */
+    uint32_t top_k;          /* K <= 32 */
+    uint32_t layers;
+    uint32_t group;          /* quantisation group, 64 */
+    uint32_t max_tokens;     /* largest `tokens` any call will pass; sizes the scratch */
+    uint32_t first_expert;   /* expert parallelism: first routed expert whose record this handle holds */
+    uint32_t local_experts;  /* number of records held (0 = all E) */
+    uint32_t reserved0;
+    uint8_t  gate_bits, up_bits, down_bits;  /* 4 or 8 per projection */
+    uint8_t  q8_signed;      /* 8-bit codes are int8 (1) or uint8 (0; the reference's Q8, qwen.metal:112-125) */
+    uint8_t  meta_dtype;     /* scales / biases: ZC_BF16 or ZC_F16 */
+    uint8_t  act_dtype;      /* x: ZC_BF16 or ZC_F32 */
+    uint8_t  out_dtype;      /* out: ZC_BF16 or ZC_F32 */
+    uint8_t  router_dtype;   /* router weight and shared-gate vector: ZC_F32 or ZC_BF16 */
+    uint8_t  has_shared;     /* layer has a shared expert with a sigmoid gate */
+    uint8_t  arith;          /* ZC_ARITH_* */
+    uint8_t  reserved[6];
+    uint64_t record_bytes;   /* payload of one record = sum over projections of codes+scales+biases */
+    uint64_t record_stride;  /* distance between records in a layer file (>= record_bytes) */
+} zc_moe_desc;
+
+/* Fills record_bytes / record_stride (stride = payload rounded up to 16 KiB, as
+ * scripts/qwen/prepare_storage.py:140-160 lays records out) from the other fields. */
+int zc_moe_desc_finalize(zc_moe_desc* desc);
+
+/* Replaces Model::Model's Metal + Resident + ExpertCache construction for this path
+ * (src/engine/model.cpp:47-117): allocates HBM for every layer's records, router and shared-expert
+ * tensors, and the scratch for max_tokens. On failure *out is NULL and zc_last_error() has the text. */
+int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out);
+void zc_moe_destroy(zc_moe* moe);
+const char* zc_moe_last_error(const zc_moe* moe);
+const char* zc_last_error(void);
+
+/* Replaces ExpertStore::read / ExpertCache::acquire (src/engine/storage.cpp:507-516, 631-674): records
+ * are copied once into HBM instead of being streamed per use. `records` holds `count` records at
+ * desc.record_stride for experts [first_expert, first_expert+count) and may be host or device memory.
+ * Record layout (expert_linear, src/engine/metal.mm:1124-1129, generalised): projections gate, up, down
+ * in that order, each [codes | scales | biases]; codes row-major [N, K*bits/8] (Q4: uint32 words of 8
+ * nibbles, k ascending from the least significant nibble); scales/biases [N, K/group] 16-bit.
+ * router_w: [E, H]; shared_record: one record or NULL; shared_gate_w: [1, H] or NULL.
+ * Any pointer may be NULL to leave that tensor as it is. */
+int zc_moe_load_layer(zc_moe* moe, uint32_t layer, const void* records, uint32_t first_expert, uint32_t count,
+                      const void* router_w, const void* shared_record, const void* shared_gate_w);
+
+/* Device addresses of a layer's resident tensors, for producers that fill HBM in place. */
+int zc_moe_layer_buffers(zc_moe* moe, uint32_t layer, void** records, void** router_w,
+                         void** shared_record, void** shared_gate_w);
+
+/* Replaces Metal::linear(router gate, x, tokens, float_output=true) (src/engine/model.cpp:434 ->
+ * src/engine/metal.mm:818-822, router_mm + router_accumulate): logits [tokens, E] fp32 with the
+ * reference's sixteen-partition accumulation order. x, logits: device memory. */
+int zc_moe_router(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, float* logits, void* stream);
+
+/* Replaces Metal::route (include/engine/metal.hpp:112, src/engine/metal.mm:261-266, route_simd
+ * qwen.metal:768-795): ids [tokens, K] int32 in rank order (unfilled ranks -1), weights [tokens, K]
+ * fp32 = softmax over the selected scores. Device memory. */
+int zc_moe_route(zc_moe* moe, const float* logits, uint32_t tokens, int32_t* ids, float* weights, void* stream);
+
+/* Replaces the host-side dispatch of Model::moe (src/engine/model.cpp:449-461, 473-474) and the row
+ * lists of encode_expert_rows (src/engine/pipeline.cpp:18-23), on the device: a stable counting sort of
+ * the flat slots p = t*K + j by expert id. offsets [E+1], perm [tokens*K]; the tokens routed to expert e
+ * are perm[offsets[e] .. offsets[e+1]) / K. Slots with an id outside [0, E) are dropped and flagged. */
+int zc_moe_permute(zc_moe* moe, const int32_t* ids, uint32_t tokens, int32_t* offsets, int32_t* perm, void* stream);
+
+/* Replaces Buf Model::moe(x, layer, tokens, ...) (src/engine/model.cpp:431-557) for short batches —
+ * the reference's decode / short-append branch (encode_expert_rows with q4_gate_mv_r2 / q4_mv_r*,
+ * src/engine/pipeline.cpp:24-25): memory-bound kernels that stream each selected record once.
+ * x [tokens, H] in act_dtype, out [tokens, H] in out_dtype, device memory, must not overlap. */
+int zc_moe_decode(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream);
+
+/* Same contract for long batches — the reference's prefill panels (src/engine/prefill.cpp:66,
+ * pipeline.cpp:18-30: gathered q4_gate_up + q4_mm + scatter_experts per expert): one grouped
+ * GEMM over all experts' row groups on the tensor cores. */
+int zc_moe_prefill(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream);
+
+/* Model::moe with the family chosen from `tokens`. */
+int zc_moe_forward(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream);
+
+/* Model::moe for callers that hold HOST tensors (the reference's Buf is CPU-visible unified memory):
+ * copies x in, runs zc_moe_forward, copies out back and waits. x_host/out_host: host memory. */
+int zc_moe_forward_host(zc_moe* moe, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host);
+
+/* The whole stack of `layers` MoE layers chained on one stream, layer l+1 reading
+ * act_dtype(out_l / rms(out_l)) — the stand-in for the residual + norm between MoE layers that the
+ * measurement uses so that no cross-layer overlap is credited. out receives the last layer's output. */
+int zc_moe_stack(zc_moe* moe, const void* x, uint32_t tokens, void* out, void* stream);
+int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* out_host);
+
+/* zc_moe_stack without graph replay: the same launches issued one by one (used with the profiler below). */
+int zc_moe_stack_eager(zc_moe* moe, const void* x, uint32_t tokens, void* out, void* stream);
+
+/* Per-kernel device timing, the counterpart of KernelConfig.profile / Metal::take_profile
+ * (include/engine/metal.hpp:31, 93; src/engine/metal.mm:510-557): between begin and end every kernel
+ * launched outside a graph is bracketed by CUDA events on its stream. end waits for the device and returns,
+ * per kernel kind k < 8, the summed milliseconds and the number of launches; zc_moe_kernel_name(k) names it. */
+int zc_moe_profile_begin(zc_moe* moe);
+int zc_moe_profile_end(zc_moe* moe, double* ms_per_kind, uint64_t* launches_per_kind);
+const char* zc_moe_kernel_name(int kind);
+
+/* Device buffers holding the last call's routing (the reference exposes the same tensors through
+ * --trace-dir: route_l, .weights, src/engine/model.cpp:447-448, 549-552). Valid until the next call. */
+int zc_moe_last_routing(zc_moe* moe, const int32_t** ids, const float** weights,
+                        const int32_t** offsets, const int32_t** perm, const float** logits);
+
+/* Blocking copy of handle-owned device memory (a resident tensor or the routing buffers above) to the host;
+ * waits for all earlier work on the device. The reference reads the same tensors in place (unified memory). */
+int zc_moe_read_device(zc_moe* moe, void* host_dst, const void* device_src, uint64_t bytes);
+
+/* Waits for the handle's work on `stream` and returns the device status word (then clears it). */
+int zc_moe_status(zc_moe* moe, void* stream, uint32_t* status);
+
+/* Number of kernel launches the handle has issued since creation (graph replays count their nodes). */
+uint64_t zc_moe_launch_count(const zc_moe* moe);
+
+/* Seeded synthetic tensors written straight into a layer's HBM buffers (benchmark and test inputs;
+ * the definition of the generator is zerocool_b200/synth.py). No counterpart in the reference, which
+ * measures on a real checkpoint. */
+int zc_synth_fill_layer(zc_moe* moe, uint32_t layer, uint64_t seed, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZC_MOE_H */

@@ -12,7 +12,7 @@ It writes
   numpy_moe_config0.npz         outputs of the reference's CPU oracle scripts/qwen/reference_numpy.py
                                 (function ``moe``, imported unmodified) on a seeded synthetic layer at
                                 the reference's native shape (hidden 2560, ffn 640, top-10, BF16
-                                metadata, shared expert), E = 16 experts, T = 5 tokens.
+                                metadata, shared expert), E = 32 experts, T = 5 tokens.
 The inputs of the second fixture are regenerated from the seed by zerocool_b200.synth, so only the
 outputs are stored.
 """
@@ -32,7 +32,7 @@ sys.path.insert(0, str(HERE.parent.parent))
 from zerocool_b200 import synth  # noqa: E402
 from zerocool_b200.records import ARITH_REFERENCE, BF16, F32, MoeConfig  # noqa: E402
 
-CONFIG0 = dict(hidden=2560, ffn=640, experts=16, top_k=10, layers=1, meta_dtype=BF16, act_dtype=F32,
+CONFIG0 = dict(hidden=2560, ffn=640, experts=32, top_k=10, layers=1, meta_dtype=BF16, act_dtype=F32,
                out_dtype=F32, router_dtype=BF16, has_shared=1, arith=ARITH_REFERENCE)
 CONFIG0_SEED, CONFIG0_TOKENS = 20260914, 5
 

@@ -1,0 +1,426 @@
+// C ABI of the B200 MoE library: handle lifetime, argument validation, layer orchestration.
+//
+// The orchestration is the device-side replacement of Model::moe (src/engine/model.cpp:431-557):
+// router -> route -> permute -> experts (gate/up, down; shared expert as one more item) -> combine,
+// all stream-ordered with no host synchronisation in between (the reference drains the GPU once per
+// layer to build the dispatch lists on the CPU, model.cpp:446).
+#include "common.cuh"
+
+#include <cstdio>
+#include <cstring>
+
+namespace zc {
+
+static thread_local std::string g_error;
+
+int fail(zc_moe* m, int code, const std::string& text) {
+    if (m) m->error = text;
+    g_error = text;
+    return code;
+}
+int check_launch(zc_moe* m, const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("CUDA launch of ") + what + ": " + cudaGetErrorString(e));
+    return ZC_OK;
+}
+
+namespace {
+
+size_t elem_bytes(int dtype) { return dtype == ZC_F32 ? 4 : 2; }
+
+int cuda_fail(zc_moe* m, cudaError_t e, const char* what) {
+    return fail(m, e == cudaErrorMemoryAllocation ? ZC_ENOMEM : ZC_EEXEC, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+template <typename T>
+int dev_alloc(zc_moe* m, T** p, size_t bytes) {
+    void* q = nullptr;
+    const cudaError_t e = cudaMalloc(&q, bytes ? bytes : 16);
+    if (e != cudaSuccess) return cuda_fail(m, e, "cudaMalloc");
+    m->allocations.push_back(q);
+    *p = static_cast<T*>(q);
+    return ZC_OK;
+}
+
+int validate_desc(const zc_moe_desc& d, std::string& why) {
+    auto bad = [&](const char* t) { why = t; return ZC_EINVAL; };
+    if (!d.hidden || !d.ffn || !d.experts || !d.top_k || !d.layers || !d.max_tokens) return bad("zero dimension in descriptor");
+    if (d.group != 64) return bad("unsupported affine matrix geometry: group must be 64");
+    if (d.hidden % 64 || d.ffn % 64) return bad("unsupported affine matrix geometry: hidden and ffn must be multiples of 64");
+    if (d.hidden > 4096) return bad("hidden above 4096 is not supported");
+    if (d.experts % 32 || d.experts > 1024) return bad("experts must be a multiple of 32 and at most 1024");
+    if (d.top_k > 32 || d.top_k > d.experts) return bad("top_k must be at most 32 and at most experts");
+    for (uint8_t b : {d.gate_bits, d.up_bits, d.down_bits}) if (b != 4 && b != 8) return bad("unsupported affine matrix geometry: bits must be 4 or 8");
+    if (d.gate_bits != d.up_bits) return bad("fused gate/up requires matching affine matrices");
+    if (d.meta_dtype != ZC_BF16 && d.meta_dtype != ZC_F16) return bad("metadata dtype must be BF16 or F16");
+    if (d.act_dtype != ZC_BF16 && d.act_dtype != ZC_F32) return bad("activation dtype must be BF16 or F32");
+    if (d.out_dtype != ZC_BF16 && d.out_dtype != ZC_F32) return bad("output dtype must be BF16 or F32");
+    if (d.router_dtype != ZC_BF16 && d.router_dtype != ZC_F32) return bad("router dtype must be BF16 or F32");
+    if (d.arith != ZC_ARITH_FP32 && d.arith != ZC_ARITH_REFERENCE) return bad("unknown arithmetic mode");
+    if (d.first_expert + (d.local_experts ? d.local_experts : d.experts) > d.experts) return bad("local expert range outside the router's experts");
+    uint64_t bytes = 0;
+    for (int p = 0; p < 3; ++p) { const Projection pr = projection_of(d, p); bytes = pr.biases + uint64_t(pr.N) * (pr.K / d.group) * 2; }
+    if (d.record_bytes != bytes) return bad("record_bytes does not match the projection geometry");
+    if (d.record_stride < d.record_bytes || d.record_stride % 16) return bad("record_stride must cover the record and be a multiple of 16");
+    return ZC_OK;
+}
+
+Call make_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out) {
+    Call c = m->scratch;
+    const LayerMem& L = m->layers[layer];
+    c.x = x; c.out = out;
+    c.records = L.records; c.router_w = L.router_w; c.shared_record = L.shared_record; c.shared_gate_w = L.shared_gate_w;
+    c.T = tokens;
+    return c;
+}
+
+int check_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const void* out) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    if (!tokens || tokens > m->d.max_tokens) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens");
+    if (!x || !out) return fail(m, ZC_EINVAL, "missing input or output buffer");
+    const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), ob = size_t(tokens) * m->d.hidden * elem_bytes(m->d.out_dtype);
+    const char* a = static_cast<const char*>(x); const char* b = static_cast<const char*>(out);
+    if (a < b + ob && b < a + xb) return fail(m, ZC_EINVAL, "invalid or overlapping output");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    return ZC_OK;
+}
+
+int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s) {
+    const Call c = make_call(m, layer, x, tokens, out);
+    int n, total = 0;
+    if ((n = launch_router(m, c, s)) < 0) return n; total += n;
+    if ((n = launch_route_permute(m, c, s, true, true)) < 0) return n; total += n;
+    if ((n = launch_experts_decode(m, c, s)) < 0) return n; total += n;
+    if ((n = launch_combine(m, c, s)) < 0) return n; total += n;
+    return total;
+}
+
+}  // namespace
+}  // namespace zc
+
+using namespace zc;
+
+extern "C" {
+
+const char* zc_last_error(void) { return g_error.c_str(); }
+const char* zc_moe_last_error(const zc_moe* m) { return m ? m->error.c_str() : g_error.c_str(); }
+uint64_t zc_moe_launch_count(const zc_moe* m) { return m ? m->launches : 0; }
+
+int zc_moe_desc_finalize(zc_moe_desc* d) {
+    if (!d) return fail(nullptr, ZC_EINVAL, "null descriptor");
+    if (!d->group) d->group = 64;
+    if (!d->hidden || !d->ffn || d->hidden % d->group || d->ffn % d->group) return fail(nullptr, ZC_EINVAL, "unsupported affine matrix geometry");
+    if (!d->local_experts) d->local_experts = d->experts - d->first_expert;
+    uint64_t bytes = 0;
+    for (int p = 0; p < 3; ++p) { const Projection pr = projection_of(*d, p); bytes = pr.biases + uint64_t(pr.N) * (pr.K / d->group) * 2; }
+    d->record_bytes = bytes;
+    d->record_stride = (bytes + 16383) / 16384 * 16384;
+    return ZC_OK;
+}
+
+int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
+    if (out) *out = nullptr;
+    if (!desc || !out) return fail(nullptr, ZC_EINVAL, "null descriptor or output");
+    zc_moe_desc d = *desc;
+    if (!d.local_experts) d.local_experts = d.experts - d.first_expert;
+    std::string why;
+    if (validate_desc(d, why) != ZC_OK) return fail(nullptr, ZC_EINVAL, why);
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) return fail(nullptr, ZC_EEXEC, "no CUDA device: this library has no CPU path");
+    if (device < 0 || device >= count) return fail(nullptr, ZC_EINVAL, "device index outside the visible devices");
+    if ((e = cudaSetDevice(device)) != cudaSuccess) return cuda_fail(nullptr, e, "cudaSetDevice");
+    cudaDeviceProp prop{};
+    cudaGetDeviceProperties(&prop, device);
+    if (prop.major < 10) return fail(nullptr, ZC_EEXEC, "this library is built for sm_100a (B200) only");
+
+    zc_moe* m = new zc_moe();
+    m->d = d; m->device = device;
+    m->layers.resize(d.layers);
+    const size_t T = d.max_tokens, H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k;
+    int rc = ZC_OK;
+    auto A = [&](auto** p, size_t bytes) { if (rc == ZC_OK) rc = dev_alloc(m, p, bytes); };
+    for (uint32_t l = 0; l < d.layers; ++l) {
+        LayerMem& L = m->layers[l];
+        A(&L.records, size_t(d.local_experts) * d.record_stride);
+        uint8_t* rw = nullptr; A(&rw, E * H * elem_bytes(d.router_dtype)); L.router_w = rw;
+        if (d.has_shared) {
+            A(&L.shared_record, d.record_stride);
+            uint8_t* gw = nullptr; A(&gw, H * elem_bytes(d.router_dtype)); L.shared_gate_w = gw;
+        }
+    }
+    Call& c = m->scratch;
+    A(&c.logits, T * E * 4); A(&c.gate_logit, T * 4); A(&c.ids, T * K * 4); A(&c.weights, T * K * 4);
+    A(&c.offsets, (E + 1) * 4); A(&c.perm, T * K * 4); A(&c.active, E * 4); A(&c.counters, 16 * 4);
+    A(&c.hbuf, (T * K + T) * F * 4); A(&c.expert_out, T * K * H * 4); A(&c.shared_out, T * H * 4); A(&c.status, 16);
+    uint8_t* p0 = nullptr; uint8_t* p1 = nullptr; uint8_t* dx = nullptr; uint8_t* dout = nullptr; uint8_t* dfin = nullptr;
+    A(&p0, T * H * 4); A(&p1, T * H * 4); A(&dx, T * H * 4); A(&dout, T * H * 4); A(&dfin, T * H * 4);
+    m->act[0] = p0; m->act[1] = p1; m->dev_x = dx; m->dev_out = dout; m->dev_final = dfin;
+    if (rc == ZC_OK && (e = cudaMemset(c.status, 0, 16)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+    if (rc == ZC_OK && (e = cudaMemset(c.counters, 0, 64)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+    if (rc == ZC_OK && (e = cudaMallocHost(&m->host_x, T * H * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMallocHost");
+    if (rc == ZC_OK && (e = cudaMallocHost(&m->host_out, T * H * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMallocHost");
+    if (rc == ZC_OK && (e = cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking)) != cudaSuccess) rc = cuda_fail(m, e, "cudaStreamCreate");
+    if (rc != ZC_OK) { g_error = m->error; zc_moe_destroy(m); return rc; }
+    c.H = d.hidden; c.F = d.ffn; c.E = d.experts; c.K = d.top_k;
+    c.first_expert = d.first_expert; c.local_experts = d.local_experts; c.record_stride = d.record_stride;
+    c.gate = projection_of(d, 0); c.up = projection_of(d, 1); c.down = projection_of(d, 2);
+    c.act_dtype = d.act_dtype; c.out_dtype = d.out_dtype; c.meta_f16 = d.meta_dtype == ZC_F16; c.router_dtype = d.router_dtype;
+    c.has_shared = d.has_shared; c.ref = d.arith == ZC_ARITH_REFERENCE; c.q8_signed = d.q8_signed;
+    *out = m;
+    return ZC_OK;
+}
+
+void zc_moe_destroy(zc_moe* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    cudaDeviceSynchronize();
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);
+    for (void* p : m->allocations) cudaFree(p);
+    if (m->host_x) cudaFreeHost(m->host_x);
+    if (m->host_out) cudaFreeHost(m->host_out);
+    if (m->own_stream) cudaStreamDestroy(m->own_stream);
+    delete m;
+}
+
+int zc_moe_load_layer(zc_moe* m, uint32_t layer, const void* records, uint32_t first_expert, uint32_t count,
+                      const void* router_w, const void* shared_record, const void* shared_gate_w) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    const zc_moe_desc& d = m->d;
+    LayerMem& L = m->layers[layer];
+    cudaError_t e;
+    if (records) {
+        if (first_expert < d.first_expert || uint64_t(first_expert) + count > uint64_t(d.first_expert) + d.local_experts)
+            return fail(m, ZC_ERANGE, "expert range outside the records this handle holds");
+        e = cudaMemcpy(L.records + size_t(first_expert - d.first_expert) * d.record_stride, records, size_t(count) * d.record_stride, cudaMemcpyDefault);
+        if (e != cudaSuccess) return cuda_fail(m, e, "copy of expert records");
+    }
+    if (router_w && (e = cudaMemcpy(L.router_w, router_w, size_t(d.experts) * d.hidden * elem_bytes(d.router_dtype), cudaMemcpyDefault)) != cudaSuccess)
+        return cuda_fail(m, e, "copy of router weight");
+    if ((shared_record || shared_gate_w) && !d.has_shared) return fail(m, ZC_EINVAL, "layer has no shared expert");
+    if (shared_record && (e = cudaMemcpy(L.shared_record, shared_record, d.record_bytes, cudaMemcpyDefault)) != cudaSuccess)
+        return cuda_fail(m, e, "copy of shared expert record");
+    if (shared_gate_w && (e = cudaMemcpy(L.shared_gate_w, shared_gate_w, size_t(d.hidden) * elem_bytes(d.router_dtype), cudaMemcpyDefault)) != cudaSuccess)
+        return cuda_fail(m, e, "copy of shared gate weight");
+    return ZC_OK;
+}
+
+int zc_moe_layer_buffers(zc_moe* m, uint32_t layer, void** records, void** router_w, void** shared_record, void** shared_gate_w) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    const LayerMem& L = m->layers[layer];
+    if (records) *records = L.records;
+    if (router_w) *router_w = L.router_w;
+    if (shared_record) *shared_record = L.shared_record;
+    if (shared_gate_w) *shared_gate_w = L.shared_gate_w;
+    return ZC_OK;
+}
+
+int zc_moe_router(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, float* logits, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    if (!tokens || tokens > m->d.max_tokens || !x || !logits) return fail(m, ZC_EINVAL, "linear input shape");
+    Call c = make_call(m, layer, x, tokens, nullptr);
+    c.logits = logits;
+    const int n = launch_router(m, c, static_cast<cudaStream_t>(stream));
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_route(zc_moe* m, const float* logits, uint32_t tokens, int32_t* ids, float* weights, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    // Metal::route: "invalid route selection buffers" (src/engine/metal.mm:262-264)
+    if (!tokens || tokens > m->d.max_tokens || !logits || !ids || !weights) return fail(m, ZC_EINVAL, "invalid route selection buffers");
+    Call c = m->scratch;
+    c.T = tokens; c.logits = const_cast<float*>(logits); c.ids = ids; c.weights = weights;
+    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), true, false);
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_permute(zc_moe* m, const int32_t* ids, uint32_t tokens, int32_t* offsets, int32_t* perm, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (!tokens || tokens > m->d.max_tokens || !ids || !offsets || !perm) return fail(m, ZC_EINVAL, "invalid permutation buffers");
+    Call c = m->scratch;
+    c.T = tokens; c.ids = const_cast<int32_t*>(ids); c.offsets = offsets; c.perm = perm;
+    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), false, true);
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_decode(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
+    int rc = check_call(m, layer, x, tokens, out);
+    if (rc != ZC_OK) return rc;
+    const int n = run_layer(m, layer, x, tokens, out, static_cast<cudaStream_t>(stream));
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_prefill(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
+    return zc_moe_decode(m, layer, x, tokens, out, stream);
+}
+
+int zc_moe_forward(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
+    return zc_moe_decode(m, layer, x, tokens, out, stream);
+}
+
+int zc_moe_forward_host(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (!tokens || tokens > m->d.max_tokens || !x_host || !out_host) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
+    const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), ob = size_t(tokens) * m->d.hidden * elem_bytes(m->d.out_dtype);
+    cudaStream_t s = m->own_stream;
+    cudaError_t e;
+    if ((e = cudaMemcpyAsync(m->dev_x, x_host, xb, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(m, e, "host to device copy");
+    int rc = zc_moe_forward(m, layer, m->dev_x, tokens, m->dev_out, s);
+    if (rc != ZC_OK) return rc;
+    if ((e = cudaMemcpyAsync(out_host, m->dev_out, ob, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return cuda_fail(m, e, "device to host copy");
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(m, e, "MoE execution");
+    return ZC_OK;
+}
+
+// Launches the chained stack on `s`: layer l reads `in` (l = 0) or the normalised previous output.
+static int stack_launches(zc_moe* m, const void* x, uint32_t tokens, void* out, cudaStream_t s) {
+    const zc_moe_desc& d = m->d;
+    int total = 0;
+    const void* in = x;
+    for (uint32_t l = 0; l < d.layers; ++l) {
+        void* layer_out = l + 1 == d.layers ? out : m->dev_out;
+        int n = run_layer(m, l, in, tokens, layer_out, s);
+        if (n < 0) return n;
+        total += n;
+        if (l + 1 < d.layers) {
+            void* next = m->act[l & 1];
+            if ((n = launch_rms_act(m, layer_out, d.out_dtype, next, d.act_dtype, tokens, d.hidden, s)) < 0) return n;
+            total += n;
+            in = next;
+        }
+    }
+    return total;
+}
+
+int zc_moe_stack(zc_moe* m, const void* x, uint32_t tokens, void* out, void* stream) {
+    int rc = check_call(m, 0, x, tokens, out);
+    if (rc != ZC_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // One CUDA graph per (tokens, x, out): the launch sequence is fixed — routing only changes which
+    // blocks find work — so replaying the graph removes the per-launch host cost of ~6 kernels a layer.
+    const uint64_t key = (uint64_t(tokens) * 0x9E3779B97F4A7C15ull) ^ reinterpret_cast<uint64_t>(x) ^ (reinterpret_cast<uint64_t>(out) << 1);
+    auto found = m->graphs.find(key);
+    if (found == m->graphs.end()) {
+        cudaStream_t cs = m->own_stream;
+        cudaError_t e;
+        // first use of each kernel outside capture, so that function attributes are set once
+        int n = stack_launches(m, x, tokens, out, cs);
+        if (n < 0) return n;
+        if ((e = cudaStreamSynchronize(cs)) != cudaSuccess) return cuda_fail(m, e, "MoE stack execution");
+        if ((e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal)) != cudaSuccess) return cuda_fail(m, e, "graph capture");
+        n = stack_launches(m, x, tokens, out, cs);
+        cudaGraph_t graph = nullptr;
+        e = cudaStreamEndCapture(cs, &graph);
+        if (n < 0) { if (graph) cudaGraphDestroy(graph); return n; }
+        if (e != cudaSuccess) return cuda_fail(m, e, "graph capture");
+        cudaGraphExec_t exec = nullptr;
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return cuda_fail(m, e, "graph instantiation");
+        found = m->graphs.emplace(key, zc_moe::Graph{exec, uint64_t(n)}).first;
+    }
+    const cudaError_t e = cudaGraphLaunch(found->second.exec, s);
+    if (e != cudaSuccess) return cuda_fail(m, e, "graph launch");
+    m->launches += found->second.nodes;
+    return ZC_OK;
+}
+
+int zc_moe_stack_host(zc_moe* m, const void* x_host, uint32_t tokens, void* out_host) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (!tokens || tokens > m->d.max_tokens || !x_host || !out_host) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
+    const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), ob = size_t(tokens) * m->d.hidden * elem_bytes(m->d.out_dtype);
+    cudaStream_t s = m->own_stream;
+    cudaError_t e;
+    if ((e = cudaMemcpyAsync(m->dev_x, x_host, xb, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(m, e, "host to device copy");
+    int rc = zc_moe_stack(m, m->dev_x, tokens, m->dev_final, s);
+    if (rc != ZC_OK) return rc;
+    if ((e = cudaMemcpyAsync(out_host, m->dev_final, ob, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return cuda_fail(m, e, "device to host copy");
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(m, e, "MoE stack execution");
+    return ZC_OK;
+}
+
+int zc_moe_last_routing(zc_moe* m, const int32_t** ids, const float** weights, const int32_t** offsets, const int32_t** perm, const float** logits) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (ids) *ids = m->scratch.ids;
+    if (weights) *weights = m->scratch.weights;
+    if (offsets) *offsets = m->scratch.offsets;
+    if (perm) *perm = m->scratch.perm;
+    if (logits) *logits = m->scratch.logits;
+    return ZC_OK;
+}
+
+int zc_moe_read_device(zc_moe* m, void* host_dst, const void* device_src, uint64_t bytes) {
+    if (!m || !host_dst || !device_src) return fail(m, ZC_EINVAL, "null handle or buffer");
+    const cudaError_t e = cudaMemcpy(host_dst, device_src, bytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(m, e, "device read");
+    return ZC_OK;
+}
+
+int zc_moe_status(zc_moe* m, void* stream, uint32_t* status) {
+    if (!m || !status) return fail(m, ZC_EINVAL, "null handle or status");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->own_stream);
+    if (e != cudaSuccess) return cuda_fail(m, e, "MoE execution");
+    if ((e = cudaMemcpy(status, m->scratch.status, 4, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail(m, e, "status read");
+    if ((e = cudaMemset(m->scratch.status, 0, 4)) != cudaSuccess) return cuda_fail(m, e, "status clear");
+    return ZC_OK;
+}
+
+int zc_moe_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, void* stream) {
+    int rc = check_call(m, 0, x, tokens, out);
+    if (rc != ZC_OK) return rc;
+    const int n = stack_launches(m, x, tokens, out, static_cast<cudaStream_t>(stream));
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+const char* zc_moe_kernel_name(int kind) {
+    static const char* names[KERNEL_KINDS] = {"router", "route", "permute", "gate_up", "down", "combine", "rms_act"};
+    return kind >= 0 && kind < KERNEL_KINDS ? names[kind] : nullptr;
+}
+
+int zc_moe_profile_begin(zc_moe* m) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    m->profiling = true;
+    return ZC_OK;
+}
+
+int zc_moe_profile_end(zc_moe* m, double* ms_per_kind, uint64_t* launches_per_kind) {
+    if (!m || !ms_per_kind || !launches_per_kind) return fail(m, ZC_EINVAL, "null handle or output");
+    m->profiling = false;
+    cudaError_t e = cudaDeviceSynchronize();
+    for (int k = 0; k < KERNEL_KINDS; ++k) { ms_per_kind[k] = 0; launches_per_kind[k] = 0; }
+    for (auto& sp : m->spans) {
+        float ms = 0;
+        if (e == cudaSuccess && cudaEventElapsedTime(&ms, sp.start, sp.stop) == cudaSuccess) { ms_per_kind[sp.kind] += ms; ++launches_per_kind[sp.kind]; }
+        cudaEventDestroy(sp.start); cudaEventDestroy(sp.stop);
+    }
+    m->spans.clear();
+    if (e != cudaSuccess) return cuda_fail(m, e, "MoE execution");
+    return ZC_OK;
+}
+
+int zc_synth_fill_layer(zc_moe* m, uint32_t layer, uint64_t seed, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    const int n = launch_synth_layer(m, layer, seed, static_cast<cudaStream_t>(stream));
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+}  // extern "C"

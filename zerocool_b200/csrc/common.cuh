@@ -1,0 +1,201 @@
+// Shared device helpers and the handle layout of the B200 MoE library.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <string>
+#include <vector>
+#include <unordered_map>
+
+#include "../../include/zc_moe.h"
+
+namespace zc {
+
+// ---------------------------------------------------------------------------------------------
+// Scalar helpers
+// ---------------------------------------------------------------------------------------------
+
+// Round fp32 to the nearest-even bf16 value, NaN stays NaN (kernels/metal/qwen.metal:17-21).
+__device__ __forceinline__ float bf_round(float x) {
+    uint32_t u = __float_as_uint(x);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return __uint_as_float(0x7fc00000u);
+    return __uint_as_float((u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u);
+}
+__device__ __forceinline__ uint16_t bf_bits(float x) { return uint16_t(__float_as_uint(bf_round(x)) >> 16); }
+__device__ __forceinline__ float bf_to_float(uint16_t v) { return __uint_as_float(uint32_t(v) << 16); }
+__device__ __forceinline__ float meta_to_float(uint16_t v, bool is_f16) {
+    return is_f16 ? __half2float(__ushort_as_half(v)) : bf_to_float(v);
+}
+
+// Sigmoid in the reference's form (qwen.metal:30-32): 1/(1+exp|x|), mirrored for x >= 0.
+__device__ __forceinline__ float sigmoid_f(float x) {
+    float y = __fdiv_rn(1.0f, 1.0f + expf(fabsf(x)));
+    return x < 0 ? y : 1.0f - y;
+}
+// BF16-staged sigmoid (qwen.metal:33-35). The exponential is evaluated in double and rounded once,
+// which is the correctly rounded single-precision value the reference's activation tables pin.
+__device__ __forceinline__ float sigmoid_bf(float x) {
+    float e = float(exp(double(fabsf(x))));
+    float y = bf_round(__fdiv_rn(1.0f, bf_round(1.0f + bf_round(e))));
+    return x < 0 ? y : bf_round(1.0f - y);
+}
+
+__device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col). Lane (g = lane/4, c = lane%4) holds
+//   a0: A[g][2c,2c+1]   a1: A[g+8][2c,2c+1]   a2: A[g][2c+8,2c+9]   a3: A[g+8][2c+8,2c+9]
+//   b0: B[2c,2c+1][g]   b1: B[2c+8,2c+9][g]
+//   d0,d1: D[g][2c,2c+1]   d2,d3: D[g+8][2c,2c+1]
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Eight 4-bit codes of one little-endian word -> four bf16x2 registers holding the integer values
+// (k0,k4) (k1,k5) (k2,k6) (k3,k7); low half first. 0x4300 is bf16 128.0, whose ulp is 1, so
+// (0x4300 | q) is exactly 128+q and the subtraction is exact.
+__device__ __forceinline__ void dequant_q4_word(uint32_t w, uint32_t (&p)[4]) {
+    const uint32_t magic = 0x43004300u, mask = 0x000f000fu;
+    const __nv_bfloat162 off = __floats2bfloat162_rn(128.0f, 128.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t v = ((w >> (4 * i)) & mask) | magic;
+        __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), off);
+        p[i] = *reinterpret_cast<uint32_t*>(&r);
+    }
+}
+// Four 8-bit codes of one word -> two bf16x2 registers (k0,k1) (k2,k3). Every integer in
+// [-128, 255] is exact in bf16. is_signed reads the byte as int8.
+__device__ __forceinline__ void dequant_q8_word(uint32_t w, bool is_signed, uint32_t (&p)[2]) {
+    if (is_signed) w ^= 0x80808080u;
+    const float off = is_signed ? 8388608.0f + 128.0f : 8388608.0f;
+    float f[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(0x4b000000u | ((w >> (8 * i)) & 0xffu)) - off;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(f[0], f[1]), hi = __floats2bfloat162_rn(f[2], f[3]);
+    p[0] = *reinterpret_cast<uint32_t*>(&lo);
+    p[1] = *reinterpret_cast<uint32_t*>(&hi);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Record geometry (expert_linear, src/engine/metal.mm:1124-1129, parametric)
+// ---------------------------------------------------------------------------------------------
+struct Projection {
+    uint64_t codes, scales, biases;  // byte offsets inside a record
+    uint32_t N, K, bits;
+};
+inline uint64_t projection_bytes(uint32_t N, uint32_t K, uint32_t bits, uint32_t group) {
+    return uint64_t(N) * K * bits / 8 + 2 * uint64_t(N) * (K / group) * 2;
+}
+inline Projection projection_of(const zc_moe_desc& d, int p) {
+    const uint32_t bits[3] = {d.gate_bits, d.up_bits, d.down_bits};
+    uint64_t offset = 0;
+    for (int i = 0; i < p; ++i) offset += projection_bytes(i == 2 ? d.hidden : d.ffn, i == 2 ? d.ffn : d.hidden, bits[i], d.group);
+    Projection r;
+    r.N = p == 2 ? d.hidden : d.ffn;
+    r.K = p == 2 ? d.ffn : d.hidden;
+    r.bits = bits[p];
+    r.codes = offset;
+    r.scales = offset + uint64_t(r.N) * r.K * r.bits / 8;
+    r.biases = r.scales + uint64_t(r.N) * (r.K / d.group) * 2;
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Handle
+// ---------------------------------------------------------------------------------------------
+struct LayerMem {
+    uint8_t* records = nullptr;       // [local_experts, record_stride]
+    void* router_w = nullptr;         // [E, H]
+    uint8_t* shared_record = nullptr; // one record, or null
+    void* shared_gate_w = nullptr;    // [1, H], or null
+};
+
+// Everything a kernel needs to know about one call, passed by value.
+struct Call {
+    const void* x;            // [T, H] act dtype
+    void* out;                // [T, H] out dtype
+    const uint8_t* records;
+    const void* router_w;
+    const uint8_t* shared_record;
+    const void* shared_gate_w;
+    float* logits;            // [T, E]
+    float* gate_logit;        // [T]
+    int32_t* ids;             // [T, K]
+    float* weights;           // [T, K]
+    int32_t* offsets;         // [E+1]
+    int32_t* perm;            // [T*K]
+    int32_t* active;          // [E] ascending ids of experts with work
+    int32_t* counters;        // [0] number of active experts
+    float* hbuf;              // [T*K + T, F]: rows in permuted slot order, then shared rows
+    float* expert_out;        // [T*K, H] by original slot
+    float* shared_out;        // [T, H]
+    uint32_t* status;
+    uint32_t T, H, F, E, K;
+    uint32_t first_expert, local_experts;
+    uint64_t record_stride;
+    Projection gate, up, down;
+    uint8_t act_dtype, out_dtype, meta_f16, router_dtype, has_shared, ref, q8_signed;
+};
+
+}  // namespace zc
+
+struct zc_moe {
+    zc_moe_desc d{};
+    int device = 0;
+    std::vector<zc::LayerMem> layers;
+    std::vector<void*> allocations;
+    zc::Call scratch{};           // scratch pointers (x/out/layer fields filled per call)
+    void* act[2] = {nullptr, nullptr};   // stack ping-pong activations [max_tokens, H]
+    void* host_x = nullptr;       // pinned staging for the host entry points
+    void* host_out = nullptr;
+    void* dev_x = nullptr;
+    void* dev_out = nullptr;
+    void* dev_final = nullptr;
+    cudaStream_t own_stream = nullptr;
+    std::string error;
+    uint64_t launches = 0;
+    struct Graph { cudaGraphExec_t exec; uint64_t nodes; };
+    std::unordered_map<uint64_t, Graph> graphs;
+    // Optional per-kernel timing (zc_moe_profile_begin/end): one event pair per launch.
+    bool profiling = false;
+    struct Span { int kind; cudaEvent_t start, stop; };
+    std::vector<Span> spans;
+};
+
+namespace zc {
+// Launchers (each returns the number of kernels launched, or a negative ZC_* code with moe->error set).
+int launch_router(zc_moe* m, const Call& c, cudaStream_t s);
+int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute);
+int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s);
+int launch_combine(zc_moe* m, const Call& c, cudaStream_t s);
+int launch_rms_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s);
+int launch_synth_layer(zc_moe* m, uint32_t layer, uint64_t seed, cudaStream_t s);
+enum KernelKind { KERNEL_ROUTER = 0, KERNEL_ROUTE, KERNEL_PERMUTE, KERNEL_GATE_UP, KERNEL_DOWN, KERNEL_COMBINE, KERNEL_RMS_ACT, KERNEL_KINDS };
+// Brackets one kernel launch with events when profiling is enabled.
+struct Timed {
+    zc_moe* m; cudaStream_t s; int kind; cudaEvent_t stop = nullptr;
+    Timed(zc_moe* m_, cudaStream_t s_, int kind_) : m(m_), s(s_), kind(kind_) {
+        if (!m->profiling) return;
+        cudaEvent_t start;
+        cudaEventCreate(&start); cudaEventCreate(&stop);
+        cudaEventRecord(start, s);
+        m->spans.push_back({kind, start, stop});
+    }
+    ~Timed() { if (stop) cudaEventRecord(stop, s); }
+};
+int fail(zc_moe* m, int code, const std::string& text);
+int check_launch(zc_moe* m, const char* what);
+}  // namespace zc
