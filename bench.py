@@ -1,0 +1,379 @@
+#!/usr/bin/env python3
+"""Benchmark of the MoE-layer hot path: decode MoE stack at the Qwen3-Next-like shape.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+A step is one pass of the 48-layer MoE stack (hidden 2048, 512 routed experts top-10 + 1 shared expert,
+ffn 512, affine-Q4 group 64 with fp16 scale/bias, bf16 activations) over one batch of tokens, the layers
+chained on one stream through x_{l+1} = bf16(out_l / rms(out_l)). All 48 layers' records (43.5 GB) are
+resident in HBM, so every step streams its weights from DRAM (inputs far larger than the 126 MB L2).
+Inputs are seeded synthetic tensors with the shapes and value distributions of the benchmark
+specification; the real checkpoint is not available.
+
+Rank 0 prints ONE JSON line. `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same
+metric through the host-buffer entry point (pinned host activations copied in and out inside the timed
+region); `roofline` reports the dominant kernel against the measured HBM bandwidth; `cpu_baseline` is the
+CPU restatement of the reference's arithmetic (oracle/) timed on this machine's host cores on a bounded
+sample. With --impl reference the same CPU code is the thing timed.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from zerocool_b200 import synth  # noqa: E402
+from zerocool_b200.records import BF16, F16, F32, MoeConfig  # noqa: E402
+
+METRIC = "MoE-layer tokens/s at Qwen3-Next shape (decode, 48-layer MoE stack)"
+SEED = 20261125
+BATCHES = (1, 4, 16, 64)
+
+
+def config(layers, max_tokens):
+    return MoeConfig(hidden=2048, ffn=512, experts=512, top_k=10, layers=layers, meta_dtype=F16, act_dtype=BF16,
+                     out_dtype=BF16, router_dtype=F32, has_shared=1, max_tokens=max_tokens)
+
+
+def workload(cfg, tokens, n_gpus):
+    return {
+        "workload": f"BASELINE config 2: decode MoE stack, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
+                    f"top-{cfg.top_k} + 1 shared, ffn {cfg.ffn}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router, "
+                    f"batch of {tokens} tokens per GPU, layers chained through bf16(out/rms(out))",
+        "tokens_per_gpu": tokens, "layers": cfg.layers,
+        "parallelism": f"dp{n_gpus}: independent replicas, tokens sharded, no data-path collective",
+        "l2": "no flush needed: each step streams the selected records of 48 different layers (GBs per step, 43.5 GB resident) through a 126 MB L2",
+        "accumulate": "f32", "weights": "q4_g64",
+    }
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def ncu_traffic():
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if there is one."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(path):
+        return json.load(open(path))
+    return {}
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [r.strip().split(",") for r in open(self.file.name) if r.strip()]
+        os.unlink(self.file.name)
+        sm, smax, power, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in rows:
+            try:
+                sm.append(float(r[0])); smax.append(float(r[1])); power.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.strip().lower() == "active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "power_w_max": float(max(power)),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def rms_glue(out):
+    """The inter-layer stand-in of the chained stack, on the CPU: bf16(out / rms(out))."""
+    from oracle import oracle
+    o = out.astype(np.float32)
+    scale = (1.0 / np.sqrt(np.mean(o * o, axis=-1, keepdims=True, dtype=np.float32))).astype(np.float32)
+    return oracle.bf(o * scale)
+
+
+def cpu_layer(cfg, layer, x, cache):
+    """One layer on the CPU checker; records of the selected experts are regenerated from the seed (cached)."""
+    from oracle import oracle
+    router = cache.setdefault(("router", layer), synth.router(cfg, SEED, layer))
+    logits = oracle.router_logits(x, router, cfg.router_dtype)
+    ids, _ = oracle.route(logits, cfg.top_k)
+    records = [None] * cfg.experts
+    for e in np.unique(ids):
+        if e >= 0:
+            records[e] = cache.setdefault(("record", layer, int(e)), synth.record(cfg, SEED, layer, int(e)))
+    shared = cache.setdefault(("shared", layer), synth.record(cfg, SEED, layer, synth.SHARED_EXPERT))
+    gate = cache.setdefault(("gate", layer), synth.shared_gate(cfg, SEED, layer))
+    t0 = time.perf_counter()
+    res = oracle.moe_layer(cfg.as_dict(), records, router, x, shared_record=shared, shared_gate_w=gate)
+    return res, time.perf_counter() - t0
+
+
+def cpu_sample(cfg, tokens, sample_layers, cache):
+    """Chained CPU run over the first `sample_layers` layers; returns seconds of arithmetic (generation excluded)."""
+    x = synth.activations(cfg, SEED, 0, tokens)
+    total = 0.0
+    for layer in range(sample_layers):
+        res, dt = cpu_layer(cfg, layer, x, cache)
+        total += dt
+        x = rms_glue(oracle_bf(res["out"]))
+    return total
+
+
+def oracle_bf(a):
+    from oracle import oracle
+    return oracle.bf(a)
+
+
+def run_reference(args):
+    """The reference arm: the CPU implementation of the path (the port under oracle/ — the reference's native
+    code is Apple Metal and cannot be built here), all host threads, on a bounded sample of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    oracle.build()
+    cfg = config(48, args.tokens)
+    sample_layers = args.cpu_layers
+    cache = {}
+    cpu_sample(cfg, args.tokens, sample_layers, cache)        # builds the record cache, untimed
+    for _ in range(max(args.warmup - 1, 0)):
+        cpu_sample(cfg, args.tokens, sample_layers, cache)
+    times = [cpu_sample(cfg, args.tokens, sample_layers, cache) for _ in range(args.steps)]
+    per_step = float(np.mean(times)) * cfg.layers / sample_layers
+    value = args.tokens / per_step
+    cores = oracle.threads()
+    sample = f"layers 0..{sample_layers - 1} of {cfg.layers} chained, {args.tokens} tokens, scaled by {cfg.layers}/{sample_layers}"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload(cfg, args.tokens, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_steps(torch, fn, steps, dist):
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = start.elapsed_time(stop)
+    if dist is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def layer_bytes(cfg, active, tokens):
+    """Algorithmic bytes of one layer: (U + S) records + the router matrix + activations in and out."""
+    a = 2
+    return (active + cfg.has_shared) * cfg.record_bytes + cfg.experts * cfg.hidden * 4 + tokens * cfg.hidden * 2 * a
+
+
+def run_ours(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as d
+        d.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = d
+    from zerocool_b200.moe import Moe
+    cfg = config(args.layers, max(BATCHES + (args.tokens,)))
+    m = Moe(cfg, local)
+    for layer in range(cfg.layers):
+        m.synth_fill_layer(layer, SEED)
+    torch.cuda.synchronize()
+    hbm_peak, peak_source = peaks()
+
+    def inputs(tokens):
+        x = synth.activations(cfg, SEED + rank, 0, tokens)
+        host = torch.from_numpy(x).to(torch.bfloat16).pin_memory()
+        return x, host, host.cuda()
+
+    # ---- parity gate, outside every timed region: layer 0 against the CPU checker -------------------
+    parity = None
+    if rank == 0 and not args.skip_parity:
+        from oracle import oracle
+        x_np, _, x_dev = inputs(args.tokens)
+        got = m.moe(0, x_dev).float().cpu().numpy()
+        routing = m.last_routing(args.tokens)
+        want, _ = cpu_layer(cfg, 0, x_np, {})
+        offsets, perm = oracle.permute(want["ids"], cfg.experts)
+        rms = float(np.sqrt(np.mean(want["out"].astype(np.float64) ** 2)))
+        bound = 2e-3 * rms + np.abs(want["out"]) * 2.0 ** -8          # tolerance + one bf16 rounding of the output
+        parity = {
+            "layer": 0, "tokens": args.tokens,
+            "ids_bit_exact": bool(np.array_equal(routing["ids"], want["ids"])),
+            "perm_bit_exact": bool(np.array_equal(routing["perm"], perm) and np.array_equal(routing["offsets"], offsets)),
+            "max_abs_err_over_rms": float(np.abs(got - want["out"]).max() / rms),
+            "within_tolerance": bool(np.all(np.abs(got - want["out"]) <= bound)),
+            "tolerance": "2e-3 x RMS + one bf16 rounding of the bf16 output",
+        }
+        if not (parity["ids_bit_exact"] and parity["perm_bit_exact"] and parity["within_tolerance"]):
+            raise RuntimeError(f"parity gate failed: {parity}")
+
+    # ---- timed region: K graph replays of the chained stack, inputs resident in HBM ------------------
+    def measure(tokens, steps, warmup):
+        _, host, x_dev = inputs(tokens)
+        out_dev = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device="cuda")
+        for _ in range(warmup):
+            m.stack(x_dev, out_dev)
+        before = m.launches
+        ms = time_steps(torch, lambda: m.stack(x_dev, out_dev), steps, dist)
+        launches = m.launches - before
+        active = m.active_counts()
+        finite = bool(torch.isfinite(out_dev.float()).all())
+        return ms, launches, active, finite, host, x_dev, out_dev
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, launches, active, finite, host, x_dev, out_dev = measure(args.tokens, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    if not finite:
+        raise RuntimeError("the chained stack produced non-finite values")
+    tokens_total = args.tokens * world
+    value = tokens_total / (ms * 1e-3)
+    step_bytes = float(sum(layer_bytes(cfg, int(a), args.tokens) for a in active))
+
+    # ---- end to end through the host-buffer entry point: pinned host x in, host out back, every step ----
+    out_host = torch.empty((args.tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory()
+    for _ in range(args.warmup):
+        m.stack_host(host, out_host)
+    e2e_ms = time_steps(torch, lambda: m.stack_host(host, out_host), args.steps, dist)
+    e2e = {"value": tokens_total / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+           "call": "zc_moe_stack_host (pinned host buffers; copies and the wait inside the timed region)"}
+
+    # ---- per-kernel device times over the same K steps (eager launches bracketed by CUDA events) --------
+    m.stack_eager(x_dev, out_dev)
+    torch.cuda.synchronize()
+    m.profile_begin()
+    for _ in range(args.steps):
+        m.stack_eager(x_dev, out_dev)
+    prof = m.profile_end()
+    total_prof = sum(v[0] for v in prof.values()) or 1.0
+    kernels = {k: {"launches": n, "avg_us": 1e3 * t / max(n, 1), "share": t / total_prof} for k, (t, n) in prof.items() if n}
+    dominant = max(kernels, key=lambda k: kernels[k]["share"])
+    active_eager = m.active_counts()
+    mean_items = float(np.mean(active_eager)) + cfg.has_shared
+    proj = {"gate_up": cfg.projection_bytes(0) + cfg.projection_bytes(1), "down": cfg.projection_bytes(2)}
+    act_bytes = {"gate_up": args.tokens * cfg.hidden * 2, "down": args.tokens * cfg.hidden * 2}
+    if dominant in proj:
+        alg = mean_items * proj[dominant] + act_bytes[dominant]
+    else:
+        alg = step_bytes / cfg.layers
+    achieved = alg / (kernels[dominant]["avg_us"] * 1e-6) / 1e9
+    traffic = ncu_traffic().get(dominant)
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "traffic": traffic, "peak_source": peak_source, "algorithmic_bytes_per_launch": alg,
+                "avg_launch_us": kernels[dominant]["avg_us"],
+                "definition": "(distinct routed experts of the layer + shared) x projection bytes of this kernel + activation bytes, averaged over the layers"}
+    step_achieved = step_bytes / (ms * 1e-3) / 1e9
+    roofline_step = {"bound": "hbm", "achieved": step_achieved, "peak": hbm_peak, "unit": "GB/s", "frac": step_achieved / hbm_peak,
+                     "algorithmic_bytes_per_step": step_bytes,
+                     "definition": "sum over layers of (U + S) x record bytes + router matrix + activations in/out, over the whole step time"}
+
+    # ---- the other decode batch sizes of the configuration (same stack, fewer steps) -------------------
+    batches = {}
+    if not args.skip_batches:
+        for t in BATCHES:
+            if t == args.tokens:
+                bms, act = ms, active
+            else:
+                bms, _, act, _, _, _, _ = measure(t, max(args.steps // 2, 5), 3)
+            b = float(sum(layer_bytes(cfg, int(a), t) for a in act))
+            batches[str(t)] = {"tokens_per_s": t * world / (bms * 1e-3), "ms_per_step": bms, "hbm_gbs": b / (bms * 1e-3) / 1e9,
+                               "frac_of_hbm_peak": b / (bms * 1e-3) / 1e9 / hbm_peak, "mean_active_experts": float(np.mean(act))}
+
+    # ---- CPU baseline on this machine's host cores, bounded sample ------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        from oracle import oracle
+        cache = {}
+        cpu_sample(cfg, args.tokens, args.cpu_layers, cache)
+        seconds = cpu_sample(cfg, args.tokens, args.cpu_layers, cache)
+        per_step = seconds * cfg.layers / args.cpu_layers
+        cpu = {"value": args.tokens / per_step, "unit": "tokens/s", "cores": oracle.threads(), "kind": "port",
+               "sample": f"layers 0..{args.cpu_layers - 1} of {cfg.layers} chained, {args.tokens} tokens, scaled by {cfg.layers}/{args.cpu_layers}; "
+                         f"{seconds:.1f} s of CPU arithmetic"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload(cfg, args.tokens, world), "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": roofline, "roofline_step": roofline_step, "kernels": kernels, "cpu_baseline": cpu, "batches": batches,
+            "parity": parity, "mean_active_experts": float(np.mean(active)),
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=64, help="token batch per GPU (the configuration names 1/4/16/64)")
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--cpu-layers", type=int, default=4, help="layers of the stack the CPU baseline runs (scaled to 48)")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-parity", action="store_true")
+    ap.add_argument("--skip-batches", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        args.cpu_layers = min(args.cpu_layers, 2)
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -138,14 +138,15 @@ int zc_moe_prefill(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, 
 int zc_moe_forward(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream);
 
 /* Model::moe for callers that hold HOST tensors (the reference's Buf is CPU-visible unified memory):
- * copies x in, runs zc_moe_forward, copies out back and waits. x_host/out_host: host memory. */
-int zc_moe_forward_host(zc_moe* moe, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host);
+ * on `stream`, copies x in, runs zc_moe_forward, copies out back, then waits for the stream.
+ * x_host/out_host: host memory (pinned memory makes the copies asynchronous to other streams). */
+int zc_moe_forward_host(zc_moe* moe, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream);
 
 /* The whole stack of `layers` MoE layers chained on one stream, layer l+1 reading
  * act_dtype(out_l / rms(out_l)) — the stand-in for the residual + norm between MoE layers that the
  * measurement uses so that no cross-layer overlap is credited. out receives the last layer's output. */
 int zc_moe_stack(zc_moe* moe, const void* x, uint32_t tokens, void* out, void* stream);
-int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* out_host);
+int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* out_host, void* stream);
 
 /* zc_moe_stack without graph replay: the same launches issued one by one (used with the profiler below). */
 int zc_moe_stack_eager(zc_moe* moe, const void* x, uint32_t tokens, void* out, void* stream);
@@ -162,6 +163,10 @@ const char* zc_moe_kernel_name(int kind);
  * --trace-dir: route_l, .weights, src/engine/model.cpp:447-448, 549-552). Valid until the next call. */
 int zc_moe_last_routing(zc_moe* moe, const int32_t** ids, const float** weights,
                         const int32_t** offsets, const int32_t** perm, const float** logits);
+
+/* Number of routed experts that received work in the most recent call of each layer, host_counts[layers]
+ * (the reference reports the same through its route trace, include/engine/route_trace.hpp). Blocking. */
+int zc_moe_active_counts(zc_moe* moe, int32_t* host_counts);
 
 /* Blocking copy of handle-owned device memory (a resident tensor or the routing buffers above) to the host;
  * waits for all earlier work on the device. The reference reads the same tensors in place (unified memory). */

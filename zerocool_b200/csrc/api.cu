@@ -71,6 +71,7 @@ Call make_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* 
     c.x = x; c.out = out;
     c.records = L.records; c.router_w = L.router_w; c.shared_record = L.shared_record; c.shared_gate_w = L.shared_gate_w;
     c.T = tokens;
+    c.layer = layer;
     return c;
 }
 
@@ -152,13 +153,13 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     }
     Call& c = m->scratch;
     A(&c.logits, T * E * 4); A(&c.gate_logit, T * 4); A(&c.ids, T * K * 4); A(&c.weights, T * K * 4);
-    A(&c.offsets, (E + 1) * 4); A(&c.perm, T * K * 4); A(&c.active, E * 4); A(&c.counters, 16 * 4);
+    A(&c.offsets, (E + 1) * 4); A(&c.perm, T * K * 4); A(&c.active, E * 4); A(&c.counters, (16 + size_t(d.layers)) * 4);
     A(&c.hbuf, (T * K + T) * F * 4); A(&c.expert_out, T * K * H * 4); A(&c.shared_out, T * H * 4); A(&c.status, 16);
     uint8_t* p0 = nullptr; uint8_t* p1 = nullptr; uint8_t* dx = nullptr; uint8_t* dout = nullptr; uint8_t* dfin = nullptr;
     A(&p0, T * H * 4); A(&p1, T * H * 4); A(&dx, T * H * 4); A(&dout, T * H * 4); A(&dfin, T * H * 4);
     m->act[0] = p0; m->act[1] = p1; m->dev_x = dx; m->dev_out = dout; m->dev_final = dfin;
     if (rc == ZC_OK && (e = cudaMemset(c.status, 0, 16)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
-    if (rc == ZC_OK && (e = cudaMemset(c.counters, 0, 64)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+    if (rc == ZC_OK && (e = cudaMemset(c.counters, 0, (16 + size_t(d.layers)) * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
     if (rc == ZC_OK && (e = cudaMallocHost(&m->host_x, T * H * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMallocHost");
     if (rc == ZC_OK && (e = cudaMallocHost(&m->host_out, T * H * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMallocHost");
     if (rc == ZC_OK && (e = cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking)) != cudaSuccess) rc = cuda_fail(m, e, "cudaStreamCreate");
@@ -270,11 +271,11 @@ int zc_moe_forward(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, vo
     return zc_moe_decode(m, layer, x, tokens, out, stream);
 }
 
-int zc_moe_forward_host(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host) {
+int zc_moe_forward_host(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream) {
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (!tokens || tokens > m->d.max_tokens || !x_host || !out_host) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
     const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), ob = size_t(tokens) * m->d.hidden * elem_bytes(m->d.out_dtype);
-    cudaStream_t s = m->own_stream;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if ((e = cudaMemcpyAsync(m->dev_x, x_host, xb, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(m, e, "host to device copy");
     int rc = zc_moe_forward(m, layer, m->dev_x, tokens, m->dev_out, s);
@@ -315,7 +316,9 @@ int zc_moe_stack(zc_moe* m, const void* x, uint32_t tokens, void* out, void* str
     if (found == m->graphs.end()) {
         cudaStream_t cs = m->own_stream;
         cudaError_t e;
-        // first use of each kernel outside capture, so that function attributes are set once
+        // First use of each kernel outside capture, so that function attributes are set once. The input
+        // may still be in flight on the caller's stream, so wait for that stream first.
+        if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(m, e, "MoE stack execution");
         int n = stack_launches(m, x, tokens, out, cs);
         if (n < 0) return n;
         if ((e = cudaStreamSynchronize(cs)) != cudaSuccess) return cuda_fail(m, e, "MoE stack execution");
@@ -337,11 +340,11 @@ int zc_moe_stack(zc_moe* m, const void* x, uint32_t tokens, void* out, void* str
     return ZC_OK;
 }
 
-int zc_moe_stack_host(zc_moe* m, const void* x_host, uint32_t tokens, void* out_host) {
+int zc_moe_stack_host(zc_moe* m, const void* x_host, uint32_t tokens, void* out_host, void* stream) {
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (!tokens || tokens > m->d.max_tokens || !x_host || !out_host) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
     const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), ob = size_t(tokens) * m->d.hidden * elem_bytes(m->d.out_dtype);
-    cudaStream_t s = m->own_stream;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if ((e = cudaMemcpyAsync(m->dev_x, x_host, xb, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(m, e, "host to device copy");
     int rc = zc_moe_stack(m, m->dev_x, tokens, m->dev_final, s);
@@ -358,6 +361,13 @@ int zc_moe_last_routing(zc_moe* m, const int32_t** ids, const float** weights, c
     if (offsets) *offsets = m->scratch.offsets;
     if (perm) *perm = m->scratch.perm;
     if (logits) *logits = m->scratch.logits;
+    return ZC_OK;
+}
+
+int zc_moe_active_counts(zc_moe* m, int32_t* host_counts) {
+    if (!m || !host_counts) return fail(m, ZC_EINVAL, "null handle or buffer");
+    const cudaError_t e = cudaMemcpy(host_counts, m->scratch.counters + 16, size_t(m->d.layers) * 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(m, e, "device read");
     return ZC_OK;
 }
 

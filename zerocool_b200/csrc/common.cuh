@@ -138,12 +138,12 @@ struct Call {
     int32_t* offsets;         // [E+1]
     int32_t* perm;            // [T*K]
     int32_t* active;          // [E] ascending ids of experts with work
-    int32_t* counters;        // [0] number of active experts
+    int32_t* counters;        // [0] number of active experts; [16 + layer] the same, kept per layer
     float* hbuf;              // [T*K + T, F]: rows in permuted slot order, then shared rows
     float* expert_out;        // [T*K, H] by original slot
     float* shared_out;        // [T, H]
     uint32_t* status;
-    uint32_t T, H, F, E, K;
+    uint32_t T, H, F, E, K, layer;
     uint32_t first_expert, local_experts;
     uint64_t record_stride;
     Projection gate, up, down;

@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const int32_t*
                                                                    uint32_t first_expert, uint32_t local_experts,
                                                                    int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
                                                                    int32_t* __restrict__ active, int32_t* __restrict__ counters,
-                                                                   uint32_t* status) {
+                                                                   uint32_t layer, uint32_t* status) {
     extern __shared__ int32_t hist[];                 // [PERMUTE_WARPS][E] per-warp counts, then cursors
     __shared__ int warp_totals[33];
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const int32_t*
     int n_active;
     const int slot = block_exclusive_scan(has_work, warp_totals, n_active);
     if (has_work) active[slot] = int32_t(threadIdx.x);
-    if (threadIdx.x == 0) counters[0] = n_active;
+    if (threadIdx.x == 0) { counters[0] = n_active; counters[16 + layer] = n_active; }
     __syncthreads();
     for (uint32_t base = begin; base < end; base += 32) {
         const uint32_t p = base + lane;
@@ -198,7 +198,7 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
         int rc;
         { Timed t(m, s, KERNEL_PERMUTE);
           permute_kernel<<<1, PERMUTE_THREADS, smem, s>>>(c.ids, c.T * c.K, c.E, c.first_expert, c.local_experts, c.offsets, c.perm,
-                                                         c.active, c.counters, c.status);
+                                                         c.active, c.counters, c.layer, c.status);
           rc = check_launch(m, "permute"); }
         if (rc < 0) return rc;
         ++launched;

@@ -26,7 +26,7 @@ EXPORTS = [
     "zc_moe_load_layer", "zc_moe_layer_buffers", "zc_moe_router", "zc_moe_route", "zc_moe_permute",
     "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_forward_host", "zc_moe_stack",
     "zc_moe_stack_host", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
-    "zc_moe_last_routing", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
+    "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
 ]
 
 
@@ -71,9 +71,10 @@ def load_library():
     lib.zc_moe_permute.argtypes = [vp, vp, u32, vp, vp, vp]
     for name in ("zc_moe_decode", "zc_moe_prefill", "zc_moe_forward"):
         getattr(lib, name).argtypes = [vp, u32, vp, u32, vp, vp]
-    lib.zc_moe_forward_host.argtypes = [vp, u32, vp, u32, vp]
+    lib.zc_moe_forward_host.argtypes = [vp, u32, vp, u32, vp, vp]
     lib.zc_moe_stack.argtypes = [vp, vp, u32, vp, vp]
-    lib.zc_moe_stack_host.argtypes = [vp, vp, u32, vp]
+    lib.zc_moe_stack_host.argtypes = [vp, vp, u32, vp, vp]
+    lib.zc_moe_active_counts.argtypes = [vp, vp]
     lib.zc_moe_stack_eager.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_profile_begin.argtypes = [vp]
     lib.zc_moe_profile_end.argtypes = [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(u64)]
@@ -231,7 +232,7 @@ class Moe:
     def moe_host(self, layer, x_host, out_host):
         """Model::moe for host tensors (pinned numpy/torch CPU memory): copies in, runs, copies out, waits."""
         tokens = x_host.shape[0]
-        self._check(self.lib.zc_moe_forward_host(self._h, layer, _ptr(x_host), tokens, _ptr(out_host)))
+        self._check(self.lib.zc_moe_forward_host(self._h, layer, _ptr(x_host), tokens, _ptr(out_host), self._stream()))
         return out_host
 
     def stack(self, x, out=None):
@@ -265,7 +266,7 @@ class Moe:
         return out
 
     def stack_host(self, x_host, out_host):
-        self._check(self.lib.zc_moe_stack_host(self._h, _ptr(x_host), x_host.shape[0], _ptr(out_host)))
+        self._check(self.lib.zc_moe_stack_host(self._h, _ptr(x_host), x_host.shape[0], _ptr(out_host), self._stream()))
         return out_host
 
     def last_routing(self, tokens):
@@ -279,6 +280,12 @@ class Moe:
         for name, p, (shape, dtype) in zip(("ids", "weights", "offsets", "perm", "logits"), ptrs, shapes):
             n = int(np.prod(shape)) * 4
             out[name] = self.read_device(p.value, n).view(dtype).reshape(shape)
+        return out
+
+    def active_counts(self):
+        """Routed experts with work in the latest call of each layer (numpy int32 [layers])."""
+        out = np.zeros(self.cfg.layers, np.int32)
+        self._check(self.lib.zc_moe_active_counts(self._h, out.ctypes.data))
         return out
 
     def status(self):
