@@ -5,7 +5,7 @@
 
 A step is one pass of the 48-layer MoE stack (hidden 2048, 512 routed experts top-10 + 1 shared expert,
 ffn 512, affine-Q4 group 64 with fp16 scale/bias, bf16 activations) over one batch of tokens, the layers
-chained on one stream through x_{l+1} = bf16(out_l / rms(out_l)). All 48 layers' records (43.5 GB) are
+chained on one stream through x_{l+1} = bf16((out_l - mean) / std) per token. All 48 layers' records (43.5 GB) are
 resident in HBM, so every step streams its weights from DRAM (inputs far larger than the 126 MB L2).
 Inputs are seeded synthetic tensors with the shapes and value distributions of the benchmark
 specification; the real checkpoint is not available.
@@ -47,7 +47,7 @@ def workload(cfg, tokens, n_gpus):
     return {
         "workload": f"BASELINE config 2: decode MoE stack, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
                     f"top-{cfg.top_k} + 1 shared, ffn {cfg.ffn}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router, "
-                    f"batch of {tokens} tokens per GPU, layers chained through bf16(out/rms(out))",
+                    f"batch of {tokens} tokens per GPU, layers chained through bf16((out-mean)/std)",
         "tokens_per_gpu": tokens, "layers": cfg.layers,
         "parallelism": f"dp{n_gpus}: independent replicas, tokens sharded, no data-path collective",
         "l2": "no flush needed: each step streams the selected records of 48 different layers (GBs per step, 43.5 GB resident) through a 126 MB L2",
@@ -111,11 +111,12 @@ class ClockSampler:
 
 
 def rms_glue(out):
-    """The inter-layer stand-in of the chained stack, on the CPU: bf16(out / rms(out))."""
+    """The inter-layer stand-in of the chained stack, on the CPU: bf16((out - mean) / std) per token."""
     from oracle import oracle
     o = out.astype(np.float32)
-    scale = (1.0 / np.sqrt(np.mean(o * o, axis=-1, keepdims=True, dtype=np.float32))).astype(np.float32)
-    return oracle.bf(o * scale)
+    d = o - o.mean(axis=-1, keepdims=True, dtype=np.float32)
+    scale = (1.0 / np.sqrt(np.mean(d * d, axis=-1, keepdims=True, dtype=np.float32))).astype(np.float32)
+    return oracle.bf(d * scale)
 
 
 def cpu_layer(cfg, layer, x, cache):

@@ -57,8 +57,8 @@ typedef struct zc_moe zc_moe;
  * (include/engine/storage.hpp:26-34: hidden 2560, ffn 640, 512 experts, top-10, Q4 group 64, BF16
  * metadata); here they are parameters. Expert record layout: see zc_moe_load_layer. */
 typedef struct zc_moe_desc {
-    uint32_t hidden;         /* H, multiple of 64 */
-    uint32_t ffn;            /* F, expert intermediate width, multiple of 64 */
+    uint32_t hidden;         /* H, multiple of 128, at most 4096 */
+    uint32_t ffn;            /* F, expert intermediate width, multiple of 128 */
     uint32_t experts;        /* E, routed experts seen by the router (multiple of 32, <= 1024) */
     uint32_t top_k;          /* K <= 32 */
     uint32_t layers;
@@ -143,10 +143,16 @@ int zc_moe_forward(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, 
 int zc_moe_forward_host(zc_moe* moe, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream);
 
 /* The whole stack of `layers` MoE layers chained on one stream, layer l+1 reading
- * act_dtype(out_l / rms(out_l)) — the stand-in for the residual + norm between MoE layers that the
- * measurement uses so that no cross-layer overlap is credited. out receives the last layer's output. */
+ * act_dtype((out_l - mean(out_l)) / std(out_l)) per token — the stand-in for the residual + norm between
+ * MoE layers that the measurement uses so that no cross-layer overlap is credited. out receives the last
+ * layer's output. */
 int zc_moe_stack(zc_moe* moe, const void* x, uint32_t tokens, void* out, void* stream);
 int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* out_host, void* stream);
+
+/* Kernel policy switches, the counterpart of KernelConfig (include/engine/metal.hpp:17-43). Options:
+ *   "fold_q4" (default 1): Q4 codes enter the tensor-core product as 1024+q / 1024+16q and the offset is
+ *   removed from the FP32 group sum; 0 removes it in FP16 before the product (exact, more instructions). */
+int zc_moe_set_option(zc_moe* moe, const char* name, int value);
 
 /* zc_moe_stack without graph replay: the same launches issued one by one (used with the profiler below). */
 int zc_moe_stack_eager(zc_moe* moe, const void* x, uint32_t tokens, void* out, void* stream);

@@ -144,8 +144,10 @@ def test_permute_is_bit_exact(torch, tokens, experts, k):
     assert int(offsets.cpu().numpy()[-1]) == tokens * k - 1
 
 
-def check_layer(torch, cfg, tokens, seed=SEED, tol=TOL, layer=0):
+def check_layer(torch, cfg, tokens, seed=SEED, tol=TOL, layer=0, fold=None):
     m = make(cfg)
+    if fold is not None:
+        m.set_option("fold_q4", fold)
     m.synth_fill_layer(layer, seed)
     x = synth.activations(cfg, seed, layer, tokens)
     out = m.moe(layer, device_x(m, x))
@@ -173,6 +175,14 @@ def test_config1_single_token_fp32(torch):
 def test_config2_decode_batches(torch, tokens):
     """BASELINE config 2 (one layer of it): 512 experts top-10 + shared, bf16 activations, token batches 1/4/16/64."""
     check_layer(torch, util.cfg2(), tokens)
+
+
+@pytest.mark.parametrize("tokens", [1, 16])
+def test_config2_exact_q4_extraction(torch, tokens):
+    """The kernel variant that removes the 1024 offset of the Q4 codes in FP16 before the tensor-core product."""
+    out_exact, want, _ = check_layer(torch, util.cfg2(), tokens, fold=0)
+    out_fold, _, _ = check_layer(torch, util.cfg2(), tokens, fold=1)
+    assert util.rel_max_error(out_fold, out_exact) < 1e-3      # FP32 tensor-core accumulation of the folded offset
 
 
 def test_config2_ragged_batch_and_bf16_output(torch):
@@ -309,7 +319,8 @@ def test_stack_host_and_device_paths_agree(torch):
         o = m.moe(l, cur)
         if l < 2:
             f = o.float()
-            cur = (f * (1.0 / torch.sqrt((f * f).mean(-1, keepdim=True)))).to(torch.bfloat16)
+            d = f - f.mean(-1, keepdim=True)
+            cur = (d * (1.0 / torch.sqrt((d * d).mean(-1, keepdim=True)))).to(torch.bfloat16)
     err = util.rel_max_error(first.float().cpu().numpy(), o.float().cpu().numpy())
     assert err < 0.05, err                # glue differs only in summation order; bf16 flips allowed
     x_host = torch.from_numpy(x_np).to(torch.bfloat16).pin_memory()

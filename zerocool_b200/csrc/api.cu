@@ -46,7 +46,7 @@ int validate_desc(const zc_moe_desc& d, std::string& why) {
     auto bad = [&](const char* t) { why = t; return ZC_EINVAL; };
     if (!d.hidden || !d.ffn || !d.experts || !d.top_k || !d.layers || !d.max_tokens) return bad("zero dimension in descriptor");
     if (d.group != 64) return bad("unsupported affine matrix geometry: group must be 64");
-    if (d.hidden % 64 || d.ffn % 64) return bad("unsupported affine matrix geometry: hidden and ffn must be multiples of 64");
+    if (d.hidden % 128 || d.ffn % 128) return bad("unsupported affine matrix geometry: hidden and ffn must be multiples of 128");
     if (d.hidden > 4096) return bad("hidden above 4096 is not supported");
     if (d.experts % 32 || d.experts > 1024) return bad("experts must be a multiple of 32 and at most 1024");
     if (d.top_k > 32 || d.top_k > d.experts) return bad("top_k must be at most 32 and at most experts");
@@ -297,7 +297,7 @@ static int stack_launches(zc_moe* m, const void* x, uint32_t tokens, void* out, 
         total += n;
         if (l + 1 < d.layers) {
             void* next = m->act[l & 1];
-            if ((n = launch_rms_act(m, layer_out, d.out_dtype, next, d.act_dtype, tokens, d.hidden, s)) < 0) return n;
+            if ((n = launch_norm_act(m, layer_out, d.out_dtype, next, d.act_dtype, tokens, d.hidden, s)) < 0) return n;
             total += n;
             in = next;
         }
@@ -398,8 +398,14 @@ int zc_moe_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, voi
     return ZC_OK;
 }
 
+int zc_moe_set_option(zc_moe* m, const char* name, int value) {
+    if (!m || !name) return fail(m, ZC_EINVAL, "null handle or option name");
+    if (!std::strcmp(name, "fold_q4")) { m->fold_q4 = value != 0; return ZC_OK; }
+    return fail(m, ZC_EINVAL, std::string("unknown option: ") + name);
+}
+
 const char* zc_moe_kernel_name(int kind) {
-    static const char* names[KERNEL_KINDS] = {"router", "route", "permute", "gate_up", "down", "combine", "rms_act"};
+    static const char* names[KERNEL_KINDS] = {"router", "route", "permute", "gate_up", "down", "combine", "norm_act"};
     return kind >= 0 && kind < KERNEL_KINDS ? names[kind] : nullptr;
 }
 

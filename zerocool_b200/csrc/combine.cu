@@ -74,35 +74,40 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(Call c) {
     }
 }
 
-// x_next[t, :] = act_dtype(in[t, :] / rms(in[t, :])): the stand-in for the residual + norm between
-// MoE layers used when the stack is timed as one dependent chain. One CTA per token.
+// x_next[t, :] = act_dtype((in[t, :] - mean) / std): the stand-in for the residual + norm between MoE
+// layers used when the stack is timed as one dependent chain. The mean is removed because the synthetic
+// weights have a non-zero mean (codes 0..15 with bias -8 scale): without centring, that common component
+// is amplified layer after layer until every token carries the same vector and routes to the same ten
+// experts, which a real model's hidden states do not do. One CTA per token.
 constexpr int RMS_THREADS = 256;
-__global__ void __launch_bounds__(RMS_THREADS) rms_act_kernel(const void* in, int in_dtype, void* out, int out_dtype, uint32_t H) {
+__device__ __forceinline__ float block_sum(float v, float* partial) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();
+    if (threadIdx.x % 32 == 0) partial[threadIdx.x / 32] = v;
+    __syncthreads();
+    float total = 0.0f;
+    for (int i = 0; i < RMS_THREADS / 32; ++i) total += partial[i];
+    return total;
+}
+__device__ __forceinline__ float load_as_float(const void* in, int dtype, size_t i) {
+    return dtype == ZC_F32 ? static_cast<const float*>(in)[i] : bf_to_float(static_cast<const uint16_t*>(in)[i]);
+}
+__global__ void __launch_bounds__(RMS_THREADS) norm_act_kernel(const void* in, int in_dtype, void* out, int out_dtype, uint32_t H) {
     const uint32_t t = blockIdx.x;
     __shared__ float partial[RMS_THREADS / 32];
-    __shared__ float scale_s;
     float sum = 0.0f;
+    for (uint32_t k = threadIdx.x; k < H; k += RMS_THREADS) sum += load_as_float(in, in_dtype, size_t(t) * H + k);
+    const float mean = block_sum(sum, partial) / float(H);
+    float sq = 0.0f;
     for (uint32_t k = threadIdx.x; k < H; k += RMS_THREADS) {
-        const float v = in_dtype == ZC_F32 ? static_cast<const float*>(in)[size_t(t) * H + k]
-                                           : bf_to_float(static_cast<const uint16_t*>(in)[size_t(t) * H + k]);
-        sum = __fmaf_rn(v, v, sum);
+        const float d = load_as_float(in, in_dtype, size_t(t) * H + k) - mean;
+        sq = __fmaf_rn(d, d, sq);
     }
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    if (threadIdx.x % 32 == 0) partial[threadIdx.x / 32] = sum;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float total = 0.0f;
-        for (int i = 0; i < RMS_THREADS / 32; ++i) total += partial[i];
-        const float mean = total / float(H);
-        scale_s = mean > 0.0f ? __fdiv_rn(1.0f, sqrtf(mean)) : 0.0f;
-    }
-    __syncthreads();
-    const float scale = scale_s;
+    const float var = block_sum(sq, partial) / float(H);
+    const float scale = var > 0.0f ? __fdiv_rn(1.0f, sqrtf(var)) : 0.0f;
     for (uint32_t k = threadIdx.x; k < H; k += RMS_THREADS) {
-        const float v = in_dtype == ZC_F32 ? static_cast<const float*>(in)[size_t(t) * H + k]
-                                           : bf_to_float(static_cast<const uint16_t*>(in)[size_t(t) * H + k]);
-        const float r = __fmul_rn(v, scale);
+        const float r = __fmul_rn(load_as_float(in, in_dtype, size_t(t) * H + k) - mean, scale);
         if (out_dtype == ZC_F32) static_cast<float*>(out)[size_t(t) * H + k] = r;
         else static_cast<uint16_t*>(out)[size_t(t) * H + k] = bf_bits(r);
     }
@@ -118,9 +123,9 @@ int launch_combine(zc_moe* m, const Call& c, cudaStream_t s) {
     return rc < 0 ? rc : 1;
 }
 
-int launch_rms_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s) {
+int launch_norm_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s) {
     int rc;
-    { Timed t(m, s, KERNEL_RMS_ACT); rms_act_kernel<<<T, RMS_THREADS, 0, s>>>(in, in_dtype, out, out_dtype, H); rc = check_launch(m, "rms_act"); }
+    { Timed t(m, s, KERNEL_NORM_ACT); norm_act_kernel<<<T, RMS_THREADS, 0, s>>>(in, in_dtype, out, out_dtype, H); rc = check_launch(m, "norm_act"); }
     return rc < 0 ? rc : 1;
 }
 

@@ -170,6 +170,7 @@ struct zc_moe {
     struct Graph { cudaGraphExec_t exec; uint64_t nodes; };
     std::unordered_map<uint64_t, Graph> graphs;
     // Optional per-kernel timing (zc_moe_profile_begin/end): one event pair per launch.
+    bool fold_q4 = true;          // Q4 codes enter the MMA with their 1024 offset (removed from the FP32 group sum)
     bool profiling = false;
     struct Span { int kind; cudaEvent_t start, stop; };
     std::vector<Span> spans;
@@ -181,9 +182,9 @@ int launch_router(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute);
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s);
-int launch_rms_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s);
+int launch_norm_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s);
 int launch_synth_layer(zc_moe* m, uint32_t layer, uint64_t seed, cudaStream_t s);
-enum KernelKind { KERNEL_ROUTER = 0, KERNEL_ROUTE, KERNEL_PERMUTE, KERNEL_GATE_UP, KERNEL_DOWN, KERNEL_COMBINE, KERNEL_RMS_ACT, KERNEL_KINDS };
+enum KernelKind { KERNEL_ROUTER = 0, KERNEL_ROUTE, KERNEL_PERMUTE, KERNEL_GATE_UP, KERNEL_DOWN, KERNEL_COMBINE, KERNEL_NORM_ACT, KERNEL_KINDS };
 // Brackets one kernel launch with events when profiling is enabled.
 struct Timed {
     zc_moe* m; cudaStream_t s; int kind; cudaEvent_t stop = nullptr;

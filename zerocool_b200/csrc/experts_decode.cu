@@ -4,38 +4,70 @@
 //   gated_linear -> q4_gate_mv_r2 / q4_gate_up (kernels/metal/qwen.metal:333-376, 71-81)
 //   linear_into  -> q4_mv_r* / q4_mm           (qwen.metal:289-330, 63-70), scatter_experts :800-803
 // issued by encode_expert_rows (src/engine/pipeline.cpp:7-31), and the shared expert of
-// Model::moe (src/engine/model.cpp:482-484), with two grouped launches per layer:
-//   gate_up_kernel: h[row, f]  = silu(gate_e . x_row) * (up_e . x_row)       for every (expert, row)
-//   down_kernel:    y[slot, c] = down_e . h_row, written at the slot's router position
+// Model::moe (src/engine/model.cpp:482-484), with two grouped launches per layer of one kernel
+// template:
+//   NMAT = 2 (gate/up): h[row, f]  = silu(gate_e . x_row) * (up_e . x_row)    for every (expert, row)
+//   NMAT = 1 (down):    y[slot, c] = down_e . h_row, written at the slot's router position
 //
-// Both stream each selected record exactly once per eight rows. The limiting resource at B200 rates
-// is instruction issue, not arithmetic: 4-bit codes arrive at ~13 T weights/s, which leaves about
-// three issue slots per weight per SM. So the multiply-accumulates run on the tensor cores as
-// m16n8k16 BF16 MMAs with up to eight token rows in the N dimension: the integer codes 0..15 (or the
-// 8-bit codes) are exact in BF16, a BF16 activation is used as it is (an FP32 activation is split into
-// two BF16 terms), products are accumulated in FP32 per 64-wide quantisation group, and the group's
-// scale and bias are applied to the FP32 accumulator in registers:
-//     acc += scale[row, g] * sum_k(q * x) + bias[row, g] * sum_k(x)
-// which is the reference's affine_dot form (qwen.metal:46-62) with an exact inner sum.
-//
-// Weight traffic: lane (g = lane/4, c = lane%4) of a warp loads 8 bytes (Q4) or 16 bytes (Q8) of rows
-// g and g+8 for group `grp` — the 16 k values [16c, 16c+16) of that group — so the four lanes of a row
-// stay inside one quantisation group, each 32-byte sector is fetched once, and loads for the next
-// chunk of groups are issued before the current chunk is multiplied. Because a dot product does not
-// care about the order of k, the MMA's k slots are bound to whatever k values fall out of the cheapest
-// nibble extraction; the activations are staged in shared memory in the matching order.
+// Each launch streams every selected record once per eight rows. At B200 rates the limiting resource
+// is instruction issue, not arithmetic: 4-bit codes arrive at ~13 T weights/s, about three issue slots
+// per weight per SM. So:
+//  * The multiply-accumulates run on the tensor cores as m16n8k16 FP16 MMAs with up to eight token
+//    rows in the N dimension. Integer codes are exact in FP16, a BF16 activation converts exactly, an
+//    FP32 activation is split into two FP16 terms, and products are accumulated in FP32 per 64-wide
+//    quantisation group. The group's scale and bias are applied to that FP32 accumulator:
+//        acc += scale[row, g] * sum_k(q * x) + bias[row, g] * sum_k(x)
+//    which is the reference's affine_dot form (qwen.metal:46-62) with an exact inner sum.
+//  * Q4 codes become FP16 with one logic operation per two weights: (w & 0x000f000f) | 0x6400 is the
+//    half2 (1024+q_lo, 1024+q_hi), and (w & 0x00f000f0) | 0x6400 is (1024+16 q, 1024+16 q). With FOLD
+//    those values go into the MMA as they are: the activation that meets a "16 q" slot is staged divided
+//    by 16 (exact), and the 1024 offset is removed from the FP32 group sum as 1024 * sum(x as staged).
+//    Without FOLD the offset and the factor 16 are removed in FP16 before the MMA (exact, 4 more ops per
+//    word).
+//  * Weights reach the warp through a private cp.async ring in shared memory (no registers held
+//    across the latency, no block-wide barrier): lane l copies 16 bytes of row l/2, so every 32-byte
+//    sector of a record is requested once, and STAGES-1 chunks are always in flight per warp.
+//  * Because a dot product does not care about the order of k, the MMA's k slots are bound to whatever
+//    k values fall out of the cheapest extraction; the activations are staged in the matching order.
+// Activations must be finite FP16 magnitudes (|x| < 65504); hidden states after a norm are O(1..100).
 #include "common.cuh"
 
 namespace zc {
 namespace {
 
-constexpr int NTOK = 8;             // token rows per MMA pass (the N of m16n8k16)
-constexpr int EXPERT_THREADS = 128; // 4 warps
-constexpr int ROW_PAD = 8;          // bf16 elements added to each staged row (keeps 16-byte reads conflict free)
+constexpr int NTOK = 8;               // token rows per MMA pass (the N of m16n8k16)
+constexpr int WARPS = 8;
+constexpr int EXPERT_THREADS = WARPS * 32;
+constexpr int ROW_PAD = 8;            // halves added to each staged row (keeps 16-byte reads conflict free)
+constexpr int STAGES = 3;             // cp.async ring depth per warp
+constexpr int CH = 2;                 // quantisation groups per ring stage
 
-template <int BITS> struct Fmt;
-template <> struct Fmt<4> { static constexpr int CH = 4, WORDS = 2; };   // groups per chunk, 32-bit words per row per group
-template <> struct Fmt<8> { static constexpr int CH = 2, WORDS = 4; };
+template <int BITS> struct Fmt {
+    static constexpr int ROWB = BITS * 8;                 // code bytes of one row of one group (64 weights)
+    static constexpr int CODES = CH * 16 * ROWB;          // code bytes of one matrix in one stage
+    static constexpr int META = 2 * 16 * 4;               // [kind][row] x CH halves
+    static constexpr int MATRIX = CODES + META;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// D(16x8, fp32) += A(16x16, fp16, row) * B(16x8, fp16, col). Lane (g = lane/4, c = lane%4) holds
+//   a0: A[g][2c,2c+1]   a1: A[g+8][2c,2c+1]   a2: A[g][2c+8,2c+9]   a3: A[g+8][2c+8,2c+9]
+//   b0: B[2c,2c+1][g]   b1: B[2c+8,2c+9][g]
+//   d0,d1: D[g][2c,2c+1]   d2,d3: D[g+8][2c,2c+1]
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 struct ItemInfo {
     const uint8_t* record;
@@ -63,19 +95,23 @@ __device__ __forceinline__ bool decode_item(const Call& c, uint32_t item, ItemIn
     return true;
 }
 
-// Stage up to NTOK source rows of K elements into shared memory as BF16 (hi, and lo when SPLIT), in
-// the k order the MMA fragments expect, and the per-group input sums Sx[grp][n].
-//   Q4 order inside each block of 8: (0,4,1,5,2,6,3,7); Q8 order: natural.
-//   REF: Sx is the reference's BF16-rounded sum of four (qwen.metal:55); otherwise plain fp32.
-template <bool Q4ORDER, bool SPLIT>
-__device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const int* rows /*[NTOK], -1 = none*/,
-                                           uint32_t K, bool ref, uint16_t* hi, uint16_t* lo, float* Sx) {
-    const uint32_t RS = K + ROW_PAD, blocks = K / 8;
-    for (uint32_t idx = threadIdx.x; idx < NTOK * blocks; idx += EXPERT_THREADS) {
-        const uint32_t n = idx / blocks, q = idx % blocks;
+// Stage the valid source rows (n < nvalid) of K elements into shared memory as FP16 (hi, and lo when
+// SPLIT), in the k order the MMA fragments expect, with the per-group sums
+//   sums[grp][n] = (Sx, Sf):  Sx = sum of x over the group (REF: the reference's BF16 sum of four,
+//   qwen.metal:55), Sf = sum of the values as staged (used to remove the folded 1024 offset).
+//   Q4 order inside each block of 8: (0,4,1,5,2,6,3,7), odd k staged / 16 when FOLD; Q8: natural order.
+// Rows n >= nvalid are left as they are: an MMA column only depends on its own B column.
+template <bool Q4ORDER, bool SPLIT, bool FOLD>
+__device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const int* rows, uint32_t nvalid,
+                                           uint32_t K, bool ref, __half* hi, __half* lo, float* sums) {
+    const uint32_t RS = K + ROW_PAD, blocks = K / 8, total = nvalid * blocks;
+    // The trip count is uniform per warp (the shuffles below need all 32 lanes); lanes past the end carry zeros.
+    for (uint32_t idx = threadIdx.x; (idx & ~31u) < total; idx += EXPERT_THREADS) {
+        const bool live = idx < total;
+        const uint32_t n = live ? idx / blocks : 0, q = live ? idx % blocks : 0;
         const int row = rows[n];
         float v[8];
-        if (row < 0) {
+        if (!live) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = 0.0f;
         } else if (src_f32) {
@@ -88,306 +124,319 @@ __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const 
 #pragma unroll
             for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(r[i] << 16); v[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u); }
         }
-        float sum;
-        if (ref) sum = bf_round(bf_round(bf_round(v[0] + v[1]) + v[2]) + v[3]) + bf_round(bf_round(bf_round(v[4] + v[5]) + v[6]) + v[7]);
-        else sum = (((v[0] + v[1]) + v[2]) + v[3]) + (((v[4] + v[5]) + v[6]) + v[7]);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        if ((q & 7) == 0) Sx[(q / 8) * NTOK + n] = sum;
-        uint16_t h[8], l[8];
+        float sx;
+        if (ref) sx = bf_round(bf_round(bf_round(v[0] + v[1]) + v[2]) + v[3]) + bf_round(bf_round(bf_round(v[4] + v[5]) + v[6]) + v[7]);
+        else sx = (((v[0] + v[1]) + v[2]) + v[3]) + (((v[4] + v[5]) + v[6]) + v[7]);
+        __half h[8], l[8];
+        float sf = 0.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            h[i] = bf_bits(v[i]);
-            if (SPLIT) l[i] = bf_bits(v[i] - bf_to_float(h[i]));
+            const float pre = (FOLD && Q4ORDER && (i & 1)) ? v[i] * 0.0625f : v[i];
+            h[i] = __float2half_rn(pre);
+            float fed = __half2float(h[i]);
+            if (SPLIT) { l[i] = __float2half_rn(pre - fed); fed += __half2float(l[i]); }
+            sf += fed;
         }
+#pragma unroll
+        for (int off = 1; off <= 4; off <<= 1) {
+            sx += __shfl_xor_sync(0xffffffffu, sx, off);
+            sf += __shfl_xor_sync(0xffffffffu, sf, off);
+        }
+        if (!live) continue;
+        if ((q & 7) == 0) *reinterpret_cast<float2*>(sums + ((q / 8) * NTOK + n) * 2) = make_float2(sx, sf);
         constexpr int order_q4[8] = {0, 4, 1, 5, 2, 6, 3, 7};
         uint32_t ph[4], pl[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int a = Q4ORDER ? order_q4[2 * i] : 2 * i, b = Q4ORDER ? order_q4[2 * i + 1] : 2 * i + 1;
-            ph[i] = uint32_t(h[a]) | (uint32_t(h[b]) << 16);
-            if (SPLIT) pl[i] = uint32_t(l[a]) | (uint32_t(l[b]) << 16);
+            ph[i] = uint32_t(__half_as_ushort(h[a])) | (uint32_t(__half_as_ushort(h[b])) << 16);
+            if (SPLIT) pl[i] = uint32_t(__half_as_ushort(l[a])) | (uint32_t(__half_as_ushort(l[b])) << 16);
         }
         *reinterpret_cast<uint4*>(hi + n * RS + q * 8) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
         if (SPLIT) *reinterpret_cast<uint4*>(lo + n * RS + q * 8) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
     }
 }
 
-// One chunk (CH groups) of one matrix for the lane's two rows (g and g+8): codes and metadata.
+// Issue the cp.async copies of one chunk (CH groups starting at grp0) of one matrix into a ring stage.
 template <int BITS>
-struct Chunk {
-    uint32_t w[2][Fmt<BITS>::CH][Fmt<BITS>::WORDS];
-    uint16_t s[2][Fmt<BITS>::CH], b[2][Fmt<BITS>::CH];
-};
-
-template <int BITS>
-__device__ __forceinline__ void load_chunk(Chunk<BITS>& ch, const uint8_t* codes, const uint16_t* scales, const uint16_t* biases,
-                                           uint32_t row0, uint32_t K, uint32_t G, uint32_t grp0, uint32_t valid, uint32_t cq) {
-    constexpr int CH = Fmt<BITS>::CH;
-    const uint32_t row_bytes = K * BITS / 8;
+__device__ __forceinline__ void issue_matrix(uint8_t* stage, const uint8_t* record, const Projection& pr, uint32_t r0, uint32_t G,
+                                             uint32_t grp0, uint32_t valid, uint32_t lane) {
+    constexpr int ROWB = Fmt<BITS>::ROWB;
+    const uint32_t row_bytes = pr.K * BITS / 8;
+    const uint8_t* codes = record + pr.codes;
+    constexpr int PIECES = 16 * ROWB / 16;          // sixteen-byte pieces per group: 32 (Q4) or 64 (Q8)
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const uint32_t row = row0 + 8 * r;
-        const uint8_t* crow = codes + size_t(row) * row_bytes;
-        const uint16_t* srow = scales + size_t(row) * G;
-        const uint16_t* brow = biases + size_t(row) * G;
+    for (int j = 0; j < CH; ++j) {
+        if (uint32_t(j) < valid) {
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-            if (uint32_t(j) < valid) {
-                const uint32_t grp = grp0 + j;
-                if constexpr (BITS == 4) {
-                    const uint2 v = ldg_nc_u2(crow + grp * 32 + cq * 8);
-                    ch.w[r][j][0] = v.x; ch.w[r][j][1] = v.y;
-                } else {
-                    const uint4 v = ldg_nc_u4(crow + grp * 64 + cq * 16);
-                    ch.w[r][j][0] = v.x; ch.w[r][j][1] = v.y; ch.w[r][j][2] = v.z; ch.w[r][j][3] = v.w;
-                }
-                ch.s[r][j] = __ldg(srow + grp);
-                ch.b[r][j] = __ldg(brow + grp);
+            for (int p = 0; p < PIECES / 32; ++p) {
+                const uint32_t piece = p * 32 + lane, row = piece / (ROWB / 16), part = piece % (ROWB / 16);
+                cp_async16(stage + (j * 16 + row) * ROWB + part * 16,
+                           codes + size_t(r0 + row) * row_bytes + size_t(grp0 + j) * ROWB + part * 16);
             }
         }
     }
+    // metadata: lane -> (kind = lane / 16, row = lane % 16); CH = 2 halves = 4 bytes. The second half is
+    // only used when that group exists; it is always inside the matrix because G is even.
+    const uint32_t kind = lane / 16, row = lane % 16;
+    const uint8_t* meta = record + (kind ? pr.biases : pr.scales) + (size_t(r0 + row) * G + grp0) * 2;
+    cp_async4(stage + Fmt<BITS>::CODES + (kind * 16 + row) * 4, meta);
 }
 
-// d(16 rows x 8 tokens) = sum over one 64-wide group of code * x, for the lane's two rows.
-template <int BITS, bool SPLIT>
-__device__ __forceinline__ void group_mma(float (&d)[4], const uint32_t (&w0)[Fmt<BITS>::WORDS], const uint32_t (&w1)[Fmt<BITS>::WORDS],
-                                          const uint4 (&bh)[2], const uint4 (&bl)[2], bool q8_signed) {
+// Q4: one word -> four half2 (k0,k4) (k1,k5) (k2,k6) (k3,k7) of its 8 codes.
+template <bool FOLD>
+__device__ __forceinline__ void dequant_q4(uint32_t w, uint32_t (&p)[4]) {
+    const uint32_t lo = 0x000f000fu, hi = 0x00f000f0u, magic = 0x64006400u;
+    const uint32_t w8 = w >> 8;
+    p[0] = (w & lo) | magic;
+    p[1] = (w & hi) | magic;
+    p[2] = (w8 & lo) | magic;
+    p[3] = (w8 & hi) | magic;
+    if (!FOLD) {
+        const __half2 k1024 = __floats2half2_rn(1024.0f, 1024.0f), k16 = __floats2half2_rn(0.0625f, 0.0625f), k64 = __floats2half2_rn(-64.0f, -64.0f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 v = *reinterpret_cast<__half2*>(&p[i]);
+            v = (i & 1) ? __hfma2(v, k16, k64) : __hsub2(v, k1024);
+            p[i] = *reinterpret_cast<uint32_t*>(&v);
+        }
+    }
+}
+// Q8: one word -> two half2 (k0,k1) (k2,k3); every integer in [-128, 255] is exact in FP16.
+__device__ __forceinline__ void dequant_q8(uint32_t w, bool is_signed, uint32_t (&p)[2]) {
+    if (is_signed) w ^= 0x80808080u;
+    const float off = is_signed ? 8388608.0f + 128.0f : 8388608.0f;
+    float f[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(0x4b000000u | ((w >> (8 * i)) & 0xffu)) - off;
+    const __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
+    p[0] = *reinterpret_cast<const uint32_t*>(&a);
+    p[1] = *reinterpret_cast<const uint32_t*>(&b);
+}
+
+// d(16 rows x 8 tokens) = sum over one 64-wide group of code * x for the lane's rows g (w0) and g+8 (w1).
+template <int BITS, bool SPLIT, bool FOLD>
+__device__ __forceinline__ void group_mma(float (&d)[4], const uint32_t* w0, const uint32_t* w1, const uint4 (&bh)[2], const uint4 (&bl)[2], bool q8_signed) {
     if constexpr (BITS == 4) {
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
             uint32_t p0[4], p1[4];
-            dequant_q4_word(w0[m], p0);
-            dequant_q4_word(w1[m], p1);
-            mma_bf16_16816(d, p0[0], p1[0], p0[1], p1[1], bh[m].x, bh[m].y);
-            mma_bf16_16816(d, p0[2], p1[2], p0[3], p1[3], bh[m].z, bh[m].w);
+            dequant_q4<FOLD>(w0[m], p0);
+            dequant_q4<FOLD>(w1[m], p1);
+            mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], bh[m].x, bh[m].y);
+            mma_f16_16816(d, p0[2], p1[2], p0[3], p1[3], bh[m].z, bh[m].w);
             if constexpr (SPLIT) {
-                mma_bf16_16816(d, p0[0], p1[0], p0[1], p1[1], bl[m].x, bl[m].y);
-                mma_bf16_16816(d, p0[2], p1[2], p0[3], p1[3], bl[m].z, bl[m].w);
+                mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], bl[m].x, bl[m].y);
+                mma_f16_16816(d, p0[2], p1[2], p0[3], p1[3], bl[m].z, bl[m].w);
             }
         }
     } else {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
             uint32_t p0[2], p1[2];
-            dequant_q8_word(w0[m], q8_signed, p0);
-            dequant_q8_word(w1[m], q8_signed, p1);
+            dequant_q8(w0[m], q8_signed, p0);
+            dequant_q8(w1[m], q8_signed, p1);
             const uint32_t b0 = (m & 1) ? bh[m / 2].z : bh[m / 2].x, b1 = (m & 1) ? bh[m / 2].w : bh[m / 2].y;
-            mma_bf16_16816(d, p0[0], p1[0], p0[1], p1[1], b0, b1);
+            mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], b0, b1);
             if constexpr (SPLIT) {
                 const uint32_t c0 = (m & 1) ? bl[m / 2].z : bl[m / 2].x, c1 = (m & 1) ? bl[m / 2].w : bl[m / 2].y;
-                mma_bf16_16816(d, p0[0], p1[0], p0[1], p1[1], c0, c1);
+                mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], c0, c1);
             }
         }
     }
 }
 
-// acc += scale * d + bias * Sx for one group of one chunk.
-template <int BITS, bool SPLIT>
-__device__ __forceinline__ void consume_group(float (&acc)[4], const Chunk<BITS>& ch, int j, const uint4 (&bh)[2], const uint4 (&bl)[2],
-                                              float2 sx, bool meta_f16, bool q8_signed) {
-    float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    group_mma<BITS, SPLIT>(d, ch.w[0][j], ch.w[1][j], bh, bl, q8_signed);
-    const float s0 = meta_to_float(ch.s[0][j], meta_f16), s1 = meta_to_float(ch.s[1][j], meta_f16);
-    const float b0 = meta_to_float(ch.b[0][j], meta_f16), b1 = meta_to_float(ch.b[1][j], meta_f16);
-    acc[0] += __fmaf_rn(s0, d[0], b0 * sx.x);
-    acc[1] += __fmaf_rn(s0, d[1], b0 * sx.y);
-    acc[2] += __fmaf_rn(s1, d[2], b1 * sx.x);
-    acc[3] += __fmaf_rn(s1, d[3], b1 * sx.y);
-}
-
-__device__ __forceinline__ void load_b(const uint16_t* rowbase, uint32_t grp, uint32_t cq, uint4 (&b)[2]) {
-    const uint16_t* p = rowbase + grp * 64 + cq * 16;
-    b[0] = *reinterpret_cast<const uint4*>(p);
-    b[1] = *reinterpret_cast<const uint4*>(p + 8);
-}
-
 // ---------------------------------------------------------------------------------------------
-// gate/up + SwiGLU. Grid: (F/16, items). A CTA computes 16 rows of gate and the same 16 rows of up
-// for all rows of its item; its four warps split K in chunks and add their partials in warp order.
+// The expert kernel. Grid: (N / (16 * RT), items) with RT = WARPS / KS row tiles per CTA.
+//   NMAT = 2: gate/up + SwiGLU into hbuf.   NMAT = 1: down projection into the router positions.
+//   KS: warps that split K for one row tile (partials added in warp order through shared memory).
 // ---------------------------------------------------------------------------------------------
-template <int BITS, bool SPLIT>
-__global__ void __launch_bounds__(EXPERT_THREADS) gate_up_kernel(Call c) {
-    constexpr int CH = Fmt<BITS>::CH;
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD>
+__global__ void __launch_bounds__(EXPERT_THREADS, 2) expert_kernel(Call c) {
+    constexpr int RT = WARPS / KS;
+    constexpr int STAGE = NMAT * Fmt<BITS>::MATRIX;
+    constexpr int WORDS = Fmt<BITS>::ROWB / 16;      // 32-bit words per lane per row per group: 2 (Q4) / 4 (Q8)
+    constexpr bool FOLDQ = FOLD && BITS == 4;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     ItemInfo it;
     if (!decode_item(c, blockIdx.y, it)) return;
-    const uint32_t K = c.H, G = K / 64, RS = K + ROW_PAD;
-    uint16_t* xhi = reinterpret_cast<uint16_t*>(smem_raw);
-    uint16_t* xlo = xhi + (SPLIT ? NTOK * RS : 0);
-    float* Sx = reinterpret_cast<float*>(xhi + (SPLIT ? 2 : 1) * NTOK * RS);
-    float* red = Sx + G * NTOK;                       // [4][2][16][NTOK]
+    const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64, RS = K + ROW_PAD;
+    __half* xhi = reinterpret_cast<__half*>(smem_raw);
+    __half* xlo = xhi + (SPLIT ? NTOK * RS : 0);
+    float* sums = reinterpret_cast<float*>(xhi + (SPLIT ? 2 : 1) * NTOK * RS);       // [G][NTOK][2]
+    uint8_t* ring = reinterpret_cast<uint8_t*>(sums + G * NTOK * 2);                  // [WARPS][STAGES][STAGE]
+    float* red = reinterpret_cast<float*>(ring + WARPS * STAGES * STAGE);             // [KS][NMAT][RT*16][NTOK] when KS > 1
     __shared__ int rows[NTOK];
+    __shared__ long long dest[NTOK];
 
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, cq = lane % 4;
-    const uint32_t r0 = blockIdx.x * 16;
-    const uint8_t* gc = it.record + c.gate.codes; const uint8_t* uc = it.record + c.up.codes;
-    const uint16_t* gs = reinterpret_cast<const uint16_t*>(it.record + c.gate.scales);
-    const uint16_t* gb = reinterpret_cast<const uint16_t*>(it.record + c.gate.biases);
-    const uint16_t* us = reinterpret_cast<const uint16_t*>(it.record + c.up.scales);
-    const uint16_t* ub = reinterpret_cast<const uint16_t*>(it.record + c.up.biases);
+    const uint32_t rt = warp / KS, ks = warp % KS;
+    const uint32_t r0 = (blockIdx.x * RT + rt) * 16;
+    const Projection pr0 = NMAT == 2 ? c.gate : c.down;
+    const Projection pr1 = c.up;
+    uint8_t* my_ring = ring + warp * STAGES * STAGE;
     const uint32_t nchunks = (G + CH - 1) / CH;
-    const bool meta_f16 = c.meta_f16, q8s = c.q8_signed;
-
-    for (uint32_t pass = 0; pass * NTOK < it.count; ++pass) {
-        __syncthreads();
-        if (threadIdx.x < NTOK) {
-            const uint32_t i = pass * NTOK + threadIdx.x;
-            rows[threadIdx.x] = i < it.count ? (it.shared ? int(i) : c.perm[it.pos0 + i] / int(c.K)) : -1;
-        }
-        __syncthreads();
-        stage_rows<BITS == 4, SPLIT>(c.x, c.act_dtype == ZC_F32, rows, K, c.ref && BITS == 4, xhi, xlo, Sx);
-        __syncthreads();
-
-        float accg[4] = {0, 0, 0, 0}, accu[4] = {0, 0, 0, 0};
-        Chunk<BITS> cg[2], cu[2];
-        uint32_t chunk = warp;
-        if (chunk < nchunks) {
-            const uint32_t grp0 = chunk * CH, valid = min(uint32_t(CH), G - grp0);
-            load_chunk<BITS>(cg[0], gc, gs, gb, r0 + g, K, G, grp0, valid, cq);
-            load_chunk<BITS>(cu[0], uc, us, ub, r0 + g, K, G, grp0, valid, cq);
-        }
-        int cur = 0;
-        for (; chunk < nchunks; chunk += 4, cur ^= 1) {
-            const uint32_t next = chunk + 4;
-            if (next < nchunks) {
-                const uint32_t grp0 = next * CH, valid = min(uint32_t(CH), G - grp0);
-                if (cur == 0) { load_chunk<BITS>(cg[1], gc, gs, gb, r0 + g, K, G, grp0, valid, cq); load_chunk<BITS>(cu[1], uc, us, ub, r0 + g, K, G, grp0, valid, cq); }
-                else          { load_chunk<BITS>(cg[0], gc, gs, gb, r0 + g, K, G, grp0, valid, cq); load_chunk<BITS>(cu[0], uc, us, ub, r0 + g, K, G, grp0, valid, cq); }
-            }
-            const uint32_t grp0 = chunk * CH, valid = min(uint32_t(CH), G - grp0);
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-                if (uint32_t(j) < valid) {
-                    const uint32_t grp = grp0 + j;
-                    uint4 bh[2], bl[2];
-                    load_b(xhi + g * RS, grp, cq, bh);
-                    if constexpr (SPLIT) load_b(xlo + g * RS, grp, cq, bl);
-                    const float2 sx = *reinterpret_cast<const float2*>(Sx + grp * NTOK + 2 * cq);
-                    if (cur == 0) { consume_group<BITS, SPLIT>(accg, cg[0], j, bh, bl, sx, meta_f16, q8s); consume_group<BITS, SPLIT>(accu, cu[0], j, bh, bl, sx, meta_f16, q8s); }
-                    else          { consume_group<BITS, SPLIT>(accg, cg[1], j, bh, bl, sx, meta_f16, q8s); consume_group<BITS, SPLIT>(accu, cu[1], j, bh, bl, sx, meta_f16, q8s); }
-                }
-            }
-        }
-        // partials of this warp: [warp][matrix][row][token]
-        float* mine = red + warp * 2 * 16 * NTOK;
-        *reinterpret_cast<float2*>(mine + (0 * 16 + g) * NTOK + 2 * cq) = make_float2(accg[0], accg[1]);
-        *reinterpret_cast<float2*>(mine + (0 * 16 + g + 8) * NTOK + 2 * cq) = make_float2(accg[2], accg[3]);
-        *reinterpret_cast<float2*>(mine + (1 * 16 + g) * NTOK + 2 * cq) = make_float2(accu[0], accu[1]);
-        *reinterpret_cast<float2*>(mine + (1 * 16 + g + 8) * NTOK + 2 * cq) = make_float2(accu[2], accu[3]);
-        __syncthreads();
-        {
-            const uint32_t row = threadIdx.x / NTOK, n = threadIdx.x % NTOK;
-            float gate = 0.0f, up = 0.0f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                gate += red[((w * 2 + 0) * 16 + row) * NTOK + n];
-                up += red[((w * 2 + 1) * 16 + row) * NTOK + n];
-            }
-            float h;
-            if (c.ref) {   // qwen.metal:71-81
-                gate = bf_round(gate); up = bf_round(up);
-                h = bf_round(bf_round(gate * sigmoid_bf(gate)) * up);
-            } else {
-                h = (gate * sigmoid_f(gate)) * up;
-            }
-            const uint32_t i = pass * NTOK + n;
-            if (i < it.count) c.hbuf[size_t(it.hrow0 + i) * c.F + r0 + row] = h;
-        }
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// down projection. Grid: (H/64, items). Each warp owns 16 output rows over the whole K = F and
-// writes its results straight to the slot's router position (the reference's linear_into /
-// scatter_experts destination, pipeline.cpp:25-28).
-// ---------------------------------------------------------------------------------------------
-template <int BITS, bool SPLIT>
-__global__ void __launch_bounds__(EXPERT_THREADS) down_kernel(Call c) {
-    constexpr int CH = Fmt<BITS>::CH;
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    ItemInfo it;
-    if (!decode_item(c, blockIdx.y, it)) return;
-    const uint32_t K = c.F, G = K / 64, RS = K + ROW_PAD;
-    uint16_t* hhi = reinterpret_cast<uint16_t*>(smem_raw);
-    uint16_t* hlo = hhi + (SPLIT ? NTOK * RS : 0);
-    float* Sx = reinterpret_cast<float*>(hhi + (SPLIT ? 2 : 1) * NTOK * RS);
-    __shared__ int rows[NTOK];
-    __shared__ long long dest[NTOK];      // element offset of the destination row, or -1
-
-    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, cq = lane % 4;
-    const uint32_t r0 = blockIdx.x * 64 + warp * 16;
-    const uint8_t* dc = it.record + c.down.codes;
-    const uint16_t* ds = reinterpret_cast<const uint16_t*>(it.record + c.down.scales);
-    const uint16_t* db = reinterpret_cast<const uint16_t*>(it.record + c.down.biases);
-    const uint32_t nchunks = (G + CH - 1) / CH;
+    const uint32_t my_n = ks < nchunks ? (nchunks - ks + KS - 1) / KS : 0;
     const bool meta_f16 = c.meta_f16, q8s = c.q8_signed;
     float* out_base = it.shared ? c.shared_out : c.expert_out;
 
+    auto issue = [&](uint32_t i) {
+        if (i < my_n) {
+            const uint32_t grp0 = (ks + i * KS) * CH, valid = min(uint32_t(CH), G - grp0);
+            uint8_t* stage = my_ring + (i % STAGES) * STAGE;
+            issue_matrix<BITS>(stage, it.record, pr0, r0, G, grp0, valid, lane);
+            if constexpr (NMAT == 2) issue_matrix<BITS>(stage + Fmt<BITS>::MATRIX, it.record, pr1, r0, G, grp0, valid, lane);
+        }
+        cp_async_commit();
+    };
+
     for (uint32_t pass = 0; pass * NTOK < it.count; ++pass) {
-        __syncthreads();
+        const uint32_t nvalid = min(uint32_t(NTOK), it.count - pass * NTOK);
+        __syncthreads();                       // everything of the previous pass has been consumed
+#pragma unroll
+        for (int i = 0; i < STAGES - 1; ++i) issue(i);   // weights do not depend on the rows: start them first
         if (threadIdx.x < NTOK) {
             const uint32_t i = pass * NTOK + threadIdx.x;
             if (i < it.count) {
-                rows[threadIdx.x] = int(it.hrow0 + i);
+                if (NMAT == 2) rows[threadIdx.x] = it.shared ? int(i) : c.perm[it.pos0 + i] / int(c.K);
+                else rows[threadIdx.x] = int(it.hrow0 + i);
                 const uint32_t slot = it.shared ? i : uint32_t(c.perm[it.pos0 + i]);
-                dest[threadIdx.x] = (long long)slot * c.H;
+                dest[threadIdx.x] = NMAT == 2 ? (long long)(it.hrow0 + i) * c.F : (long long)slot * c.H;
             } else { rows[threadIdx.x] = -1; dest[threadIdx.x] = -1; }
         }
         __syncthreads();
-        stage_rows<BITS == 4, SPLIT>(c.hbuf, true, rows, K, c.ref && BITS == 4, hhi, hlo, Sx);
+        stage_rows<BITS == 4, SPLIT, FOLDQ>(NMAT == 2 ? c.x : static_cast<const void*>(c.hbuf), NMAT == 2 ? c.act_dtype == ZC_F32 : true,
+                                            rows, nvalid, K, c.ref && BITS == 4, xhi, xlo, sums);
         __syncthreads();
 
-        float acc[4] = {0, 0, 0, 0};
-        Chunk<BITS> cd[2];
-        {
-            const uint32_t valid = min(uint32_t(CH), G);
-            load_chunk<BITS>(cd[0], dc, ds, db, r0 + g, K, G, 0, valid, cq);
-        }
-        int cur = 0;
-        for (uint32_t chunk = 0; chunk < nchunks; ++chunk, cur ^= 1) {
-            const uint32_t next = chunk + 1;
-            if (next < nchunks) {
-                const uint32_t grp0 = next * CH, valid = min(uint32_t(CH), G - grp0);
-                if (cur == 0) load_chunk<BITS>(cd[1], dc, ds, db, r0 + g, K, G, grp0, valid, cq);
-                else          load_chunk<BITS>(cd[0], dc, ds, db, r0 + g, K, G, grp0, valid, cq);
-            }
-            const uint32_t grp0 = chunk * CH, valid = min(uint32_t(CH), G - grp0);
+        float acc[NMAT][4];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) { acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f; }
+
+        for (uint32_t i = 0; i < my_n; ++i) {
+            cp_async_wait<STAGES - 2>();
+            __syncwarp();
+            const uint8_t* stage = my_ring + (i % STAGES) * STAGE;
+            const uint32_t grp0 = (ks + i * KS) * CH, valid = min(uint32_t(CH), G - grp0);
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
                 if (uint32_t(j) < valid) {
                     const uint32_t grp = grp0 + j;
                     uint4 bh[2], bl[2];
-                    load_b(hhi + g * RS, grp, cq, bh);
-                    if constexpr (SPLIT) load_b(hlo + g * RS, grp, cq, bl);
-                    const float2 sx = *reinterpret_cast<const float2*>(Sx + grp * NTOK + 2 * cq);
-                    if (cur == 0) consume_group<BITS, SPLIT>(acc, cd[0], j, bh, bl, sx, meta_f16, q8s);
-                    else          consume_group<BITS, SPLIT>(acc, cd[1], j, bh, bl, sx, meta_f16, q8s);
+                    const __half* bp = xhi + g * RS + grp * 64 + cq * 16;
+                    bh[0] = *reinterpret_cast<const uint4*>(bp);
+                    bh[1] = *reinterpret_cast<const uint4*>(bp + 8);
+                    if constexpr (SPLIT) {
+                        const __half* lp = xlo + g * RS + grp * 64 + cq * 16;
+                        bl[0] = *reinterpret_cast<const uint4*>(lp);
+                        bl[1] = *reinterpret_cast<const uint4*>(lp + 8);
+                    }
+                    const float4 sm = *reinterpret_cast<const float4*>(sums + (grp * NTOK + 2 * cq) * 2);   // Sx, Sf of tokens 2cq, 2cq+1
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        const uint8_t* ms = stage + m * Fmt<BITS>::MATRIX;
+                        uint32_t w0[WORDS], w1[WORDS];
+                        if constexpr (BITS == 4) {
+                            const uint2 a = *reinterpret_cast<const uint2*>(ms + (j * 16 + g) * 32 + cq * 8);
+                            const uint2 b = *reinterpret_cast<const uint2*>(ms + (j * 16 + g + 8) * 32 + cq * 8);
+                            w0[0] = a.x; w0[1] = a.y; w1[0] = b.x; w1[1] = b.y;
+                        } else {
+                            const uint4 a = *reinterpret_cast<const uint4*>(ms + (j * 16 + g) * 64 + cq * 16);
+                            const uint4 b = *reinterpret_cast<const uint4*>(ms + (j * 16 + g + 8) * 64 + cq * 16);
+                            w0[0] = a.x; w0[1] = a.y; w0[2] = a.z; w0[3] = a.w; w1[0] = b.x; w1[1] = b.y; w1[2] = b.z; w1[3] = b.w;
+                        }
+                        float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        group_mma<BITS, SPLIT, FOLDQ>(d, w0, w1, bh, bl, q8s);
+                        const uint16_t* mt = reinterpret_cast<const uint16_t*>(ms + Fmt<BITS>::CODES);   // [kind][row][CH]
+                        const float s0 = meta_to_float(mt[(0 * 16 + g) * 2 + j], meta_f16), s1 = meta_to_float(mt[(0 * 16 + g + 8) * 2 + j], meta_f16);
+                        const float b0 = meta_to_float(mt[(1 * 16 + g) * 2 + j], meta_f16), b1 = meta_to_float(mt[(1 * 16 + g + 8) * 2 + j], meta_f16);
+                        if constexpr (FOLDQ) {
+                            d[0] = __fmaf_rn(-1024.0f, sm.y, d[0]); d[1] = __fmaf_rn(-1024.0f, sm.w, d[1]);
+                            d[2] = __fmaf_rn(-1024.0f, sm.y, d[2]); d[3] = __fmaf_rn(-1024.0f, sm.w, d[3]);
+                        }
+                        acc[m][0] = __fmaf_rn(s0, d[0], acc[m][0]); acc[m][0] = __fmaf_rn(b0, sm.x, acc[m][0]);
+                        acc[m][1] = __fmaf_rn(s0, d[1], acc[m][1]); acc[m][1] = __fmaf_rn(b0, sm.z, acc[m][1]);
+                        acc[m][2] = __fmaf_rn(s1, d[2], acc[m][2]); acc[m][2] = __fmaf_rn(b1, sm.x, acc[m][2]);
+                        acc[m][3] = __fmaf_rn(s1, d[3], acc[m][3]); acc[m][3] = __fmaf_rn(b1, sm.z, acc[m][3]);
+                    }
                 }
             }
+            __syncwarp();
+            issue(i + STAGES - 1);
         }
-        // lane holds rows g, g+8 for tokens 2cq, 2cq+1
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t n = 2 * cq + (i & 1), row = r0 + g + 8 * (i >> 1);
+        cp_async_wait<0>();
+
+        // The lane holds rows g, g+8 of its tile for tokens 2cq, 2cq+1.
+        auto finish = [&](uint32_t row_in_cta, uint32_t n, float a0, float a1) {
             const long long d = dest[n];
-            if (d >= 0) out_base[d + row] = c.ref ? bf_round(acc[i]) : acc[i];
+            if (d < 0) return;
+            const uint32_t row = blockIdx.x * RT * 16 + row_in_cta;
+            if constexpr (NMAT == 2) {
+                float h;
+                if (c.ref) {   // qwen.metal:71-81
+                    const float gate = bf_round(a0), up = bf_round(a1);
+                    h = bf_round(bf_round(gate * sigmoid_bf(gate)) * up);
+                } else {
+                    h = (a0 * sigmoid_f(a0)) * a1;
+                }
+                c.hbuf[d + row] = h;
+            } else {
+                out_base[d + row] = c.ref ? bf_round(a0) : a0;
+            }
+        };
+        if constexpr (KS == 1) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                finish(rt * 16 + g + 8 * (i >> 1), 2 * cq + (i & 1), acc[0][i], acc[NMAT - 1][i]);
+        } else {
+            // partials: [ks][matrix][row in CTA][token]
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+                float* mine = red + ((ks * NMAT + m) * RT * 16 + rt * 16) * NTOK;
+                *reinterpret_cast<float2*>(mine + g * NTOK + 2 * cq) = make_float2(acc[m][0], acc[m][1]);
+                *reinterpret_cast<float2*>(mine + (g + 8) * NTOK + 2 * cq) = make_float2(acc[m][2], acc[m][3]);
+            }
+            __syncthreads();
+            for (uint32_t o = threadIdx.x; o < RT * 16 * NTOK; o += EXPERT_THREADS) {
+                const uint32_t row = o / NTOK, n = o % NTOK;
+                float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+                for (int k = 0; k < KS; ++k) {
+                    a0 += red[((k * NMAT + 0) * RT * 16 + row) * NTOK + n];
+                    if constexpr (NMAT == 2) a1 += red[((k * NMAT + 1) * RT * 16 + row) * NTOK + n];
+                }
+                finish(row, n, a0, a1);
+            }
         }
     }
 }
 
-template <void (*kernel)(Call)>
-int launch_one(zc_moe* m, dim3 grid, size_t smem, const Call& c, cudaStream_t s, const char* what, int kind) {
-    if (smem > 200 * 1024) return fail(m, ZC_EINVAL, std::string(what) + ": shape needs too much shared memory");
-    static bool configured = false;   // one flag per kernel instantiation
-    if (!configured) {
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        configured = true;
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD>
+int launch_expert(zc_moe* m, const Call& c, uint32_t items, cudaStream_t s) {
+    constexpr int RT = WARPS / KS;
+    const uint32_t K = NMAT == 2 ? c.H : c.F, N = NMAT == 2 ? c.F : c.H, G = K / 64;
+    const size_t smem = size_t(SPLIT ? 2 : 1) * NTOK * (K + ROW_PAD) * 2 + size_t(G) * NTOK * 2 * 4 +
+                        size_t(WARPS) * STAGES * NMAT * Fmt<BITS>::MATRIX + (KS > 1 ? size_t(KS) * NMAT * RT * 16 * NTOK * 4 : 0);
+    if (smem > 220 * 1024) return fail(m, ZC_EINVAL, "expert kernel: shape needs too much shared memory");
+    if (N % (16 * RT)) return fail(m, ZC_EINVAL, "expert kernel: rows not a multiple of the CTA tile");
+    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD>;
+    static size_t configured = 0;       // one per instantiation of this function template
+    if (smem > configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return check_launch(m, "expert kernel attribute");
+        configured = smem;
     }
-    Timed t(m, s, kind);
-    kernel<<<grid, EXPERT_THREADS, smem, s>>>(c);
-    return check_launch(m, what);
+    Timed t(m, s, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN);
+    kernel<<<dim3(N / (16 * RT), items), EXPERT_THREADS, smem, s>>>(c);
+    return check_launch(m, NMAT == 2 ? "gate_up" : "down");
+}
+
+template <int NMAT, int KS>
+int dispatch_expert(zc_moe* m, const Call& c, uint32_t items, bool split, uint32_t bits, bool fold, cudaStream_t s) {
+    if (bits == 4) {
+        if (fold) return split ? launch_expert<4, true, NMAT, KS, true>(m, c, items, s) : launch_expert<4, false, NMAT, KS, true>(m, c, items, s);
+        return split ? launch_expert<4, true, NMAT, KS, false>(m, c, items, s) : launch_expert<4, false, NMAT, KS, false>(m, c, items, s);
+    }
+    return split ? launch_expert<8, true, NMAT, KS, false>(m, c, items, s) : launch_expert<8, false, NMAT, KS, false>(m, c, items, s);
 }
 
 }  // namespace
@@ -395,28 +444,20 @@ int launch_one(zc_moe* m, dim3 grid, size_t smem, const Call& c, cudaStream_t s,
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s) {
     const uint32_t routed = c.T * c.K < c.local_experts ? c.T * c.K : c.local_experts;
     const uint32_t items = routed + (c.has_shared ? 1 : 0);
-    // A BF16 activation is exact as one BF16 term; an FP32 activation needs two, except under the
+    // A BF16 activation is exact as one FP16 term; an FP32 activation needs two, except under the
     // reference arithmetic, whose FP32 buffers hold BF16 values by contract.
     const bool split_x = c.act_dtype == ZC_F32 && !c.ref;
     const bool split_h = !c.ref;      // h is FP32 unless the reference rounds it to BF16
-    {
-        const uint32_t K = c.H, G = K / 64;
-        const size_t smem = size_t(split_x ? 2 : 1) * NTOK * (K + ROW_PAD) * 2 + size_t(G) * NTOK * 4 + 4 * 2 * 16 * NTOK * 4;
-        const dim3 grid(c.F / 16, items);
-        int rc;
-        if (c.gate.bits == 4) rc = split_x ? launch_one<gate_up_kernel<4, true>>(m, grid, smem, c, s, "gate_up", KERNEL_GATE_UP) : launch_one<gate_up_kernel<4, false>>(m, grid, smem, c, s, "gate_up", KERNEL_GATE_UP);
-        else rc = split_x ? launch_one<gate_up_kernel<8, true>>(m, grid, smem, c, s, "gate_up", KERNEL_GATE_UP) : launch_one<gate_up_kernel<8, false>>(m, grid, smem, c, s, "gate_up", KERNEL_GATE_UP);
-        if (rc < 0) return rc;
-    }
-    {
-        const uint32_t K = c.F, G = K / 64;
-        const size_t smem = size_t(split_h ? 2 : 1) * NTOK * (K + ROW_PAD) * 2 + size_t(G) * NTOK * 4;
-        const dim3 grid(c.H / 64, items);
-        int rc;
-        if (c.down.bits == 4) rc = split_h ? launch_one<down_kernel<4, true>>(m, grid, smem, c, s, "down", KERNEL_DOWN) : launch_one<down_kernel<4, false>>(m, grid, smem, c, s, "down", KERNEL_DOWN);
-        else rc = split_h ? launch_one<down_kernel<8, true>>(m, grid, smem, c, s, "down", KERNEL_DOWN) : launch_one<down_kernel<8, false>>(m, grid, smem, c, s, "down", KERNEL_DOWN);
-        if (rc < 0) return rc;
-    }
+    const bool fold = m->fold_q4;
+    // Few rows in flight: split K over all eight warps so that even one token fills the machine.
+    const bool small = c.T * (c.K + (c.has_shared ? 1 : 0)) <= 64;
+    int rc;
+    if (small) rc = dispatch_expert<2, 8>(m, c, items, split_x, c.gate.bits, fold, s);
+    else rc = dispatch_expert<2, 2>(m, c, items, split_x, c.gate.bits, fold, s);
+    if (rc < 0) return rc;
+    if (small) rc = dispatch_expert<1, 2>(m, c, items, split_h, c.down.bits, fold, s);
+    else rc = dispatch_expert<1, 1>(m, c, items, split_h, c.down.bits, fold, s);
+    if (rc < 0) return rc;
     return 2;
 }
 

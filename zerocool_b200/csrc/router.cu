@@ -119,9 +119,9 @@ int launch_router(zc_moe* m, const Call& c, cudaStream_t s) {
     const uint32_t rows = c.E + (c.has_shared ? 1 : 0);
     const uint32_t chunks = (c.T + TT - 1) / TT;
     const uint32_t gx = (rows + ER - 1) / ER;
-    // Enough blocks along the token axis to fill the machine a few times over for long batches.
-    uint32_t gy = 1;
-    if (chunks > 8) { gy = (chunks + 7) / 8; if (gy > 64) gy = 64; }
+    // One chunk of tokens per block while that keeps the grid within a few thousand blocks (the rows are
+    // re-read from L2); longer batches walk several chunks per block.
+    uint32_t gy = chunks < 32 ? chunks : 32;
     const uint32_t per = (chunks + gy - 1) / gy;
     gy = (chunks + per - 1) / per;
     int rc;

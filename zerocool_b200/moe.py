@@ -25,7 +25,7 @@ EXPORTS = [
     "zc_moe_desc_finalize", "zc_moe_create", "zc_moe_destroy", "zc_moe_last_error", "zc_last_error",
     "zc_moe_load_layer", "zc_moe_layer_buffers", "zc_moe_router", "zc_moe_route", "zc_moe_permute",
     "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_forward_host", "zc_moe_stack",
-    "zc_moe_stack_host", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
+    "zc_moe_stack_host", "zc_moe_set_option", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
     "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
 ]
 
@@ -75,6 +75,7 @@ def load_library():
     lib.zc_moe_stack.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_stack_host.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_active_counts.argtypes = [vp, vp]
+    lib.zc_moe_set_option.argtypes = [vp, ctypes.c_char_p, i32]
     lib.zc_moe_stack_eager.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_profile_begin.argtypes = [vp]
     lib.zc_moe_profile_end.argtypes = [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(u64)]
@@ -242,6 +243,9 @@ class Moe:
             out = torch.empty((tokens, self.cfg.hidden), dtype=self.out_torch, device=self.device)
         self._check(self.lib.zc_moe_stack(self._h, _ptr(x), tokens, _ptr(out), self._stream()))
         return out
+
+    def set_option(self, name, value):
+        self._check(self.lib.zc_moe_set_option(self._h, name.encode(), int(value)))
 
     def stack_eager(self, x, out=None):
         torch = self._torch

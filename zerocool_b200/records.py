@@ -81,8 +81,8 @@ class MoeConfig:
         return d
 
     def validate(self):
-        if self.hidden % 16 or self.hidden % self.group or self.ffn % self.group:
-            raise ValueError("hidden must be a multiple of 16 and of the group; ffn a multiple of the group")
+        if self.hidden % 128 or self.ffn % 128:
+            raise ValueError("hidden and ffn must be multiples of 128")
         if self.group != 64:
             raise ValueError("only group 64 is supported")
         for p in range(3):
