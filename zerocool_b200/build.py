@@ -38,7 +38,8 @@ def build(force=False, verbose=False, ptxas_info=False):
         obj = os.path.join(CSRC, name[:-3] + ".o")
         objects.append(obj)
         if force or _stale(obj, [src] + headers):
-            cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
+            extra = os.environ.get("ZC_NVCC_FLAGS", "").split()
+            cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
             r = subprocess.run(cmd, capture_output=True, text=True, env=env)
             if verbose or ptxas_info or r.returncode:
                 sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)

@@ -87,13 +87,17 @@ int check_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const 
     return ZC_OK;
 }
 
-int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s) {
+// One layer: router partials -> route + permutation (one launch) -> gate/up -> down -> combine.
+// With `next` set the combine also writes the normalised input of the following layer (the chained stack).
+int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next = nullptr) {
     const Call c = make_call(m, layer, x, tokens, out);
     int n, total = 0;
-    if ((n = launch_router(m, c, s)) < 0) return n; total += n;
-    if ((n = launch_route_permute(m, c, s, true, true)) < 0) return n; total += n;
+    if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
+    if ((n = launch_route_permute(m, c, s, true, true, false)) < 0) return n; total += n;
     if ((n = launch_experts_decode(m, c, s)) < 0) return n; total += n;
-    if ((n = launch_combine(m, c, s)) < 0) return n; total += n;
+    if (next) n = launch_combine_norm(m, c, next, m->d.act_dtype, s);
+    else n = launch_combine(m, c, s);
+    if (n < 0) return n; total += n;
     return total;
 }
 
@@ -154,6 +158,10 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     Call& c = m->scratch;
     A(&c.logits, T * E * 4); A(&c.gate_logit, T * 4); A(&c.ids, T * K * 4); A(&c.weights, T * K * 4);
     A(&c.offsets, (E + 1) * 4); A(&c.perm, T * K * 4); A(&c.active, E * 4); A(&c.counters, (16 + size_t(d.layers)) * 4);
+    A(&m->router_partial, 16 * T * size_t(router_rows_padded(d)) * 4);
+    const size_t done_n = size_t(router_rows_padded(d) / 32) * ((T + 7) / 8);
+    A(&m->router_done, done_n * 4);
+    if (rc == ZC_OK && (e = cudaMemset(m->router_done, 0, done_n * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
     A(&c.hbuf, (T * K + T) * F * 4); A(&c.expert_out, T * K * H * 4); A(&c.shared_out, T * H * 4); A(&c.status, 16);
     uint8_t* p0 = nullptr; uint8_t* p1 = nullptr; uint8_t* dx = nullptr; uint8_t* dout = nullptr; uint8_t* dfin = nullptr;
     A(&p0, T * H * 4); A(&p1, T * H * 4); A(&dx, T * H * 4); A(&dout, T * H * 4); A(&dfin, T * H * 4);
@@ -237,7 +245,7 @@ int zc_moe_route(zc_moe* m, const float* logits, uint32_t tokens, int32_t* ids, 
     if (!tokens || tokens > m->d.max_tokens || !logits || !ids || !weights) return fail(m, ZC_EINVAL, "invalid route selection buffers");
     Call c = m->scratch;
     c.T = tokens; c.logits = const_cast<float*>(logits); c.ids = ids; c.weights = weights;
-    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), true, false);
+    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), true, false, false);
     if (n < 0) return n;
     m->launches += n;
     return ZC_OK;
@@ -248,7 +256,7 @@ int zc_moe_permute(zc_moe* m, const int32_t* ids, uint32_t tokens, int32_t* offs
     if (!tokens || tokens > m->d.max_tokens || !ids || !offsets || !perm) return fail(m, ZC_EINVAL, "invalid permutation buffers");
     Call c = m->scratch;
     c.T = tokens; c.ids = const_cast<int32_t*>(ids); c.offsets = offsets; c.perm = perm;
-    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), false, true);
+    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), false, true, false);
     if (n < 0) return n;
     m->launches += n;
     return ZC_OK;
@@ -291,16 +299,12 @@ static int stack_launches(zc_moe* m, const void* x, uint32_t tokens, void* out, 
     int total = 0;
     const void* in = x;
     for (uint32_t l = 0; l < d.layers; ++l) {
-        void* layer_out = l + 1 == d.layers ? out : m->dev_out;
-        int n = run_layer(m, l, in, tokens, layer_out, s);
+        const bool last = l + 1 == d.layers;
+        void* next = last ? nullptr : m->act[l & 1];
+        int n = run_layer(m, l, in, tokens, last ? out : m->dev_out, s, next);
         if (n < 0) return n;
         total += n;
-        if (l + 1 < d.layers) {
-            void* next = m->act[l & 1];
-            if ((n = launch_norm_act(m, layer_out, d.out_dtype, next, d.act_dtype, tokens, d.hidden, s)) < 0) return n;
-            total += n;
-            in = next;
-        }
+        in = next;
     }
     return total;
 }

@@ -158,6 +158,8 @@ struct zc_moe {
     std::vector<zc::LayerMem> layers;
     std::vector<void*> allocations;
     zc::Call scratch{};           // scratch pointers (x/out/layer fields filled per call)
+    uint32_t* router_done = nullptr;     // arrival counters of the router's (row tile, token tile) pairs
+    float* router_partial = nullptr;     // [16, max_tokens, rows_padded] partition sums of the router
     void* act[2] = {nullptr, nullptr};   // stack ping-pong activations [max_tokens, H]
     void* host_x = nullptr;       // pinned staging for the host entry points
     void* host_out = nullptr;
@@ -179,9 +181,12 @@ struct zc_moe {
 namespace zc {
 // Launchers (each returns the number of kernels launched, or a negative ZC_* code with moe->error set).
 int launch_router(zc_moe* m, const Call& c, cudaStream_t s);
-int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute);
+int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s);
+uint32_t router_rows_padded(const zc_moe_desc& d);
+int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute, bool from_partials);
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s);
+int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cudaStream_t s);
 int launch_norm_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s);
 int launch_synth_layer(zc_moe* m, uint32_t layer, uint64_t seed, cudaStream_t s);
 enum KernelKind { KERNEL_ROUTER = 0, KERNEL_ROUTE, KERNEL_PERMUTE, KERNEL_GATE_UP, KERNEL_DOWN, KERNEL_COMBINE, KERNEL_NORM_ACT, KERNEL_KINDS };

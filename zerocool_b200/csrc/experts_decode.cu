@@ -39,7 +39,16 @@ constexpr int NTOK = 8;               // token rows per MMA pass (the N of m16n8
 constexpr int WARPS = 8;
 constexpr int EXPERT_THREADS = WARPS * 32;
 constexpr int ROW_PAD = 8;            // halves added to each staged row (keeps 16-byte reads conflict free)
-constexpr int STAGES = 3;             // cp.async ring depth per warp
+#ifndef ZC_STAGES
+#define ZC_STAGES 3
+#endif
+#ifndef ZC_MIN_BLOCKS
+#define ZC_MIN_BLOCKS 2
+#endif
+#ifndef ZC_MIN_BLOCKS_DOWN
+#define ZC_MIN_BLOCKS_DOWN 4
+#endif
+constexpr int STAGES = ZC_STAGES;     // cp.async ring depth per warp
 constexpr int CH = 2;                 // quantisation groups per ring stage
 
 template <int BITS> struct Fmt {
@@ -50,12 +59,6 @@ template <int BITS> struct Fmt {
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
@@ -69,21 +72,33 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Same product with the addend taken from c (the first MMA of a group starts from the folded offset).
+__device__ __forceinline__ void mma_f16_16816_c(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
+                                                float c0, float c1, float c2, float c3) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+
 struct ItemInfo {
     const uint8_t* record;
     uint32_t count;     // rows of this item
-    uint32_t pos0;      // routed: first position in perm; shared: 0
+    uint32_t pos0;      // routed: first position in perm; shared: first token of this block of rows
     uint32_t hrow0;     // first row in hbuf
     bool shared;
 };
 
+// Items of a launch: the shared expert contributes one item per NTOK tokens (so that its row blocks run
+// in parallel instead of as passes of one CTA), then one item per routed expert that received work.
 __device__ __forceinline__ bool decode_item(const Call& c, uint32_t item, ItemInfo& it) {
     if (c.has_shared) {
-        if (item == 0) {
-            it.record = c.shared_record; it.count = c.T; it.pos0 = 0; it.hrow0 = c.T * c.K; it.shared = true;
+        const uint32_t blocks = (c.T + NTOK - 1) / NTOK;
+        if (item < blocks) {
+            it.record = c.shared_record; it.pos0 = item * NTOK; it.count = min(uint32_t(NTOK), c.T - it.pos0);
+            it.hrow0 = c.T * c.K + it.pos0; it.shared = true;
             return true;
         }
-        --item;
+        item -= blocks;
     }
     if (item >= uint32_t(c.counters[0])) return false;
     const uint32_t e = uint32_t(c.active[item]);
@@ -97,8 +112,9 @@ __device__ __forceinline__ bool decode_item(const Call& c, uint32_t item, ItemIn
 
 // Stage the valid source rows (n < nvalid) of K elements into shared memory as FP16 (hi, and lo when
 // SPLIT), in the k order the MMA fragments expect, with the per-group sums
-//   sums[grp][n] = (Sx, Sf):  Sx = sum of x over the group (REF: the reference's BF16 sum of four,
-//   qwen.metal:55), Sf = sum of the values as staged (used to remove the folded 1024 offset).
+//   sums[grp][n] = (Sx, P):  Sx = sum of x over the group (REF: the reference's BF16 sum of four,
+//   qwen.metal:55), P = -1024 * sum of the values as staged: the MMA accumulator starts from P, which
+//   removes the folded 1024 offset of the codes (0 without FOLD).
 //   Q4 order inside each block of 8: (0,4,1,5,2,6,3,7), odd k staged / 16 when FOLD; Q8: natural order.
 // Rows n >= nvalid are left as they are: an MMA column only depends on its own B column.
 template <bool Q4ORDER, bool SPLIT, bool FOLD>
@@ -143,7 +159,7 @@ __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const 
             sf += __shfl_xor_sync(0xffffffffu, sf, off);
         }
         if (!live) continue;
-        if ((q & 7) == 0) *reinterpret_cast<float2*>(sums + ((q / 8) * NTOK + n) * 2) = make_float2(sx, sf);
+        if ((q & 7) == 0) *reinterpret_cast<float2*>(sums + ((q / 8) * NTOK + n) * 2) = make_float2(sx, FOLD ? -1024.0f * sf : 0.0f);
         constexpr int order_q4[8] = {0, 4, 1, 5, 2, 6, 3, 7};
         uint32_t ph[4], pl[4];
 #pragma unroll
@@ -157,30 +173,58 @@ __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const 
     }
 }
 
-// Issue the cp.async copies of one chunk (CH groups starting at grp0) of one matrix into a ring stage.
+// Source of one matrix for this lane's cp.async copies: lane l copies 16-byte piece l (and l+32 for Q8)
+// of each group's 16 x ROWB code block, and 4 bytes of metadata (kind = l/16, row = l%16).
 template <int BITS>
-__device__ __forceinline__ void issue_matrix(uint8_t* stage, const uint8_t* record, const Projection& pr, uint32_t r0, uint32_t G,
-                                             uint32_t grp0, uint32_t valid, uint32_t lane) {
-    constexpr int ROWB = Fmt<BITS>::ROWB;
-    const uint32_t row_bytes = pr.K * BITS / 8;
-    const uint8_t* codes = record + pr.codes;
-    constexpr int PIECES = 16 * ROWB / 16;          // sixteen-byte pieces per group: 32 (Q4) or 64 (Q8)
+struct LaneSource {
+    const uint8_t* codes;      // record + codes offset + this lane's byte offset inside a group block row
+    const uint8_t* meta;       // record + scales or biases offset (by kind)
+    uint32_t row_bytes, meta_row, meta_dst;
+    uint32_t code_row[BITS / 4];   // row inside the tile of each of this lane's pieces
+    uint32_t code_dst[BITS / 4];   // byte offset of the piece inside a group's stage block
+    const uint8_t* tile_codes[BITS / 4];   // set per tile: source of group 0 for each piece
+    const uint8_t* tile_meta;              // set per tile: source of group 0 metadata
+    __device__ __forceinline__ void init(const uint8_t* record, const Projection& pr, uint32_t lane) {
+        constexpr int ROWB = Fmt<BITS>::ROWB, PARTS = ROWB / 16;
+        row_bytes = pr.K * BITS / 8;
 #pragma unroll
-    for (int j = 0; j < CH; ++j) {
-        if (uint32_t(j) < valid) {
-#pragma unroll
-            for (int p = 0; p < PIECES / 32; ++p) {
-                const uint32_t piece = p * 32 + lane, row = piece / (ROWB / 16), part = piece % (ROWB / 16);
-                cp_async16(stage + (j * 16 + row) * ROWB + part * 16,
-                           codes + size_t(r0 + row) * row_bytes + size_t(grp0 + j) * ROWB + part * 16);
-            }
+        for (int p = 0; p < BITS / 4; ++p) {
+            const uint32_t piece = p * 32 + lane;
+            code_row[p] = piece / PARTS;
+            code_dst[p] = (piece / PARTS) * ROWB + (piece % PARTS) * 16;
         }
+        codes = record + pr.codes + (lane % PARTS) * 16;
+        meta = record + (lane / 16 ? pr.biases : pr.scales);
+        meta_row = lane % 16;
+        meta_dst = ((lane % 16) * 2 + lane / 16) * 4;
     }
-    // metadata: lane -> (kind = lane / 16, row = lane % 16); CH = 2 halves = 4 bytes. The second half is
-    // only used when that group exists; it is always inside the matrix because G is even.
-    const uint32_t kind = lane / 16, row = lane % 16;
-    const uint8_t* meta = record + (kind ? pr.biases : pr.scales) + (size_t(r0 + row) * G + grp0) * 2;
-    cp_async4(stage + Fmt<BITS>::CODES + (kind * 16 + row) * 4, meta);
+    __device__ __forceinline__ void set_tile(uint32_t row0, uint32_t G) {
+#pragma unroll
+        for (int p = 0; p < BITS / 4; ++p) tile_codes[p] = codes + size_t(row0 + code_row[p]) * row_bytes;
+        tile_meta = meta + size_t(row0 + meta_row) * G * 2;
+    }
+};
+
+// Issue the cp.async copies of one chunk (CH groups starting at grp0) of one matrix into a ring stage.
+// Stage layout: codes [CH][16 rows][ROWB], then metadata [16 rows][kind][CH] halves.
+template <int BITS>
+__device__ __forceinline__ void issue_matrix(uint32_t stage, const LaneSource<BITS>& src, uint32_t grp0) {
+    constexpr int ROWB = Fmt<BITS>::ROWB;
+#pragma unroll
+    for (int p = 0; p < BITS / 4; ++p) {
+        const uint8_t* g0 = src.tile_codes[p] + grp0 * ROWB;
+#pragma unroll
+        for (int j = 0; j < CH; ++j)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + j * 16 * ROWB + src.code_dst[p]), "l"(g0 + j * ROWB) : "memory");
+    }
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(stage + Fmt<BITS>::CODES + src.meta_dst), "l"(src.tile_meta + grp0 * 2) : "memory");
+}
+
+// (a & b) | c in one logic instruction.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
 
 // Q4: one word -> four half2 (k0,k4) (k1,k5) (k2,k6) (k3,k7) of its 8 codes.
@@ -188,10 +232,10 @@ template <bool FOLD>
 __device__ __forceinline__ void dequant_q4(uint32_t w, uint32_t (&p)[4]) {
     const uint32_t lo = 0x000f000fu, hi = 0x00f000f0u, magic = 0x64006400u;
     const uint32_t w8 = w >> 8;
-    p[0] = (w & lo) | magic;
-    p[1] = (w & hi) | magic;
-    p[2] = (w8 & lo) | magic;
-    p[3] = (w8 & hi) | magic;
+    p[0] = and_or(w, lo, magic);
+    p[1] = and_or(w, hi, magic);
+    p[2] = and_or(w8, lo, magic);
+    p[3] = and_or(w8, hi, magic);
     if (!FOLD) {
         const __half2 k1024 = __floats2half2_rn(1024.0f, 1024.0f), k16 = __floats2half2_rn(0.0625f, 0.0625f), k64 = __floats2half2_rn(-64.0f, -64.0f);
 #pragma unroll
@@ -216,14 +260,15 @@ __device__ __forceinline__ void dequant_q8(uint32_t w, bool is_signed, uint32_t 
 
 // d(16 rows x 8 tokens) = sum over one 64-wide group of code * x for the lane's rows g (w0) and g+8 (w1).
 template <int BITS, bool SPLIT, bool FOLD>
-__device__ __forceinline__ void group_mma(float (&d)[4], const uint32_t* w0, const uint32_t* w1, const uint4 (&bh)[2], const uint4 (&bl)[2], bool q8_signed) {
+__device__ __forceinline__ void group_mma(float (&d)[4], float c0, float c1, const uint32_t* w0, const uint32_t* w1, const uint4 (&bh)[2], const uint4 (&bl)[2], bool q8_signed) {
     if constexpr (BITS == 4) {
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
             uint32_t p0[4], p1[4];
             dequant_q4<FOLD>(w0[m], p0);
             dequant_q4<FOLD>(w1[m], p1);
-            mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], bh[m].x, bh[m].y);
+            if (m == 0) mma_f16_16816_c(d, p0[0], p1[0], p0[1], p1[1], bh[m].x, bh[m].y, c0, c1, c0, c1);
+            else mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], bh[m].x, bh[m].y);
             mma_f16_16816(d, p0[2], p1[2], p0[3], p1[3], bh[m].z, bh[m].w);
             if constexpr (SPLIT) {
                 mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], bl[m].x, bl[m].y);
@@ -237,7 +282,8 @@ __device__ __forceinline__ void group_mma(float (&d)[4], const uint32_t* w0, con
             dequant_q8(w0[m], q8_signed, p0);
             dequant_q8(w1[m], q8_signed, p1);
             const uint32_t b0 = (m & 1) ? bh[m / 2].z : bh[m / 2].x, b1 = (m & 1) ? bh[m / 2].w : bh[m / 2].y;
-            mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], b0, b1);
+            if (m == 0) mma_f16_16816_c(d, p0[0], p1[0], p0[1], p1[1], b0, b1, c0, c1, c0, c1);
+            else mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], b0, b1);
             if constexpr (SPLIT) {
                 const uint32_t c0 = (m & 1) ? bl[m / 2].z : bl[m / 2].x, c1 = (m & 1) ? bl[m / 2].w : bl[m / 2].y;
                 mma_f16_16816(d, p0[0], p1[0], p0[1], p1[1], c0, c1);
@@ -247,12 +293,14 @@ __device__ __forceinline__ void group_mma(float (&d)[4], const uint32_t* w0, con
 }
 
 // ---------------------------------------------------------------------------------------------
-// The expert kernel. Grid: (N / (16 * RT), items) with RT = WARPS / KS row tiles per CTA.
+// The expert kernel. Grid: (N / (16 * RT * tiles_per_warp), items) with RT = WARPS / KS row tiles side
+// by side in a CTA; a warp walks `tiles_per_warp` consecutive 16-row tiles, and its cp.async ring keeps
+// streaming across the tile boundaries.
 //   NMAT = 2: gate/up + SwiGLU into hbuf.   NMAT = 1: down projection into the router positions.
 //   KS: warps that split K for one row tile (partials added in warp order through shared memory).
 // ---------------------------------------------------------------------------------------------
-template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD>
-__global__ void __launch_bounds__(EXPERT_THREADS, 2) expert_kernel(Call c) {
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16>
+__global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN : ZC_MIN_BLOCKS) expert_kernel(Call c, uint32_t tiles_per_warp) {
     constexpr int RT = WARPS / KS;
     constexpr int STAGE = NMAT * Fmt<BITS>::MATRIX;
     constexpr int WORDS = Fmt<BITS>::ROWB / 16;      // 32-bit words per lane per row per group: 2 (Q4) / 4 (Q8)
@@ -271,36 +319,46 @@ __global__ void __launch_bounds__(EXPERT_THREADS, 2) expert_kernel(Call c) {
 
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, cq = lane % 4;
     const uint32_t rt = warp / KS, ks = warp % KS;
-    const uint32_t r0 = (blockIdx.x * RT + rt) * 16;
-    const Projection pr0 = NMAT == 2 ? c.gate : c.down;
-    const Projection pr1 = c.up;
+    const uint32_t first_tile = (blockIdx.x * RT + rt) * tiles_per_warp;
     uint8_t* my_ring = ring + warp * STAGES * STAGE;
-    const uint32_t nchunks = (G + CH - 1) / CH;
+    const uint32_t nchunks = G / CH;                 // G is even
     const uint32_t my_n = ks < nchunks ? (nchunks - ks + KS - 1) / KS : 0;
-    const bool meta_f16 = c.meta_f16, q8s = c.q8_signed;
+    const uint32_t my_tiles = my_n ? tiles_per_warp : 0;
+    const bool q8s = c.q8_signed;
     float* out_base = it.shared ? c.shared_out : c.expert_out;
-
-    auto issue = [&](uint32_t i) {
-        if (i < my_n) {
-            const uint32_t grp0 = (ks + i * KS) * CH, valid = min(uint32_t(CH), G - grp0);
-            uint8_t* stage = my_ring + (i % STAGES) * STAGE;
-            issue_matrix<BITS>(stage, it.record, pr0, r0, G, grp0, valid, lane);
-            if constexpr (NMAT == 2) issue_matrix<BITS>(stage + Fmt<BITS>::MATRIX, it.record, pr1, r0, G, grp0, valid, lane);
-        }
-        cp_async_commit();
-    };
+    LaneSource<BITS> src[NMAT];
+    src[0].init(it.record, NMAT == 2 ? c.gate : c.down, lane);
+    if constexpr (NMAT == 2) src[1].init(it.record, c.up, lane);
 
     for (uint32_t pass = 0; pass * NTOK < it.count; ++pass) {
         const uint32_t nvalid = min(uint32_t(NTOK), it.count - pass * NTOK);
+        uint32_t is_tile = 0, is_chunk = 0, is_slot = 0;        // producer position in the flattened (tile, chunk) sequence
+        const uint32_t ring_base = smem_u32(my_ring);
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) src[m].set_tile(first_tile * 16, G);
+        auto issue = [&]() {
+            if (is_tile < my_tiles) {
+                const uint32_t stage = ring_base + is_slot * STAGE, grp0 = (ks + is_chunk * KS) * CH;
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) issue_matrix<BITS>(stage + m * Fmt<BITS>::MATRIX, src[m], grp0);
+                if (++is_chunk == my_n) {
+                    is_chunk = 0; ++is_tile;
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) src[m].set_tile((first_tile + is_tile) * 16, G);
+                }
+            }
+            cp_async_commit();
+            is_slot = is_slot + 1 == STAGES ? 0 : is_slot + 1;
+        };
         __syncthreads();                       // everything of the previous pass has been consumed
 #pragma unroll
-        for (int i = 0; i < STAGES - 1; ++i) issue(i);   // weights do not depend on the rows: start them first
+        for (int i = 0; i < STAGES - 1; ++i) issue();    // weights do not depend on the rows: start them first
         if (threadIdx.x < NTOK) {
             const uint32_t i = pass * NTOK + threadIdx.x;
             if (i < it.count) {
-                if (NMAT == 2) rows[threadIdx.x] = it.shared ? int(i) : c.perm[it.pos0 + i] / int(c.K);
+                if (NMAT == 2) rows[threadIdx.x] = it.shared ? int(it.pos0 + i) : c.perm[it.pos0 + i] / int(c.K);
                 else rows[threadIdx.x] = int(it.hrow0 + i);
-                const uint32_t slot = it.shared ? i : uint32_t(c.perm[it.pos0 + i]);
+                const uint32_t slot = it.shared ? it.pos0 + i : uint32_t(c.perm[it.pos0 + i]);
                 dest[threadIdx.x] = NMAT == 2 ? (long long)(it.hrow0 + i) * c.F : (long long)slot * c.H;
             } else { rows[threadIdx.x] = -1; dest[threadIdx.x] = -1; }
         }
@@ -309,68 +367,10 @@ __global__ void __launch_bounds__(EXPERT_THREADS, 2) expert_kernel(Call c) {
                                             rows, nvalid, K, c.ref && BITS == 4, xhi, xlo, sums);
         __syncthreads();
 
-        float acc[NMAT][4];
-#pragma unroll
-        for (int m = 0; m < NMAT; ++m) { acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f; }
-
-        for (uint32_t i = 0; i < my_n; ++i) {
-            cp_async_wait<STAGES - 2>();
-            __syncwarp();
-            const uint8_t* stage = my_ring + (i % STAGES) * STAGE;
-            const uint32_t grp0 = (ks + i * KS) * CH, valid = min(uint32_t(CH), G - grp0);
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-                if (uint32_t(j) < valid) {
-                    const uint32_t grp = grp0 + j;
-                    uint4 bh[2], bl[2];
-                    const __half* bp = xhi + g * RS + grp * 64 + cq * 16;
-                    bh[0] = *reinterpret_cast<const uint4*>(bp);
-                    bh[1] = *reinterpret_cast<const uint4*>(bp + 8);
-                    if constexpr (SPLIT) {
-                        const __half* lp = xlo + g * RS + grp * 64 + cq * 16;
-                        bl[0] = *reinterpret_cast<const uint4*>(lp);
-                        bl[1] = *reinterpret_cast<const uint4*>(lp + 8);
-                    }
-                    const float4 sm = *reinterpret_cast<const float4*>(sums + (grp * NTOK + 2 * cq) * 2);   // Sx, Sf of tokens 2cq, 2cq+1
-#pragma unroll
-                    for (int m = 0; m < NMAT; ++m) {
-                        const uint8_t* ms = stage + m * Fmt<BITS>::MATRIX;
-                        uint32_t w0[WORDS], w1[WORDS];
-                        if constexpr (BITS == 4) {
-                            const uint2 a = *reinterpret_cast<const uint2*>(ms + (j * 16 + g) * 32 + cq * 8);
-                            const uint2 b = *reinterpret_cast<const uint2*>(ms + (j * 16 + g + 8) * 32 + cq * 8);
-                            w0[0] = a.x; w0[1] = a.y; w1[0] = b.x; w1[1] = b.y;
-                        } else {
-                            const uint4 a = *reinterpret_cast<const uint4*>(ms + (j * 16 + g) * 64 + cq * 16);
-                            const uint4 b = *reinterpret_cast<const uint4*>(ms + (j * 16 + g + 8) * 64 + cq * 16);
-                            w0[0] = a.x; w0[1] = a.y; w0[2] = a.z; w0[3] = a.w; w1[0] = b.x; w1[1] = b.y; w1[2] = b.z; w1[3] = b.w;
-                        }
-                        float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                        group_mma<BITS, SPLIT, FOLDQ>(d, w0, w1, bh, bl, q8s);
-                        const uint16_t* mt = reinterpret_cast<const uint16_t*>(ms + Fmt<BITS>::CODES);   // [kind][row][CH]
-                        const float s0 = meta_to_float(mt[(0 * 16 + g) * 2 + j], meta_f16), s1 = meta_to_float(mt[(0 * 16 + g + 8) * 2 + j], meta_f16);
-                        const float b0 = meta_to_float(mt[(1 * 16 + g) * 2 + j], meta_f16), b1 = meta_to_float(mt[(1 * 16 + g + 8) * 2 + j], meta_f16);
-                        if constexpr (FOLDQ) {
-                            d[0] = __fmaf_rn(-1024.0f, sm.y, d[0]); d[1] = __fmaf_rn(-1024.0f, sm.w, d[1]);
-                            d[2] = __fmaf_rn(-1024.0f, sm.y, d[2]); d[3] = __fmaf_rn(-1024.0f, sm.w, d[3]);
-                        }
-                        acc[m][0] = __fmaf_rn(s0, d[0], acc[m][0]); acc[m][0] = __fmaf_rn(b0, sm.x, acc[m][0]);
-                        acc[m][1] = __fmaf_rn(s0, d[1], acc[m][1]); acc[m][1] = __fmaf_rn(b0, sm.z, acc[m][1]);
-                        acc[m][2] = __fmaf_rn(s1, d[2], acc[m][2]); acc[m][2] = __fmaf_rn(b1, sm.x, acc[m][2]);
-                        acc[m][3] = __fmaf_rn(s1, d[3], acc[m][3]); acc[m][3] = __fmaf_rn(b1, sm.z, acc[m][3]);
-                    }
-                }
-            }
-            __syncwarp();
-            issue(i + STAGES - 1);
-        }
-        cp_async_wait<0>();
-
         // The lane holds rows g, g+8 of its tile for tokens 2cq, 2cq+1.
-        auto finish = [&](uint32_t row_in_cta, uint32_t n, float a0, float a1) {
+        auto finish = [&](uint32_t row, uint32_t n, float a0, float a1) {
             const long long d = dest[n];
             if (d < 0) return;
-            const uint32_t row = blockIdx.x * RT * 16 + row_in_cta;
             if constexpr (NMAT == 2) {
                 float h;
                 if (c.ref) {   // qwen.metal:71-81
@@ -384,66 +384,142 @@ __global__ void __launch_bounds__(EXPERT_THREADS, 2) expert_kernel(Call c) {
                 out_base[d + row] = c.ref ? bf_round(a0) : a0;
             }
         };
-        if constexpr (KS == 1) {
+
+        uint32_t slot = 0;
+        for (uint32_t tile = 0; tile < tiles_per_warp; ++tile) {
+            float acc[NMAT][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                finish(rt * 16 + g + 8 * (i >> 1), 2 * cq + (i & 1), acc[0][i], acc[NMAT - 1][i]);
-        } else {
-            // partials: [ks][matrix][row in CTA][token]
+            for (int m = 0; m < NMAT; ++m) { acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f; }
+            for (uint32_t i = 0; i < my_n; ++i) {
+                cp_async_wait<STAGES - 2>();
+                __syncwarp();
+                const uint8_t* stage = my_ring + slot * STAGE;
+                slot = slot + 1 == STAGES ? 0 : slot + 1;
+                const uint32_t grp0 = (ks + i * KS) * CH;
+                float sc[NMAT][2][CH], bi[NMAT][2][CH];          // scale and bias of rows g, g+8 for the CH groups
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
-                float* mine = red + ((ks * NMAT + m) * RT * 16 + rt * 16) * NTOK;
-                *reinterpret_cast<float2*>(mine + g * NTOK + 2 * cq) = make_float2(acc[m][0], acc[m][1]);
-                *reinterpret_cast<float2*>(mine + (g + 8) * NTOK + 2 * cq) = make_float2(acc[m][2], acc[m][3]);
-            }
-            __syncthreads();
-            for (uint32_t o = threadIdx.x; o < RT * 16 * NTOK; o += EXPERT_THREADS) {
-                const uint32_t row = o / NTOK, n = o % NTOK;
-                float a0 = 0.0f, a1 = 0.0f;
+                for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-                for (int k = 0; k < KS; ++k) {
-                    a0 += red[((k * NMAT + 0) * RT * 16 + row) * NTOK + n];
-                    if constexpr (NMAT == 2) a1 += red[((k * NMAT + 1) * RT * 16 + row) * NTOK + n];
+                    for (int r = 0; r < 2; ++r) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(stage + m * Fmt<BITS>::MATRIX + Fmt<BITS>::CODES + (g + 8 * r) * 8);
+                        if constexpr (META_F16) {
+                            const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                            const float2 b2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                            sc[m][r][0] = s2.x; sc[m][r][1] = s2.y; bi[m][r][0] = b2.x; bi[m][r][1] = b2.y;
+                        } else {
+                            sc[m][r][0] = __uint_as_float(raw.x << 16); sc[m][r][1] = __uint_as_float(raw.x & 0xffff0000u);
+                            bi[m][r][0] = __uint_as_float(raw.y << 16); bi[m][r][1] = __uint_as_float(raw.y & 0xffff0000u);
+                        }
+                    }
                 }
-                finish(row, n, a0, a1);
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    const uint32_t grp = grp0 + j;
+                    uint4 bh[2], bl[2];
+                    const __half* bp = xhi + g * RS + grp * 64 + cq * 16;
+                    bh[0] = *reinterpret_cast<const uint4*>(bp);
+                    bh[1] = *reinterpret_cast<const uint4*>(bp + 8);
+                    if constexpr (SPLIT) {
+                        const __half* lp = xlo + g * RS + grp * 64 + cq * 16;
+                        bl[0] = *reinterpret_cast<const uint4*>(lp);
+                        bl[1] = *reinterpret_cast<const uint4*>(lp + 8);
+                    }
+                    const float4 sm = *reinterpret_cast<const float4*>(sums + (grp * NTOK + 2 * cq) * 2);   // (Sx, P) of tokens 2cq, 2cq+1
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        const uint8_t* ms = stage + m * Fmt<BITS>::MATRIX;
+                        uint32_t w0[WORDS], w1[WORDS];
+                        if constexpr (BITS == 4) {
+                            const uint2 a = *reinterpret_cast<const uint2*>(ms + (j * 16 + g) * 32 + cq * 8);
+                            const uint2 b = *reinterpret_cast<const uint2*>(ms + (j * 16 + g + 8) * 32 + cq * 8);
+                            w0[0] = a.x; w0[1] = a.y; w1[0] = b.x; w1[1] = b.y;
+                        } else {
+                            const uint4 a = *reinterpret_cast<const uint4*>(ms + (j * 16 + g) * 64 + cq * 16);
+                            const uint4 b = *reinterpret_cast<const uint4*>(ms + (j * 16 + g + 8) * 64 + cq * 16);
+                            w0[0] = a.x; w0[1] = a.y; w0[2] = a.z; w0[3] = a.w; w1[0] = b.x; w1[1] = b.y; w1[2] = b.z; w1[3] = b.w;
+                        }
+                        float d[4];
+                        group_mma<BITS, SPLIT, FOLDQ>(d, sm.y, sm.w, w0, w1, bh, bl, q8s);    // starts from P: removes the folded offset
+                        acc[m][0] = __fmaf_rn(sc[m][0][j], d[0], acc[m][0]); acc[m][0] = __fmaf_rn(bi[m][0][j], sm.x, acc[m][0]);
+                        acc[m][1] = __fmaf_rn(sc[m][0][j], d[1], acc[m][1]); acc[m][1] = __fmaf_rn(bi[m][0][j], sm.z, acc[m][1]);
+                        acc[m][2] = __fmaf_rn(sc[m][1][j], d[2], acc[m][2]); acc[m][2] = __fmaf_rn(bi[m][1][j], sm.x, acc[m][2]);
+                        acc[m][3] = __fmaf_rn(sc[m][1][j], d[3], acc[m][3]); acc[m][3] = __fmaf_rn(bi[m][1][j], sm.z, acc[m][3]);
+                    }
+                }
+                __syncwarp();
+                issue();
+            }
+            const uint32_t cta_row0 = blockIdx.x * RT * tiles_per_warp * 16;
+            if constexpr (KS == 1) {
+                const uint32_t row0 = (first_tile + tile) * 16;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) finish(row0 + g + 8 * (i >> 1), 2 * cq + (i & 1), acc[0][i], acc[NMAT - 1][i]);
+            } else {
+                // partials: [ks][matrix][row tile in CTA][row][token]
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) {
+                    float* mine = red + ((ks * NMAT + m) * RT * 16 + rt * 16) * NTOK;
+                    *reinterpret_cast<float2*>(mine + g * NTOK + 2 * cq) = make_float2(acc[m][0], acc[m][1]);
+                    *reinterpret_cast<float2*>(mine + (g + 8) * NTOK + 2 * cq) = make_float2(acc[m][2], acc[m][3]);
+                }
+                __syncthreads();
+                for (uint32_t o = threadIdx.x; o < RT * 16 * NTOK; o += EXPERT_THREADS) {
+                    const uint32_t r = o / NTOK, n = o % NTOK;
+                    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < KS; ++k) {
+                        a0 += red[((k * NMAT + 0) * RT * 16 + r) * NTOK + n];
+                        if constexpr (NMAT == 2) a1 += red[((k * NMAT + 1) * RT * 16 + r) * NTOK + n];
+                    }
+                    // row tile r/16 of this CTA walks tiles (blockIdx.x*RT + r/16) * tiles_per_warp + tile
+                    finish(cta_row0 + ((r / 16) * tiles_per_warp + tile) * 16 + r % 16, n, a0, a1);
+                }
+                __syncthreads();
             }
         }
+        cp_async_wait<0>();
     }
 }
 
-template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD>
-int launch_expert(zc_moe* m, const Call& c, uint32_t items, cudaStream_t s) {
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16>
+int launch_expert(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
     constexpr int RT = WARPS / KS;
     const uint32_t K = NMAT == 2 ? c.H : c.F, N = NMAT == 2 ? c.F : c.H, G = K / 64;
     const size_t smem = size_t(SPLIT ? 2 : 1) * NTOK * (K + ROW_PAD) * 2 + size_t(G) * NTOK * 2 * 4 +
                         size_t(WARPS) * STAGES * NMAT * Fmt<BITS>::MATRIX + (KS > 1 ? size_t(KS) * NMAT * RT * 16 * NTOK * 4 : 0);
     if (smem > 220 * 1024) return fail(m, ZC_EINVAL, "expert kernel: shape needs too much shared memory");
-    if (N % (16 * RT)) return fail(m, ZC_EINVAL, "expert kernel: rows not a multiple of the CTA tile");
-    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD>;
+    while (tiles_per_warp > 1 && N % (16 * RT * tiles_per_warp)) --tiles_per_warp;
+    if (N % (16 * RT * tiles_per_warp)) return fail(m, ZC_EINVAL, "expert kernel: rows not a multiple of the CTA tile");
+    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16>;
     static size_t configured = 0;       // one per instantiation of this function template
     if (smem > configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return check_launch(m, "expert kernel attribute");
         configured = smem;
     }
     Timed t(m, s, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN);
-    kernel<<<dim3(N / (16 * RT), items), EXPERT_THREADS, smem, s>>>(c);
+    kernel<<<dim3(N / (16 * RT * tiles_per_warp), items), EXPERT_THREADS, smem, s>>>(c, tiles_per_warp);
     return check_launch(m, NMAT == 2 ? "gate_up" : "down");
 }
 
-template <int NMAT, int KS>
-int dispatch_expert(zc_moe* m, const Call& c, uint32_t items, bool split, uint32_t bits, bool fold, cudaStream_t s) {
+template <int NMAT, int KS, bool META_F16>
+int dispatch_bits(zc_moe* m, const Call& c, uint32_t items, uint32_t tpw, bool split, uint32_t bits, bool fold, cudaStream_t s) {
     if (bits == 4) {
-        if (fold) return split ? launch_expert<4, true, NMAT, KS, true>(m, c, items, s) : launch_expert<4, false, NMAT, KS, true>(m, c, items, s);
-        return split ? launch_expert<4, true, NMAT, KS, false>(m, c, items, s) : launch_expert<4, false, NMAT, KS, false>(m, c, items, s);
+        if (fold) return split ? launch_expert<4, true, NMAT, KS, true, META_F16>(m, c, items, tpw, s) : launch_expert<4, false, NMAT, KS, true, META_F16>(m, c, items, tpw, s);
+        return split ? launch_expert<4, true, NMAT, KS, false, META_F16>(m, c, items, tpw, s) : launch_expert<4, false, NMAT, KS, false, META_F16>(m, c, items, tpw, s);
     }
-    return split ? launch_expert<8, true, NMAT, KS, false>(m, c, items, s) : launch_expert<8, false, NMAT, KS, false>(m, c, items, s);
+    return split ? launch_expert<8, true, NMAT, KS, false, META_F16>(m, c, items, tpw, s) : launch_expert<8, false, NMAT, KS, false, META_F16>(m, c, items, tpw, s);
+}
+template <int NMAT, int KS>
+int dispatch_expert(zc_moe* m, const Call& c, uint32_t items, uint32_t tpw, bool split, uint32_t bits, bool fold, cudaStream_t s) {
+    return c.meta_f16 ? dispatch_bits<NMAT, KS, true>(m, c, items, tpw, split, bits, fold, s)
+                      : dispatch_bits<NMAT, KS, false>(m, c, items, tpw, split, bits, fold, s);
 }
 
 }  // namespace
 
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s) {
     const uint32_t routed = c.T * c.K < c.local_experts ? c.T * c.K : c.local_experts;
-    const uint32_t items = routed + (c.has_shared ? 1 : 0);
+    const uint32_t items = routed + (c.has_shared ? (c.T + NTOK - 1) / NTOK : 0);
     // A BF16 activation is exact as one FP16 term; an FP32 activation needs two, except under the
     // reference arithmetic, whose FP32 buffers hold BF16 values by contract.
     const bool split_x = c.act_dtype == ZC_F32 && !c.ref;
@@ -452,11 +528,11 @@ int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s) {
     // Few rows in flight: split K over all eight warps so that even one token fills the machine.
     const bool small = c.T * (c.K + (c.has_shared ? 1 : 0)) <= 64;
     int rc;
-    if (small) rc = dispatch_expert<2, 8>(m, c, items, split_x, c.gate.bits, fold, s);
-    else rc = dispatch_expert<2, 2>(m, c, items, split_x, c.gate.bits, fold, s);
+    if (small) rc = dispatch_expert<2, 8>(m, c, items, 1, split_x, c.gate.bits, fold, s);
+    else rc = dispatch_expert<2, 1>(m, c, items, 1, split_x, c.gate.bits, fold, s);
     if (rc < 0) return rc;
-    if (small) rc = dispatch_expert<1, 2>(m, c, items, split_h, c.down.bits, fold, s);
-    else rc = dispatch_expert<1, 1>(m, c, items, split_h, c.down.bits, fold, s);
+    if (small) rc = dispatch_expert<1, 2>(m, c, items, 1, split_h, c.down.bits, fold, s);
+    else rc = dispatch_expert<1, 1>(m, c, items, 2, split_h, c.down.bits, fold, s);
     if (rc < 0) return rc;
     return 2;
 }

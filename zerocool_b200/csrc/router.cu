@@ -1,132 +1,175 @@
 // Router logits (and the shared-expert gate scalar) in fp32 with a pinned accumulation order.
 //
 // Replaces router_mm + router_accumulate (kernels/metal/qwen.metal:512-534, launched from
-// src/engine/metal.mm:818-822). The order is part of the contract because one last-bit change in a
-// logit can flip a top-k decision: K is cut into sixteen contiguous partitions, each partition is a
-// k-ascending chain of fused multiply-adds, and the sixteen partials are added in order 0..15.
+// src/engine/metal.mm:818-822) and keeps their structure: K is cut into sixteen contiguous partitions,
+// each partition is a k-ascending chain of fused multiply-adds that one thread owns, the sixteen
+// partials go to memory as [16, T, rows], and they are added in order 0..15 by the last of the sixteen
+// partition CTAs of a tile to finish. The order is part of the contract
+// because one last-bit change in a logit can flip a top-k decision; it reproduces the MLX bit patterns
+// the reference's own test holds (tests/test_qwen.cpp:798-826).
 //
-// Mapping: a CTA owns ER consecutive router rows, staged once in shared memory, and walks the token
-// batch in chunks of TT tokens. A thread owns one (row, partition) chain for TT/TG tokens; the
-// sixteen partition owners of a row sit in one half-warp, so the ordered final sum is sixteen
-// shuffles. Rows are padded by four floats so that the sixteen partitions of a row start in
-// different banks for 128-bit reads.
+// router_partial_kernel: grid (row tiles of 32, 16 partitions, token tiles). A CTA stages its slice of
+// x (k-major) and of the router rows (k-major) in shared memory, then every thread runs its chains:
+// TT = 64: 4 tokens x 2 rows per thread; TT = 8: one (token, row) per thread.
 #include "common.cuh"
 
 namespace zc {
 namespace {
 
-constexpr int ER = 4;      // router rows per CTA
-constexpr int TG = 2;      // token groups per chunk
-constexpr int ROUTER_THREADS = ER * 16 * TG;
+constexpr int ROUTER_THREADS = 256;
+constexpr int ROW_TILE = 32;
 
 template <int TT>
-__global__ void __launch_bounds__(ROUTER_THREADS) router_kernel(Call c, uint32_t chunks_per_block) {
+__global__ void __launch_bounds__(ROUTER_THREADS) router_partial_kernel(Call c, float* __restrict__ partial, uint32_t rows_padded,
+                                                                         uint32_t* __restrict__ tile_done, uint32_t reduce) {
     extern __shared__ __align__(16) float smem[];
-    constexpr int TPT = TT / TG;
-    const uint32_t H = c.H, part = H / 16, PS = part + 4;
-    float* Ws = smem;                       // [ER][16][PS]
-    float* Xs = smem + ER * 16 * PS;        // [TT][16][PS]
+    const uint32_t H = c.H, part = H / 16;
+    float* xs = smem;                    // [part][TT]
+    float* ws = smem + part * TT;        // [part][ROW_TILE]
+    const uint32_t e0 = blockIdx.x * ROW_TILE, p = blockIdx.y, t0 = blockIdx.z * TT;
     const uint32_t rows_total = c.E + (c.has_shared ? 1u : 0u);
-    const uint32_t e0 = blockIdx.x * ER;
     const uint32_t tid = threadIdx.x;
+    const uint32_t k0 = p * part;
 
-    // Stage this CTA's rows as fp32.
-    const uint32_t quads = H / 4;
-    for (uint32_t idx = tid; idx < ER * quads; idx += ROUTER_THREADS) {
-        const uint32_t r = idx / quads, k = (idx % quads) * 4, e = e0 + r;
+    // x slice -> xs[k][t]
+    for (uint32_t task = tid; task < TT * (part / 8); task += ROUTER_THREADS) {
+        const uint32_t tt = task % TT, kb = task / TT, t = t0 + tt;
+        float v[8];
+        if (t < c.T) {
+            if (c.act_dtype == ZC_F32) {
+                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(c.x) + size_t(t) * H + k0 + kb * 8);
+                const float4 a = __ldg(src), b = __ldg(src + 1);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            } else {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(c.x) + size_t(t) * H + k0 + kb * 8));
+                const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(r[i] << 16); v[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u); }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xs[(kb * 8 + i) * TT + tt] = v[i];
+    }
+    // router rows -> ws[k][e]
+    for (uint32_t task = tid; task < ROW_TILE * (part / 4); task += ROUTER_THREADS) {
+        const uint32_t el = task % ROW_TILE, kq = task / ROW_TILE, e = e0 + el;
         float4 v = make_float4(0, 0, 0, 0);
         if (e < rows_total) {
             const void* base = e < c.E ? c.router_w : c.shared_gate_w;
             const size_t row = e < c.E ? e : 0;
             if (c.router_dtype == ZC_F32) {
-                v = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + row * H + k));
+                v = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + row * H + k0 + kq * 4));
             } else {
-                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(base) + row * H + k));
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(base) + row * H + k0 + kq * 4));
                 v = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
                                 __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
             }
         }
-        *reinterpret_cast<float4*>(Ws + (r * 16 + k / part) * PS + k % part) = v;
+        ws[(kq * 4 + 0) * ROW_TILE + el] = v.x;
+        ws[(kq * 4 + 1) * ROW_TILE + el] = v.y;
+        ws[(kq * 4 + 2) * ROW_TILE + el] = v.z;
+        ws[(kq * 4 + 3) * ROW_TILE + el] = v.w;
     }
+    __syncthreads();
 
-    const uint32_t p = tid & 15, el = (tid >> 4) % ER, tg = tid / (16 * ER);
-    const uint32_t lane = tid & 31;
-    const uint32_t e = e0 + el;
-    const float* wrow = Ws + (el * 16 + p) * PS;
-
-    const uint32_t first_chunk = blockIdx.y * chunks_per_block;
-    for (uint32_t ch = first_chunk; ch < first_chunk + chunks_per_block; ++ch) {
-        const uint32_t t0 = ch * TT;
-        if (t0 >= c.T) break;
-        __syncthreads();   // previous chunk fully consumed (and Ws visible on the first pass)
-        for (uint32_t idx = tid; idx < TT * quads; idx += ROUTER_THREADS) {
-            const uint32_t tt = idx / quads, k = (idx % quads) * 4, t = t0 + tt;
-            float4 v = make_float4(0, 0, 0, 0);
-            if (t < c.T) {
-                if (c.act_dtype == ZC_F32) {
-                    v = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(c.x) + size_t(t) * H + k));
-                } else {
-                    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(c.x) + size_t(t) * H + k));
-                    v = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                                    __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
-                }
-            }
-            *reinterpret_cast<float4*>(Xs + (tt * 16 + k / part) * PS + k % part) = v;
+    if constexpr (TT == 64) {
+        const uint32_t tx = tid % 16, ty = tid / 16;        // rows 2tx, 2tx+1; tokens 4ty .. 4ty+3
+        float acc[4][2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = 0.0f;
+#pragma unroll 4
+        for (uint32_t k = 0; k < part; ++k) {
+            const float4 xv = *reinterpret_cast<const float4*>(xs + k * TT + ty * 4);
+            const float2 wv = *reinterpret_cast<const float2*>(ws + k * ROW_TILE + tx * 2);
+            acc[0][0] = __fmaf_rn(xv.x, wv.x, acc[0][0]); acc[0][1] = __fmaf_rn(xv.x, wv.y, acc[0][1]);
+            acc[1][0] = __fmaf_rn(xv.y, wv.x, acc[1][0]); acc[1][1] = __fmaf_rn(xv.y, wv.y, acc[1][1]);
+            acc[2][0] = __fmaf_rn(xv.z, wv.x, acc[2][0]); acc[2][1] = __fmaf_rn(xv.z, wv.y, acc[2][1]);
+            acc[3][0] = __fmaf_rn(xv.w, wv.x, acc[3][0]); acc[3][1] = __fmaf_rn(xv.w, wv.y, acc[3][1]);
         }
-        __syncthreads();
-
-        float acc[TPT];
 #pragma unroll
-        for (int j = 0; j < TPT; ++j) acc[j] = 0.0f;
-        for (uint32_t kk = 0; kk < part; kk += 4) {
-            const float4 w = *reinterpret_cast<const float4*>(wrow + kk);
-#pragma unroll
-            for (int j = 0; j < TPT; ++j) {
-                const float4 xv = *reinterpret_cast<const float4*>(Xs + ((tg * TPT + j) * 16 + p) * PS + kk);
-                acc[j] = __fmaf_rn(xv.x, w.x, acc[j]);
-                acc[j] = __fmaf_rn(xv.y, w.y, acc[j]);
-                acc[j] = __fmaf_rn(xv.z, w.z, acc[j]);
-                acc[j] = __fmaf_rn(xv.w, w.w, acc[j]);
-            }
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t t = t0 + ty * 4 + i;
+            if (t < c.T) *reinterpret_cast<float2*>(partial + (size_t(p) * c.T + t) * rows_padded + e0 + tx * 2) = make_float2(acc[i][0], acc[i][1]);
         }
-        // Ordered sum of the sixteen partials; every lane of the half-warp computes it.
-#pragma unroll
-        for (int j = 0; j < TPT; ++j) {
-            float sum = 0.0f;
-#pragma unroll
-            for (int q = 0; q < 16; ++q) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, acc[j], (lane & 16) + q));
-            const uint32_t t = t0 + tg * TPT + j;
-            if (p == 0 && t < c.T) {
-                if (e < c.E) c.logits[size_t(t) * c.E + e] = sum;
-                else if (e == c.E && c.has_shared) c.gate_logit[t] = sum;
-            }
+    } else if constexpr (TT == 16) {
+        const uint32_t tx = tid % 16, ty = tid / 16;        // rows 2tx, 2tx+1; token ty
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 8
+        for (uint32_t k = 0; k < part; ++k) {
+            const float xv = xs[k * TT + ty];
+            const float2 wv = *reinterpret_cast<const float2*>(ws + k * ROW_TILE + tx * 2);
+            a0 = __fmaf_rn(xv, wv.x, a0);
+            a1 = __fmaf_rn(xv, wv.y, a1);
         }
+        const uint32_t t = t0 + ty;
+        if (t < c.T) *reinterpret_cast<float2*>(partial + (size_t(p) * c.T + t) * rows_padded + e0 + tx * 2) = make_float2(a0, a1);
+    } else {
+        const uint32_t el = tid % ROW_TILE, tt = tid / ROW_TILE;   // TT == 8
+        float acc = 0.0f;
+#pragma unroll 8
+        for (uint32_t k = 0; k < part; ++k) acc = __fmaf_rn(xs[k * TT + tt], ws[k * ROW_TILE + el], acc);
+        const uint32_t t = t0 + tt;
+        if (t < c.T) partial[(size_t(p) * c.T + t) * rows_padded + e0 + el] = acc;
+    }
+    if (!reduce) return;
+    // The last of the sixteen partition CTAs of this (row tile, token tile) adds the partials in order
+    // 0..15, starting from zero like router_accumulate (qwen.metal:529-534).
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    uint32_t* counter = tile_done + blockIdx.z * gridDim.x + blockIdx.x;
+    if (tid == 0) last = atomicAdd(counter, 1u) == 15u;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (tid == 0) *counter = 0;
+    for (uint32_t o = tid; o < TT * ROW_TILE; o += ROUTER_THREADS) {
+        const uint32_t tt = o / ROW_TILE, el = o % ROW_TILE, t = t0 + tt, e = e0 + el;
+        if (t >= c.T || e >= rows_total) continue;
+        float sum = 0.0f;
+#pragma unroll
+        for (uint32_t q = 0; q < 16; ++q) sum = __fadd_rn(sum, __ldcg(partial + (size_t(q) * c.T + t) * rows_padded + e));
+        if (e < c.E) c.logits[size_t(t) * c.E + e] = sum;
+        else c.gate_logit[t] = sum;
     }
 }
 
 }  // namespace
 
-int launch_router(zc_moe* m, const Call& c, cudaStream_t s) {
-    constexpr int TT = 8;
-    const uint32_t PS = c.H / 16 + 4;
-    const size_t smem = size_t(ER + TT) * 16 * PS * sizeof(float);
-    if (smem > 227 * 1024) return fail(m, ZC_EINVAL, "hidden too large for the router kernel");
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(router_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        configured = true;
+uint32_t router_rows_padded(const zc_moe_desc& d) { return (d.experts + (d.has_shared ? 1 : 0) + ROW_TILE - 1) / ROW_TILE * ROW_TILE; }
+
+int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s) {
+    const uint32_t part = c.H / 16;
+    const uint32_t rows_padded = router_rows_padded(m->d);
+    // Token tile: small tiles give many short CTAs (and a short ordered-sum tail) for decode batches;
+    // long batches use the 64-token tile, which re-reads the router rows least often.
+    const int which = c.T <= 8 ? 0 : c.T <= 128 ? 1 : 2;
+    const uint32_t TT = which == 0 ? 8 : which == 1 ? 16 : 64;
+    const size_t smem = size_t(part) * (TT + ROW_TILE) * sizeof(float);
+    static size_t configured[3] = {0, 0, 0};
+    if (smem > configured[which]) {
+        cudaError_t e = which == 0 ? cudaFuncSetAttribute(router_partial_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
+                      : which == 1 ? cudaFuncSetAttribute(router_partial_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
+                                   : cudaFuncSetAttribute(router_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return check_launch(m, "router attribute");
+        configured[which] = smem;
     }
-    const uint32_t rows = c.E + (c.has_shared ? 1 : 0);
-    const uint32_t chunks = (c.T + TT - 1) / TT;
-    const uint32_t gx = (rows + ER - 1) / ER;
-    // One chunk of tokens per block while that keeps the grid within a few thousand blocks (the rows are
-    // re-read from L2); longer batches walk several chunks per block.
-    uint32_t gy = chunks < 32 ? chunks : 32;
-    const uint32_t per = (chunks + gy - 1) / gy;
-    gy = (chunks + per - 1) / per;
+    const dim3 grid(rows_padded / ROW_TILE, 16, (c.T + TT - 1) / TT);
     int rc;
-    { Timed t(m, s, KERNEL_ROUTER); router_kernel<TT><<<dim3(gx, gy), ROUTER_THREADS, smem, s>>>(c, per); rc = check_launch(m, "router"); }
+    {
+        Timed t(m, s, KERNEL_ROUTER);
+        if (which == 0) router_partial_kernel<8><<<grid, ROUTER_THREADS, smem, s>>>(c, m->router_partial, rows_padded, m->router_done, 1);
+        else if (which == 1) router_partial_kernel<16><<<grid, ROUTER_THREADS, smem, s>>>(c, m->router_partial, rows_padded, m->router_done, 1);
+        else router_partial_kernel<64><<<grid, ROUTER_THREADS, smem, s>>>(c, m->router_partial, rows_padded, m->router_done, 1);
+        rc = check_launch(m, "router");
+    }
     return rc < 0 ? rc : 1;
 }
+
+// The router operator: one launch (partials, then the ordered sum by the last partition CTA of each tile).
+int launch_router(zc_moe* m, const Call& c, cudaStream_t s) { return launch_router_partial(m, c, s); }
 
 }  // namespace zc
