@@ -112,6 +112,21 @@ int zc_moe_layer_buffers(zc_moe* moe, uint32_t layer, void** records, void** rou
  * reference's sixteen-partition accumulation order. x, logits: device memory. */
 int zc_moe_router(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, float* logits, void* stream);
 
+/* Router logits without any allocation. No counterpart in the reference: it exists for callers that cannot
+ * call cudaMalloc (so cannot create a handle) — code running while the host engine's allocator owns all of
+ * HBM, while another thread captures a CUDA graph, or in a loop that may not take the allocator lock.
+ * Same arithmetic and results as zc_moe_router. x [tokens, hidden] (act_dtype), router_w [experts, hidden]
+ * (router_dtype) and logits [tokens, experts] fp32 are device memory of the current device.
+ * Limits (rejected with ZC_EINVAL beyond them): tokens <= 64, experts <= 512 (multiple of 32), hidden <= 3072
+ * (multiple of 128). The scratch is a 2 MiB + 4 KiB array inside the library image, held by every GPU that
+ * loads the library until the process exits. The first call on a device looks up that array's device address
+ * (cudaGetSymbolAddress); make that first call before any stream capture begins. All calls share the array,
+ * which keeps the previous call's contents: the call clears the counters it needs at zero itself, and two
+ * calls that overlap on the GPU (different streams, or different threads) race — serialise them.
+ * Calls no cudaMalloc, cudaFree or allocating library routine. */
+int zc_router_logits_noalloc(const void* x, int act_dtype, const void* router_w, int router_dtype,
+                             uint32_t tokens, uint32_t hidden, uint32_t experts, float* logits, void* stream);
+
 /* Replaces Metal::route (include/engine/metal.hpp:112, src/engine/metal.mm:261-266, route_simd
  * qwen.metal:768-795): ids [tokens, K] int32 in rank order (unfilled ranks -1), weights [tokens, K]
  * fp32 = softmax over the selected scores. Device memory. */

@@ -173,3 +173,70 @@ int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s) {
 int launch_router(zc_moe* m, const Call& c, cudaStream_t s) { return launch_router_partial(m, c, s); }
 
 }  // namespace zc
+
+// ---------------------------------------------------------------------------------------------
+// Router logits for callers that must not allocate device memory.
+//
+// Some hosts of this library run inside a region where cudaMalloc is forbidden or would deadlock: a
+// plugin called while the engine's own caching allocator holds all of HBM, a callback that runs while
+// another thread is capturing a CUDA graph (allocation calls are illegal then), or a real-time loop
+// that may not take the allocator's lock. zc_moe_create allocates, so those callers cannot own a
+// handle. This entry point needs none: the router kernel's scratch — the [16, tokens, experts]
+// partition sums and the tile arrival counters — lives in a fixed array inside the library image.
+// ---------------------------------------------------------------------------------------------
+namespace zc {
+namespace {
+constexpr uint32_t NOALLOC_MAX_TOKENS = 64, NOALLOC_MAX_EXPERTS = 512, NOALLOC_MAX_HIDDEN = 3072;
+constexpr size_t NOALLOC_PARTIAL_BYTES = size_t(16) * NOALLOC_MAX_TOKENS * NOALLOC_MAX_EXPERTS * sizeof(float);   // 2 MiB
+constexpr size_t NOALLOC_COUNTER_BYTES = 4096;       // (experts / 32) x (tokens / 8) counters at most = 128 words
+// Held by every GPU that loads the library until the process exits: 2 MiB + 4 KiB.
+static __device__ __align__(256) unsigned char noalloc_scratch[NOALLOC_PARTIAL_BYTES + NOALLOC_COUNTER_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+unsigned char* noalloc_address[NOALLOC_MAX_DEVICES] = {};   // device address of the array, per device
+}  // namespace
+}  // namespace zc
+
+extern "C" int zc_router_logits_noalloc(const void* x, int act_dtype, const void* router_w, int router_dtype,
+                                        uint32_t tokens, uint32_t hidden, uint32_t experts, float* logits, void* stream) {
+    using namespace zc;
+    if (!x || !router_w || !logits) return fail(nullptr, ZC_EINVAL, "linear input shape");
+    if (!tokens || tokens > NOALLOC_MAX_TOKENS)
+        return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: tokens must be 1..64 (the built-in scratch is sized for 64)");
+    if (!experts || experts % 32 || experts > NOALLOC_MAX_EXPERTS)
+        return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: experts must be a multiple of 32, at most 512");
+    if (!hidden || hidden % 128 || hidden > NOALLOC_MAX_HIDDEN)
+        return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: hidden must be a multiple of 128, at most 3072");
+    if ((act_dtype != ZC_BF16 && act_dtype != ZC_F32) || (router_dtype != ZC_BF16 && router_dtype != ZC_F32))
+        return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: dtypes must be BF16 or F32");
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail(nullptr, ZC_EEXEC, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+    if (device < 0 || device >= NOALLOC_MAX_DEVICES) return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: device index above 63");
+    if (!noalloc_address[device]) {
+        // Set-up, once per device, with that device current: in host code the array's name is only a
+        // stand-in, the kernel needs the address the runtime gives for it on this device.
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, noalloc_scratch);
+        if (e != cudaSuccess || !p) return fail(nullptr, ZC_EEXEC, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+        noalloc_address[device] = static_cast<unsigned char*>(p);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* partial = reinterpret_cast<float*>(noalloc_address[device]);
+    uint32_t* counters = reinterpret_cast<uint32_t*>(noalloc_address[device] + NOALLOC_PARTIAL_BYTES);
+    // The counters must start at zero (a call cut short by an error would leave them dirty); the partial
+    // sums are fully rewritten for the (tokens, experts) of this call before they are read.
+    if ((e = cudaMemsetAsync(counters, 0, NOALLOC_COUNTER_BYTES, s)) != cudaSuccess)
+        return fail(nullptr, ZC_EEXEC, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+    Call c{};
+    c.x = x; c.router_w = router_w; c.logits = logits;
+    c.T = tokens; c.H = hidden; c.E = experts; c.act_dtype = uint8_t(act_dtype); c.router_dtype = uint8_t(router_dtype); c.has_shared = 0;
+    const uint32_t part = hidden / 16, rows_padded = experts;      // a multiple of the 32-row tile already
+    const bool tiny = tokens <= 8;
+    const uint32_t TT = tiny ? 8 : 16;
+    const size_t smem = size_t(part) * (TT + ROW_TILE) * sizeof(float);   // at most 36 KiB: no opt-in attribute needed
+    const dim3 grid(rows_padded / ROW_TILE, 16, (tokens + TT - 1) / TT);
+    if (tiny) router_partial_kernel<8><<<grid, ROUTER_THREADS, smem, s>>>(c, partial, rows_padded, counters, 1);
+    else router_partial_kernel<16><<<grid, ROUTER_THREADS, smem, s>>>(c, partial, rows_padded, counters, 1);
+    return check_launch(nullptr, "router (no-alloc)");
+}

@@ -23,7 +23,7 @@ STATUS_INVALID_ROUTE = 1
 
 EXPORTS = [
     "zc_moe_desc_finalize", "zc_moe_create", "zc_moe_destroy", "zc_moe_last_error", "zc_last_error",
-    "zc_moe_load_layer", "zc_moe_layer_buffers", "zc_moe_router", "zc_moe_route", "zc_moe_permute",
+    "zc_moe_load_layer", "zc_moe_layer_buffers", "zc_moe_router", "zc_router_logits_noalloc", "zc_moe_route", "zc_moe_permute",
     "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_forward_host", "zc_moe_stack",
     "zc_moe_stack_host", "zc_moe_set_option", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
     "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
@@ -67,6 +67,7 @@ def load_library():
     lib.zc_moe_load_layer.argtypes = [vp, u32, vp, u32, u32, vp, vp, vp]
     lib.zc_moe_layer_buffers.argtypes = [vp, u32, ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp)]
     lib.zc_moe_router.argtypes = [vp, u32, vp, u32, vp, vp]
+    lib.zc_router_logits_noalloc.argtypes = [vp, i32, vp, i32, u32, u32, u32, vp, vp]
     lib.zc_moe_route.argtypes = [vp, vp, u32, vp, vp, vp]
     lib.zc_moe_permute.argtypes = [vp, vp, u32, vp, vp, vp]
     for name in ("zc_moe_decode", "zc_moe_prefill", "zc_moe_forward"):
