@@ -50,6 +50,7 @@ extern "C" {
 
 /* Bits of the device status word. */
 #define ZC_STATUS_INVALID_ROUTE 1u   /* "invalid router output", src/engine/model.cpp:459 */
+#define ZC_STATUS_TIMEOUT       2u   /* a bounded device-side wait of the prefill kernels ran out */
 
 typedef struct zc_moe zc_moe;
 
@@ -175,7 +176,7 @@ int zc_moe_stack_eager(zc_moe* moe, const void* x, uint32_t tokens, void* out, v
 /* Per-kernel device timing, the counterpart of KernelConfig.profile / Metal::take_profile
  * (include/engine/metal.hpp:31, 93; src/engine/metal.mm:510-557): between begin and end every kernel
  * launched outside a graph is bracketed by CUDA events on its stream. end waits for the device and returns,
- * per kernel kind k < 8, the summed milliseconds and the number of launches; zc_moe_kernel_name(k) names it. */
+ * per kernel kind k < 16, the summed milliseconds and the number of launches; zc_moe_kernel_name(k) names it. */
 int zc_moe_profile_begin(zc_moe* moe);
 int zc_moe_profile_end(zc_moe* moe, double* ms_per_kind, uint64_t* launches_per_kind);
 const char* zc_moe_kernel_name(int kind);

@@ -1,0 +1,94 @@
+"""GPU parity tests of the prefill family (tcgen05 grouped GEMM) through the C ABI: ids and permutation
+bit-exact, outputs within 2e-3 x RMS of the CPU checker, on even, skewed and ragged expert loads."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests import util
+from tests.test_moe_gpu import TOL, device_x, make, oracle_layer
+from zerocool_b200 import synth
+from zerocool_b200.records import BF16, F32
+
+pytestmark = pytest.mark.gpu
+SEED = 77
+
+
+def run_prefill(cfg, tokens, router=None):
+    import torch
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    if router is not None:
+        m.load_layer(0, router_w=router)
+    x = synth.activations(cfg, SEED, 0, tokens)
+    out = m.prefill(0, device_x(m, x)).float().cpu().numpy()
+    routing = m.last_routing(tokens)
+    assert m.status() == 0                                    # no invalid route, no device-side timeout
+    return m, x, out, routing
+
+
+def check_against_oracle(cfg, x, out, routing, router=None):
+    records = util.selected_records(cfg, SEED, 0, routing["ids"])
+    want = oracle.moe_layer(cfg.as_dict(), records, synth.router(cfg, SEED, 0) if router is None else router, x,
+                            shared_record=synth.record(cfg, SEED, 0, synth.SHARED_EXPERT) if cfg.has_shared else None,
+                            shared_gate_w=synth.shared_gate(cfg, SEED, 0) if cfg.has_shared else None)
+    assert np.array_equal(routing["ids"], want["ids"])
+    offsets, perm = oracle.permute(want["ids"], cfg.experts)
+    assert np.array_equal(routing["offsets"], offsets) and np.array_equal(routing["perm"], perm)
+    err = util.rel_max_error(out, want["out"])
+    print("prefill max-abs error / RMS:", err)
+    assert err <= TOL, err
+    return err
+
+
+def test_prefill_matches_oracle_small_experts():
+    """64 experts, 300 tokens: ~47 rows per expert, one token tile each, plus the shared expert's three tiles."""
+    cfg = util.cfg2(experts=64, max_tokens=512)
+    m, x, out, routing = run_prefill(cfg, 300)
+    check_against_oracle(cfg, x, out, routing)
+
+
+def test_prefill_equals_decode_family_on_skewed_loads():
+    """Router rows scaled by a Zipf-like factor: a few experts receive hundreds of rows (several 128-token
+    tiles), many receive a handful or none. The prefill family must agree with the decode family."""
+    cfg = util.cfg2(experts=128, max_tokens=1024)
+    router = synth.router(cfg, SEED, 0).copy()
+    router *= (1.0 + 60.0 / (1.0 + np.arange(cfg.experts, dtype=np.float32)))[:, None]
+    tokens = 700
+    m, x, out, routing = run_prefill(cfg, tokens, router=router)
+    counts = np.diff(routing["offsets"])
+    assert counts.max() > 256 and (counts < 16).sum() > 4           # genuinely skewed and ragged
+    dec = m.decode(0, device_x(m, x)).float().cpu().numpy()
+    assert m.status() == 0
+    print("loads max", counts.max(), "below 16:", int((counts < 16).sum()), "prefill vs decode:", util.rel_max_error(out, dec))
+    assert util.rel_max_error(out, dec) <= TOL
+    # spot-check the first 24 tokens against the CPU checker
+    sub = oracle.moe_layer(cfg.as_dict(), util.selected_records(cfg, SEED, 0, routing["ids"][:24]), router, x[:24],
+                           shared_record=synth.record(cfg, SEED, 0, synth.SHARED_EXPERT), shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    assert np.array_equal(sub["ids"], routing["ids"][:24])
+    assert util.rel_max_error(out[:24], sub["out"]) <= TOL
+
+
+def test_prefill_config5_shape():
+    """hidden 4096 (config 5's geometry), no shared expert, a token count that is not a multiple of 16."""
+    cfg = util.cfg2(hidden=4096, experts=32, top_k=4, has_shared=0, max_tokens=512)
+    m, x, out, routing = run_prefill(cfg, 261)
+    check_against_oracle(cfg, x, out, routing)
+
+
+def test_forward_picks_the_family_by_token_count():
+    cfg = util.cfg2(experts=64, max_tokens=512)
+    import torch
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    x = device_x(m, synth.activations(cfg, SEED, 0, 320))
+    before = m.launches
+    a = m.moe(0, x)
+    used = m.launches - before
+    b = m.prefill(0, x)
+    assert torch.equal(a, b) and used == 7              # router, route, tiles, activations, gate/up, down, combine
+    small = device_x(m, synth.activations(cfg, SEED, 0, 8))
+    before = m.launches
+    m.moe(0, small)
+    assert m.launches - before == 5
+    with pytest.raises(ValueError):
+        make(util.cfg2(experts=64, max_tokens=16)).prefill(0, small)

@@ -89,12 +89,15 @@ int check_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const 
 
 // One layer: router partials -> route + permutation (one launch) -> gate/up -> down -> combine.
 // With `next` set the combine also writes the normalised input of the following layer (the chained stack).
-int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next = nullptr) {
+// family: 0 = decode kernels, 1 = prefill kernels (tensor-core grouped GEMM), -1 = by token count.
+int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next = nullptr, int family = -1) {
     const Call c = make_call(m, layer, x, tokens, out);
+    if (family < 0) family = tokens >= 256 ? 1 : 0;
+    if (family == 1 && !m->pf_tiles) family = 0;      // formats the prefill kernels do not take, or a decode-sized handle
     int n, total = 0;
     if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
     if ((n = launch_route_permute(m, c, s, true, true, false)) < 0) return n; total += n;
-    if ((n = launch_experts_decode(m, c, s)) < 0) return n; total += n;
+    if ((n = family == 1 ? launch_experts_prefill(m, c, s) : launch_experts_decode(m, c, s)) < 0) return n; total += n;
     if (next) n = launch_combine_norm(m, c, next, m->d.act_dtype, s);
     else n = launch_combine(m, c, s);
     if (n < 0) return n; total += n;
@@ -162,7 +165,13 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     const size_t done_n = size_t(router_rows_padded(d) / 32) * ((T + 7) / 8);
     A(&m->router_done, done_n * 4);
     if (rc == ZC_OK && (e = cudaMemset(m->router_done, 0, done_n * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
-    A(&c.hbuf, (T * K + T) * F * 4); A(&c.expert_out, T * K * H * 4); A(&c.shared_out, T * H * 4); A(&c.status, 16);
+    A(&c.hbuf, (T * K + T) * F * 4);
+    if (prefill_supported(d) && T > 64) {
+        A(&m->xp, T * H * 2); A(&m->hbuf16, (T * K + T) * F * 2);
+        m->pf_max_tiles = uint32_t(prefill_tile_capacity(d));
+        uint8_t* tl = nullptr; A(&tl, m->pf_max_tiles * prefill_tile_bytes()); m->pf_tiles = tl;
+        A(&m->pf_ntiles, 16);
+    } A(&c.expert_out, T * K * H * 4); A(&c.shared_out, T * H * 4); A(&c.status, 16);
     uint8_t* p0 = nullptr; uint8_t* p1 = nullptr; uint8_t* dx = nullptr; uint8_t* dout = nullptr; uint8_t* dfin = nullptr;
     A(&p0, T * H * 4); A(&p1, T * H * 4); A(&dx, T * H * 4); A(&dout, T * H * 4); A(&dfin, T * H * 4);
     m->act[0] = p0; m->act[1] = p1; m->dev_x = dx; m->dev_out = dout; m->dev_final = dfin;
@@ -262,21 +271,26 @@ int zc_moe_permute(zc_moe* m, const int32_t* ids, uint32_t tokens, int32_t* offs
     return ZC_OK;
 }
 
-int zc_moe_decode(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
+static int forward_family(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream, int family) {
     int rc = check_call(m, layer, x, tokens, out);
     if (rc != ZC_OK) return rc;
-    const int n = run_layer(m, layer, x, tokens, out, static_cast<cudaStream_t>(stream));
+    const int n = run_layer(m, layer, x, tokens, out, static_cast<cudaStream_t>(stream), nullptr, family);
     if (n < 0) return n;
     m->launches += n;
     return ZC_OK;
 }
 
+int zc_moe_decode(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
+    return forward_family(m, layer, x, tokens, out, stream, 0);
+}
+
 int zc_moe_prefill(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
-    return zc_moe_decode(m, layer, x, tokens, out, stream);
+    if (m && !m->pf_tiles) return fail(m, ZC_EINVAL, "prefill kernels need Q4 projections, BF16 activations, FP32 arithmetic and max_tokens above 64");
+    return forward_family(m, layer, x, tokens, out, stream, 1);
 }
 
 int zc_moe_forward(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
-    return zc_moe_decode(m, layer, x, tokens, out, stream);
+    return forward_family(m, layer, x, tokens, out, stream, -1);
 }
 
 int zc_moe_forward_host(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream) {
@@ -409,7 +423,8 @@ int zc_moe_set_option(zc_moe* m, const char* name, int value) {
 }
 
 const char* zc_moe_kernel_name(int kind) {
-    static const char* names[KERNEL_KINDS] = {"router", "route", "permute", "gate_up", "down", "combine", "norm_act"};
+    static const char* names[KERNEL_KINDS] = {"router", "route", "permute", "gate_up", "down", "combine", "norm_act",
+                                              "prefill_prep", "prefill_gate_up", "prefill_down"};
     return kind >= 0 && kind < KERNEL_KINDS ? names[kind] : nullptr;
 }
 

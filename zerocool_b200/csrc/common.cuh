@@ -158,6 +158,11 @@ struct zc_moe {
     std::vector<zc::LayerMem> layers;
     std::vector<void*> allocations;
     zc::Call scratch{};           // scratch pointers (x/out/layer fields filled per call)
+    __half* xp = nullptr;                // [max_tokens, H] FP16 activations in the prefill kernels' k order
+    __half* hbuf16 = nullptr;            // [max_tokens*K + max_tokens, F] FP16 SwiGLU outputs (prefill)
+    void* pf_tiles = nullptr;            // tile list of the prefill launches
+    int32_t* pf_ntiles = nullptr;
+    uint32_t pf_max_tiles = 0;
     uint32_t* router_done = nullptr;     // arrival counters of the router's (row tile, token tile) pairs
     float* router_partial = nullptr;     // [16, max_tokens, rows_padded] partition sums of the router
     void* act[2] = {nullptr, nullptr};   // stack ping-pong activations [max_tokens, H]
@@ -185,11 +190,16 @@ int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s);
 uint32_t router_rows_padded(const zc_moe_desc& d);
 int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute, bool from_partials);
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s);
+int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s);
+bool prefill_supported(const zc_moe_desc& d);
+size_t prefill_tile_capacity(const zc_moe_desc& d);
+size_t prefill_tile_bytes();
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cudaStream_t s);
 int launch_norm_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s);
 int launch_synth_layer(zc_moe* m, uint32_t layer, uint64_t seed, cudaStream_t s);
-enum KernelKind { KERNEL_ROUTER = 0, KERNEL_ROUTE, KERNEL_PERMUTE, KERNEL_GATE_UP, KERNEL_DOWN, KERNEL_COMBINE, KERNEL_NORM_ACT, KERNEL_KINDS };
+enum KernelKind { KERNEL_ROUTER = 0, KERNEL_ROUTE, KERNEL_PERMUTE, KERNEL_GATE_UP, KERNEL_DOWN, KERNEL_COMBINE, KERNEL_NORM_ACT,
+                  KERNEL_PREFILL_PREP, KERNEL_PREFILL_GATE_UP, KERNEL_PREFILL_DOWN, KERNEL_KINDS };
 // Brackets one kernel launch with events when profiling is enabled.
 struct Timed {
     zc_moe* m; cudaStream_t s; int kind; cudaEvent_t stop = nullptr;

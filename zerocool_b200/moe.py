@@ -260,11 +260,11 @@ class Moe:
 
     def profile_end(self):
         """dict kernel name -> (total ms, launches) since profile_begin."""
-        ms = (ctypes.c_double * 8)()
-        n = (ctypes.c_uint64 * 8)()
+        ms = (ctypes.c_double * 16)()
+        n = (ctypes.c_uint64 * 16)()
         self._check(self.lib.zc_moe_profile_end(self._h, ms, n))
         out = {}
-        for k in range(8):
+        for k in range(16):
             name = self.lib.zc_moe_kernel_name(k)
             if name:
                 out[name.decode()] = (ms[k], int(n[k]))
