@@ -43,7 +43,17 @@ def config(layers, max_tokens):
                      out_dtype=BF16, router_dtype=F32, has_shared=1, max_tokens=max_tokens)
 
 
-def workload(cfg, tokens, n_gpus):
+def workload(cfg, tokens, n_gpus, kind="decode"):
+    if kind == "prefill":
+        return {
+            "workload": f"BASELINE config 3: prefill grouped GEMM, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
+                        f"top-{cfg.top_k} + 1 shared, ffn {cfg.ffn}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router with an additive "
+                        f"Zipf(s=1.1) per-expert logit bias, sequence of {tokens} tokens per GPU, layers chained through bf16((out-mean)/std)",
+            "tokens_per_gpu": tokens, "layers": cfg.layers,
+            "parallelism": f"dp{n_gpus}: independent replicas, tokens sharded, no data-path collective",
+            "l2": "no flush needed: every layer streams its 906 MB of records (43.5 GB resident) through a 126 MB L2",
+            "accumulate": "f32", "weights": "q4_g64 fed to tcgen05.mma as two exact FP16 terms",
+        }
     return {
         "workload": f"BASELINE config 2: decode MoE stack, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
                     f"top-{cfg.top_k} + 1 shared, ffn {cfg.ffn}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router, "
@@ -61,6 +71,14 @@ def peaks():
         p = json.load(open(path))
         return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["bf16_tflops"]), float(p["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops burst / sustained)"
+    return 1590.0, 1400.0, "fallback (1.59 PFLOP/s burst, earlier measurement on this pool)"
 
 
 def ncu_traffic():
@@ -119,11 +137,14 @@ def rms_glue(out):
     return oracle.bf(d * scale)
 
 
-def cpu_layer(cfg, layer, x, cache):
+def cpu_layer(cfg, layer, x, cache, bias=None):
     """One layer on the CPU checker; records of the selected experts are regenerated from the seed (cached)."""
     from oracle import oracle
     router = cache.setdefault(("router", layer), synth.router(cfg, SEED, layer))
+    keep = oracle.set_router_bias(bias)
     logits = oracle.router_logits(x, router, cfg.router_dtype)
+    oracle.set_router_bias(None)
+    del keep
     ids, _ = oracle.route(logits, cfg.top_k)
     records = [None] * cfg.experts
     for e in np.unique(ids):
@@ -132,7 +153,7 @@ def cpu_layer(cfg, layer, x, cache):
     shared = cache.setdefault(("shared", layer), synth.record(cfg, SEED, layer, synth.SHARED_EXPERT))
     gate = cache.setdefault(("gate", layer), synth.shared_gate(cfg, SEED, layer))
     t0 = time.perf_counter()
-    res = oracle.moe_layer(cfg.as_dict(), records, router, x, shared_record=shared, shared_gate_w=gate)
+    res = oracle.moe_layer(cfg.as_dict(), records, router, x, shared_record=shared, shared_gate_w=gate, router_bias=bias)
     return res, time.perf_counter() - t0
 
 
@@ -222,10 +243,15 @@ def run_ours(args):
         d.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = d
     from zerocool_b200.moe import Moe
-    cfg = config(args.layers, max(BATCHES + (args.tokens,)))
+    prefill = args.workload == "prefill"
+    cfg = config(args.layers, args.tokens if prefill else max(BATCHES + (args.tokens,)))
     m = Moe(cfg, local)
+    biases = {}
     for layer in range(cfg.layers):
         m.synth_fill_layer(layer, SEED)
+        if prefill:
+            biases[layer] = synth.zipf_router_bias(cfg, SEED, layer)
+            m.set_router_bias(layer, biases[layer])
     torch.cuda.synchronize()
     hbm_peak, peak_source = peaks()
 
@@ -241,12 +267,19 @@ def run_ours(args):
         x_np, _, x_dev = inputs(args.tokens)
         got = m.moe(0, x_dev).float().cpu().numpy()
         routing = m.last_routing(args.tokens)
-        want, _ = cpu_layer(cfg, 0, x_np, {})
-        offsets, perm = oracle.permute(want["ids"], cfg.experts)
+        checked = min(args.tokens, 64)          # tokens are independent: the checker runs the first 64 of a long batch
+        want, _ = cpu_layer(cfg, 0, x_np[:checked], {}, biases.get(0))
+        got = got[:checked]
+        ids_all = routing["ids"]
+        routing = dict(routing, ids=ids_all[:checked])
+        if checked == args.tokens:
+            offsets, perm = oracle.permute(want["ids"], cfg.experts)
+        else:                                   # permutation of the whole batch from the device's own (checked below) ids
+            offsets, perm = oracle.permute(ids_all, cfg.experts)
         rms = float(np.sqrt(np.mean(want["out"].astype(np.float64) ** 2)))
         bound = 2e-3 * rms + np.abs(want["out"]) * 2.0 ** -8          # tolerance + one bf16 rounding of the output
         parity = {
-            "layer": 0, "tokens": args.tokens,
+            "layer": 0, "tokens": args.tokens, "tokens_checked_against_cpu": checked,
             "ids_bit_exact": bool(np.array_equal(routing["ids"], want["ids"])),
             "perm_bit_exact": bool(np.array_equal(routing["perm"], perm) and np.array_equal(routing["offsets"], offsets)),
             "max_abs_err_over_rms": float(np.abs(got - want["out"]).max() / rms),
@@ -311,6 +344,18 @@ def run_ours(args):
                 "traffic": traffic, "peak_source": peak_source, "algorithmic_bytes_per_launch": alg,
                 "avg_launch_us": kernels[dominant]["avg_us"],
                 "definition": "(distinct routed experts of the layer + shared) x projection bytes of this kernel + activation bytes, averaged over the layers"}
+    if prefill:
+        burst, sustained, tsource = tensor_peak()
+        rows = args.tokens * (cfg.top_k + cfg.has_shared)
+        flops = {"prefill_gate_up": 2.0 * rows * 2 * cfg.ffn * cfg.hidden, "prefill_down": 2.0 * rows * cfg.hidden * cfg.ffn}
+        if dominant in flops:
+            tf = flops[dominant] / (kernels[dominant]["avg_us"] * 1e-6) / 1e12
+            roofline = {"bound": "tensor", "kernel": dominant, "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst,
+                        "traffic": traffic, "peak_source": tsource, "algorithmic_flops_per_launch": flops[dominant],
+                        "avg_launch_us": kernels[dominant]["avg_us"], "frac_of_sustained": tf / sustained,
+                        "definition": "2 x routed-and-shared rows x output columns x K of this launch (useful flops; the tensor cores "
+                                      "issue twice that because each weight is fed as two exact FP16 terms)",
+                        "hbm_gbs_of_this_launch": (cfg.experts + 1) * proj["gate_up" if dominant == "prefill_gate_up" else "down"] / (kernels[dominant]["avg_us"] * 1e-6) / 1e9}
     step_achieved = step_bytes / (ms * 1e-3) / 1e9
     roofline_step = {"bound": "hbm", "achieved": step_achieved, "peak": hbm_peak, "unit": "GB/s", "frac": step_achieved / hbm_peak,
                      "algorithmic_bytes_per_step": step_bytes,
@@ -318,7 +363,12 @@ def run_ours(args):
 
     # ---- the other decode batch sizes of the configuration (same stack, fewer steps) -------------------
     batches = {}
-    if not args.skip_batches:
+    if prefill:
+        burst, sustained, _ = tensor_peak()
+        step_flops = cfg.layers * 6.0 * args.tokens * (cfg.top_k + cfg.has_shared) * cfg.hidden * cfg.ffn
+        roofline_step.update({"tensor_tflops": step_flops / (ms * 1e-3) / 1e12, "frac_of_tensor_peak": step_flops / (ms * 1e-3) / 1e12 / burst,
+                              "algorithmic_flops_per_step": step_flops})
+    if not args.skip_batches and not prefill:
         for t in BATCHES:
             if t == args.tokens:
                 bms, act = ms, active
@@ -330,7 +380,7 @@ def run_ours(args):
 
     # ---- CPU baseline on this machine's host cores, bounded sample ------------------------------------
     cpu = None
-    if rank == 0 and world == 1 and not args.skip_cpu:
+    if rank == 0 and world == 1 and not args.skip_cpu and not prefill:
         from oracle import oracle
         cache = {}
         cpu_sample(cfg, args.tokens, args.cpu_layers, cache)
@@ -344,7 +394,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload(cfg, args.tokens, world), "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "config": workload(cfg, args.tokens, world, args.workload), "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "roofline": roofline, "roofline_step": roofline_step, "kernels": kernels, "cpu_baseline": cpu, "batches": batches,
             "parity": parity, "mean_active_experts": float(np.mean(active)),
         }
@@ -360,7 +410,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--tokens", type=int, default=64, help="token batch per GPU (the configuration names 1/4/16/64)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: BASELINE config 2 (the headline); prefill: config 3 (grouped GEMM, Zipf-skewed loads)")
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU: decode 1/4/16/64 (default 64), prefill 2048/8192 (default 2048)")
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers of the stack the CPU baseline runs (scaled to 48)")
     ap.add_argument("--skip-cpu", action="store_true")
@@ -369,6 +421,8 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if not args.tokens:
+        args.tokens = 2048 if args.workload == "prefill" else 64
     if args.impl == "reference":
         args.cpu_layers = min(args.cpu_layers, 2)
         run_reference(args)

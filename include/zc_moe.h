@@ -104,6 +104,11 @@ const char* zc_last_error(void);
 int zc_moe_load_layer(zc_moe* moe, uint32_t layer, const void* records, uint32_t first_expert, uint32_t count,
                       const void* router_w, const void* shared_record, const void* shared_gate_w);
 
+/* Optional per-expert additive bias on the router logits of a layer (fp32 [E], host or device; NULL removes
+ * it), added after the partition sum. The reference's router has none; the benchmark's skewed-load
+ * configuration (Zipf bias on the logits) needs it. */
+int zc_moe_set_router_bias(zc_moe* moe, uint32_t layer, const float* bias);
+
 /* Device addresses of a layer's resident tensors, for producers that fill HBM in place. */
 int zc_moe_layer_buffers(zc_moe* moe, uint32_t layer, void** records, void** router_w,
                          void** shared_record, void** shared_gate_w);

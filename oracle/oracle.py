@@ -151,7 +151,14 @@ def combine(cfg, expert_out, weights, shared=None, gate=None):
     return out
 
 
-def moe_layer(cfg, records, router_w, x, shared_record=None, shared_gate_w=None, want_intermediates=False):
+def set_router_bias(bias):
+    """fp32 [E] array added to the logits of every later router call, or None. Returns the array to keep alive."""
+    keep = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    lib().zco_set_router_bias(_p(keep))
+    return keep
+
+
+def moe_layer(cfg, records, router_w, x, shared_record=None, shared_gate_w=None, want_intermediates=False, router_bias=None):
     """Whole layer. ``records``: sequence of E uint8 arrays (or None for experts known to be unselected),
     or one [E, stride] uint8 array. x: fp32 [T,H]. Returns dict(out, ids, weights[, logits, expert_out, shared, gate])."""
     d = make_desc(cfg)
@@ -179,9 +186,12 @@ def moe_layer(cfg, records, router_w, x, shared_record=None, shared_gate_w=None,
     if d.has_shared:
         shared_record = np.ascontiguousarray(shared_record, dtype=np.uint8)
         shared_gate_w = np.ascontiguousarray(shared_gate_w)
+    keep_bias = set_router_bias(router_bias)
     rc = lib().zco_moe_layer(ctypes.byref(d), ptrs, _p(router_w), _p(shared_record) if d.has_shared else None,
                              _p(shared_gate_w) if d.has_shared else None, _p(x), ctypes.c_uint32(T), _p(out), _p(ids),
                              _p(weights), _p(logits), _p(eo), _p(so), _p(go))
+    set_router_bias(None)
+    del keep_bias
     if rc == -1:
         raise ValueError("invalid router output")
     if rc == -2:

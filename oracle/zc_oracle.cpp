@@ -244,6 +244,11 @@ void expert_row(const Desc& d, const uint8_t* record, const float* x, float* h, 
 
 extern "C" {
 
+// Optional additive per-expert bias on the router logits (the benchmark's skewed-load configuration); the
+// reference's router has none. Applied after the partition sum.
+static const float* g_router_bias = nullptr;
+void zco_set_router_bias(const float* bias) { g_router_bias = bias; }
+
 int zco_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -267,7 +272,7 @@ void zco_router_logits(const float* x, const void* w, int w_dtype, uint32_t T, u
     #pragma omp parallel for schedule(static) collapse(2)
     for (int64_t t = 0; t < int64_t(T); ++t)
         for (int64_t e = 0; e < int64_t(E); ++e)
-            logits[t * E + e] = router_dot(x + t * H, w, w_dtype, size_t(e), H);
+            logits[t * E + e] = router_dot(x + t * H, w, w_dtype, size_t(e), H) + (g_router_bias ? g_router_bias[e] : 0.0f);
 }
 
 void zco_route(const float* logits, uint32_t T, uint32_t E, uint32_t K, int32_t* ids, float* weights) {

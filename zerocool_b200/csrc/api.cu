@@ -70,6 +70,7 @@ Call make_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* 
     const LayerMem& L = m->layers[layer];
     c.x = x; c.out = out;
     c.records = L.records; c.router_w = L.router_w; c.shared_record = L.shared_record; c.shared_gate_w = L.shared_gate_w;
+    c.router_bias = L.bias_set ? L.router_bias : nullptr;
     c.T = tokens;
     c.layer = layer;
     return c;
@@ -153,6 +154,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         LayerMem& L = m->layers[l];
         A(&L.records, size_t(d.local_experts) * d.record_stride);
         uint8_t* rw = nullptr; A(&rw, E * H * elem_bytes(d.router_dtype)); L.router_w = rw;
+        A(&L.router_bias, E * 4);
         if (d.has_shared) {
             A(&L.shared_record, d.record_stride);
             uint8_t* gw = nullptr; A(&gw, H * elem_bytes(d.router_dtype)); L.shared_gate_w = gw;
@@ -222,6 +224,19 @@ int zc_moe_load_layer(zc_moe* m, uint32_t layer, const void* records, uint32_t f
         return cuda_fail(m, e, "copy of shared expert record");
     if (shared_gate_w && (e = cudaMemcpy(L.shared_gate_w, shared_gate_w, size_t(d.hidden) * elem_bytes(d.router_dtype), cudaMemcpyDefault)) != cudaSuccess)
         return cuda_fail(m, e, "copy of shared gate weight");
+    return ZC_OK;
+}
+
+int zc_moe_set_router_bias(zc_moe* m, uint32_t layer, const float* bias) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    LayerMem& L = m->layers[layer];
+    if (!bias) { L.bias_set = false; return ZC_OK; }
+    const cudaError_t e = cudaMemcpy(L.router_bias, bias, size_t(m->d.experts) * 4, cudaMemcpyDefault);
+    if (e != cudaSuccess) return cuda_fail(m, e, "copy of router bias");
+    L.bias_set = true;
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);   // captured launches hold the old argument
+    m->graphs.clear();
     return ZC_OK;
 }
 

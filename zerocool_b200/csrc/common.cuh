@@ -121,6 +121,8 @@ struct LayerMem {
     void* router_w = nullptr;         // [E, H]
     uint8_t* shared_record = nullptr; // one record, or null
     void* shared_gate_w = nullptr;    // [1, H], or null
+    float* router_bias = nullptr;     // [E] added to the logits after the partition sum; storage always present
+    bool bias_set = false;
 };
 
 // Everything a kernel needs to know about one call, passed by value.
@@ -131,6 +133,7 @@ struct Call {
     const void* router_w;
     const uint8_t* shared_record;
     const void* shared_gate_w;
+    const float* router_bias;   // [E] or null
     float* logits;            // [T, E]
     float* gate_logit;        // [T]
     int32_t* ids;             // [T, K]

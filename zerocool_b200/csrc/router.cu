@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_partial_kernel(Call c, 
         float sum = 0.0f;
 #pragma unroll
         for (uint32_t q = 0; q < 16; ++q) sum = __fadd_rn(sum, __ldcg(partial + (size_t(q) * c.T + t) * rows_padded + e));
-        if (e < c.E) c.logits[size_t(t) * c.E + e] = sum;
+        if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(sum, c.router_bias[e]) : sum;
         else c.gate_logit[t] = sum;
     }
 }

@@ -23,7 +23,7 @@ STATUS_INVALID_ROUTE = 1
 
 EXPORTS = [
     "zc_moe_desc_finalize", "zc_moe_create", "zc_moe_destroy", "zc_moe_last_error", "zc_last_error",
-    "zc_moe_load_layer", "zc_moe_layer_buffers", "zc_moe_router", "zc_router_logits_noalloc", "zc_moe_route", "zc_moe_permute",
+    "zc_moe_load_layer", "zc_moe_set_router_bias", "zc_moe_layer_buffers", "zc_moe_router", "zc_router_logits_noalloc", "zc_moe_route", "zc_moe_permute",
     "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_forward_host", "zc_moe_stack",
     "zc_moe_stack_host", "zc_moe_set_option", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
     "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
@@ -65,6 +65,7 @@ def load_library():
     lib.zc_moe_last_error.restype = ctypes.c_char_p
     lib.zc_last_error.restype = ctypes.c_char_p
     lib.zc_moe_load_layer.argtypes = [vp, u32, vp, u32, u32, vp, vp, vp]
+    lib.zc_moe_set_router_bias.argtypes = [vp, u32, vp]
     lib.zc_moe_layer_buffers.argtypes = [vp, u32, ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp)]
     lib.zc_moe_router.argtypes = [vp, u32, vp, u32, vp, vp]
     lib.zc_router_logits_noalloc.argtypes = [vp, i32, vp, i32, u32, u32, u32, vp, vp]
@@ -164,6 +165,11 @@ class Moe:
         count = 0 if records is None else int(records.shape[0])
         keep = [np.ascontiguousarray(a) if isinstance(a, np.ndarray) else a for a in (records, router_w, shared_record, shared_gate_w)]
         self._check(self.lib.zc_moe_load_layer(self._h, layer, _ptr(keep[0]), first_expert, count, _ptr(keep[1]), _ptr(keep[2]), _ptr(keep[3])))
+
+    def set_router_bias(self, layer, bias):
+        """bias: fp32 numpy [E] (or None to remove it)."""
+        keep = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        self._check(self.lib.zc_moe_set_router_bias(self._h, layer, _ptr(keep)))
 
     def synth_fill_layer(self, layer, seed):
         self._check(self.lib.zc_synth_fill_layer(self._h, layer, seed, self._stream()))

@@ -125,3 +125,13 @@ def activations(cfg: MoeConfig, seed, layer, tokens, first_token=0):
         bits = float_to_meta(x, BF16)
         x = (bits.astype(np.uint32) << 16).view(np.float32)
     return x
+
+
+def zipf_router_bias(cfg: MoeConfig, seed, layer, s=1.1):
+    """Per-expert additive logit bias b_e = -s * ln(rank_e) with ranks 1..E in a seeded random order: expert
+    loads then follow a Zipf(s)-like law on top of the input-dependent logits (skewed-load configuration)."""
+    key = stream_key(seed, stream_id(layer, 0, 0, 5))
+    order = np.argsort(rand32(key, np.arange(cfg.experts, dtype=np.uint64)), kind="stable")
+    rank = np.empty(cfg.experts, np.int64)
+    rank[order] = np.arange(1, cfg.experts + 1)
+    return (-s * np.log(rank.astype(np.float64))).astype(np.float32)
