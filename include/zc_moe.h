@@ -158,6 +158,23 @@ int zc_moe_prefill(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, 
 /* Model::moe with the family chosen from `tokens`. */
 int zc_moe_forward(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream);
 
+/* Expert parallelism over the ranks of one node (no counterpart in the reference, a single-GPU engine).
+ * A handle created with first_expert / local_experts holds one contiguous range of every layer's experts;
+ * router, shared expert and shared gate are replicated. Per layer and rank:
+ *   zc_moe_ep_dispatch: router + route + permutation of the local tokens over ALL experts; writes the token
+ *     rows in expert order (rows [tokens*K, H], act dtype) and their expert ids (row_experts [tokens*K]).
+ *     Rows for one owner rank are contiguous; the split sizes are differences of the permutation offsets
+ *     (zc_moe_last_routing) at the ranks' expert boundaries. The caller exchanges rows and ids (all-to-all).
+ *   zc_moe_ep_experts: the routed experts of this handle on n_rows received rows (any order, each tagged with
+ *     its global expert id inside this handle's range); y [n_rows, H] fp32 in the same row order.
+ *     n_rows <= max_tokens * top_k * ranks.
+ *   zc_moe_ep_combine: y_sorted [tokens*K, H] fp32 — the results of this rank's own rows, returned by the
+ *     reverse all-to-all in the order zc_moe_ep_dispatch wrote them — is scattered to the router slots and
+ *     reduced in fixed slot order with the locally computed shared expert into out. */
+int zc_moe_ep_dispatch(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* rows, int32_t* row_experts, void* stream);
+int zc_moe_ep_experts(zc_moe* moe, uint32_t layer, const void* rows, const int32_t* row_experts, uint32_t n_rows, float* y, void* stream);
+int zc_moe_ep_combine(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, const float* y_sorted, void* out, void* stream);
+
 /* Model::moe for callers that hold HOST tensors (the reference's Buf is CPU-visible unified memory):
  * on `stream`, copies x in, runs zc_moe_forward, copies out back, then waits for the stream.
  * x_host/out_host: host memory (pinned memory makes the copies asynchronous to other streams). */

@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libzc_moe.so")
-SOURCES = ["api.cu", "router.cu", "route.cu", "experts_decode.cu", "experts_prefill.cu", "combine.cu", "synth.cu"]
+SOURCES = ["api.cu", "router.cu", "route.cu", "experts_decode.cu", "experts_prefill.cu", "combine.cu", "ep.cu", "synth.cu"]
 HEADERS = ["common.cuh", os.path.join("..", "..", "include", "zc_moe.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]

@@ -174,6 +174,18 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         uint8_t* tl = nullptr; A(&tl, m->pf_max_tiles * prefill_tile_bytes()); m->pf_tiles = tl;
         A(&m->pf_ntiles, 16);
     } A(&c.expert_out, T * K * H * 4); A(&c.shared_out, T * H * 4); A(&c.status, 16);
+    A(&m->zero_counters, (16 + size_t(d.layers)) * 4);
+    if (rc == ZC_OK && (e = cudaMemset(m->zero_counters, 0, (16 + size_t(d.layers)) * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+    if (d.local_experts < d.experts) {
+        // expert parallelism: rows can arrive from every rank's tokens
+        const size_t ranks = (d.experts + d.local_experts - 1) / d.local_experts;
+        const size_t R = T * K * ranks;
+        m->ep_rows_cap = uint32_t(R);
+        Call& q = m->ep;
+        A(&q.offsets, (E + 1) * 4); A(&q.perm, R * 4); A(&q.active, E * 4); A(&q.counters, (16 + size_t(d.layers)) * 4);
+        A(&q.hbuf, R * F * 4);
+        if (rc == ZC_OK && (e = cudaMemset(q.counters, 0, (16 + size_t(d.layers)) * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+    }
     uint8_t* p0 = nullptr; uint8_t* p1 = nullptr; uint8_t* dx = nullptr; uint8_t* dout = nullptr; uint8_t* dfin = nullptr;
     A(&p0, T * H * 4); A(&p1, T * H * 4); A(&dx, T * H * 4); A(&dout, T * H * 4); A(&dfin, T * H * 4);
     m->act[0] = p0; m->act[1] = p1; m->dev_x = dx; m->dev_out = dout; m->dev_final = dfin;
@@ -188,6 +200,13 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     c.gate = projection_of(d, 0); c.up = projection_of(d, 1); c.down = projection_of(d, 2);
     c.act_dtype = d.act_dtype; c.out_dtype = d.out_dtype; c.meta_f16 = d.meta_dtype == ZC_F16; c.router_dtype = d.router_dtype;
     c.has_shared = d.has_shared; c.ref = d.arith == ZC_ARITH_REFERENCE; c.q8_signed = d.q8_signed;
+    if (m->ep_rows_cap) {
+        Call& q = m->ep;
+        const Call keep = q;
+        q = c;                                   // geometry and formats
+        q.offsets = keep.offsets; q.perm = keep.perm; q.active = keep.active; q.counters = keep.counters; q.hbuf = keep.hbuf;
+        q.K = 1; q.has_shared = 0;
+    }
     *out = m;
     return ZC_OK;
 }
@@ -306,6 +325,58 @@ int zc_moe_prefill(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, vo
 
 int zc_moe_forward(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
     return forward_family(m, layer, x, tokens, out, stream, -1);
+}
+
+// ---- expert parallelism -------------------------------------------------------------------------
+int zc_moe_ep_dispatch(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* rows, int32_t* row_experts, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    if (!tokens || tokens > m->d.max_tokens || !x || !rows || !row_experts) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const Call c = make_call(m, layer, x, tokens, nullptr);
+    int n, total = 0;
+    if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
+    if ((n = launch_route_permute(m, c, s, true, true, false)) < 0) return n; total += n;
+    if ((n = launch_ep_gather(m, c, rows, row_experts, s)) < 0) return n; total += n;
+    m->launches += total;
+    return ZC_OK;
+}
+
+int zc_moe_ep_experts(zc_moe* m, uint32_t layer, const void* rows, const int32_t* row_experts, uint32_t n_rows, float* y, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    if (!m->ep_rows_cap) return fail(m, ZC_EINVAL, "the handle holds every expert: expert parallelism needs local_experts < experts");
+    if (n_rows > m->ep_rows_cap) return fail(m, ZC_EINVAL, "more rows than max_tokens x top_k x ranks");
+    if (!n_rows) return ZC_OK;
+    if (!rows || !row_experts || !y) return fail(m, ZC_EINVAL, "missing buffer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    Call c = m->ep;
+    const LayerMem& L = m->layers[layer];
+    c.x = rows; c.records = L.records; c.ids = const_cast<int32_t*>(row_experts); c.expert_out = y; c.T = n_rows; c.layer = layer;
+    c.status = m->scratch.status;
+    int n, total = 0;
+    if ((n = launch_route_permute(m, c, s, false, true, false)) < 0) return n; total += n;
+    if ((n = launch_experts_decode(m, c, s)) < 0) return n; total += n;
+    m->launches += total;
+    return ZC_OK;
+}
+
+int zc_moe_ep_combine(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const float* y_sorted, void* out, void* stream) {
+    int rc = check_call(m, layer, x, tokens, out);
+    if (rc != ZC_OK) return rc;
+    if (!y_sorted) return fail(m, ZC_EINVAL, "missing buffer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    Call c = make_call(m, layer, x, tokens, out);
+    int n, total = 0;
+    if ((n = launch_ep_scatter(m, c, y_sorted, s)) < 0) return n; total += n;
+    if (c.has_shared) {
+        Call sh = c;
+        sh.counters = m->zero_counters;          // no routed items: only the shared expert's blocks find work
+        if ((n = launch_experts_decode(m, sh, s)) < 0) return n; total += n;
+    }
+    if ((n = launch_combine(m, c, s)) < 0) return n; total += n;
+    m->launches += total;
+    return ZC_OK;
 }
 
 int zc_moe_forward_host(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream) {

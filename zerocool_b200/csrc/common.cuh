@@ -167,6 +167,9 @@ struct zc_moe {
     int32_t* pf_ntiles = nullptr;
     uint32_t pf_max_tiles = 0;
     uint32_t* router_done = nullptr;     // arrival counters of the router's (row tile, token tile) pairs
+    zc::Call ep{};                       // second scratch set: the experts step of expert parallelism (rows from all ranks)
+    uint32_t ep_rows_cap = 0;
+    int32_t* zero_counters = nullptr;    // an always-zero counter block (launches that run the shared expert only)
     float* router_partial = nullptr;     // [16, max_tokens, rows_padded] partition sums of the router
     void* act[2] = {nullptr, nullptr};   // stack ping-pong activations [max_tokens, H]
     void* host_x = nullptr;       // pinned staging for the host entry points
@@ -198,6 +201,8 @@ bool prefill_supported(const zc_moe_desc& d);
 size_t prefill_tile_capacity(const zc_moe_desc& d);
 size_t prefill_tile_bytes();
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s);
+int launch_ep_gather(zc_moe* m, const Call& c, void* rows, int32_t* row_experts, cudaStream_t s);
+int launch_ep_scatter(zc_moe* m, const Call& c, const float* y, cudaStream_t s);
 int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cudaStream_t s);
 int launch_norm_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s);
 int launch_synth_layer(zc_moe* m, uint32_t layer, uint64_t seed, cudaStream_t s);

@@ -24,7 +24,7 @@ STATUS_INVALID_ROUTE = 1
 EXPORTS = [
     "zc_moe_desc_finalize", "zc_moe_create", "zc_moe_destroy", "zc_moe_last_error", "zc_last_error",
     "zc_moe_load_layer", "zc_moe_set_router_bias", "zc_moe_layer_buffers", "zc_moe_router", "zc_router_logits_noalloc", "zc_moe_route", "zc_moe_permute",
-    "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_forward_host", "zc_moe_stack",
+    "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_ep_dispatch", "zc_moe_ep_experts", "zc_moe_ep_combine", "zc_moe_forward_host", "zc_moe_stack",
     "zc_moe_stack_host", "zc_moe_set_option", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
     "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
 ]
@@ -73,6 +73,9 @@ def load_library():
     lib.zc_moe_permute.argtypes = [vp, vp, u32, vp, vp, vp]
     for name in ("zc_moe_decode", "zc_moe_prefill", "zc_moe_forward"):
         getattr(lib, name).argtypes = [vp, u32, vp, u32, vp, vp]
+    lib.zc_moe_ep_dispatch.argtypes = [vp, u32, vp, u32, vp, vp, vp]
+    lib.zc_moe_ep_experts.argtypes = [vp, u32, vp, vp, u32, vp, vp]
+    lib.zc_moe_ep_combine.argtypes = [vp, u32, vp, u32, vp, vp, vp]
     lib.zc_moe_forward_host.argtypes = [vp, u32, vp, u32, vp, vp]
     lib.zc_moe_stack.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_stack_host.argtypes = [vp, vp, u32, vp, vp]
@@ -236,6 +239,32 @@ class Moe:
 
     def prefill(self, layer, x, out=None):
         return self._run(self.lib.zc_moe_prefill, layer, x, out)
+
+    # -- expert parallelism (device-side pieces; zerocool_b200/ep.py drives the exchange) ---------------
+    def ep_dispatch(self, layer, x):
+        """-> (rows [T*K, H] act dtype in expert order, row_experts int32 [T*K], offsets numpy int32 [E+1])."""
+        torch = self._torch
+        tokens = x.shape[0]
+        rows = torch.empty((tokens * self.cfg.top_k, self.cfg.hidden), dtype=self.act_torch, device=self.device)
+        experts = torch.full((tokens * self.cfg.top_k,), -1, dtype=torch.int32, device=self.device)
+        self._check(self.lib.zc_moe_ep_dispatch(self._h, layer, _ptr(x), tokens, _ptr(rows), _ptr(experts), self._stream()))
+        return rows, experts, self.last_routing(tokens)["offsets"]
+
+    def ep_experts(self, layer, rows, row_experts):
+        torch = self._torch
+        n = rows.shape[0]
+        y = torch.empty((n, self.cfg.hidden), dtype=torch.float32, device=self.device)
+        if n:
+            self._check(self.lib.zc_moe_ep_experts(self._h, layer, _ptr(rows), _ptr(row_experts), n, _ptr(y), self._stream()))
+        return y
+
+    def ep_combine(self, layer, x, y_sorted, out=None):
+        torch = self._torch
+        tokens = x.shape[0]
+        if out is None:
+            out = torch.empty((tokens, self.cfg.hidden), dtype=self.out_torch, device=self.device)
+        self._check(self.lib.zc_moe_ep_combine(self._h, layer, _ptr(x), tokens, _ptr(y_sorted), _ptr(out), self._stream()))
+        return out
 
     def moe_host(self, layer, x_host, out_host):
         """Model::moe for host tensors (pinned numpy/torch CPU memory): copies in, runs, copies out, waits."""
