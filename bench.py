@@ -229,6 +229,77 @@ def layer_bytes(cfg, active, tokens):
     return (active + cfg.has_shared) * cfg.record_bytes + cfg.experts * cfg.hidden * 4 + tokens * cfg.hidden * 2 * a
 
 
+def run_ep(args):
+    """BASELINE config 5: expert-parallel stack on N GPUs (hidden 4096, 512 experts top-10 sharded 512/N per GPU,
+    ffn 512, Q4 g64), 256-token decode batch split over the ranks, NCCL all-to-all dispatch/combine."""
+    import torch
+    import torch.distributed as dist
+    from zerocool_b200.ep import ExpertParallel
+    from zerocool_b200.moe import Moe
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise RuntimeError("--workload ep needs at least two ranks (torch.distributed.run --nproc-per-node N)")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    total_tokens = args.tokens
+    t_local = total_tokens // world
+    per = 512 // world
+    cfg = MoeConfig(hidden=4096, ffn=512, experts=512, top_k=10, layers=args.layers, meta_dtype=F16, act_dtype=BF16, out_dtype=BF16,
+                    router_dtype=F32, has_shared=0, max_tokens=t_local, first_expert=rank * per, local_experts=per)
+    m = Moe(cfg, local)
+    for layer in range(cfg.layers):
+        m.synth_fill_layer(layer, SEED)
+    torch.cuda.synchronize()
+    ep = ExpertParallel(m, cfg.experts, rank, world, dist)
+    x0 = torch.from_numpy(synth.activations(cfg, SEED + rank, 0, t_local)).to(device="cuda", dtype=torch.bfloat16)
+    rows_moved = [0]
+
+    def step():
+        x = x0
+        for layer in range(cfg.layers):
+            out = ep.moe(layer, x)
+            rows_moved[0] += ep.last_plan["rows_sent"]
+            if layer + 1 < cfg.layers:
+                f = out.float()
+                d = f - f.mean(-1, keepdim=True)
+                x = (d * torch.rsqrt((d * d).mean(-1, keepdim=True))).to(torch.bfloat16)
+        return out
+
+    for _ in range(args.warmup):
+        out = step()
+    before, rows_moved[0] = m.launches, 0
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = time_steps(torch, step, args.steps, dist)
+    clocks = sampler.stop() if sampler else None
+    launches = m.launches - before
+    finite = bool(torch.isfinite(out.float()).all())
+    hbm_peak, peak_source = peaks()
+    active = torch.tensor([float(m.active_counts().mean())], device="cuda")
+    dist.all_reduce(active)
+    if rank == 0:
+        value = total_tokens / (ms * 1e-3)
+        # algorithmic bytes of the whole job per step: distinct experts touched on every rank x record bytes + router on every rank
+        step_bytes = cfg.layers * (float(active.item()) * cfg.record_bytes + world * cfg.experts * cfg.hidden * 4 + total_tokens * cfg.hidden * 4)
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"BASELINE config 5: expert-parallel stack, {cfg.layers} layers, hidden 4096, 512 experts top-10 ({per} per GPU), ffn 512, "
+                                   f"affine-Q4 g64, {total_tokens}-token decode batch ({t_local} per GPU), NCCL all-to-all dispatch/combine, "
+                                   "layers chained through bf16((out-mean)/std)",
+                       "parallelism": f"ep{world}", "tokens_total": total_tokens, "layers": cfg.layers,
+                       "l2": "no flush needed: each rank streams its selected records of 48 layers (GBs per step)"},
+            "gpu_launches": int(launches), "clocks": clocks, "finite": finite,
+            "roofline_step": {"bound": "hbm", "achieved": step_bytes / (ms * 1e-3) / 1e9 / world, "peak": hbm_peak, "unit": "GB/s per GPU",
+                              "frac": step_bytes / (ms * 1e-3) / 1e9 / world / hbm_peak, "peak_source": peak_source,
+                              "mean_active_experts_all_ranks": float(active.item())},
+            "nvlink_rows_per_step_rank0": rows_moved[0] / max(args.steps, 1),
+            "e2e": None, "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run_ours(args):
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -410,7 +481,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep"],
                     help="decode: BASELINE config 2 (the headline); prefill: config 3 (grouped GEMM, Zipf-skewed loads)")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU: decode 1/4/16/64 (default 64), prefill 2048/8192 (default 2048)")
     ap.add_argument("--layers", type=int, default=48)
@@ -422,10 +493,12 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if not args.tokens:
-        args.tokens = 2048 if args.workload == "prefill" else 64
+        args.tokens = {"prefill": 2048, "ep": 256}.get(args.workload, 64)
     if args.impl == "reference":
         args.cpu_layers = min(args.cpu_layers, 2)
         run_reference(args)
+    elif args.workload == "ep":
+        run_ep(args)
     else:
         run_ours(args)
 
