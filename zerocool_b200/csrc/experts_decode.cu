@@ -25,8 +25,13 @@
 //    Without FOLD the offset and the factor 16 are removed in FP16 before the MMA (exact, 4 more ops per
 //    word).
 //  * Weights reach the warp through a private cp.async ring in shared memory (no registers held
-//    across the latency, no block-wide barrier): lane l copies 16 bytes of row l/2, so every 32-byte
-//    sector of a record is requested once, and STAGES-1 chunks are always in flight per warp.
+//    across the latency, no block-wide barrier). A stage holds CH quantisation groups of a 16-row tile:
+//    each row's CH * 32 (Q4) or CH * 64 (Q8) contiguous code bytes are fetched as 16-byte pieces by
+//    adjacent lanes, so every sector of a record is requested once; the 32/64-byte blocks of a row are
+//    XOR-swizzled by the row index so that the fragment reads stay bank-conflict free. The refill of a
+//    slot is issued before the chunk that was waited for is multiplied, so STAGES-1 chunks are in
+//    flight while the warp computes.
+//  * Lanes whose token row is absent (fewer than eight rows in the pass) skip the activation reads.
 //  * Because a dot product does not care about the order of k, the MMA's k slots are bound to whatever
 //    k values fall out of the cheapest extraction; the activations are staged in the matching order.
 // Activations must be finite FP16 magnitudes (|x| < 65504); hidden states after a norm are O(1..100).
@@ -39,22 +44,23 @@ constexpr int NTOK = 8;               // token rows per MMA pass (the N of m16n8
 constexpr int WARPS = 8;
 constexpr int EXPERT_THREADS = WARPS * 32;
 constexpr int ROW_PAD = 8;            // halves added to each staged row (keeps 16-byte reads conflict free)
-#ifndef ZC_STAGES
-#define ZC_STAGES 3
-#endif
 #ifndef ZC_MIN_BLOCKS
 #define ZC_MIN_BLOCKS 2
 #endif
 #ifndef ZC_MIN_BLOCKS_DOWN
 #define ZC_MIN_BLOCKS_DOWN 4
 #endif
-constexpr int STAGES = ZC_STAGES;     // cp.async ring depth per warp
-constexpr int CH = 2;                 // quantisation groups per ring stage
 
-template <int BITS> struct Fmt {
+// One ring stage of one matrix holds CHT quantisation groups of 16 rows: for every row one LINE of CHT x ROWB
+// contiguous code bytes (a full 128-byte line for Q4 with four groups and for Q8 with two), then the metadata.
+template <int BITS, int CHT> struct Fmt {
     static constexpr int ROWB = BITS * 8;                 // code bytes of one row of one group (64 weights)
-    static constexpr int CODES = CH * 16 * ROWB;          // code bytes of one matrix in one stage
-    static constexpr int META = 2 * 16 * 4;               // [kind][row] x CH halves
+    static constexpr int LINE = CHT * ROWB;               // code bytes of one row in one stage
+    static constexpr int PIECES = LINE / 16;              // 16-byte pieces (= lanes) per row
+    static constexpr int ROWS_PER_PASS = 32 / PIECES;
+    static constexpr int PASSES = 16 / ROWS_PER_PASS;
+    static constexpr int CODES = 16 * LINE;
+    static constexpr int META = 16 * 2 * CHT * 2;         // [row][scale, bias][CHT] halves
     static constexpr int MATRIX = CODES + META;
 };
 
@@ -79,6 +85,9 @@ __device__ __forceinline__ void mma_f16_16816_c(float (&d)[4], uint32_t a0, uint
                  : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
 }
+
+// Ring depth per warp: two stages of four groups or three of two keep the same bytes in flight.
+__host__ __device__ constexpr int stages_for(int matrices_per_warp, int ch) { return (ch == 4 && matrices_per_warp == 2) ? 2 : 3; }
 
 struct ItemInfo {
     const uint8_t* record;
@@ -173,51 +182,44 @@ __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const 
     }
 }
 
-// Source of one matrix for this lane's cp.async copies: lane l copies 16-byte piece l (and l+32 for Q8)
-// of each group's 16 x ROWB code block, and 4 bytes of metadata (kind = l/16, row = l%16).
-template <int BITS>
+// Source of one matrix for this lane's cp.async copies. A pass of the warp copies ROWS_PER_PASS rows: the
+// PIECES lanes of a row fetch its LINE as one contiguous run (one 128-byte request per row where the line is
+// 128 bytes, instead of one request per 32-byte sector). In shared memory a row's groups are stored with
+// the group index xor-ed by (row mod CHT), which keeps the MMA's row-strided reads free of bank conflicts.
+template <int BITS, int CHT>
 struct LaneSource {
-    const uint8_t* codes;      // record + codes offset + this lane's byte offset inside a group block row
-    const uint8_t* meta;       // record + scales or biases offset (by kind)
-    uint32_t row_bytes, meta_row, meta_dst;
-    uint32_t code_row[BITS / 4];   // row inside the tile of each of this lane's pieces
-    uint32_t code_dst[BITS / 4];   // byte offset of the piece inside a group's stage block
-    const uint8_t* tile_codes[BITS / 4];   // set per tile: source of group 0 for each piece
-    const uint8_t* tile_meta;              // set per tile: source of group 0 metadata
-    __device__ __forceinline__ void init(const uint8_t* record, const Projection& pr, uint32_t lane) {
-        constexpr int ROWB = Fmt<BITS>::ROWB, PARTS = ROWB / 16;
+    using F = Fmt<BITS, CHT>;
+    const uint8_t* codes;      // record + codes offset + (row in pass) * row_bytes + piece * 16
+    const uint8_t* meta;       // record + scales or biases offset (by kind) + row * G * 2
+    uint32_t row_bytes, dst0, meta_dst;
+    const uint8_t* tile_codes; // set per tile
+    const uint8_t* tile_meta;
+    __device__ __forceinline__ void init(const uint8_t* record, const Projection& pr, uint32_t lane, uint32_t G) {
         row_bytes = pr.K * BITS / 8;
-#pragma unroll
-        for (int p = 0; p < BITS / 4; ++p) {
-            const uint32_t piece = p * 32 + lane;
-            code_row[p] = piece / PARTS;
-            code_dst[p] = (piece / PARTS) * ROWB + (piece % PARTS) * 16;
-        }
-        codes = record + pr.codes + (lane % PARTS) * 16;
-        meta = record + (lane / 16 ? pr.biases : pr.scales);
-        meta_row = lane % 16;
-        meta_dst = ((lane % 16) * 2 + lane / 16) * 4;
+        const uint32_t piece = lane % F::PIECES, rip = lane / F::PIECES;
+        const uint32_t block = piece * 16 / F::ROWB, within = piece * 16 % F::ROWB;
+        dst0 = rip * F::LINE + ((block ^ (rip & (CHT - 1))) * F::ROWB) + within;
+        codes = record + pr.codes + size_t(rip) * row_bytes + piece * 16;
+        meta = record + (lane / 16 ? pr.biases : pr.scales) + size_t(lane % 16) * G * 2;
+        meta_dst = F::CODES + ((lane % 16) * 2 + lane / 16) * CHT * 2;
     }
     __device__ __forceinline__ void set_tile(uint32_t row0, uint32_t G) {
-#pragma unroll
-        for (int p = 0; p < BITS / 4; ++p) tile_codes[p] = codes + size_t(row0 + code_row[p]) * row_bytes;
-        tile_meta = meta + size_t(row0 + meta_row) * G * 2;
+        tile_codes = codes + size_t(row0) * row_bytes;
+        tile_meta = meta + size_t(row0) * G * 2;
     }
 };
 
-// Issue the cp.async copies of one chunk (CH groups starting at grp0) of one matrix into a ring stage.
-// Stage layout: codes [CH][16 rows][ROWB], then metadata [16 rows][kind][CH] halves.
-template <int BITS>
-__device__ __forceinline__ void issue_matrix(uint32_t stage, const LaneSource<BITS>& src, uint32_t grp0) {
-    constexpr int ROWB = Fmt<BITS>::ROWB;
+// Issue the cp.async copies of one chunk (CHT groups starting at grp0) of one matrix into a ring stage.
+template <int BITS, int CHT>
+__device__ __forceinline__ void issue_matrix(uint32_t stage, const LaneSource<BITS, CHT>& src, uint32_t grp0) {
+    using F = Fmt<BITS, CHT>;
+    const uint8_t* g0 = src.tile_codes + grp0 * F::ROWB;
 #pragma unroll
-    for (int p = 0; p < BITS / 4; ++p) {
-        const uint8_t* g0 = src.tile_codes[p] + grp0 * ROWB;
-#pragma unroll
-        for (int j = 0; j < CH; ++j)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + j * 16 * ROWB + src.code_dst[p]), "l"(g0 + j * ROWB) : "memory");
-    }
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(stage + Fmt<BITS>::CODES + src.meta_dst), "l"(src.tile_meta + grp0 * 2) : "memory");
+    for (int p = 0; p < F::PASSES; ++p)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + src.dst0 + p * F::ROWS_PER_PASS * F::LINE),
+                     "l"(g0 + size_t(p * F::ROWS_PER_PASS) * src.row_bytes) : "memory");
+    if constexpr (CHT == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(stage + src.meta_dst), "l"(src.tile_meta + grp0 * 2) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(stage + src.meta_dst), "l"(src.tile_meta + grp0 * 2) : "memory");
 }
 
 // (a & b) | c in one logic instruction.
@@ -299,11 +301,19 @@ __device__ __forceinline__ void group_mma(float (&d)[4], float c0, float c1, con
 //   NMAT = 2: gate/up + SwiGLU into hbuf.   NMAT = 1: down projection into the router positions.
 //   KS: warps that split K for one row tile (partials added in warp order through shared memory).
 // ---------------------------------------------------------------------------------------------
-template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16>
-__global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN : ZC_MIN_BLOCKS) expert_kernel(Call c, uint32_t tiles_per_warp) {
-    constexpr int RT = WARPS / KS;
-    constexpr int STAGE = NMAT * Fmt<BITS>::MATRIX;
-    constexpr int WORDS = Fmt<BITS>::ROWB / 16;      // 32-bit words per lane per row per group: 2 (Q4) / 4 (Q8)
+//   MW: 1 = a warp streams all NMAT matrices of its rows; 2 (gate/up only) = gate and up of the same rows
+//       go to two different warps, which halves the registers and ring of a warp (three CTAs per SM instead
+//       of two) at the price of meeting in shared memory for the SwiGLU.
+//   CH: quantisation groups per ring stage (4 when K is a multiple of 256, else 2; Q8 always 2).
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH>
+__global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN : (MW == 2 ? 3 : ZC_MIN_BLOCKS)) expert_kernel(Call c, uint32_t tiles_per_warp) {
+    using F = Fmt<BITS, CH>;
+    constexpr int STAGES = stages_for(NMAT / MW, CH);
+    constexpr int WM = NMAT / MW;                    // matrices per warp
+    constexpr int RT = WARPS / (KS * MW);
+    constexpr int STAGE = WM * F::MATRIX;
+    constexpr bool VIA_SMEM = KS > 1 || MW > 1;
+    constexpr int WORDS = F::ROWB / 16;              // 32-bit words per lane per row per group: 2 (Q4) / 4 (Q8)
     constexpr bool FOLDQ = FOLD && BITS == 4;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     ItemInfo it;
@@ -313,38 +323,41 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
     __half* xlo = xhi + (SPLIT ? NTOK * RS : 0);
     float* sums = reinterpret_cast<float*>(xhi + (SPLIT ? 2 : 1) * NTOK * RS);       // [G][NTOK][2]
     uint8_t* ring = reinterpret_cast<uint8_t*>(sums + G * NTOK * 2);                  // [WARPS][STAGES][STAGE]
-    float* red = reinterpret_cast<float*>(ring + WARPS * STAGES * STAGE);             // [KS][NMAT][RT*16][NTOK] when KS > 1
+    float* red = reinterpret_cast<float*>(ring + WARPS * STAGES * STAGE);             // [KS][NMAT][RT*16][NTOK] when VIA_SMEM
     __shared__ int rows[NTOK];
     __shared__ long long dest[NTOK];
 
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, cq = lane % 4;
-    const uint32_t rt = warp / KS, ks = warp % KS;
+    const uint32_t mw = warp % MW, ks = (warp / MW) % KS, rt = warp / (MW * KS);
     const uint32_t first_tile = (blockIdx.x * RT + rt) * tiles_per_warp;
     uint8_t* my_ring = ring + warp * STAGES * STAGE;
-    const uint32_t nchunks = G / CH;                 // G is even
+    const uint32_t nchunks = G / CH;                 // G is a multiple of CH
     const uint32_t my_n = ks < nchunks ? (nchunks - ks + KS - 1) / KS : 0;
     const uint32_t my_tiles = my_n ? tiles_per_warp : 0;
     const bool q8s = c.q8_signed;
     float* out_base = it.shared ? c.shared_out : c.expert_out;
-    LaneSource<BITS> src[NMAT];
-    src[0].init(it.record, NMAT == 2 ? c.gate : c.down, lane);
-    if constexpr (NMAT == 2) src[1].init(it.record, c.up, lane);
+    LaneSource<BITS, CH> src[WM];
+#pragma unroll
+    for (int j = 0; j < WM; ++j) {
+        const uint32_t mi = mw * WM + j;             // 0 = gate (or down), 1 = up
+        src[j].init(it.record, NMAT == 1 ? c.down : (mi == 0 ? c.gate : c.up), lane, G);
+    }
 
     for (uint32_t pass = 0; pass * NTOK < it.count; ++pass) {
         const uint32_t nvalid = min(uint32_t(NTOK), it.count - pass * NTOK);
         uint32_t is_tile = 0, is_chunk = 0, is_slot = 0;        // producer position in the flattened (tile, chunk) sequence
         const uint32_t ring_base = smem_u32(my_ring);
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m) src[m].set_tile(first_tile * 16, G);
+        for (int m = 0; m < WM; ++m) src[m].set_tile(first_tile * 16, G);
         auto issue = [&]() {
             if (is_tile < my_tiles) {
                 const uint32_t stage = ring_base + is_slot * STAGE, grp0 = (ks + is_chunk * KS) * CH;
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) issue_matrix<BITS>(stage + m * Fmt<BITS>::MATRIX, src[m], grp0);
+                for (int m = 0; m < WM; ++m) issue_matrix<BITS, CH>(stage + m * F::MATRIX, src[m], grp0);
                 if (++is_chunk == my_n) {
                     is_chunk = 0; ++is_tile;
 #pragma unroll
-                    for (int m = 0; m < NMAT; ++m) src[m].set_tile((first_tile + is_tile) * 16, G);
+                    for (int m = 0; m < WM; ++m) src[m].set_tile((first_tile + is_tile) * 16, G);
                 }
             }
             cp_async_commit();
@@ -387,78 +400,88 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
 
         uint32_t slot = 0;
         for (uint32_t tile = 0; tile < tiles_per_warp; ++tile) {
-            float acc[NMAT][4];
+            float acc[WM][4];
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m) { acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f; }
+            for (int m = 0; m < WM; ++m) { acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f; }
             for (uint32_t i = 0; i < my_n; ++i) {
                 cp_async_wait<STAGES - 2>();
                 __syncwarp();
                 const uint8_t* stage = my_ring + slot * STAGE;
                 slot = slot + 1 == STAGES ? 0 : slot + 1;
+                issue();          // refills the slot consumed by the previous iteration while this chunk is multiplied
                 const uint32_t grp0 = (ks + i * KS) * CH;
-                float sc[NMAT][2][CH], bi[NMAT][2][CH];          // scale and bias of rows g, g+8 for the CH groups
+                uint32_t mraw[WM][2][CH];                        // per row: CH scale halves then CH bias halves, two per word
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
+                for (int m = 0; m < WM; ++m) {
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
-                        const uint2 raw = *reinterpret_cast<const uint2*>(stage + m * Fmt<BITS>::MATRIX + Fmt<BITS>::CODES + (g + 8 * r) * 8);
-                        if constexpr (META_F16) {
-                            const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-                            const float2 b2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                            sc[m][r][0] = s2.x; sc[m][r][1] = s2.y; bi[m][r][0] = b2.x; bi[m][r][1] = b2.y;
+                        const uint8_t* mp = stage + m * F::MATRIX + F::CODES + (g + 8 * r) * (4 * CH);
+                        if constexpr (CH == 4) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(mp);
+                            mraw[m][r][0] = v.x; mraw[m][r][1] = v.y; mraw[m][r][2] = v.z; mraw[m][r][3] = v.w;
                         } else {
-                            sc[m][r][0] = __uint_as_float(raw.x << 16); sc[m][r][1] = __uint_as_float(raw.x & 0xffff0000u);
-                            bi[m][r][0] = __uint_as_float(raw.y << 16); bi[m][r][1] = __uint_as_float(raw.y & 0xffff0000u);
+                            const uint2 v = *reinterpret_cast<const uint2*>(mp);
+                            mraw[m][r][0] = v.x; mraw[m][r][1] = v.y;
                         }
                     }
                 }
+                // scale / bias of row r (0: g, 1: g+8) for group j of the chunk, converted where it is used
+                auto meta_of = [&](int m, int r, int j, bool bias) {
+                    const uint32_t word = mraw[m][r][(bias ? CH / 2 : 0) + j / 2];
+                    const uint16_t bits = (j & 1) ? uint16_t(word >> 16) : uint16_t(word & 0xffffu);
+                    return META_F16 ? __half2float(__ushort_as_half(bits)) : bf_to_float(bits);
+                };
 #pragma unroll
                 for (int j = 0; j < CH; ++j) {
                     const uint32_t grp = grp0 + j;
                     uint4 bh[2], bl[2];
-                    const __half* bp = xhi + g * RS + grp * 64 + cq * 16;
-                    bh[0] = *reinterpret_cast<const uint4*>(bp);
-                    bh[1] = *reinterpret_cast<const uint4*>(bp + 8);
-                    if constexpr (SPLIT) {
-                        const __half* lp = xlo + g * RS + grp * 64 + cq * 16;
-                        bl[0] = *reinterpret_cast<const uint4*>(lp);
-                        bl[1] = *reinterpret_cast<const uint4*>(lp + 8);
+                    bh[0] = bh[1] = bl[0] = bl[1] = make_uint4(0, 0, 0, 0);
+                    if (g < nvalid) {             // lanes of absent token rows skip the reads (their MMA columns are never stored)
+                        const __half* bp = xhi + g * RS + grp * 64 + cq * 16;
+                        bh[0] = *reinterpret_cast<const uint4*>(bp);
+                        bh[1] = *reinterpret_cast<const uint4*>(bp + 8);
+                        if constexpr (SPLIT) {
+                            const __half* lp = xlo + g * RS + grp * 64 + cq * 16;
+                            bl[0] = *reinterpret_cast<const uint4*>(lp);
+                            bl[1] = *reinterpret_cast<const uint4*>(lp + 8);
+                        }
                     }
                     const float4 sm = *reinterpret_cast<const float4*>(sums + (grp * NTOK + 2 * cq) * 2);   // (Sx, P) of tokens 2cq, 2cq+1
 #pragma unroll
-                    for (int m = 0; m < NMAT; ++m) {
-                        const uint8_t* ms = stage + m * Fmt<BITS>::MATRIX;
+                    for (int m = 0; m < WM; ++m) {
+                        const uint8_t* ms = stage + m * F::MATRIX;
                         uint32_t w0[WORDS], w1[WORDS];
+                        const uint32_t blk = ((uint32_t(j) ^ (g & (CH - 1))) * F::ROWB);      // (g + 8) mod CH == g mod CH
                         if constexpr (BITS == 4) {
-                            const uint2 a = *reinterpret_cast<const uint2*>(ms + (j * 16 + g) * 32 + cq * 8);
-                            const uint2 b = *reinterpret_cast<const uint2*>(ms + (j * 16 + g + 8) * 32 + cq * 8);
+                            const uint2 a = *reinterpret_cast<const uint2*>(ms + g * F::LINE + blk + cq * 8);
+                            const uint2 b = *reinterpret_cast<const uint2*>(ms + (g + 8) * F::LINE + blk + cq * 8);
                             w0[0] = a.x; w0[1] = a.y; w1[0] = b.x; w1[1] = b.y;
                         } else {
-                            const uint4 a = *reinterpret_cast<const uint4*>(ms + (j * 16 + g) * 64 + cq * 16);
-                            const uint4 b = *reinterpret_cast<const uint4*>(ms + (j * 16 + g + 8) * 64 + cq * 16);
+                            const uint4 a = *reinterpret_cast<const uint4*>(ms + g * F::LINE + blk + cq * 16);
+                            const uint4 b = *reinterpret_cast<const uint4*>(ms + (g + 8) * F::LINE + blk + cq * 16);
                             w0[0] = a.x; w0[1] = a.y; w0[2] = a.z; w0[3] = a.w; w1[0] = b.x; w1[1] = b.y; w1[2] = b.z; w1[3] = b.w;
                         }
                         float d[4];
                         group_mma<BITS, SPLIT, FOLDQ>(d, sm.y, sm.w, w0, w1, bh, bl, q8s);    // starts from P: removes the folded offset
-                        acc[m][0] = __fmaf_rn(sc[m][0][j], d[0], acc[m][0]); acc[m][0] = __fmaf_rn(bi[m][0][j], sm.x, acc[m][0]);
-                        acc[m][1] = __fmaf_rn(sc[m][0][j], d[1], acc[m][1]); acc[m][1] = __fmaf_rn(bi[m][0][j], sm.z, acc[m][1]);
-                        acc[m][2] = __fmaf_rn(sc[m][1][j], d[2], acc[m][2]); acc[m][2] = __fmaf_rn(bi[m][1][j], sm.x, acc[m][2]);
-                        acc[m][3] = __fmaf_rn(sc[m][1][j], d[3], acc[m][3]); acc[m][3] = __fmaf_rn(bi[m][1][j], sm.z, acc[m][3]);
+                        const float s0 = meta_of(m, 0, j, false), s1 = meta_of(m, 1, j, false), b0 = meta_of(m, 0, j, true), b1 = meta_of(m, 1, j, true);
+                        acc[m][0] = __fmaf_rn(s0, d[0], acc[m][0]); acc[m][0] = __fmaf_rn(b0, sm.x, acc[m][0]);
+                        acc[m][1] = __fmaf_rn(s0, d[1], acc[m][1]); acc[m][1] = __fmaf_rn(b0, sm.z, acc[m][1]);
+                        acc[m][2] = __fmaf_rn(s1, d[2], acc[m][2]); acc[m][2] = __fmaf_rn(b1, sm.x, acc[m][2]);
+                        acc[m][3] = __fmaf_rn(s1, d[3], acc[m][3]); acc[m][3] = __fmaf_rn(b1, sm.z, acc[m][3]);
                     }
                 }
                 __syncwarp();
-                issue();
             }
             const uint32_t cta_row0 = blockIdx.x * RT * tiles_per_warp * 16;
-            if constexpr (KS == 1) {
+            if constexpr (!VIA_SMEM) {
                 const uint32_t row0 = (first_tile + tile) * 16;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) finish(row0 + g + 8 * (i >> 1), 2 * cq + (i & 1), acc[0][i], acc[NMAT - 1][i]);
+                for (int i = 0; i < 4; ++i) finish(row0 + g + 8 * (i >> 1), 2 * cq + (i & 1), acc[0][i], acc[WM - 1][i]);
             } else {
                 // partials: [ks][matrix][row tile in CTA][row][token]
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    float* mine = red + ((ks * NMAT + m) * RT * 16 + rt * 16) * NTOK;
+                for (int m = 0; m < WM; ++m) {
+                    float* mine = red + ((ks * NMAT + mw * WM + m) * RT * 16 + rt * 16) * NTOK;
                     *reinterpret_cast<float2*>(mine + g * NTOK + 2 * cq) = make_float2(acc[m][0], acc[m][1]);
                     *reinterpret_cast<float2*>(mine + (g + 8) * NTOK + 2 * cq) = make_float2(acc[m][2], acc[m][3]);
                 }
@@ -481,16 +504,17 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
     }
 }
 
-template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16>
-int launch_expert(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
-    constexpr int RT = WARPS / KS;
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH>
+int launch_expert_ch(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
+    constexpr int RT = WARPS / (KS * MW);
+    constexpr int STAGES = stages_for(NMAT / MW, CH);
     const uint32_t K = NMAT == 2 ? c.H : c.F, N = NMAT == 2 ? c.F : c.H, G = K / 64;
     const size_t smem = size_t(SPLIT ? 2 : 1) * NTOK * (K + ROW_PAD) * 2 + size_t(G) * NTOK * 2 * 4 +
-                        size_t(WARPS) * STAGES * NMAT * Fmt<BITS>::MATRIX + (KS > 1 ? size_t(KS) * NMAT * RT * 16 * NTOK * 4 : 0);
+                        size_t(WARPS) * STAGES * (NMAT / MW) * Fmt<BITS, CH>::MATRIX + ((KS > 1 || MW > 1) ? size_t(KS) * NMAT * RT * 16 * NTOK * 4 : 0);
     if (smem > 220 * 1024) return fail(m, ZC_EINVAL, "expert kernel: shape needs too much shared memory");
     while (tiles_per_warp > 1 && N % (16 * RT * tiles_per_warp)) --tiles_per_warp;
     if (N % (16 * RT * tiles_per_warp)) return fail(m, ZC_EINVAL, "expert kernel: rows not a multiple of the CTA tile");
-    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16>;
+    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH>;
     static size_t configured = 0;       // one per instantiation of this function template
     if (smem > configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return check_launch(m, "expert kernel attribute");
@@ -501,18 +525,25 @@ int launch_expert(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_w
     return check_launch(m, NMAT == 2 ? "gate_up" : "down");
 }
 
-template <int NMAT, int KS, bool META_F16>
+// Two groups per ring stage for every shape: four groups per stage (a full 128-byte line per Q4 row) leaves room
+// for only two stages next to the staged rows and measured 13 % slower on gate/up at hidden 2048.
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW>
+int launch_expert(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
+    return launch_expert_ch<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, 2>(m, c, items, tiles_per_warp, s);
+}
+
+template <int NMAT, int KS, bool META_F16, int MW>
 int dispatch_bits(zc_moe* m, const Call& c, uint32_t items, uint32_t tpw, bool split, uint32_t bits, bool fold, cudaStream_t s) {
     if (bits == 4) {
-        if (fold) return split ? launch_expert<4, true, NMAT, KS, true, META_F16>(m, c, items, tpw, s) : launch_expert<4, false, NMAT, KS, true, META_F16>(m, c, items, tpw, s);
-        return split ? launch_expert<4, true, NMAT, KS, false, META_F16>(m, c, items, tpw, s) : launch_expert<4, false, NMAT, KS, false, META_F16>(m, c, items, tpw, s);
+        if (fold) return split ? launch_expert<4, true, NMAT, KS, true, META_F16, MW>(m, c, items, tpw, s) : launch_expert<4, false, NMAT, KS, true, META_F16, MW>(m, c, items, tpw, s);
+        return split ? launch_expert<4, true, NMAT, KS, false, META_F16, MW>(m, c, items, tpw, s) : launch_expert<4, false, NMAT, KS, false, META_F16, MW>(m, c, items, tpw, s);
     }
-    return split ? launch_expert<8, true, NMAT, KS, false, META_F16>(m, c, items, tpw, s) : launch_expert<8, false, NMAT, KS, false, META_F16>(m, c, items, tpw, s);
+    return split ? launch_expert<8, true, NMAT, KS, false, META_F16, MW>(m, c, items, tpw, s) : launch_expert<8, false, NMAT, KS, false, META_F16, MW>(m, c, items, tpw, s);
 }
-template <int NMAT, int KS>
+template <int NMAT, int KS, int MW = 1>
 int dispatch_expert(zc_moe* m, const Call& c, uint32_t items, uint32_t tpw, bool split, uint32_t bits, bool fold, cudaStream_t s) {
-    return c.meta_f16 ? dispatch_bits<NMAT, KS, true>(m, c, items, tpw, split, bits, fold, s)
-                      : dispatch_bits<NMAT, KS, false>(m, c, items, tpw, split, bits, fold, s);
+    return c.meta_f16 ? dispatch_bits<NMAT, KS, true, MW>(m, c, items, tpw, split, bits, fold, s)
+                      : dispatch_bits<NMAT, KS, false, MW>(m, c, items, tpw, split, bits, fold, s);
 }
 
 }  // namespace

@@ -17,11 +17,14 @@ namespace zc {
 namespace {
 
 constexpr int ROUTER_THREADS = 256;
-constexpr int ROW_TILE = 32;
+constexpr int ROW_TILE_PAD = 64;      // rows are padded to a multiple of this in the partials buffer
 
+// TT tokens x ROW_TILE rows per CTA: TT = 8 -> 32 rows (one output per thread), TT = 16 -> 32 rows (two),
+// TT = 32 -> 64 rows (four tokens x two rows per thread: eight chains share two shared-memory reads per k).
 template <int TT>
 __global__ void __launch_bounds__(ROUTER_THREADS) router_partial_kernel(Call c, float* __restrict__ partial, uint32_t rows_padded,
                                                                          uint32_t* __restrict__ tile_done, uint32_t reduce) {
+    constexpr int ROW_TILE = TT == 32 ? 64 : 32;
     extern __shared__ __align__(16) float smem[];
     const uint32_t H = c.H, part = H / 16;
     float* xs = smem;                    // [part][TT]
@@ -53,30 +56,65 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_partial_kernel(Call c, 
 #pragma unroll
         for (int i = 0; i < 8; ++i) xs[(kb * 8 + i) * TT + tt] = v[i];
     }
-    // router rows -> ws[k][e]
-    for (uint32_t task = tid; task < ROW_TILE * (part / 4); task += ROUTER_THREADS) {
-        const uint32_t el = task % ROW_TILE, kq = task / ROW_TILE, e = e0 + el;
-        float4 v = make_float4(0, 0, 0, 0);
-        if (e < rows_total) {
-            const void* base = e < c.E ? c.router_w : c.shared_gate_w;
-            const size_t row = e < c.E ? e : 0;
-            if (c.router_dtype == ZC_F32) {
-                v = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + row * H + k0 + kq * 4));
-            } else {
-                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(base) + row * H + k0 + kq * 4));
-                v = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                                __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+    // router rows -> ws[k][e]; four loads are issued before their stores so that a thread pays the memory
+    // latency once per batch, not once per 16 bytes
+    const uint32_t wtasks = ROW_TILE * (part / 4);
+    for (uint32_t first = tid; first < wtasks; first += 4 * ROUTER_THREADS) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t task = first + u * ROUTER_THREADS;
+            v[u] = make_float4(0, 0, 0, 0);
+            if (task < wtasks) {
+                const uint32_t el = task % ROW_TILE, kq = task / ROW_TILE, e = e0 + el;
+                if (e < rows_total) {
+                    const void* base = e < c.E ? c.router_w : c.shared_gate_w;
+                    const size_t row = e < c.E ? e : 0;
+                    if (c.router_dtype == ZC_F32) {
+                        v[u] = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + row * H + k0 + kq * 4));
+                    } else {
+                        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(base) + row * H + k0 + kq * 4));
+                        v[u] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                           __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                    }
+                }
             }
         }
-        ws[(kq * 4 + 0) * ROW_TILE + el] = v.x;
-        ws[(kq * 4 + 1) * ROW_TILE + el] = v.y;
-        ws[(kq * 4 + 2) * ROW_TILE + el] = v.z;
-        ws[(kq * 4 + 3) * ROW_TILE + el] = v.w;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t task = first + u * ROUTER_THREADS;
+            if (task < wtasks) {
+                const uint32_t el = task % ROW_TILE, kq = task / ROW_TILE;
+                ws[(kq * 4 + 0) * ROW_TILE + el] = v[u].x;
+                ws[(kq * 4 + 1) * ROW_TILE + el] = v[u].y;
+                ws[(kq * 4 + 2) * ROW_TILE + el] = v[u].z;
+                ws[(kq * 4 + 3) * ROW_TILE + el] = v[u].w;
+            }
+        }
     }
     __syncthreads();
 
     if constexpr (TT == 64) {
         const uint32_t tx = tid % 16, ty = tid / 16;        // rows 2tx, 2tx+1; tokens 4ty .. 4ty+3
+        float acc[4][2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = 0.0f;
+#pragma unroll 4
+        for (uint32_t k = 0; k < part; ++k) {
+            const float4 xv = *reinterpret_cast<const float4*>(xs + k * TT + ty * 4);
+            const float2 wv = *reinterpret_cast<const float2*>(ws + k * ROW_TILE + tx * 2);
+            acc[0][0] = __fmaf_rn(xv.x, wv.x, acc[0][0]); acc[0][1] = __fmaf_rn(xv.x, wv.y, acc[0][1]);
+            acc[1][0] = __fmaf_rn(xv.y, wv.x, acc[1][0]); acc[1][1] = __fmaf_rn(xv.y, wv.y, acc[1][1]);
+            acc[2][0] = __fmaf_rn(xv.z, wv.x, acc[2][0]); acc[2][1] = __fmaf_rn(xv.z, wv.y, acc[2][1]);
+            acc[3][0] = __fmaf_rn(xv.w, wv.x, acc[3][0]); acc[3][1] = __fmaf_rn(xv.w, wv.y, acc[3][1]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t t = t0 + ty * 4 + i;
+            if (t < c.T) *reinterpret_cast<float2*>(partial + (size_t(p) * c.T + t) * rows_padded + e0 + tx * 2) = make_float2(acc[i][0], acc[i][1]);
+        }
+    } else if constexpr (TT == 32) {
+        const uint32_t tx = tid % 32, ty = tid / 32;        // rows 2tx, 2tx+1; tokens 4ty .. 4ty+3
         float acc[4][2];
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = 0.0f;
@@ -126,43 +164,60 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_partial_kernel(Call c, 
     if (!last) return;
     __threadfence();
     if (tid == 0) *counter = 0;
-    for (uint32_t o = tid; o < TT * ROW_TILE; o += ROUTER_THREADS) {
-        const uint32_t tt = o / ROW_TILE, el = o % ROW_TILE, t = t0 + tt, e = e0 + el;
-        if (t >= c.T || e >= rows_total) continue;
-        float sum = 0.0f;
+    constexpr int PER = TT * ROW_TILE / ROUTER_THREADS;      // outputs per thread: 1, 2 or 8
+    constexpr int BATCH = PER < 4 ? PER : 4;                 // outputs whose 16 loads are in flight together
+#pragma unroll 1
+    for (int b = 0; b < PER; b += BATCH) {
+        float v[BATCH][16];
 #pragma unroll
-        for (uint32_t q = 0; q < 16; ++q) sum = __fadd_rn(sum, __ldcg(partial + (size_t(q) * c.T + t) * rows_padded + e));
-        if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(sum, c.router_bias[e]) : sum;
-        else c.gate_logit[t] = sum;
+        for (int i = 0; i < BATCH; ++i) {
+            const uint32_t o = tid + (b + i) * ROUTER_THREADS, tt = o / ROW_TILE, el = o % ROW_TILE, t = t0 + tt, e = e0 + el;
+            const bool live = t < c.T && e < rows_total;
+#pragma unroll
+            for (uint32_t q = 0; q < 16; ++q) v[i][q] = live ? __ldcg(partial + (size_t(q) * c.T + t) * rows_padded + e) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const uint32_t o = tid + (b + i) * ROUTER_THREADS, tt = o / ROW_TILE, el = o % ROW_TILE, t = t0 + tt, e = e0 + el;
+            if (t >= c.T || e >= rows_total) continue;
+            float sum = 0.0f;
+#pragma unroll
+            for (uint32_t q = 0; q < 16; ++q) sum = __fadd_rn(sum, v[i][q]);
+            if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(sum, c.router_bias[e]) : sum;
+            else c.gate_logit[t] = sum;
+        }
     }
 }
 
 }  // namespace
 
-uint32_t router_rows_padded(const zc_moe_desc& d) { return (d.experts + (d.has_shared ? 1 : 0) + ROW_TILE - 1) / ROW_TILE * ROW_TILE; }
+uint32_t router_rows_padded(const zc_moe_desc& d) { return (d.experts + (d.has_shared ? 1 : 0) + ROW_TILE_PAD - 1) / ROW_TILE_PAD * ROW_TILE_PAD; }
 
 int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s) {
     const uint32_t part = c.H / 16;
     const uint32_t rows_padded = router_rows_padded(m->d);
-    // Token tile: small tiles give many short CTAs (and a short ordered-sum tail) for decode batches;
-    // long batches use the 64-token tile, which re-reads the router rows least often.
-    const int which = c.T <= 8 ? 0 : c.T <= 128 ? 1 : 2;
-    const uint32_t TT = which == 0 ? 8 : which == 1 ? 16 : 64;
-    const size_t smem = size_t(part) * (TT + ROW_TILE) * sizeof(float);
+    // Token tile: 8 tokens x 32 rows for single-digit batches, 32 tokens x 64 rows beyond (eight chains per
+    // thread share two shared-memory reads per k); long batches use the 64-token tile, which re-reads the
+    // router rows least often.
+    const int which = c.T <= 8 ? 0 : c.T <= 512 ? 1 : 2;
+    const uint32_t TT = which == 0 ? 8 : which == 1 ? 32 : 64;
+    const uint32_t row_tile = which == 1 ? 64 : 32;
+    const size_t smem = size_t(part) * (TT + row_tile) * sizeof(float);
     static size_t configured[3] = {0, 0, 0};
     if (smem > configured[which]) {
         cudaError_t e = which == 0 ? cudaFuncSetAttribute(router_partial_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
-                      : which == 1 ? cudaFuncSetAttribute(router_partial_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
+                      : which == 1 ? cudaFuncSetAttribute(router_partial_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
                                    : cudaFuncSetAttribute(router_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return check_launch(m, "router attribute");
         configured[which] = smem;
     }
-    const dim3 grid(rows_padded / ROW_TILE, 16, (c.T + TT - 1) / TT);
+    const uint32_t rows_total = c.E + (c.has_shared ? 1 : 0);
+    const dim3 grid((rows_total + row_tile - 1) / row_tile, 16, (c.T + TT - 1) / TT);
     int rc;
     {
         Timed t(m, s, KERNEL_ROUTER);
         if (which == 0) router_partial_kernel<8><<<grid, ROUTER_THREADS, smem, s>>>(c, m->router_partial, rows_padded, m->router_done, 1);
-        else if (which == 1) router_partial_kernel<16><<<grid, ROUTER_THREADS, smem, s>>>(c, m->router_partial, rows_padded, m->router_done, 1);
+        else if (which == 1) router_partial_kernel<32><<<grid, ROUTER_THREADS, smem, s>>>(c, m->router_partial, rows_padded, m->router_done, 1);
         else router_partial_kernel<64><<<grid, ROUTER_THREADS, smem, s>>>(c, m->router_partial, rows_padded, m->router_done, 1);
         rc = check_launch(m, "router");
     }
@@ -234,8 +289,8 @@ extern "C" int zc_router_logits_noalloc(const void* x, int act_dtype, const void
     const uint32_t part = hidden / 16, rows_padded = experts;      // a multiple of the 32-row tile already
     const bool tiny = tokens <= 8;
     const uint32_t TT = tiny ? 8 : 16;
-    const size_t smem = size_t(part) * (TT + ROW_TILE) * sizeof(float);   // at most 36 KiB: no opt-in attribute needed
-    const dim3 grid(rows_padded / ROW_TILE, 16, (tokens + TT - 1) / TT);
+    const size_t smem = size_t(part) * (TT + 32) * sizeof(float);   // at most 36 KiB: no opt-in attribute needed
+    const dim3 grid(rows_padded / 32, 16, (tokens + TT - 1) / TT);
     if (tiny) router_partial_kernel<8><<<grid, ROUTER_THREADS, smem, s>>>(c, partial, rows_padded, counters, 1);
     else router_partial_kernel<16><<<grid, ROUTER_THREADS, smem, s>>>(c, partial, rows_padded, counters, 1);
     return check_launch(nullptr, "router (no-alloc)");
