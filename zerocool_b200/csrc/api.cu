@@ -97,7 +97,7 @@ int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* o
     if (family == 1 && !m->pf_tiles) family = 0;      // formats the prefill kernels do not take, or a decode-sized handle
     int n, total = 0;
     if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
-    if ((n = launch_route_permute(m, c, s, true, true, false)) < 0) return n; total += n;
+    if ((n = launch_route_permute(m, c, s, true, true)) < 0) return n; total += n;
     if ((n = family == 1 ? launch_experts_prefill(m, c, s) : launch_experts_decode(m, c, s)) < 0) return n; total += n;
     if (next) n = launch_combine_norm(m, c, next, m->d.act_dtype, s);
     else n = launch_combine(m, c, s);
@@ -288,7 +288,7 @@ int zc_moe_route(zc_moe* m, const float* logits, uint32_t tokens, int32_t* ids, 
     if (!tokens || tokens > m->d.max_tokens || !logits || !ids || !weights) return fail(m, ZC_EINVAL, "invalid route selection buffers");
     Call c = m->scratch;
     c.T = tokens; c.logits = const_cast<float*>(logits); c.ids = ids; c.weights = weights;
-    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), true, false, false);
+    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), true, false);
     if (n < 0) return n;
     m->launches += n;
     return ZC_OK;
@@ -299,7 +299,7 @@ int zc_moe_permute(zc_moe* m, const int32_t* ids, uint32_t tokens, int32_t* offs
     if (!tokens || tokens > m->d.max_tokens || !ids || !offsets || !perm) return fail(m, ZC_EINVAL, "invalid permutation buffers");
     Call c = m->scratch;
     c.T = tokens; c.ids = const_cast<int32_t*>(ids); c.offsets = offsets; c.perm = perm;
-    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), false, true, false);
+    const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), false, true);
     if (n < 0) return n;
     m->launches += n;
     return ZC_OK;
@@ -336,7 +336,7 @@ int zc_moe_ep_dispatch(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens
     const Call c = make_call(m, layer, x, tokens, nullptr);
     int n, total = 0;
     if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
-    if ((n = launch_route_permute(m, c, s, true, true, false)) < 0) return n; total += n;
+    if ((n = launch_route_permute(m, c, s, true, true)) < 0) return n; total += n;
     if ((n = launch_ep_gather(m, c, rows, row_experts, s)) < 0) return n; total += n;
     m->launches += total;
     return ZC_OK;
@@ -355,7 +355,7 @@ int zc_moe_ep_experts(zc_moe* m, uint32_t layer, const void* rows, const int32_t
     c.x = rows; c.records = L.records; c.ids = const_cast<int32_t*>(row_experts); c.expert_out = y; c.T = n_rows; c.layer = layer;
     c.status = m->scratch.status;
     int n, total = 0;
-    if ((n = launch_route_permute(m, c, s, false, true, false)) < 0) return n; total += n;
+    if ((n = launch_route_permute(m, c, s, false, true)) < 0) return n; total += n;
     if ((n = launch_experts_decode(m, c, s)) < 0) return n; total += n;
     m->launches += total;
     return ZC_OK;

@@ -15,40 +15,62 @@ namespace {
 constexpr int COMBINE_THREADS = 256;
 constexpr int MAX_K = 32;
 
-__device__ __forceinline__ float4 slot_product(const Call& c, uint32_t t, uint32_t j, uint32_t col, const float* w, const int* valid) {
-    float4 y = make_float4(0, 0, 0, 0);
-    if (valid[j]) y = *reinterpret_cast<const float4*>(c.expert_out + (size_t(t) * c.K + j) * c.H + col);
-    return make_float4(__fmul_rn(y.x, w[j]), __fmul_rn(y.y, w[j]), __fmul_rn(y.z, w[j]), __fmul_rn(y.w, w[j]));
-}
+__device__ __forceinline__ float4 mul4(float4 y, float w) { return make_float4(__fmul_rn(y.x, w), __fmul_rn(y.y, w), __fmul_rn(y.z, w), __fmul_rn(y.w, w)); }
 __device__ __forceinline__ float4 add4(float4 a, float4 b) {
     return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
 }
 
-// Combined value of four consecutive columns of token t (before the output rounding).
-__device__ __forceinline__ void combine_columns(const Call& c, uint32_t t, uint32_t col, const float* w, const int* valid, float (&r)[4]) {
-    const uint32_t n = c.K < 8 ? c.K : 8;
-    float4 partial[8];
+// Combined value of four consecutive columns of token t (before the output rounding). KMAX >= top_k is the
+// compile-time slot count: every slot's 16 bytes (and the shared expert's) are requested before the first is
+// used, so that a thread waits for one memory round trip, not one per slot. A slot whose id is invalid is read
+// too (the buffer always holds T x K rows) and replaced by zero.
+template <int KMAX>
+__device__ __forceinline__ void combine_columns(const Call& c, uint32_t t, uint32_t col, float (&r)[4]) {
+    const float4* base = reinterpret_cast<const float4*>(c.expert_out + size_t(t) * c.K * c.H + col);
+    const uint32_t stride = c.H / 4;
+    float4 y[KMAX];
 #pragma unroll
-    for (uint32_t i = 0; i < 8; ++i) {
-        if (i < n) {
-            float4 p = slot_product(c, t, i, col, w, valid);
-            for (uint32_t j = i + 8; j < c.K; j += 8) p = add4(p, slot_product(c, t, j, col, w, valid));
-            partial[i] = p;
-        }
+    for (int j = 0; j < KMAX; ++j) {
+        y[j] = make_float4(0, 0, 0, 0);
+        if (uint32_t(j) < c.K) y[j] = __ldcg(base + size_t(j) * stride);
     }
-    float4 total = n > 1 ? add4(partial[0], partial[1]) : partial[0];
+    // Router weight and validity of every slot: the same addresses for the whole CTA (one broadcast transaction
+    // per warp), requested together with the rows instead of through a staged copy and a barrier.
+    float w[KMAX];
+    int id[KMAX];
 #pragma unroll
-    for (uint32_t i = 2; i < 8; ++i) if (i < n) total = add4(total, partial[i]);
+    for (int j = 0; j < KMAX; ++j) {
+        w[j] = 0.0f; id[j] = -1;
+        if (uint32_t(j) < c.K) { w[j] = __ldcg(c.weights + size_t(t) * c.K + j); id[j] = __ldcg(c.ids + size_t(t) * c.K + j); }
+    }
+    float4 sh = make_float4(0, 0, 0, 0);
+    float gate_logit = 0.0f;
+    if (c.has_shared) {
+        sh = __ldcg(reinterpret_cast<const float4*>(c.shared_out + size_t(t) * c.H + col));
+        gate_logit = __ldcg(c.gate_logit + t);
+    }
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+        if (uint32_t(j) < c.K) y[j] = mul4(id[j] >= 0 ? y[j] : make_float4(0, 0, 0, 0), w[j]);
+    }
+    // partial_i = sum over j = i, i+8, ... in ascending j; then (partial_0 + partial_1) + partial_2 ...
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+        for (int j = i + 8; j < KMAX; j += 8) if (uint32_t(j) < c.K) y[i] = add4(y[i], y[j]);
+    }
+    float4 total = y[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) if (uint32_t(i) < c.K) total = add4(total, y[i]);
     r[0] = total.x; r[1] = total.y; r[2] = total.z; r[3] = total.w;
     if (c.has_shared) {
-        const float4 sh = *reinterpret_cast<const float4*>(c.shared_out + size_t(t) * c.H + col);
         const float s[4] = {sh.x, sh.y, sh.z, sh.w};
         if (c.ref) {
-            const float gate = bf_round(sigmoid_bf(bf_round(c.gate_logit[t])));
+            const float gate = bf_round(sigmoid_bf(bf_round(gate_logit)));
 #pragma unroll
             for (int i = 0; i < 4; ++i) r[i] = bf_round(__fadd_rn(bf_round(r[i]), bf_round(__fmul_rn(gate, s[i]))));
         } else {
-            const float gate = sigmoid_f(c.gate_logit[t]);
+            const float gate = sigmoid_f(gate_logit);
 #pragma unroll
             for (int i = 0; i < 4; ++i) r[i] = __fadd_rn(r[i], __fmul_rn(gate, s[i]));
         }
@@ -67,19 +89,13 @@ __device__ __forceinline__ void store4(void* base, int dtype, size_t index, cons
     }
 }
 
+template <int KMAX>
 __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(Call c) {
     const uint32_t t = blockIdx.y;
     const uint32_t col = (blockIdx.x * COMBINE_THREADS + threadIdx.x) * 4;
-    __shared__ float w[MAX_K];
-    __shared__ int valid[MAX_K];
-    if (threadIdx.x < c.K) {
-        w[threadIdx.x] = c.weights[size_t(t) * c.K + threadIdx.x];
-        valid[threadIdx.x] = c.ids[size_t(t) * c.K + threadIdx.x] >= 0;
-    }
-    __syncthreads();
     if (col >= c.H) return;
     float r[4];
-    combine_columns(c, t, col, w, valid, r);
+    combine_columns<KMAX>(c, t, col, r);
     store4(c.out, c.out_dtype, size_t(t) * c.H + col, r);
 }
 
@@ -87,21 +103,15 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(Call c) {
 // layer output (rounded to the output dtype, as a separate combine launch would have stored it), keeps it
 // in shared memory, and writes next[t, :] = act_dtype((out - mean) / std). See norm_act_kernel.
 constexpr int CN_THREADS = 512;
+template <int KMAX>
 __global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(Call c, void* next, int next_dtype) {
     extern __shared__ float row[];          // [H]
-    __shared__ float w[MAX_K];
-    __shared__ int valid[MAX_K];
     __shared__ float partial[CN_THREADS / 32];
     const uint32_t t = blockIdx.x;
-    if (threadIdx.x < c.K) {
-        w[threadIdx.x] = c.weights[size_t(t) * c.K + threadIdx.x];
-        valid[threadIdx.x] = c.ids[size_t(t) * c.K + threadIdx.x] >= 0;
-    }
-    __syncthreads();
     float sum = 0.0f;
     for (uint32_t col = threadIdx.x * 4; col < c.H; col += CN_THREADS * 4) {
         float r[4];
-        combine_columns(c, t, col, w, valid, r);
+        combine_columns<KMAX>(c, t, col, r);
 #pragma unroll
         for (int i = 0; i < 4; ++i) { if (c.out_dtype != ZC_F32) r[i] = bf_round(r[i]); row[col + i] = r[i]; sum += r[i]; }
     }
@@ -176,14 +186,17 @@ int launch_combine(zc_moe* m, const Call& c, cudaStream_t s) {
     if (c.K > MAX_K) return fail(m, ZC_EINVAL, "top_k above 32");
     const dim3 grid((c.H / 4 + COMBINE_THREADS - 1) / COMBINE_THREADS, c.T);
     int rc;
-    { Timed t(m, s, KERNEL_COMBINE); combine_kernel<<<grid, COMBINE_THREADS, 0, s>>>(c); rc = check_launch(m, "combine"); }
+    { Timed t(m, s, KERNEL_COMBINE); if (c.K <= 8) combine_kernel<8><<<grid, COMBINE_THREADS, 0, s>>>(c); else if (c.K <= 16) combine_kernel<16><<<grid, COMBINE_THREADS, 0, s>>>(c); else combine_kernel<32><<<grid, COMBINE_THREADS, 0, s>>>(c);
+      rc = check_launch(m, "combine"); }
     return rc < 0 ? rc : 1;
 }
 
 int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cudaStream_t s) {
     if (c.K > MAX_K) return fail(m, ZC_EINVAL, "top_k above 32");
     int rc;
-    { Timed t(m, s, KERNEL_COMBINE); combine_norm_kernel<<<c.T, CN_THREADS, c.H * sizeof(float), s>>>(c, next, next_dtype); rc = check_launch(m, "combine_norm"); }
+    { Timed t(m, s, KERNEL_COMBINE); const size_t smem = c.H * sizeof(float);
+      if (c.K <= 8) combine_norm_kernel<8><<<c.T, CN_THREADS, smem, s>>>(c, next, next_dtype); else if (c.K <= 16) combine_norm_kernel<16><<<c.T, CN_THREADS, smem, s>>>(c, next, next_dtype); else combine_norm_kernel<32><<<c.T, CN_THREADS, smem, s>>>(c, next, next_dtype);
+      rc = check_launch(m, "combine_norm"); }
     return rc < 0 ? rc : 1;
 }
 

@@ -194,7 +194,7 @@ namespace zc {
 int launch_router(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s);
 uint32_t router_rows_padded(const zc_moe_desc& d);
-int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute, bool from_partials);
+int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute);
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s);
 bool prefill_supported(const zc_moe_desc& d);

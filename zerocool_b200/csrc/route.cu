@@ -20,68 +20,71 @@ constexpr int ROUTE_THREADS = 256;
 constexpr int ROUTE_WARPS = ROUTE_THREADS / 32;
 
 struct RouteArgs {
-    const float* logits_in;     // [T, E] when the logits already exist
-    const float* partial;       // [16, T, rows_padded] router partials, or null
-    float* logits_out;          // [T, E], written when reading partials
-    float* gate_logit;          // [T], written when reading partials and the layer has a shared expert
+    const float* logits;        // [T, E]
     int32_t* ids; float* weights;
-    uint32_t T, E, K, rows_padded, has_shared;
+    uint32_t T, E, K;
     uint32_t* status;
     // permutation tail (run by the last CTA to finish when do_permute is set)
     int32_t* offsets; int32_t* perm; int32_t* active; int32_t* counters; uint32_t* done;
     uint32_t first_expert, local_experts, layer, do_permute;
 };
 
-// One warp per token.
+// Order-preserving integer image of a score: a larger float gives a larger key, +0 and -0 share one key (they
+// compare equal, so the lower expert index must win), and 0 means "cannot be selected" (NaN or -inf).
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t u = __float_as_uint(__fadd_rn(v, 0.0f));          // -0 + 0 = +0
+    const uint32_t k = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return v > __int_as_float(0xff800000) ? k : 0u;
+}
+
+// One warp per token. Lane l holds the keys of experts l, l+32, ... in registers; a round is a register tree for
+// the lane's best (ties to the lower slot), one warp max-reduce of the key and one warp min-reduce of the index
+// among the lanes that hold that key. `row` is the warp's shared-memory copy of the scores (the winner's own
+// value is read back from it, which keeps a signed zero like the reference's re-read of the logit).
 template <int MAXC>
-__device__ __forceinline__ void route_token(const RouteArgs& a, uint32_t t, uint32_t lane, float* scores, int32_t* selected) {
+__device__ __forceinline__ void route_token(const RouteArgs& a, uint32_t t, uint32_t lane, float* row, float* scores, int32_t* selected) {
     const uint32_t E = a.E, K = a.K, nc = E / 32;
     const float ninf = __int_as_float(0xff800000);
-    float cand[MAXC];
-    if (a.partial) {
-        // ordered sum of the sixteen router partials, starting from zero (qwen.metal:529-534)
+    uint32_t key[MAXC];
+    const float* src = a.logits + size_t(t) * E;
 #pragma unroll
-        for (int i = 0; i < MAXC; ++i) {
-            float sum = ninf;
-            if (uint32_t(i) < nc) {
-                sum = 0.0f;
-#pragma unroll
-                for (uint32_t p = 0; p < 16; ++p) sum = __fadd_rn(sum, __ldcg(a.partial + (size_t(p) * a.T + t) * a.rows_padded + lane + 32 * i));
-                a.logits_out[size_t(t) * E + lane + 32 * i] = sum;
-            }
-            cand[i] = sum;
+    for (int i = 0; i < MAXC; ++i) {
+        key[i] = 0u;
+        if (uint32_t(i) < nc) {
+            const float v = __ldcg(src + lane + 32 * i);
+            row[lane + 32 * i] = v;
+            key[i] = order_key(v);
         }
-        if (a.has_shared && lane == 0) {
-            float sum = 0.0f;
-#pragma unroll
-            for (uint32_t p = 0; p < 16; ++p) sum = __fadd_rn(sum, __ldcg(a.partial + (size_t(p) * a.T + t) * a.rows_padded + E));
-            a.gate_logit[t] = sum;
-        }
-    } else {
-        const float* row = a.logits_in + size_t(t) * E;
-#pragma unroll
-        for (int i = 0; i < MAXC; ++i) cand[i] = uint32_t(i) < nc ? row[lane + 32 * i] : ninf;
     }
     for (uint32_t j = 0; j < K; ++j) {
-        float best = ninf;
-        uint32_t index = E;
+        // lane's best key and its slot: pairwise tree, the right element wins only when strictly larger
+        uint32_t bk[MAXC / 2], bs[MAXC / 2];
 #pragma unroll
-        for (int i = 0; i < MAXC; ++i) if (cand[i] > best) { best = cand[i]; index = lane + 32 * i; }
-        float maximum = best;
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, off));
-        uint32_t winner = best == maximum ? index : E;
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) winner = min(winner, __shfl_xor_sync(0xffffffffu, winner, off));
-        // The winner's own value (keeps signed zero, like the reference's re-read of the logit).
-        float mine = ninf;
-#pragma unroll
-        for (int i = 0; i < MAXC; ++i) if (lane + 32 * i == winner) { mine = cand[i]; cand[i] = ninf; }
-        const float score = __shfl_sync(0xffffffffu, mine, winner & 31);
-        if (lane == 0) {
-            selected[j] = winner < E ? int32_t(winner) : -1;
-            scores[j] = winner < E ? score : ninf;
+        for (int i = 0; i < MAXC / 2; ++i) {
+            const bool right = key[2 * i + 1] > key[2 * i];
+            bk[i] = right ? key[2 * i + 1] : key[2 * i];
+            bs[i] = right ? 2 * i + 1 : 2 * i;
         }
+#pragma unroll
+        for (int width = MAXC / 4; width >= 1; width /= 2) {
+#pragma unroll
+            for (int i = 0; i < width; ++i) {
+                const bool right = bk[2 * i + 1] > bk[2 * i];
+                bk[i] = right ? bk[2 * i + 1] : bk[2 * i];
+                bs[i] = right ? bs[2 * i + 1] : bs[2 * i];
+            }
+        }
+        const uint32_t top = __reduce_max_sync(0xffffffffu, bk[0]);
+        const uint32_t mine = (bk[0] == top && top != 0u) ? lane + 32 * bs[0] : 0xffffffffu;
+        const uint32_t winner = __reduce_min_sync(0xffffffffu, mine);       // 0xffffffff: nothing left to select
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i) key[i] = (lane + 32 * i == winner) ? 0u : key[i];
+        if (lane == 0) selected[j] = winner < E ? int32_t(winner) : -1;
+    }
+    __syncwarp();
+    if (lane < K) {
+        const int32_t id = selected[lane];
+        scores[lane] = id >= 0 ? row[id] : ninf;
     }
     __syncwarp();
     float values[4], sum = 0.0f;
@@ -110,26 +113,28 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, uint32_t t, uint
 }
 
 constexpr int PERMUTE_THREADS = 1024;
+constexpr int PERMUTE_CACHE = 4;          // 32-slot chunks of a warp's range kept in registers between the two passes
+constexpr int PERMUTE_OWN = 4;            // consecutive experts owned by one thread in the scan (E <= 4 x threads)
 
-// Exclusive scan of one value per thread over a CTA of NT threads; returns the exclusive prefix and the total.
+// Exclusive scan of one 64-bit value per thread over a CTA of NT threads; returns the exclusive prefix and the total.
 template <int NT>
-__device__ __forceinline__ int block_exclusive_scan(int value, int* warp_totals, int& total) {
+__device__ __forceinline__ unsigned long long block_exclusive_scan(unsigned long long value, unsigned long long* warp_totals, unsigned long long& total) {
     constexpr int NW = NT / 32;
     const uint32_t lane = threadIdx.x % 32, warp = threadIdx.x / 32;
-    int inclusive = value;
+    unsigned long long inclusive = value;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, inclusive, off);
+        const unsigned long long n = __shfl_up_sync(0xffffffffu, inclusive, off);
         if (lane >= uint32_t(off)) inclusive += n;
     }
     if (lane == 31) warp_totals[warp] = inclusive;
     __syncthreads();
     if (warp == 0) {
-        int w = lane < NW ? warp_totals[lane] : 0;
-        int inc = w;
+        const unsigned long long w = lane < NW ? warp_totals[lane] : 0ull;
+        unsigned long long inc = w;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
-            const int n = __shfl_up_sync(0xffffffffu, inc, off);
+            const unsigned long long n = __shfl_up_sync(0xffffffffu, inc, off);
             if (lane >= uint32_t(off)) inc += n;
         }
         if (lane < NW) warp_totals[lane] = inc - w;   // exclusive prefix of the warp totals
@@ -137,84 +142,116 @@ __device__ __forceinline__ int block_exclusive_scan(int value, int* warp_totals,
     }
     __syncthreads();
     total = warp_totals[32];
-    const int result = warp_totals[warp] + inclusive - value;
-    __syncthreads();
-    return result;
+    return warp_totals[warp] + inclusive - value;
 }
 
-// Stable counting sort of the slots by expert id by one CTA of NT threads (hist: [NT/32][E] ints).
-template <int NT>
+// Stable counting sort of the slots by expert id by one CTA of NT threads (hist: [NT/32][E] ints, zero on entry).
+// Each warp owns a contiguous range of slots. Pass 1 counts per (warp, expert); one scan over the experts (each
+// thread owns up to PERMUTE_OWN consecutive ones; slot counts in the low word and "has work" flags in the high
+// word of one 64-bit scan) turns the counts into starting positions; pass 2 places the slots. CACHED keeps the
+// ids of the warp's range in registers between the passes (ranges up to 32 x PERMUTE_CACHE slots).
+template <int NT, bool CACHED>
 __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots, uint32_t E,
                                              uint32_t first_expert, uint32_t local_experts,
                                              int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
                                              int32_t* __restrict__ active, int32_t* __restrict__ counters,
-                                             uint32_t layer, uint32_t* status, int32_t* hist) {
+                                             uint32_t layer, uint32_t* status, int32_t* hist, uint32_t range) {
     constexpr int NW = NT / 32;
-    __shared__ int warp_totals[33];
+    __shared__ unsigned long long warp_totals[33];
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    for (uint32_t i = threadIdx.x; i < NW * E; i += NT) hist[i] = 0;
-    __syncthreads();
-    // Contiguous slot range of this warp, a multiple of 32 long so that chunks stay aligned.
-    const uint32_t range = ((slots + NW - 1) / NW + 31) / 32 * 32;
     const uint32_t begin = min(slots, warp * range), end = min(slots, begin + range);
     int32_t* mine = hist + warp * E;
+    int32_t cached[PERMUTE_CACHE];
+    if constexpr (CACHED) {
+#pragma unroll
+        for (int q = 0; q < PERMUTE_CACHE; ++q) {
+            const uint32_t p = begin + 32 * q + lane;
+            cached[q] = p < end ? __ldcg(ids + p) : -1;
+        }
+    }
     bool bad = false;
-    for (uint32_t base = begin; base < end; base += 32) {
-        const uint32_t p = base + lane;
-        int32_t id = p < end ? __ldcg(ids + p) : -1;
+    auto count_chunk = [&](uint32_t p, int32_t id) {
         const bool valid = id >= 0 && uint32_t(id) < E;
         bad |= p < end && !valid;
         const uint32_t key = valid ? uint32_t(id) : E + lane;     // invalid lanes match nobody
         const uint32_t peers = __match_any_sync(0xffffffffu, key);
         if (valid && (peers & ((1u << lane) - 1)) == 0) mine[id] += __popc(peers);
         __syncwarp();
+    };
+    if constexpr (CACHED) {
+#pragma unroll
+        for (int q = 0; q < PERMUTE_CACHE; ++q) if (begin + 32 * q < end) count_chunk(begin + 32 * q + lane, cached[q]);
+    } else {
+        for (uint32_t base = begin; base < end; base += 32) count_chunk(base + lane, base + lane < end ? __ldcg(ids + base + lane) : -1);
     }
     if (bad) atomicOr(status, ZC_STATUS_INVALID_ROUTE);
     __syncthreads();
-    // Experts in passes of NT: per-warp counts become per-warp starting ranks; running offset carried across passes.
-    int carry = 0, carry_active = 0;
-    for (uint32_t e0 = 0; e0 < E; e0 += NT) {
-        const uint32_t e = e0 + threadIdx.x;
-        int count = 0;
-        if (e < E) {
-            for (int w = 0; w < NW; ++w) {
-                const int n = hist[w * E + e];
-                hist[w * E + e] = count;
-                count += n;
-            }
+    // Per-warp counts become per-warp starting ranks inside the expert; the scan gives the expert's first position.
+    const uint32_t own = (E + NT - 1) / NT;                        // <= PERMUTE_OWN, checked at launch
+    const uint32_t e_first = threadIdx.x * own;
+    int count[PERMUTE_OWN];
+    unsigned long long packed = 0;
+#pragma unroll
+    for (int q = 0; q < PERMUTE_OWN; ++q) {
+        const uint32_t e = e_first + q;
+        count[q] = 0;
+        if (uint32_t(q) < own && e < E) {
+            int running = 0;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) { const int n = hist[w * E + e]; hist[w * E + e] = running; running += n; }
+            count[q] = running;
+            const bool has_work = running > 0 && e >= first_expert && e < first_expert + local_experts;
+            packed += (unsigned long long)(running) | ((unsigned long long)(has_work ? 1 : 0) << 32);
         }
-        int total;
-        const int offset = carry + block_exclusive_scan<NT>(count, warp_totals, total);
-        if (e < E) {
-            offsets[e] = offset;
-            for (int w = 0; w < NW; ++w) hist[w * E + e] += offset;
-        }
-        carry += total;
-        // Ascending list of locally held experts that received work.
-        const int has_work = e < E && e >= first_expert && e < first_expert + local_experts && count > 0;
-        int n_active;
-        const int slot = carry_active + block_exclusive_scan<NT>(has_work, warp_totals, n_active);
-        if (has_work) active[slot] = int32_t(e);
-        carry_active += n_active;
     }
-    if (threadIdx.x == 0) { offsets[E] = carry; counters[0] = carry_active; counters[16 + layer] = carry_active; }
+    unsigned long long total;
+    const unsigned long long before = block_exclusive_scan<NT>(packed, warp_totals, total);
+    int offset = int(uint32_t(before)), slot = int(before >> 32);
+#pragma unroll
+    for (int q = 0; q < PERMUTE_OWN; ++q) {
+        const uint32_t e = e_first + q;
+        if (uint32_t(q) < own && e < E) {
+            offsets[e] = offset;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) hist[w * E + e] += offset;
+            if (count[q] > 0 && e >= first_expert && e < first_expert + local_experts) active[slot++] = int32_t(e);
+            offset += count[q];
+        }
+    }
+    if (threadIdx.x == 0) { offsets[E] = int(uint32_t(total)); counters[0] = int(total >> 32); counters[16 + layer] = int(total >> 32); }
     __syncthreads();
-    for (uint32_t base = begin; base < end; base += 32) {
-        const uint32_t p = base + lane;
-        int32_t id = p < end ? __ldcg(ids + p) : -1;
+    auto place_chunk = [&](uint32_t p, int32_t id) {
         const bool valid = id >= 0 && uint32_t(id) < E;
         const uint32_t key = valid ? uint32_t(id) : E + lane;
         const uint32_t peers = __match_any_sync(0xffffffffu, key);
-        const uint32_t before = peers & ((1u << lane) - 1);
+        const uint32_t before_me = peers & ((1u << lane) - 1);
         int cursor = 0;
         if (valid) cursor = mine[id];
         __syncwarp();
         if (valid) {
-            perm[cursor + __popc(before)] = int32_t(p);
-            if (before == 0) mine[id] = cursor + __popc(peers);
+            perm[cursor + __popc(before_me)] = int32_t(p);
+            if (before_me == 0) mine[id] = cursor + __popc(peers);
         }
         __syncwarp();
+    };
+    if constexpr (CACHED) {
+#pragma unroll
+        for (int q = 0; q < PERMUTE_CACHE; ++q) if (begin + 32 * q < end) place_chunk(begin + 32 * q + lane, cached[q]);
+    } else {
+        for (uint32_t base = begin; base < end; base += 32) place_chunk(base + lane, base + lane < end ? __ldcg(ids + base + lane) : -1);
     }
+}
+
+// Contiguous slot range of one warp: a multiple of 32 long so that chunks stay aligned.
+__host__ __device__ inline uint32_t permute_range(uint32_t slots, uint32_t warps) { return ((slots + warps - 1) / warps + 31) / 32 * 32; }
+
+template <int NT>
+__device__ __forceinline__ void permute_any(const int32_t* ids, uint32_t slots, uint32_t E, uint32_t first_expert, uint32_t local_experts,
+                                            int32_t* offsets, int32_t* perm, int32_t* active, int32_t* counters, uint32_t layer,
+                                            uint32_t* status, int32_t* hist) {
+    const uint32_t range = permute_range(slots, NT / 32);
+    if (range <= 32 * PERMUTE_CACHE) permute_body<NT, true>(ids, slots, E, first_expert, local_experts, offsets, perm, active, counters, layer, status, hist, range);
+    else permute_body<NT, false>(ids, slots, E, first_expert, local_experts, offsets, perm, active, counters, layer, status, hist, range);
 }
 
 __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const int32_t* __restrict__ ids, uint32_t slots, uint32_t E,
@@ -223,11 +260,14 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const int32_t*
                                                                    int32_t* __restrict__ active, int32_t* __restrict__ counters,
                                                                    uint32_t layer, uint32_t* status) {
     extern __shared__ int32_t hist[];
-    permute_body<PERMUTE_THREADS>(ids, slots, E, first_expert, local_experts, offsets, perm, active, counters, layer, status, hist);
+    for (uint32_t i = threadIdx.x; i < (PERMUTE_THREADS / 32) * E; i += PERMUTE_THREADS) hist[i] = 0;
+    __syncthreads();
+    permute_any<PERMUTE_THREADS>(ids, slots, E, first_expert, local_experts, offsets, perm, active, counters, layer, status, hist);
 }
 
 // Route (one warp per token, eight tokens per CTA) and, when asked, the permutation as the tail of the
-// last CTA to finish, so that a layer needs one launch for both.
+// last CTA to finish, so that a layer needs one launch for both. Dynamic shared memory: the eight score rows
+// [8][E] floats, reused as the [8][E] histogram of the permutation.
 template <int MAXC>
 __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
     extern __shared__ int32_t hist[];
@@ -236,32 +276,33 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
     __shared__ bool last;
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t t = blockIdx.x * ROUTE_WARPS + warp;
-    if (t < a.T) route_token<MAXC>(a, t, lane, scores[warp], selected[warp]);
+    if (t < a.T) route_token<MAXC>(a, t, lane, reinterpret_cast<float*>(hist) + warp * a.E, scores[warp], selected[warp]);
     if (!a.do_permute) return;
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) last = atomicAdd(a.done, 1u) == gridDim.x - 1;
+    for (uint32_t i = threadIdx.x; i < ROUTE_WARPS * a.E; i += ROUTE_THREADS) hist[i] = 0;      // overlaps the atomic's round trip
     __syncthreads();
     if (!last) return;
     __threadfence();
     if (threadIdx.x == 0) *a.done = 0;
-    permute_body<ROUTE_THREADS>(a.ids, a.T * a.K, a.E, a.first_expert, a.local_experts, a.offsets, a.perm, a.active, a.counters, a.layer, a.status, hist);
+    permute_any<ROUTE_THREADS>(a.ids, a.T * a.K, a.E, a.first_expert, a.local_experts, a.offsets, a.perm, a.active, a.counters, a.layer, a.status, hist);
 }
 
 }  // namespace
 
-// do_route with partials: the router's [16, T, rows] partial sums are reduced in order on the fly.
-int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute, bool from_partials) {
+int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute) {
     int launched = 0;
+    if (c.E % 32 || c.E > 1024) return fail(m, ZC_EINVAL, "route: experts must be a multiple of 32, at most 1024");
+    if (c.K > 32) return fail(m, ZC_EINVAL, "route: top_k above 32");
     const size_t hist_bytes = size_t(PERMUTE_THREADS / 32) * c.E * sizeof(int32_t);
     if (do_route) {
         RouteArgs a{};
-        a.logits_in = c.logits; a.partial = from_partials ? m->router_partial : nullptr; a.logits_out = c.logits; a.gate_logit = c.gate_logit;
-        a.ids = c.ids; a.weights = c.weights; a.T = c.T; a.E = c.E; a.K = c.K; a.rows_padded = router_rows_padded(m->d);
-        a.has_shared = c.has_shared; a.status = c.status;
+        a.logits = c.logits;
+        a.ids = c.ids; a.weights = c.weights; a.T = c.T; a.E = c.E; a.K = c.K; a.status = c.status;
         a.offsets = c.offsets; a.perm = c.perm; a.active = c.active; a.counters = c.counters; a.done = reinterpret_cast<uint32_t*>(c.counters + 1);
         a.first_expert = c.first_expert; a.local_experts = c.local_experts; a.layer = c.layer; a.do_permute = do_permute;
-        const size_t smem = do_permute ? size_t(ROUTE_THREADS / 32) * c.E * sizeof(int32_t) : 0;
+        const size_t smem = size_t(ROUTE_THREADS / 32) * c.E * sizeof(int32_t);
         const bool small = c.E <= 512;
         static size_t configured[2] = {0, 0};
         if (smem > configured[small]) {
