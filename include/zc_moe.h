@@ -189,7 +189,11 @@ int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* ou
 
 /* Kernel policy switches, the counterpart of KernelConfig (include/engine/metal.hpp:17-43). Options:
  *   "fold_q4" (default 1): Q4 codes enter the tensor-core product as 1024+q / 1024+16q and the offset is
- *   removed from the FP32 group sum; 0 removes it in FP16 before the product (exact, more instructions). */
+ *   removed from the FP32 group sum; 0 removes it in FP16 before the product (exact, more instructions).
+ *   "pdl" (default 1; environment ZC_MOE_PDL=0 at create time): the kernels of a layer are launched with
+ *   programmatic stream serialization, so that each one's set-up and weight prefetch overlap the tail of the
+ *   kernel before it; results are identical either way.
+ * Changing an option drops the cached graphs of zc_moe_stack. */
 int zc_moe_set_option(zc_moe* moe, const char* name, int value);
 
 /* zc_moe_stack without graph replay: the same launches issued one by one (used with the profiler below). */

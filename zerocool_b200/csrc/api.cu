@@ -5,6 +5,7 @@
 // all stream-ordered with no host synchronisation in between (the reference drains the GPU once per
 // layer to build the dispatch lists on the CPU, model.cpp:446).
 #include "common.cuh"
+#include <cstdlib>
 
 #include <cstdio>
 #include <cstring>
@@ -146,6 +147,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
 
     zc_moe* m = new zc_moe();
     m->d = d; m->device = device;
+    if (const char* v = std::getenv("ZC_MOE_PDL")) m->pdl = uint32_t(std::strtoul(v, nullptr, 0)) ? (std::strtoul(v, nullptr, 0) == 1 ? 0xffffffffu : uint32_t(std::strtoul(v, nullptr, 0))) : 0u;   // 0 off, 1 on, else a mask of kernel kinds
     m->layers.resize(d.layers);
     const size_t T = d.max_tokens, H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k;
     int rc = ZC_OK;
@@ -504,7 +506,13 @@ int zc_moe_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, voi
 
 int zc_moe_set_option(zc_moe* m, const char* name, int value) {
     if (!m || !name) return fail(m, ZC_EINVAL, "null handle or option name");
-    if (!std::strcmp(name, "fold_q4")) { m->fold_q4 = value != 0; return ZC_OK; }
+    const bool fold = !std::strcmp(name, "fold_q4"), pdl = !std::strcmp(name, "pdl");
+    if (fold || pdl) {
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);      // captured launches hold the old choice
+        m->graphs.clear();
+        if (fold) m->fold_q4 = value != 0; else m->pdl = value == 0 ? 0u : value == 1 ? 0xffffffffu : uint32_t(value);
+        return ZC_OK;
+    }
     return fail(m, ZC_EINVAL, std::string("unknown option: ") + name);
 }
 

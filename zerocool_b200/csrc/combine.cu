@@ -93,6 +93,8 @@ template <int KMAX>
 __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(Call c) {
     const uint32_t t = blockIdx.y;
     const uint32_t col = (blockIdx.x * COMBINE_THREADS + threadIdx.x) * 4;
+    pdl_wait();
+    pdl_launch_dependents();
     if (col >= c.H) return;
     float r[4];
     combine_columns<KMAX>(c, t, col, r);
@@ -108,6 +110,8 @@ __global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(Call c, void* 
     extern __shared__ float row[];          // [H]
     __shared__ float partial[CN_THREADS / 32];
     const uint32_t t = blockIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
     float sum = 0.0f;
     for (uint32_t col = threadIdx.x * 4; col < c.H; col += CN_THREADS * 4) {
         float r[4];
@@ -186,7 +190,8 @@ int launch_combine(zc_moe* m, const Call& c, cudaStream_t s) {
     if (c.K > MAX_K) return fail(m, ZC_EINVAL, "top_k above 32");
     const dim3 grid((c.H / 4 + COMBINE_THREADS - 1) / COMBINE_THREADS, c.T);
     int rc;
-    { Timed t(m, s, KERNEL_COMBINE); if (c.K <= 8) combine_kernel<8><<<grid, COMBINE_THREADS, 0, s>>>(c); else if (c.K <= 16) combine_kernel<16><<<grid, COMBINE_THREADS, 0, s>>>(c); else combine_kernel<32><<<grid, COMBINE_THREADS, 0, s>>>(c);
+    { Timed t(m, s, KERNEL_COMBINE); auto k = c.K <= 8 ? combine_kernel<8> : c.K <= 16 ? combine_kernel<16> : combine_kernel<32>;
+      launch_chained(m, KERNEL_COMBINE, k, grid, dim3(COMBINE_THREADS), 0, s, nullptr, 0, c);
       rc = check_launch(m, "combine"); }
     return rc < 0 ? rc : 1;
 }
@@ -195,7 +200,8 @@ int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cu
     if (c.K > MAX_K) return fail(m, ZC_EINVAL, "top_k above 32");
     int rc;
     { Timed t(m, s, KERNEL_COMBINE); const size_t smem = c.H * sizeof(float);
-      if (c.K <= 8) combine_norm_kernel<8><<<c.T, CN_THREADS, smem, s>>>(c, next, next_dtype); else if (c.K <= 16) combine_norm_kernel<16><<<c.T, CN_THREADS, smem, s>>>(c, next, next_dtype); else combine_norm_kernel<32><<<c.T, CN_THREADS, smem, s>>>(c, next, next_dtype);
+      auto k = c.K <= 8 ? combine_norm_kernel<8> : c.K <= 16 ? combine_norm_kernel<16> : combine_norm_kernel<32>;
+      launch_chained(m, KERNEL_COMBINE, k, dim3(c.T), dim3(CN_THREADS), smem, s, nullptr, 0, c, next, next_dtype);
       rc = check_launch(m, "combine_norm"); }
     return rc < 0 ? rc : 1;
 }

@@ -183,6 +183,7 @@ struct zc_moe {
     struct Graph { cudaGraphExec_t exec; uint64_t nodes; };
     std::unordered_map<uint64_t, Graph> graphs;
     // Optional per-kernel timing (zc_moe_profile_begin/end): one event pair per launch.
+    uint32_t pdl = 0xffffffffu;   // bit per KernelKind: that kernel launches with programmatic stream serialization (see launch_chained)
     bool fold_q4 = true;          // Q4 codes enter the MMA with their 1024 offset (removed from the FP32 group sum)
     bool profiling = false;
     struct Span { int kind; cudaEvent_t start, stop; };
@@ -222,4 +223,34 @@ struct Timed {
 };
 int fail(zc_moe* m, int code, const std::string& text);
 int check_launch(zc_moe* m, const char* what);
+
+// Programmatic dependent launch. The kernels of a layer form a chain on one stream; each is launched with
+// "programmatic stream serialization", which lets its CTAs be placed on SMs that the previous kernel no longer
+// needs and run everything that does not depend on that kernel (index set-up, weight prefetch) before
+// pdl_wait(). pdl_wait() returns once the previous kernel has completed and its writes are visible. Rules kept
+// by every kernel launched through launch_chained: it calls pdl_wait() before its first read of anything an
+// earlier kernel of the chain wrote and before its first global write, and calls pdl_launch_dependents() only
+// after pdl_wait() - so the kernel after it cannot start before the kernel before it has finished, and at most
+// two kernels of the chain ever overlap. Both calls do nothing in a launch without the attribute.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(const zc_moe* m, int kind, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                  const cudaLaunchAttribute* extra, int n_extra, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[4];
+    int n = 0;
+    for (int i = 0; i < n_extra && i < 3; ++i) attr[n++] = extra[i];
+    if (m && kind >= 0 && ((m->pdl >> kind) & 1u) && !m->profiling) {      // event pairs around a launch would serialise it anyway
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr; cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
 }  // namespace zc

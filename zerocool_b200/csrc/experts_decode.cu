@@ -316,6 +316,10 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
     constexpr int WORDS = F::ROWB / 16;              // 32-bit words per lane per row per group: 2 (Q4) / 4 (Q8)
     constexpr bool FOLDQ = FOLD && BITS == 4;
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    // gate/up follows the routing kernel and needs its lists at once. down follows gate/up, whose own wait has
+    // already seen the routing kernel complete: the item, the row lists and the first weight stages of down are
+    // set up while gate/up is still draining, and only the read of the SwiGLU rows waits for it.
+    if constexpr (NMAT == 2) { pdl_wait(); pdl_launch_dependents(); }
     ItemInfo it;
     if (!decode_item(c, blockIdx.y, it)) return;
     const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64, RS = K + ROW_PAD;
@@ -376,6 +380,7 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
             } else { rows[threadIdx.x] = -1; dest[threadIdx.x] = -1; }
         }
         __syncthreads();
+        if constexpr (NMAT == 1) { pdl_wait(); pdl_launch_dependents(); }
         stage_rows<BITS == 4, SPLIT, FOLDQ>(NMAT == 2 ? c.x : static_cast<const void*>(c.hbuf), NMAT == 2 ? c.act_dtype == ZC_F32 : true,
                                             rows, nvalid, K, c.ref && BITS == 4, xhi, xlo, sums);
         __syncthreads();
@@ -521,7 +526,8 @@ int launch_expert_ch(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_pe
         configured = smem;
     }
     Timed t(m, s, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN);
-    kernel<<<dim3(N / (16 * RT * tiles_per_warp), items), EXPERT_THREADS, smem, s>>>(c, tiles_per_warp);
+    const cudaError_t e = launch_chained(m, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN, kernel, dim3(N / (16 * RT * tiles_per_warp), items), dim3(EXPERT_THREADS), smem, s, nullptr, 0, c, tiles_per_warp);
+    if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("expert kernel launch: ") + cudaGetErrorString(e));
     return check_launch(m, NMAT == 2 ? "gate_up" : "down");
 }
 

@@ -276,6 +276,8 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
     __shared__ bool last;
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t t = blockIdx.x * ROUTE_WARPS + warp;
+    pdl_wait();
+    pdl_launch_dependents();
     if (t < a.T) route_token<MAXC>(a, t, lane, reinterpret_cast<float*>(hist) + warp * a.E, scores[warp], selected[warp]);
     if (!a.do_permute) return;
     __threadfence();
@@ -315,8 +317,9 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
         int rc;
         {
             Timed t(m, s, KERNEL_ROUTE);
-            if (small) route_kernel<16><<<grid, ROUTE_THREADS, smem, s>>>(a);
-            else route_kernel<32><<<grid, ROUTE_THREADS, smem, s>>>(a);
+            const cudaError_t e = small ? launch_chained(m, KERNEL_ROUTE, route_kernel<16>, dim3(grid), dim3(ROUTE_THREADS), smem, s, nullptr, 0, a)
+                                        : launch_chained(m, KERNEL_ROUTE, route_kernel<32>, dim3(grid), dim3(ROUTE_THREADS), smem, s, nullptr, 0, a);
+            if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("route launch: ") + cudaGetErrorString(e));
             rc = check_launch(m, "route");
         }
         if (rc < 0) return rc;

@@ -12,6 +12,7 @@
 // x (k-major) and of the router rows (k-major) in shared memory, then every thread runs its chains:
 // TT = 64: 4 tokens x 2 rows per thread; TT = 8: one (token, row) per thread.
 #include "common.cuh"
+#include <cooperative_groups.h>
 
 namespace zc {
 namespace {
@@ -33,6 +34,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_partial_kernel(Call c, 
     const uint32_t rows_total = c.E + (c.has_shared ? 1u : 0u);
     const uint32_t tid = threadIdx.x;
     const uint32_t k0 = p * part;
+    pdl_wait();
 
     // x slice -> xs[k][t]
     for (uint32_t task = tid; task < TT * (part / 8); task += ROUTER_THREADS) {
@@ -189,11 +191,245 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_partial_kernel(Call c, 
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Cluster form of the same computation, used whenever the device can host its clusters. A thread-block
+// cluster of eight CTAs covers the sixteen partitions of one (row tile, token tile): CTA r computes
+// partitions 2r and 2r+1. The partials never leave the chip: each CTA leaves its two [TT][rows] partial tiles in
+// its shared memory, and after one cluster barrier every CTA adds, in order 0..15 from zero, the sixteen
+// partials of its eighth of the outputs, read from its peers' shared memory. Compared with the global-memory
+// form this removes the partial store, the fence, the arrival counter and the tail that one CTA ran alone.
+//
+// Staging: x and the router rows keep their row-major [row][k] layout in shared memory (leading dimension
+// KC + 4 floats, which spreads eight consecutive rows over all banks for 16-byte reads), so fp32 rows are
+// copied with 16-byte cp.async and everything is in flight at once: one memory round trip before the chains.
+// Thread (tx = lane, ty = warp) owns rows tx (and tx + 32) x tokens ty*TPT.. x both partitions: up to 32
+// independent chains, each still the k-ascending fused multiply-add chain of its partition.
+namespace cg = cooperative_groups;
+constexpr int CLUSTER_PARTS = 2;                      // partitions per CTA
+constexpr int CLUSTER_SIZE = 16 / CLUSTER_PARTS;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+
+template <int TT, int RPT>
+__global__ void __launch_bounds__(ROUTER_THREADS) router_cluster_kernel(Call c) {
+    constexpr int ROW_TILE = 32 * RPT, TPT = TT / 8;
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ __align__(16) float smem[];
+    const uint32_t H = c.H, part = H / 16, KC = CLUSTER_PARTS * part, LD = KC + 4;
+    float* ws = smem;                         // [ROW_TILE][LD]
+    float* xs = ws + ROW_TILE * LD;           // [TT][LD]
+    float* ps = xs + TT * LD;                 // [2][TT][ROW_TILE]
+    const uint32_t e0 = blockIdx.x * ROW_TILE, cr = blockIdx.y, t0 = blockIdx.z * TT;
+    const uint32_t rows_total = c.E + (c.has_shared ? 1u : 0u);
+    const uint32_t tid = threadIdx.x, k0 = cr * KC;
+
+    // ---- stage: the rows first (weights), then x (registers when it needs a conversion) ----
+    constexpr int XB = 4;                     // x tasks (8 values each) a thread keeps in flight
+    const uint32_t xtasks = TT * (KC / 8);
+    const bool x32 = c.act_dtype == ZC_F32, w32 = c.router_dtype == ZC_F32;
+    auto stage_rows = [&]() {
+        const uint32_t wtasks = ROW_TILE * (KC / 4);
+        if (w32) {
+            for (uint32_t task = tid; task < wtasks; task += ROUTER_THREADS) {
+                const uint32_t el = task / (KC / 4), kq = task % (KC / 4), e = e0 + el;
+                float* dst = ws + el * LD + kq * 4;
+                if (e < rows_total) {
+                    const float* base = e < c.E ? static_cast<const float*>(c.router_w) + size_t(e) * H : static_cast<const float*>(c.shared_gate_w);
+                    cp_async16(dst, base + k0 + kq * 4);
+                } else {
+                    *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0);
+                }
+            }
+        } else {
+            for (uint32_t first = tid; first < wtasks; first += 4 * ROUTER_THREADS) {
+                uint2 raw[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t task = first + u * ROUTER_THREADS;
+                    raw[u] = make_uint2(0, 0);
+                    if (task < wtasks) {
+                        const uint32_t el = task / (KC / 4), kq = task % (KC / 4), e = e0 + el;
+                        if (e < rows_total) {
+                            const uint16_t* base = e < c.E ? static_cast<const uint16_t*>(c.router_w) + size_t(e) * H : static_cast<const uint16_t*>(c.shared_gate_w);
+                            raw[u] = __ldg(reinterpret_cast<const uint2*>(base + k0 + kq * 4));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t task = first + u * ROUTER_THREADS;
+                    if (task < wtasks) {
+                        const uint32_t el = task / (KC / 4), kq = task % (KC / 4);
+                        *reinterpret_cast<float4*>(ws + el * LD + kq * 4) =
+                            make_float4(__uint_as_float(raw[u].x << 16), __uint_as_float(raw[u].x & 0xffff0000u),
+                                        __uint_as_float(raw[u].y << 16), __uint_as_float(raw[u].y & 0xffff0000u));
+                    }
+                }
+            }
+        }
+    };
+    // The router rows are weights: their copies start before the previous kernel of the chain has finished.
+    stage_rows();
+    pdl_wait();
+    pdl_launch_dependents();
+    if (x32) {
+        for (uint32_t task = tid; task < xtasks * 2; task += ROUTER_THREADS) {       // 16-byte pieces
+            const uint32_t tt = task / (KC / 4), kq = task % (KC / 4), t = t0 + tt;
+            float* dst = xs + tt * LD + kq * 4;
+            if (t < c.T) cp_async16(dst, static_cast<const float*>(c.x) + size_t(t) * H + k0 + kq * 4);
+            else *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0);
+        }
+    } else {
+        for (uint32_t first = tid; first < xtasks; first += XB * ROUTER_THREADS) {
+            uint4 raw[XB];
+#pragma unroll
+            for (int u = 0; u < XB; ++u) {
+                const uint32_t task = first + u * ROUTER_THREADS;
+                raw[u] = make_uint4(0, 0, 0, 0);
+                if (task < xtasks) {
+                    const uint32_t tt = task / (KC / 8), kb = task % (KC / 8), t = t0 + tt;
+                    if (t < c.T) raw[u] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(c.x) + size_t(t) * H + k0 + kb * 8));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < XB; ++u) {
+                const uint32_t task = first + u * ROUTER_THREADS;
+                if (task < xtasks) {
+                    const uint32_t tt = task / (KC / 8), kb = task % (KC / 8);
+                    const uint32_t r[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                    float4* dst = reinterpret_cast<float4*>(xs + tt * LD + kb * 8);
+                    dst[0] = make_float4(__uint_as_float(r[0] << 16), __uint_as_float(r[0] & 0xffff0000u), __uint_as_float(r[1] << 16), __uint_as_float(r[1] & 0xffff0000u));
+                    dst[1] = make_float4(__uint_as_float(r[2] << 16), __uint_as_float(r[2] & 0xffff0000u), __uint_as_float(r[3] << 16), __uint_as_float(r[3] & 0xffff0000u));
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    // ---- chains ----
+    const uint32_t tx = tid % 32, ty = tid / 32;
+    float acc[CLUSTER_PARTS][TPT][RPT];
+#pragma unroll
+    for (int pp = 0; pp < CLUSTER_PARTS; ++pp)
+#pragma unroll
+        for (int j = 0; j < TPT; ++j)
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) acc[pp][j][i] = 0.0f;
+    const float* wrow = ws + tx * LD;
+    const float* xrow = xs + ty * TPT * LD;
+#pragma unroll 2
+    for (uint32_t k = 0; k < part; k += 4) {
+#pragma unroll
+        for (int pp = 0; pp < CLUSTER_PARTS; ++pp) {
+            float4 wv[RPT], xv[TPT];
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) wv[i] = *reinterpret_cast<const float4*>(wrow + i * 32 * LD + pp * part + k);
+#pragma unroll
+            for (int j = 0; j < TPT; ++j) xv[j] = *reinterpret_cast<const float4*>(xrow + j * LD + pp * part + k);
+#pragma unroll
+            for (int j = 0; j < TPT; ++j)
+#pragma unroll
+                for (int i = 0; i < RPT; ++i) {
+                    float a = acc[pp][j][i];
+                    a = __fmaf_rn(xv[j].x, wv[i].x, a);
+                    a = __fmaf_rn(xv[j].y, wv[i].y, a);
+                    a = __fmaf_rn(xv[j].z, wv[i].z, a);
+                    a = __fmaf_rn(xv[j].w, wv[i].w, a);
+                    acc[pp][j][i] = a;
+                }
+        }
+    }
+#pragma unroll
+    for (int pp = 0; pp < CLUSTER_PARTS; ++pp)
+#pragma unroll
+        for (int j = 0; j < TPT; ++j)
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) ps[(pp * TT + ty * TPT + j) * ROW_TILE + tx + 32 * i] = acc[pp][j][i];
+    cluster.sync();
+
+    // ---- ordered sum of the sixteen partials (router_accumulate, qwen.metal:529-534) for this CTA's outputs ----
+    constexpr uint32_t OUT_PER_CTA = TT * ROW_TILE / CLUSTER_SIZE;
+    for (uint32_t o = cr * OUT_PER_CTA + tid; o < (cr + 1) * OUT_PER_CTA; o += ROUTER_THREADS) {
+        const uint32_t tt = o / ROW_TILE, el = o % ROW_TILE, t = t0 + tt, e = e0 + el;
+        float v[16];
+#pragma unroll
+        for (uint32_t q = 0; q < 16; ++q) {
+            const float* remote = cluster.map_shared_rank(ps + ((q % CLUSTER_PARTS) * TT + tt) * ROW_TILE + el, q / CLUSTER_PARTS);
+            v[q] = *remote;
+        }
+        float sum = 0.0f;
+#pragma unroll
+        for (uint32_t q = 0; q < 16; ++q) sum = __fadd_rn(sum, v[q]);
+        if (t < c.T && e < rows_total) {
+            if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(sum, c.router_bias[e]) : sum;
+            else c.gate_logit[t] = sum;
+        }
+    }
+    cluster.sync();          // nobody leaves while a peer may still read its partials
+}
+
+template <int TT, int RPT>
+int launch_router_cluster(zc_moe* m, const Call& c, cudaStream_t s) {
+    constexpr int ROW_TILE = 32 * RPT;
+    const uint32_t KC = CLUSTER_PARTS * (c.H / 16), LD = KC + 4;
+    const size_t smem = (size_t(ROW_TILE + TT) * LD + size_t(CLUSTER_PARTS) * TT * ROW_TILE) * sizeof(float);
+    const uint32_t rows_total = c.E + (c.has_shared ? 1 : 0);
+    auto kernel = router_cluster_kernel<TT, RPT>;
+    const dim3 grid((rows_total + ROW_TILE - 1) / ROW_TILE, CLUSTER_SIZE, (c.T + TT - 1) / TT);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = CLUSTER_SIZE; attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg{};           // for the occupancy query
+    cfg.gridDim = grid; cfg.blockDim = dim3(ROUTER_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    static size_t configured = 0;       // per instantiation
+    static int usable = -1;             // -1 unknown, 0 the device cannot host a cluster of this shape, 1 yes
+    if (smem > 200 * 1024) return 0;
+    if (smem > configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) { cudaGetLastError(); return 0; }
+        configured = smem;
+        usable = -1;
+    }
+    if (usable < 0) {
+        int clusters = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+        if (e != cudaSuccess) cudaGetLastError();
+        usable = (e == cudaSuccess && clusters > 0) ? 1 : 0;
+    }
+    if (!usable) return 0;
+    int rc;
+    {
+        Timed t(m, s, KERNEL_ROUTER);
+        // Early launch pays for short batches (the row prefetch hides behind the previous kernel); from 64 tokens on
+        // the prefetch of several token tiles competes with that kernel and measured 2 % slower per layer.
+        const cudaError_t e = launch_chained(m, c.T <= 32 ? int(KERNEL_ROUTER) : -1, kernel, grid, dim3(ROUTER_THREADS), smem, s, attr, 1, c);
+        if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("router (cluster) launch: ") + cudaGetErrorString(e));
+        rc = check_launch(m, "router");
+    }
+    return rc < 0 ? rc : 1;
+}
+
 }  // namespace
 
 uint32_t router_rows_padded(const zc_moe_desc& d) { return (d.experts + (d.has_shared ? 1 : 0) + ROW_TILE_PAD - 1) / ROW_TILE_PAD * ROW_TILE_PAD; }
 
 int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s) {
+    // Cluster form first (returns 0 when the device cannot host it: fall through to the global-memory form).
+    {
+        int n;
+        // Small tiles up to 128 tokens: at 64 tokens, 544 CTAs of 16 tokens x 32 rows measured 19 us against 21 us
+        // (32 x 32) and 25 us (32 x 64, whose 144 large CTAs do not all find a cluster slot in the first wave).
+        if (c.T <= 8) n = launch_router_cluster<8, 1>(m, c, s);
+        else if (c.T <= 128) n = launch_router_cluster<16, 1>(m, c, s);
+        else if (c.T <= 512) n = launch_router_cluster<32, 1>(m, c, s);
+        else n = launch_router_cluster<64, 2>(m, c, s);
+        if (n != 0) return n;
+    }
     const uint32_t part = c.H / 16;
     const uint32_t rows_padded = router_rows_padded(m->d);
     // Token tile: 8 tokens x 32 rows for single-digit batches, 32 tokens x 64 rows beyond (eight chains per
