@@ -419,15 +419,14 @@ int launch_router_cluster(zc_moe* m, const Call& c, cudaStream_t s) {
 uint32_t router_rows_padded(const zc_moe_desc& d) { return (d.experts + (d.has_shared ? 1 : 0) + ROW_TILE_PAD - 1) / ROW_TILE_PAD * ROW_TILE_PAD; }
 
 int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s) {
-    // Cluster form first (returns 0 when the device cannot host it: fall through to the global-memory form).
+    // Cluster form for short batches (returns 0 when the device cannot host it: fall through to the global-memory form).
     {
         int n;
         // Small tiles up to 128 tokens: at 64 tokens, 544 CTAs of 16 tokens x 32 rows measured 19 us against 21 us
         // (32 x 32) and 25 us (32 x 64, whose 144 large CTAs do not all find a cluster slot in the first wave).
         if (c.T <= 8) n = launch_router_cluster<8, 1>(m, c, s);
         else if (c.T <= 128) n = launch_router_cluster<16, 1>(m, c, s);
-        else if (c.T <= 512) n = launch_router_cluster<32, 1>(m, c, s);
-        else n = launch_router_cluster<64, 2>(m, c, s);
+        else n = 0;       // long batches: the 64-token tiles of the global-memory form re-read the rows least (237 us against 307-381 us at 2048 tokens)
         if (n != 0) return n;
     }
     const uint32_t part = c.H / 16;
