@@ -62,6 +62,10 @@ template <int BITS, int CHT> struct Fmt {
     static constexpr int CODES = 16 * LINE;
     static constexpr int META = 16 * 2 * CHT * 2;         // [row][scale, bias][CHT] halves
     static constexpr int MATRIX = CODES + META;
+    // Rows whose lines fall into the same 128-byte bank window are ROWS_PER_WINDOW apart; the block index of a row is
+    // xor-ed with swizzle(row) so that rows read together by one MMA fragment load use different banks.
+    static constexpr int ROWS_PER_WINDOW = LINE >= 128 ? 1 : 128 / LINE;
+    __host__ __device__ static constexpr uint32_t swizzle(uint32_t row) { return (row / ROWS_PER_WINDOW) & (CHT - 1); }
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -185,7 +189,7 @@ __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const 
 // Source of one matrix for this lane's cp.async copies. A pass of the warp copies ROWS_PER_PASS rows: the
 // PIECES lanes of a row fetch its LINE as one contiguous run (one 128-byte request per row where the line is
 // 128 bytes, instead of one request per 32-byte sector). In shared memory a row's groups are stored with
-// the group index xor-ed by (row mod CHT), which keeps the MMA's row-strided reads free of bank conflicts.
+// the group index xor-ed by Fmt::swizzle(row), which keeps the MMA's row-strided reads free of bank conflicts.
 template <int BITS, int CHT>
 struct LaneSource {
     using F = Fmt<BITS, CHT>;
@@ -198,7 +202,7 @@ struct LaneSource {
         row_bytes = pr.K * BITS / 8;
         const uint32_t piece = lane % F::PIECES, rip = lane / F::PIECES;
         const uint32_t block = piece * 16 / F::ROWB, within = piece * 16 % F::ROWB;
-        dst0 = rip * F::LINE + ((block ^ (rip & (CHT - 1))) * F::ROWB) + within;
+        dst0 = rip * F::LINE + ((block ^ F::swizzle(rip)) * F::ROWB) + within;      // swizzle(rip) == swizzle(row): passes add multiples of 4 rows
         codes = record + pr.codes + size_t(rip) * row_bytes + piece * 16;
         meta = record + (lane / 16 ? pr.biases : pr.scales) + size_t(lane % 16) * G * 2;
         meta_dst = F::CODES + ((lane % 16) * 2 + lane / 16) * CHT * 2;
@@ -456,7 +460,7 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
                     for (int m = 0; m < WM; ++m) {
                         const uint8_t* ms = stage + m * F::MATRIX;
                         uint32_t w0[WORDS], w1[WORDS];
-                        const uint32_t blk = ((uint32_t(j) ^ (g & (CH - 1))) * F::ROWB);      // (g + 8) mod CH == g mod CH
+                        const uint32_t blk = ((uint32_t(j) ^ F::swizzle(g)) * F::ROWB);           // swizzle(g + 8) == swizzle(g)
                         if constexpr (BITS == 4) {
                             const uint2 a = *reinterpret_cast<const uint2*>(ms + g * F::LINE + blk + cq * 8);
                             const uint2 b = *reinterpret_cast<const uint2*>(ms + (g + 8) * F::LINE + blk + cq * 8);
@@ -566,10 +570,16 @@ int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s) {
     const bool small = c.T * (c.K + (c.has_shared ? 1 : 0)) <= 64;
     int rc;
     if (small) rc = dispatch_expert<2, 8>(m, c, items, 1, split_x, c.gate.bits, fold, s);
-    else rc = dispatch_expert<2, 1>(m, c, items, 1, split_x, c.gate.bits, fold, s);
+#ifndef ZC_TPW_GU
+#define ZC_TPW_GU 2
+#endif
+#ifndef ZC_TPW_DN
+#define ZC_TPW_DN 4
+#endif
+    else rc = dispatch_expert<2, 1>(m, c, items, ZC_TPW_GU, split_x, c.gate.bits, fold, s);
     if (rc < 0) return rc;
     if (small) rc = dispatch_expert<1, 2>(m, c, items, 1, split_h, c.down.bits, fold, s);
-    else rc = dispatch_expert<1, 1>(m, c, items, 2, split_h, c.down.bits, fold, s);
+    else rc = dispatch_expert<1, 1>(m, c, items, ZC_TPW_DN, split_h, c.down.bits, fold, s);
     if (rc < 0) return rc;
     return 2;
 }
