@@ -48,7 +48,7 @@ constexpr int ROW_PAD = 8;            // halves added to each staged row (keeps 
 #define ZC_MIN_BLOCKS 2
 #endif
 #ifndef ZC_MIN_BLOCKS_DOWN
-#define ZC_MIN_BLOCKS_DOWN 4
+#define ZC_MIN_BLOCKS_DOWN 3
 #endif
 
 // One ring stage of one matrix holds CHT quantisation groups of 16 rows: for every row one LINE of CHT x ROWB
@@ -535,10 +535,15 @@ int launch_expert_ch(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_pe
     return check_launch(m, NMAT == 2 ? "gate_up" : "down");
 }
 
-// Two groups per ring stage for every shape: four groups per stage (a full 128-byte line per Q4 row) leaves room
-// for only two stages next to the staged rows and measured 13 % slower on gate/up at hidden 2048.
+// Two groups per ring stage for gate/up: four groups per stage (a full 128-byte line per Q4 row) leave room for
+// only two stages next to the staged rows and measured 13 % slower at hidden 2048.
 template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW>
 int launch_expert(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
+    // down, whose K is short (eight groups at ffn 512), is bound by instruction issue: four groups per stage halve
+    // its per-stage bookkeeping (three stages still fit beside its small row tile).
+    if constexpr (BITS == 4 && NMAT == 1 && KS == 1) {
+        if ((c.F / 64) % 4 == 0) return launch_expert_ch<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, 4>(m, c, items, tiles_per_warp, s);
+    }
     return launch_expert_ch<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, 2>(m, c, items, tiles_per_warp, s);
 }
 
