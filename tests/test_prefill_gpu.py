@@ -48,7 +48,7 @@ def test_prefill_matches_oracle_small_experts():
 
 
 def test_prefill_equals_decode_family_on_skewed_loads():
-    """Router rows scaled by a Zipf-like factor: a few experts receive hundreds of rows (several 128-token
+    """Router rows scaled by a Zipf-like factor: a few experts receive hundreds of rows (several 64-token
     tiles), many receive a handful or none. The prefill family must agree with the decode family."""
     cfg = util.cfg2(experts=128, max_tokens=1024)
     router = synth.router(cfg, SEED, 0).copy()
@@ -68,6 +68,38 @@ def test_prefill_equals_decode_family_on_skewed_loads():
     assert util.rel_max_error(out[:24], sub["out"]) <= TOL
 
 
+def test_prefill_with_asymmetric_biases():
+    """bias != -8 scale: the second term of the affine form, (8 s + b) * sum(x), is then not zero and runs through
+    the correction stages of the kernel (metadata tile times the activations' group sums)."""
+    from zerocool_b200.records import build_record, float_to_meta
+    cfg = util.cfg2(experts=32, top_k=4, max_tokens=512)
+    rng = np.random.default_rng(5)
+
+    def skewed(expert):
+        parts = []
+        for p in range(3):
+            codes, sbits, bbits = synth.projection_parts(cfg, SEED, 0, expert, p)
+            s = sbits.view(np.float16).astype(np.float32)
+            b = -8.0 * s + rng.uniform(-0.03, 0.03, size=s.shape).astype(np.float32)
+            parts.append((codes, sbits, float_to_meta(b, cfg.meta_dtype).reshape(bbits.shape)))
+        return build_record(cfg, parts)
+
+    records = [skewed(e) for e in range(cfg.experts)]
+    shared = skewed(synth.SHARED_EXPERT)
+    m = make(cfg)
+    m.load_layer(0, records=np.stack(records), router_w=synth.router(cfg, SEED, 0), shared_record=shared, shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    x = synth.activations(cfg, SEED, 0, 200)
+    out = m.prefill(0, device_x(m, x)).float().cpu().numpy()
+    assert m.status() == 0
+    want = oracle.moe_layer(cfg.as_dict(), records, synth.router(cfg, SEED, 0), x, shared_record=shared, shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    assert np.array_equal(m.last_routing(200)["ids"], want["ids"])
+    err = util.rel_max_error(out, want["out"])
+    print("asymmetric biases, prefill max-abs error / RMS:", err)
+    assert err <= TOL, err
+    dec = m.decode(0, device_x(m, x)).float().cpu().numpy()
+    assert util.rel_max_error(dec, want["out"]) <= TOL
+
+
 def test_prefill_config5_shape():
     """hidden 4096 (config 5's geometry), no shared expert, a token count that is not a multiple of 16."""
     cfg = util.cfg2(hidden=4096, experts=32, top_k=4, has_shared=0, max_tokens=512)
@@ -85,7 +117,7 @@ def test_forward_picks_the_family_by_token_count():
     a = m.moe(0, x)
     used = m.launches - before
     b = m.prefill(0, x)
-    assert torch.equal(a, b) and used == 7              # router, route, tiles, activations, gate/up, down, combine
+    assert torch.equal(a, b) and used == 9              # router, route, tiles, activations, sums, gate/up, sums, down, combine
     small = device_x(m, synth.activations(cfg, SEED, 0, 8))
     before = m.launches
     m.moe(0, small)

@@ -162,6 +162,8 @@ struct zc_moe {
     std::vector<void*> allocations;
     zc::Call scratch{};           // scratch pointers (x/out/layer fields filled per call)
     __half* xp = nullptr;                // [max_tokens, H] FP16 activations in the prefill kernels' k order
+    __half* xsum = nullptr;              // [max_tokens, 4 H/64] group sums of xp (prefill correction stages)
+    __half* hsum = nullptr;              // [max_tokens*K + max_tokens, 4 F/64] group sums of hbuf16
     __half* hbuf16 = nullptr;            // [max_tokens*K + max_tokens, F] FP16 SwiGLU outputs (prefill)
     void* pf_tiles = nullptr;            // tile list of the prefill launches
     int32_t* pf_ntiles = nullptr;

@@ -5,28 +5,37 @@
 // :71-81, :63-70, :800-803) with two launches per layer over a tile list that covers every expert.
 //
 // Formulation ("weights as M"): for one expert, D[weight row, token] = W[rows, K] . X^T[K, tokens]. The
-// 128-row weight tile is the M of tcgen05.mma, the expert's tokens are the N (padded to 16, at most 128
+// 128-row weight tile is the M of tcgen05.mma, the expert's tokens are the N (padded to 16, at most 64
 // per tile), so a ragged or skewed expert load costs at most 15 padded columns instead of a padded
-// 128-row token tile, and every weight is fetched and dequantised once per 128 tokens of its expert.
-//   NMAT = 2: gate and up tiles of the same 128 rows accumulate side by side in TMEM (columns [0,N) and
-//             [N,2N)); the epilogue reads both, applies SwiGLU and stores h as FP16 in the k order the
-//             second launch consumes.
-//   NMAT = 1: the down projection; the epilogue writes FP32 rows at the slots' router positions.
+// 128-row token tile. At 2048 tokens over 512 experts (40 tokens per expert) the launch moves 0.56 bytes per
+// 80 flops: it is bound by the weight stream from HBM, not by the tensor cores, so the kernel is built to keep
+// the dequantisation cheap and many bytes in flight.
 //
-// Roles in a CTA of 160 threads: warps 0-3 are producers, then the epilogue; warp 4 owns TMEM
-// (tcgen05.alloc / dealloc) and one of its lanes issues the MMAs.
-//   producer thread r: dequantises weight row r of the tile for one 64-wide quantisation group per stage
-//     (w = s*q + b in FP16, one rounding; eight codes -> one 16-byte store). The packed codes reach it
-//     through a thread-private cp.async ring three stages ahead; the token rows (already FP16, in the
-//     matching k order) are copied by cp.async straight into the B tile two stages ahead. Stage buffers
-//     use the no-swizzle K-major core-matrix layout ([rows/8][8 k-chunks][8 rows][16 bytes]; LBO = 128,
-//     SBO = 1024).
-//   a stage is handed over with fence.proxy.async + mbarrier arrive; the MMA lane waits, issues
-//     4 (k steps of 16) x NMAT x 2 (hi, lo weight terms) tcgen05.mma, and frees the stage with tcgen05.commit.
-// Precision: an FP16 weight s*q+b rounded once costs ~2e-4 relative rms per projection, and three projections
-// plus the FP16 intermediate put the layer's max-abs error at ~2.5e-3 x RMS, above the 2e-3 bound. The weights
-// are therefore fed as two exact-product FP16 terms (see pf_dequant_word); what remains is the single FP16
-// rounding of the intermediate h (~1.4e-3 x RMS max-abs at a few hundred thousand outputs).
+// Arithmetic (the reference's affine form, qwen.metal:46-62, regrouped):
+//     sum_k (s_g q_k + b_g) x_k  =  s_g * sum_k (q_k - 8) x_k  +  (8 s_g + b_g) * sum_k x_k      per 64-wide group g
+//   * the tensor cores multiply the exact integers q - 8 (FP16) with the FP16 activations, one fresh TMEM
+//     accumulator per group (four buffers rotate);
+//   * the epilogue warps read each group's accumulator (tcgen05.ld) and add it into FP32 registers scaled by
+//     s_g - the scale never enters an FP16 product, so no weight is rounded;
+//   * the second term is itself a small product over the groups: A' = [s_0..s_G-1 | b_0..b_G-1] (the record's
+//     own FP16 metadata) times B' = [8 S_0.. | S_0..] with S_g = sum of the token's activations in group g,
+//     carried as two FP16 terms (hi, lo). It runs as extra stages after the K loop (K' in blocks of 64, hi then lo)
+//     and is added with scale 1.
+//   NMAT = 2: gate and up tiles of the same 128 rows sit side by side in TMEM; the final epilogue applies
+//             SwiGLU and stores h as FP16 in the k order the second launch consumes.
+//   NMAT = 1: the down projection; the final epilogue writes FP32 rows at the slots' router positions.
+//
+// Roles in a CTA of 416 threads: warps 0-3 producers, warp 4 owns TMEM (alloc / dealloc) and one of its lanes
+// issues the MMAs, warps 5-12 are the epilogue (warp w reads TMEM lanes 32 (w mod 4) ..; two warps share a lane
+// quadrant and split the token columns).
+//   producer thread r: turns the packed codes of weight row r for one group per stage into 64 FP16 integers
+//     (one lop3 per two codes + one FP16 add or fma, eight 16-byte stores). The packed codes reach it through a
+//     thread-private cp.async ring several stages ahead; the token rows (already FP16, in the matching k order)
+//     are copied by cp.async straight into the B tile. Stage buffers use the no-swizzle K-major core-matrix
+//     layout ([rows/8][k chunks][8 rows][16 bytes]; LBO = 128, SBO = 128 x chunks).
+//   a stage is handed over with fence.proxy.async + mbarrier arrive; the MMA lane waits for the stage and for the
+//     accumulator buffer to be drained, issues 4 (k steps of 16) x NMAT tcgen05.mma and signals with tcgen05.commit
+//     both "stage buffers free" and "accumulator full".
 // Every wait is bounded: after ~2^22 polls a role sets ZC_STATUS_TIMEOUT, raises the CTA's abort flag and
 // leaves its loop; the CTA then frees its TMEM and exits.
 #include "common.cuh"
@@ -34,12 +43,13 @@
 namespace zc {
 namespace {
 
-constexpr int PF_THREADS = 160;
+constexpr int PF_THREADS = 416;        // 4 producer warps, 1 MMA / TMEM warp, 8 epilogue warps
+constexpr uint32_t PF_ACC = 4;         // TMEM accumulator buffers (one 64-wide group each)
 constexpr int PF_M = 128;
-constexpr int PF_NMAX = 128;          // tokens per tile (the N of the MMA, padded to 16)
+constexpr int PF_NMAX = 64;           // tokens per tile (the N of the MMA, padded to 16)
 constexpr uint32_t PF_A_BYTES = PF_M * 128;          // one matrix, one stage: 128 rows x 64 halves
 constexpr uint32_t PF_B_BYTES = PF_NMAX * 128;
-constexpr uint32_t PF_POLL_LIMIT = 1u << 22;
+constexpr uint32_t PF_POLL_LIMIT = 1u << 20;     // attempts of a bounded wait (each suspends for at most ~1 us: about one second in all)
 
 struct PfTile { int32_t expert, row0, rows, shared; };
 
@@ -50,28 +60,29 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pf_smem(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+// One attempt: mbarrier.try_wait suspends the thread until the phase completes or the time hint (1 us) passes
+// (it wakes as soon as the barrier flips, unlike a poll followed by a sleep).
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(pf_smem(bar)), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(pf_smem(bar)), "r"(parity), "r"(1000u) : "memory");       // suspend for at most ~1 us per attempt
     return ok != 0;
 }
 // Bounded wait. Returns false (and raises the abort flag) when the phase did not complete in time or
 // another role has already given up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
     for (uint32_t i = 0; i < PF_POLL_LIMIT; ++i) {
-        if (mbar_test(bar, parity)) return true;
+        if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (i > 64) __nanosleep(40);
     }
     *abort_flag = 1;
     atomicOr(status, ZC_STATUS_TIMEOUT);
     return false;
 }
 
-// K-major, no swizzle: start address, LBO = 128 B (next k chunk), SBO = 1024 B (next 8 rows), version 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(128 >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46);
+// K-major, no swizzle: start address, LBO = 128 B (next k chunk), SBO = sbo bytes (next 8 rows), version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t sbo = 1024) {
+    return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(128 >> 4) << 16) | (uint64_t(sbo >> 4) << 32) | (1ull << 46);
 }
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -97,27 +108,20 @@ __device__ __forceinline__ uint32_t pf_and_or(uint32_t a, uint32_t b, uint32_t c
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-// Eight Q4 codes of one word -> the weights s*q + b as two FP16 terms whose sum has (almost) no rounding:
-//   hi = s_hi * (q - 8)            exact: s_hi keeps 6 significant bits of the scale, q - 8 has 4
-//   lo = s_lo * (q - 8) + (b + 8s) s_lo * (q - 8) is exact too; the only rounding is at the size of the
-//                                  residual bias b + 8s, which is zero for symmetric codes (b = -8 s)
-// Both come out as (k0,k4) (k1,k5) (k2,k6) (k3,k7). The tensor cores add hi.x + lo.x in FP32.
-__device__ __forceinline__ void pf_dequant_word(uint32_t w, __half2 s_hi, __half2 s_lo, __half2 resid, uint4& hi, uint4& lo) {
+// Eight Q4 codes of one word -> the integers q - 8 as FP16, in the order (k0,k4) (k1,k5) (k2,k6) (k3,k7).
+// (w & 0x000f000f) | 0x6400 is the half2 (1024 + q, 1024 + q'); the nibbles one position up give 1024 + 16 q.
+__device__ __forceinline__ uint4 pf_dequant_word(uint32_t w) {
     const uint32_t mlo = 0x000f000fu, mhi = 0x00f000f0u, magic = 0x64006400u;
     const __half2 k1032 = __floats2half2_rn(1032.0f, 1032.0f), k16 = __floats2half2_rn(0.0625f, 0.0625f), k72 = __floats2half2_rn(-72.0f, -72.0f);
     const uint32_t w8 = w >> 8;
     uint32_t p[4] = {pf_and_or(w, mlo, magic), pf_and_or(w, mhi, magic), pf_and_or(w8, mlo, magic), pf_and_or(w8, mhi, magic)};
-    uint32_t h[4], l[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         __half2 q = *reinterpret_cast<__half2*>(&p[i]);
-        q = (i & 1) ? __hfma2(q, k16, k72) : __hsub2(q, k1032);      // exact integer q - 8
-        const __half2 a = __hmul2(q, s_hi), b = __hfma2(q, s_lo, resid);
-        h[i] = *reinterpret_cast<const uint32_t*>(&a);
-        l[i] = *reinterpret_cast<const uint32_t*>(&b);
+        q = (i & 1) ? __hfma2(q, k16, k72) : __hsub2(q, k1032);      // exact
+        p[i] = *reinterpret_cast<const uint32_t*>(&q);
     }
-    hi = make_uint4(h[0], h[1], h[2], h[3]);
-    lo = make_uint4(l[0], l[1], l[2], l[3]);
+    return make_uint4(p[0], p[1], p[2], p[3]);
 }
 
 // Tile list: one entry per (expert with work, block of PF_NMAX of its rows), the shared expert's token
@@ -171,6 +175,34 @@ __global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, _
     *reinterpret_cast<uint4*>(xp + i * 8) = *reinterpret_cast<uint4*>(h);
 }
 
+// Per row of an FP16 matrix [rows, K] and per 64-wide group g: S_g = sum of the row's values in the group (FP32 sum),
+// stored as the B' operand of the correction stages, [8 hi_0.. | hi_0.. | 8 lo_0.. | lo_0..] with hi = fp16(S),
+// lo = fp16(S - hi) (4 G halves per row). One warp per row.
+__global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, uint32_t K, __half* __restrict__ sums) {
+    const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
+    if (row >= rows) return;
+    const uint32_t G = K / 64;
+    for (uint32_t g0 = 0; g0 < G; g0 += 4) {             // a lane adds one 16-byte piece; eight lanes cover a group
+        const uint32_t g = g0 + lane / 8;
+        float sum = 0.0f;
+        if (g < G) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + size_t(row) * K + g * 64 + (lane % 8) * 8);
+            const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); sum += f.x; sum += f.y; }
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (g < G && lane % 8 == 0) {
+            const __half hi = __float2half_rn(sum), lo = __float2half_rn(sum - __half2float(hi));
+            __half* dst = sums + size_t(row) * 4 * G;
+            dst[g] = __float2half_rn(8.0f * __half2float(hi)); dst[G + g] = hi;
+            dst[2 * G + g] = __float2half_rn(8.0f * __half2float(lo)); dst[3 * G + g] = lo;
+        }
+    }
+}
+
 __device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -178,63 +210,71 @@ __device__ __forceinline__ void pf_cp4(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
-constexpr int PF_RAW = 4;      // depth of the per-thread ring of packed codes
+constexpr uint32_t PF_STAGES = 2;      // A stage buffers (written by the producers, read by the MMAs)
+// Prefetch distance D (template parameter of the kernel): the packed codes and the token rows of stage ks + D are
+// requested while stage ks is dequantised, so that D stages of work (a few thousand cycles) cover the memory
+// latency. Token-row (B) ring: D + 2 slots; per-thread ring of packed codes: D + 1 slots.
 
-// Shared memory of one CTA (dynamic, 1024-byte aligned for the tile buffers): a ring of A stages (each
-// matrix as a hi and a lo tile), a ring of B stages, and the per-thread rings of packed codes and metadata.
+// Shared memory of one CTA (dynamic, 1024-byte aligned for the tile buffers).
 template <int NMAT>
 struct PfSmem {
-    static constexpr uint32_t SA = NMAT == 2 ? 2 : 3;                 // A ring depth
-    static constexpr uint32_t SB = 3;                                 // B ring depth
-    static constexpr uint32_t A_STAGE = NMAT * 2 * PF_A_BYTES;        // [matrix][hi, lo]
-    static constexpr uint32_t A_RING = SA * A_STAGE;
-    static constexpr uint32_t B_RING = SB * PF_B_BYTES;
-    static constexpr uint32_t RAW = PF_RAW * NMAT * 128 * 32;         // [slot][matrix][thread][32 B]
-    static constexpr uint32_t META = PF_RAW * NMAT * 128 * 8;         // [slot][matrix][thread][s0 s1 b0 b1]
-    static constexpr uint32_t TOTAL = A_RING + B_RING + RAW + META + 1024;   // + alignment slack
+    static constexpr uint32_t A_STAGE = NMAT * PF_A_BYTES;
+    static constexpr uint32_t A_RING = PF_STAGES * A_STAGE;
+    __host__ __device__ static uint32_t b_ring(uint32_t D) { return (D + 2) * PF_B_BYTES; }
+    __host__ __device__ static uint32_t raw_bytes(uint32_t D) { return (D + 1) * NMAT * 128 * 32; }         // [slot][matrix][thread][32 B]
+    // metadata tiles: per matrix 128 rows x 2 G halves in the A' layout (16 x 2 G / 8 core matrices of 128 B)
+    static uint32_t meta_bytes(uint32_t G) { return NMAT * 128 * 2 * G * 2; }
+    static uint32_t total(uint32_t G, uint32_t D) { return A_RING + b_ring(D) + raw_bytes(D) + meta_bytes(G) + 1024; }   // + alignment slack
 };
 
 // Grid: (weight-row tiles of 128, tiles of the list). See the file header for the roles.
-template <int NMAT, bool META_F16>
+// bsrc: FP16 token rows [.., K]; bsum: their group sums [.., 4 G] (pf_sums_kernel).
+template <int NMAT, bool META_F16, int D>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const PfTile* __restrict__ tiles, const int32_t* __restrict__ ntiles,
-                                                                 const __half* __restrict__ bsrc, __half* __restrict__ hdst) {
+                                                                 const __half* __restrict__ bsrc, const __half* __restrict__ bsum,
+                                                                 __half* __restrict__ hdst) {
     using S = PfSmem<NMAT>;
+    constexpr uint32_t PF_RAW = D + 1, PF_BS = D + 2;
     extern __shared__ uint8_t pf_raw_smem[];
-    __shared__ __align__(8) uint64_t full_bar[3], done_bar[3], accum_bar;     // indexed by stage % 3
+    __shared__ __align__(8) uint64_t full_bar[PF_STAGES], done_bar[PF_STAGES], acc_full[PF_ACC], acc_free[PF_ACC], meta_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile uint32_t abort_flag;
-    __shared__ const __half* brow[PF_NMAX];       // source row of each token row of the tile
+    __shared__ uint32_t brow[PF_NMAX];            // source row index of each token row of the tile
     __shared__ long long drow[PF_NMAX];           // destination element offset of each token row
     if (blockIdx.y >= uint32_t(*ntiles)) return;
     const PfTile tile = tiles[blockIdx.y];
-    const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64, nst = G;
+    const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
+    // K stages, then the correction stages: K' = 2 G in blocks of at most 64, each as a hi and a lo term
+    const uint32_t kb = 2 * G < 64 ? 2 * G : 64, nblk = 2 * G / kb, nst = G + 2 * nblk;
     const uint32_t N = uint32_t(tile.rows), Npad = (N + 15) & ~15u;
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t r0 = blockIdx.x * PF_M;
     const uint32_t base = (pf_smem(pf_raw_smem) + 1023) & ~1023u;
-    const uint32_t b_ring = base + S::A_RING, raw_base = b_ring + S::B_RING, meta_base = raw_base + S::RAW;
+    const uint32_t b_ring = base + S::A_RING, raw_base = b_ring + S::b_ring(D), meta_base = raw_base + S::raw_bytes(D);
+    const uint32_t meta_sbo = (2 * G / 8) * 128, meta_tile = 128 * 2 * G * 2;      // A' tile of one matrix
     const uint8_t* record = tile.shared ? c.shared_record : c.records + size_t(uint32_t(tile.expert) - c.first_expert) * c.record_stride;
 
     // ---- set-up ----------------------------------------------------------------------------------
     if (tid == 0) {
-        for (int i = 0; i < 3; ++i) { mbar_init(&full_bar[i], 128); mbar_init(&done_bar[i], 1); }
-        mbar_init(&accum_bar, 1);
+        for (uint32_t i = 0; i < PF_STAGES; ++i) { mbar_init(&full_bar[i], 4); mbar_init(&done_bar[i], 1); }
+        for (uint32_t i = 0; i < PF_ACC; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_free[i], 8); }
+        mbar_init(&meta_bar, 4);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < N) {
         const uint32_t i = uint32_t(tile.row0) + tid;
         if (tile.shared) {
-            brow[tid] = bsrc + (NMAT == 2 ? size_t(i) * K : (size_t(c.T) * c.K + i) * K);
+            brow[tid] = NMAT == 2 ? i : c.T * c.K + i;
             drow[tid] = NMAT == 2 ? (long long)(size_t(c.T) * c.K + i) * c.F : (long long)i * c.H;
         } else {
             const uint32_t pos = uint32_t(c.offsets[tile.expert]) + i, slot = uint32_t(c.perm[pos]);
-            brow[tid] = bsrc + (NMAT == 2 ? size_t(slot / c.K) * K : size_t(pos) * K);
+            brow[tid] = NMAT == 2 ? slot / c.K : pos;
             drow[tid] = NMAT == 2 ? (long long)pos * c.F : (long long)slot * c.H;
         }
     }
     uint32_t ncols = 32;
-    while (ncols < NMAT * Npad) ncols <<= 1;
+    while (ncols < PF_ACC * NMAT * Npad) ncols <<= 1;     // PF_ACC accumulator buffers of NMAT x Npad columns
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pf_smem(&tmem_base_s)), "r"(ncols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -244,150 +284,219 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
     uint32_t* status = c.status;
+    const Projection pr[2] = {NMAT == 2 ? c.gate : c.down, c.up};
 
     if (warp < 4) {
         // ---- producers -----------------------------------------------------------------------------
         const uint32_t r = tid;                                   // weight row of the tile
-        const Projection pr[2] = {NMAT == 2 ? c.gate : c.down, c.up};
-        const uint8_t* codes[NMAT]; const uint8_t* scales[NMAT]; const uint8_t* biases[NMAT];
+        const uint8_t* codes[NMAT];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) codes[m] = record + pr[m].codes + size_t(r0 + r) * (K / 2);
+        // metadata of row r -> A' tiles [s_0..s_G-1 | b_0..b_G-1] as FP16, core-matrix layout
 #pragma unroll
         for (int m = 0; m < NMAT; ++m) {
-            codes[m] = record + pr[m].codes + size_t(r0 + r) * (K / 2);
-            scales[m] = record + pr[m].scales + size_t(r0 + r) * G * 2;
-            biases[m] = record + pr[m].biases + size_t(r0 + r) * G * 2;
+            const uint8_t* sc = record + pr[m].scales + size_t(r0 + r) * G * 2;
+            const uint8_t* bi = record + pr[m].biases + size_t(r0 + r) * G * 2;
+            const uint32_t dst = meta_base + m * meta_tile + (r / 8) * meta_sbo + (r % 8) * 16;
+            for (uint32_t ch = 0; ch < G / 8; ++ch) {
+                if (META_F16) {
+                    pf_cp16(dst + ch * 128, sc + ch * 16);
+                    pf_cp16(dst + (G / 8 + ch) * 128, bi + ch * 16);
+                } else {
+                    const uint4 a = *reinterpret_cast<const uint4*>(sc + ch * 16), b = *reinterpret_cast<const uint4*>(bi + ch * 16);
+                    const uint32_t ra[4] = {a.x, a.y, a.z, a.w}, rb[4] = {b.x, b.y, b.z, b.w};
+                    uint32_t ha[4], hb[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __half2 x = __floats2half2_rn(__uint_as_float(ra[i] << 16), __uint_as_float(ra[i] & 0xffff0000u));
+                        const __half2 y = __floats2half2_rn(__uint_as_float(rb[i] << 16), __uint_as_float(rb[i] & 0xffff0000u));
+                        ha[i] = *reinterpret_cast<const uint32_t*>(&x); hb[i] = *reinterpret_cast<const uint32_t*>(&y);
+                    }
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + ch * 128), "r"(ha[0]), "r"(ha[1]), "r"(ha[2]), "r"(ha[3]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (G / 8 + ch) * 128), "r"(hb[0]), "r"(hb[1]), "r"(hb[2]), "r"(hb[3]) : "memory");
+                }
+            }
         }
-        auto issue_raw = [&](uint32_t ks) {          // packed codes (and, for even groups, metadata of two groups)
-            if (ks >= nst) return;
+        auto issue_raw = [&](uint32_t ks) {          // packed codes of group ks
+            if (ks >= G) return;
             const uint32_t slot = ks % PF_RAW;
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
                 const uint32_t dst = raw_base + ((slot * NMAT + m) * 128 + r) * 32;
                 pf_cp16(dst, codes[m] + ks * 32);
                 pf_cp16(dst + 16, codes[m] + ks * 32 + 16);
-                if ((ks & 1) == 0) {
-                    const uint32_t md = meta_base + (((ks / 2) % PF_RAW * NMAT + m) * 128 + r) * 8;
-                    pf_cp4(md, scales[m] + ks * 2);
-                    pf_cp4(md + 4, biases[m] + ks * 2);
-                }
             }
         };
-        auto issue_b = [&](uint32_t ks) {            // token rows of stage ks, 16-byte pieces straight into the tile
+        // token rows of stage ks, 16-byte pieces straight into the tile: 64 k of the rows for a K stage, the 2 G
+        // group sums (hi for stage G, lo for stage G+1) for a correction stage
+        auto issue_b = [&](uint32_t ks) {
             if (ks >= nst) return;
-            const uint32_t bs = b_ring + (ks % S::SB) * PF_B_BYTES;
-            for (uint32_t q = tid; q < N * 8; q += 128) {
-                const uint32_t j = q / 8, kc = q % 8;
-                pf_cp16(bs + (j / 8) * 1024 + kc * 128 + (j % 8) * 16, brow[j] + ks * 64 + kc * 8);
+            const uint32_t bs = b_ring + (ks % PF_BS) * PF_B_BYTES;
+            const bool main = ks < G;
+            const uint32_t chunks = main ? 8 : kb / 8;
+            const uint32_t term = main ? 0 : (ks - G) / nblk, blk = main ? 0 : (ks - G) % nblk;     // hi / lo, block of K'
+            for (uint32_t q = tid; q < N * chunks; q += 128) {
+                const uint32_t j = q / chunks, kc = q % chunks;
+                const __half* src = main ? bsrc + size_t(brow[j]) * K + ks * 64 + kc * 8
+                                         : bsum + size_t(brow[j]) * 4 * G + term * 2 * G + blk * kb + kc * 8;
+                pf_cp16(bs + (j / 8) * (chunks * 128) + kc * 128 + (j % 8) * 16, src);
             }
         };
         bool ok = true;
-        issue_b(0); issue_raw(0); issue_raw(1); issue_raw(2);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        issue_b(1);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        // done_bar[j % 3] completes phase j / 3 when the MMAs of stage j have drained.
-        auto stage_done = [&](uint32_t j) { return mbar_wait(&done_bar[j % 3], (j / 3) & 1, &abort_flag, status); };
-        for (uint32_t ks = 0; ks < nst && ok; ++ks) {
-            // codes and token rows of stage ks were committed at least two groups ago
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-            // the A buffer of this stage was last read by stage ks - SA
-            if (ks >= S::SA) ok = stage_done(ks - S::SA);
-            if (!ok) break;
-            const uint32_t as = base + (ks % S::SA) * S::A_STAGE;
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
-                const uint32_t src = raw_base + (((ks % PF_RAW) * NMAT + m) * 128 + r) * 32;
-                const uint32_t md = meta_base + (((ks / 2) % PF_RAW * NMAT + m) * 128 + r) * 8 + (ks & 1) * 2;
-                uint4 w0, w1;
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(src));
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(src + 16));
-                uint16_t sb, bb;
-                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sb) : "r"(md));
-                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(bb) : "r"(md + 4));
-                __half sh, bh;
-                if (META_F16) { sh = __ushort_as_half(sb); bh = __ushort_as_half(bb); }
-                else { sh = __float2half_rn(bf_to_float(sb)); bh = __float2half_rn(bf_to_float(bb)); }
-                const __half shi = __ushort_as_half(uint16_t(__half_as_ushort(sh) & 0xffe0u));     // top 6 significant bits
-                const __half slo = __hsub(sh, shi);                                                 // exact
-                const __half res = __hfma(sh, __float2half_rn(8.0f), bh);                           // b + 8 s
-                const __half2 s_hi = __half2half2(shi), s_lo = __half2half2(slo), resid = __half2half2(res);
-                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                const uint32_t dst = as + m * 2 * PF_A_BYTES + (r / 8) * 1024 + (r % 8) * 16;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    uint4 hi, lo;
-                    pf_dequant_word(words[i], s_hi, s_lo, resid, hi, lo);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + i * 128), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + PF_A_BYTES + i * 128), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&full_bar[ks % 3]);
-            // The B buffer of stage ks+2 was last read by stage ks-1, whose MMAs ran while this stage was
-            // being dequantised: wait for them, then start the copies of stage ks+2 and the codes of ks+3.
-            if (ks >= 1 && ks + 2 < nst) ok = stage_done(ks - 1);
-            if (!ok) break;
-            issue_b(ks + 2);
-            issue_raw(ks + 3);
+        // prologue: copy group j holds the token rows and the codes of stage j (group 0 also the metadata)
+#pragma unroll 1
+        for (uint32_t j = 0; j < uint32_t(D); ++j) {
+            issue_b(j); issue_raw(j);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-
-        // ---- epilogue: TMEM lane 32*warp + lane is weight row r; columns are the tile's tokens --------
-        if (ok) ok = mbar_wait(&accum_bar, 0, &abort_flag, status);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-            const uint32_t lane_addr = tmem_base + ((warp * 32) << 16);
-            const uint32_t row = r0 + r;
-            float* out_base = tile.shared ? c.shared_out : c.expert_out;
-            for (uint32_t c0 = 0; c0 < Npad; c0 += 16) {
-                uint32_t a[16], b[16];
-                tmem_ld16(lane_addr + c0, a);
-                if constexpr (NMAT == 2) tmem_ld16(lane_addr + Npad + c0, b);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // done_bar[j % PF_STAGES] completes phase j / PF_STAGES when the MMAs of stage j have drained.
+        auto stage_done = [&](uint32_t j) { return mbar_wait(&done_bar[j % PF_STAGES], (j / PF_STAGES) & 1, &abort_flag, status); };
+        for (uint32_t ks = 0; ks < nst && ok; ++ks) {
+            // group ks (token rows and codes of this stage) is complete when at most D - 1 later groups are pending
+            asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
+            // the A buffer of this stage was last read by stage ks - PF_STAGES; MMAs complete in order, so every
+            // earlier stage has drained too and the B slot of stage ks + D (last used by stage ks - 2) is free
+            if (ks >= PF_STAGES) ok = stage_done(ks - PF_STAGES);
+            ok = __all_sync(0xffffffffu, ok);          // warp-uniform: the hand-over below synchronises the warp
+            if (!ok) break;
+            issue_b(ks + D);
+            issue_raw(ks + D);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (ks < G) {
+                const uint32_t as = base + (ks % PF_STAGES) * S::A_STAGE;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint32_t t = c0 + j;
-                    if (t < N) {
-                        const float g = __uint_as_float(a[j]);
-                        if constexpr (NMAT == 2) {
-                            const float u = __uint_as_float(b[j]);
-                            const float h = (g * sigmoid_f(g)) * u;
-                            hdst[drow[t] + (row & ~7u) + pf_pos8(row & 7)] = __float2half_rn(h);
-                        } else {
-                            out_base[drow[t] + row] = g;
-                        }
+                for (int m = 0; m < NMAT; ++m) {
+                    const uint32_t src = raw_base + (((ks % PF_RAW) * NMAT + m) * 128 + r) * 32;
+                    uint4 w0, w1;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(src));
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(src + 16));
+                    const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                    const uint32_t dst = as + m * PF_A_BYTES + (r / 8) * 1024 + (r % 8) * 16;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint4 v = pf_dequant_word(words[i]);
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + i * 128), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
                     }
                 }
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // one arrival per warp: 128 arrivals on one barrier would serialise in shared memory
+            __syncwarp();
+            if (lane == 0) {
+                if (ks == 0) mbar_arrive(&meta_bar);      // one-shot: the metadata tiles (first copy group) are in place
+                mbar_arrive(&full_bar[ks % PF_STAGES]);
+            }
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (warp == 4) {
         // ---- MMA issue: one lane of warp 4 ------------------------------------------------------------
         if (lane == 0) {
             // instruction descriptor: D = F32, A = B = F16, both K-major, N = Npad, M = 128
             const uint32_t idesc = (1u << 4) | ((Npad >> 3) << 17) | ((PF_M >> 4) << 24);
             bool ok = true;
             for (uint32_t ks = 0; ks < nst; ++ks) {
-                ok = mbar_wait(&full_bar[ks % 3], (ks / 3) & 1, &abort_flag, status);
+                ok = mbar_wait(&full_bar[ks % PF_STAGES], (ks / PF_STAGES) & 1, &abort_flag, status);
+                if (ok && ks >= PF_ACC) ok = mbar_wait(&acc_free[ks % PF_ACC], ((ks / PF_ACC) - 1) & 1, &abort_flag, status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t as = base + (ks % S::SA) * S::A_STAGE, bs = b_ring + (ks % S::SB) * PF_B_BYTES;
+                const uint32_t bs = b_ring + (ks % PF_BS) * PF_B_BYTES;
+                const uint32_t acc = tmem_base + (ks % PF_ACC) * NMAT * Npad;
+                if (ks < G) {
+                    const uint32_t as = base + (ks % PF_STAGES) * S::A_STAGE;
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t bdesc = umma_desc(bs + kk * 256);
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t bdesc = umma_desc(bs + kk * 256);
 #pragma unroll
-                    for (int m = 0; m < NMAT; ++m) {
-                        umma_f16(tmem_base + m * Npad, umma_desc(as + (m * 2 + 0) * PF_A_BYTES + kk * 256), bdesc, idesc, (ks | kk) != 0);
-                        umma_f16(tmem_base + m * Npad, umma_desc(as + (m * 2 + 1) * PF_A_BYTES + kk * 256), bdesc, idesc, 1);
+                        for (int m = 0; m < NMAT; ++m) umma_f16(acc + m * Npad, umma_desc(as + m * PF_A_BYTES + kk * 256), bdesc, idesc, kk != 0);
+                    }
+                } else {
+                    const uint32_t blk = (ks - G) % nblk;
+                    for (uint32_t kk = 0; kk < kb / 16; ++kk) {
+                        const uint64_t bdesc = umma_desc(bs + kk * 256, (kb / 8) * 128);
+#pragma unroll
+                        for (int m = 0; m < NMAT; ++m)
+                            umma_f16(acc + m * Npad, umma_desc(meta_base + m * meta_tile + blk * (kb / 8) * 128 + kk * 256, meta_sbo), bdesc, idesc, kk != 0);
                     }
                 }
-                umma_commit(&done_bar[ks % 3]);
+                umma_commit(&done_bar[ks % PF_STAGES]);
+                umma_commit(&acc_full[ks % PF_ACC]);
             }
-            if (ok) umma_commit(&accum_bar);
         }
         __syncwarp();
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    } else {
+        // ---- epilogue: TMEM lane 32 * (warp mod 4) + lane is weight row r; columns are the tile's tokens. Two
+        // warps share a lane quadrant: set 0 takes the 16-column chunks 0 and 2, set 1 the chunks 1 and 3. ----
+        const uint32_t r = (warp % 4) * 32 + lane, set = (warp - 5) / 4;
+        const uint32_t lane_addr = tmem_base + (((warp % 4) * 32) << 16);
+        float acc[NMAT][2][16];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[m][h][j] = 0.0f;
+        bool ok = true;
+        // the metadata tiles are written by the producers (cp.async): wait for their one-shot barrier
+        ok = __all_sync(0xffffffffu, mbar_wait(&meta_bar, 0, &abort_flag, status));
+        for (uint32_t ks = 0; ks < nst && ok; ++ks) {
+            float scale[NMAT];
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+                scale[m] = 1.0f;
+                if (ks < G) {
+                    uint16_t bits;
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(bits) : "r"(meta_base + m * meta_tile + (r / 8) * meta_sbo + (ks / 8) * 128 + (r % 8) * 16 + (ks % 8) * 2));
+                    scale[m] = __half2float(__ushort_as_half(bits));
+                }
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[ks % PF_ACC], (ks / PF_ACC) & 1, &abort_flag, status));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t buf = lane_addr + (ks % PF_ACC) * NMAT * Npad;
+            uint32_t d[NMAT][2][16];
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t c0 = (2 * h + set) * 16;
+                    if (c0 < Npad) tmem_ld16(buf + m * Npad + c0, d[m][h]);
+                }
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_free[ks % PF_ACC]);
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if ((2 * h + set) * 16 < Npad) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc[m][h][j] = __fmaf_rn(scale[m], __uint_as_float(d[m][h][j]), acc[m][h][j]);
+                    }
+                }
+        }
+        if (ok) {
+            const uint32_t row = r0 + r;
+            float* out_base = tile.shared ? c.shared_out : c.expert_out;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint32_t t = (2 * h + set) * 16 + j;
+                    if (t < N) {
+                        const float g = acc[0][h][j];
+                        if constexpr (NMAT == 2) {
+                            const float u = acc[NMAT - 1][h][j];
+                            const float hv = (g * sigmoid_f(g)) * u;
+                            hdst[drow[t] + (row & ~7u) + pf_pos8(row & 7)] = __float2half_rn(hv);
+                        } else {
+                            out_base[drow[t] + row] = g;
+                        }
+                    }
+                }
+        }
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 4) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -395,20 +504,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
     }
 }
 
-template <int NMAT, bool META_F16>
-int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, cudaStream_t s) {
+template <int NMAT, bool META_F16, int D>
+int launch_prefill_d(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, size_t smem, cudaStream_t s) {
     const uint32_t N = NMAT == 2 ? c.F : c.H;
-    if (N % PF_M) return fail(m, ZC_EINVAL, "prefill kernel: rows not a multiple of 128");
-    auto kernel = prefill_kernel<NMAT, META_F16>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PfSmem<NMAT>::TOTAL)) != cudaSuccess)
+    auto kernel = prefill_kernel<NMAT, META_F16, D>;
+    static size_t configured = 0;
+    if (smem > configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
             return check_launch(m, "prefill kernel attribute");
-        configured = true;
+        configured = smem;
     }
     Timed t(m, s, NMAT == 2 ? KERNEL_PREFILL_GATE_UP : KERNEL_PREFILL_DOWN);
-    kernel<<<dim3(N / PF_M, m->pf_max_tiles), PF_THREADS, PfSmem<NMAT>::TOTAL, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, m->hbuf16);
+    kernel<<<dim3(N / PF_M, m->pf_max_tiles), PF_THREADS, smem, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, bsum, m->hbuf16);
     return check_launch(m, NMAT == 2 ? "prefill gate_up" : "prefill down");
+}
+
+template <int NMAT, bool META_F16>
+int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, cudaStream_t s) {
+    const uint32_t N = NMAT == 2 ? c.F : c.H, K = NMAT == 2 ? c.H : c.F, G = K / 64;
+    if (N % PF_M) return fail(m, ZC_EINVAL, "prefill kernel: rows not a multiple of 128");
+    if (G % 8) return fail(m, ZC_EINVAL, "prefill kernel: K must be a multiple of 512");
+    const size_t limit = 227 * 1024;
+    if (PfSmem<NMAT>::total(G, 6) <= limit) return launch_prefill_d<NMAT, META_F16, 6>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 6), s);
+    if (PfSmem<NMAT>::total(G, 3) <= limit) return launch_prefill_d<NMAT, META_F16, 3>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 3), s);
+    return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
 }
 
 }  // namespace
@@ -422,7 +541,7 @@ size_t prefill_tile_bytes() { return sizeof(PfTile); }
 bool prefill_supported(const zc_moe_desc& d) {
     // BF16 activations convert to FP16 exactly; an FP32 activation would need a second FP16 term.
     return d.gate_bits == 4 && d.up_bits == 4 && d.down_bits == 4 && d.arith == ZC_ARITH_FP32 && d.act_dtype == ZC_BF16 &&
-           d.ffn % 128 == 0 && d.hidden % 128 == 0;
+           d.ffn % 512 == 0 && d.hidden % 512 == 0 && d.hidden <= 4096;
 }
 
 // tile list -> FP16 activations -> gate/up (+SwiGLU) -> down. Routing must already be in place.
@@ -440,11 +559,22 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
         pf_prepare_x_kernel<<<unsigned((blocks + 255) / 256), 256, 0, s>>>(c.x, c.act_dtype, m->xp, blocks);
         if ((rc = check_launch(m, "prefill activations")) < 0) return rc;
     }
-    rc = c.meta_f16 ? launch_prefill<2, true>(m, c, m->xp, s) : launch_prefill<2, false>(m, c, m->xp, s);
+    {
+        Timed t(m, s, KERNEL_PREFILL_PREP);
+        pf_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(m->xp, c.T, c.H, m->xsum);
+        if ((rc = check_launch(m, "prefill activation sums")) < 0) return rc;
+    }
+    rc = c.meta_f16 ? launch_prefill<2, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, false>(m, c, m->xp, m->xsum, s);
     if (rc < 0) return rc;
-    rc = c.meta_f16 ? launch_prefill<1, true>(m, c, m->hbuf16, s) : launch_prefill<1, false>(m, c, m->hbuf16, s);
+    {
+        Timed t(m, s, KERNEL_PREFILL_PREP);
+        const uint32_t rows = c.T * c.K + c.T;
+        pf_sums_kernel<<<(rows * 32 + 255) / 256, 256, 0, s>>>(m->hbuf16, rows, c.F, m->hsum);
+        if ((rc = check_launch(m, "prefill intermediate sums")) < 0) return rc;
+    }
+    rc = c.meta_f16 ? launch_prefill<1, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, false>(m, c, m->hbuf16, m->hsum, s);
     if (rc < 0) return rc;
-    return 4;
+    return 6;
 }
 
 }  // namespace zc

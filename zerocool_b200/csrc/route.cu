@@ -182,7 +182,13 @@ __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots,
 #pragma unroll
         for (int q = 0; q < PERMUTE_CACHE; ++q) if (begin + 32 * q < end) count_chunk(begin + 32 * q + lane, cached[q]);
     } else {
-        for (uint32_t base = begin; base < end; base += 32) count_chunk(base + lane, base + lane < end ? __ldcg(ids + base + lane) : -1);
+        for (uint32_t blk = begin; blk < end; blk += 32 * PERMUTE_CACHE) {      // four loads in flight per lane
+            int32_t v[PERMUTE_CACHE];
+#pragma unroll
+            for (int q = 0; q < PERMUTE_CACHE; ++q) { const uint32_t p = blk + 32 * q + lane; v[q] = p < end ? __ldcg(ids + p) : -1; }
+#pragma unroll
+            for (int q = 0; q < PERMUTE_CACHE; ++q) if (blk + 32 * q < end) count_chunk(blk + 32 * q + lane, v[q]);
+        }
     }
     if (bad) atomicOr(status, ZC_STATUS_INVALID_ROUTE);
     __syncthreads();
@@ -238,7 +244,13 @@ __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots,
 #pragma unroll
         for (int q = 0; q < PERMUTE_CACHE; ++q) if (begin + 32 * q < end) place_chunk(begin + 32 * q + lane, cached[q]);
     } else {
-        for (uint32_t base = begin; base < end; base += 32) place_chunk(base + lane, base + lane < end ? __ldcg(ids + base + lane) : -1);
+        for (uint32_t blk = begin; blk < end; blk += 32 * PERMUTE_CACHE) {
+            int32_t v[PERMUTE_CACHE];
+#pragma unroll
+            for (int q = 0; q < PERMUTE_CACHE; ++q) { const uint32_t p = blk + 32 * q + lane; v[q] = p < end ? __ldcg(ids + p) : -1; }
+#pragma unroll
+            for (int q = 0; q < PERMUTE_CACHE; ++q) if (blk + 32 * q < end) place_chunk(blk + 32 * q + lane, v[q]);
+        }
     }
 }
 
@@ -298,6 +310,10 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
     if (c.E % 32 || c.E > 1024) return fail(m, ZC_EINVAL, "route: experts must be a multiple of 32, at most 1024");
     if (c.K > 32) return fail(m, ZC_EINVAL, "route: top_k above 32");
     const size_t hist_bytes = size_t(PERMUTE_THREADS / 32) * c.E * sizeof(int32_t);
+    // Long batches: the permutation runs as its own launch of 1024 threads instead of as the tail of one 256-thread
+    // routing CTA (20480 slots at 2048 tokens).
+    const bool separate = do_route && do_permute && size_t(c.T) * c.K > 4096;
+    if (separate) do_permute = false;
     if (do_route) {
         RouteArgs a{};
         a.logits = c.logits;
@@ -324,7 +340,8 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
         }
         if (rc < 0) return rc;
         ++launched;
-    } else if (do_permute) {
+    }
+    if (separate || (!do_route && do_permute)) {
         static bool configured = false;
         if (!configured) {
             cudaFuncSetAttribute(permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
