@@ -70,7 +70,14 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait. Returns false (and raises the abort flag) when the phase did not complete in time or
 // another role has already given up.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {       // non-blocking probe
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(pf_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
+    if (mbar_test(bar, parity)) return true;          // the common case in a pipeline that runs ahead
     for (uint32_t i = 0; i < PF_POLL_LIMIT; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
@@ -206,9 +213,6 @@ __global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, ui
 __device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void pf_cp4(uint32_t dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
 
 constexpr uint32_t PF_STAGES = 2;      // A stage buffers (written by the producers, read by the MMAs)
 // Prefetch distance D (template parameter of the kernel): the packed codes and the token rows of stage ks + D are
@@ -250,6 +254,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t r0 = blockIdx.x * PF_M;
     const uint32_t base = (pf_smem(pf_raw_smem) + 1023) & ~1023u;
+    uint8_t* const sm = pf_raw_smem + (base - pf_smem(pf_raw_smem));       // the same place as a generic pointer
+    auto at = [&](uint32_t shared_addr) { return sm + (shared_addr - base); };
     const uint32_t b_ring = base + S::A_RING, raw_base = b_ring + S::b_ring(D), meta_base = raw_base + S::raw_bytes(D);
     const uint32_t meta_sbo = (2 * G / 8) * 128, meta_tile = 128 * 2 * G * 2;      // A' tile of one matrix
     const uint8_t* record = tile.shared ? c.shared_record : c.records + size_t(uint32_t(tile.expert) - c.first_expert) * c.record_stride;
@@ -317,6 +323,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
                 }
             }
         }
+        // K stages: this thread's pieces of the token rows, addresses prepared once (q = tid + 128 i: row q / 8, chunk q % 8)
+        const __half* bsrc_i[PF_NMAX * 8 / 128];
+        uint32_t bdst_i[PF_NMAX * 8 / 128];
+#pragma unroll
+        for (int i = 0; i < PF_NMAX * 8 / 128; ++i) {
+            const uint32_t q = tid + 128 * i, j = q / 8, kc = q % 8;
+            bsrc_i[i] = j < N ? bsrc + size_t(brow[j]) * K + kc * 8 : nullptr;
+            bdst_i[i] = (j / 8) * 1024 + kc * 128 + (j % 8) * 16;
+        }
         auto issue_raw = [&](uint32_t ks) {          // packed codes of group ks
             if (ks >= G) return;
             const uint32_t slot = ks % PF_RAW;
@@ -333,7 +348,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
             if (ks >= nst) return;
             const uint32_t bs = b_ring + (ks % PF_BS) * PF_B_BYTES;
             const bool main = ks < G;
-            const uint32_t chunks = main ? 8 : kb / 8;
+            if (main) {
+#pragma unroll
+                for (int i = 0; i < PF_NMAX * 8 / 128; ++i) if (bsrc_i[i]) pf_cp16(bs + bdst_i[i], bsrc_i[i] + ks * 64);
+                return;
+            }
+            const uint32_t chunks = kb / 8;
             const uint32_t term = main ? 0 : (ks - G) / nblk, blk = main ? 0 : (ks - G) % nblk;     // hi / lo, block of K'
             for (uint32_t q = tid; q < N * chunks; q += 128) {
                 const uint32_t j = q / chunks, kc = q % chunks;
@@ -367,15 +387,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
                     const uint32_t src = raw_base + (((ks % PF_RAW) * NMAT + m) * 128 + r) * 32;
-                    uint4 w0, w1;
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(src));
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(src + 16));
+                    const uint4 w0 = *reinterpret_cast<const uint4*>(at(src)), w1 = *reinterpret_cast<const uint4*>(at(src + 16));
                     const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
                     const uint32_t dst = as + m * PF_A_BYTES + (r / 8) * 1024 + (r % 8) * 16;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const uint4 v = pf_dequant_word(words[i]);
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + i * 128), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                        *reinterpret_cast<uint4*>(at(dst + i * 128)) = v;
                     }
                 }
             }
@@ -393,6 +411,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
         if (lane == 0) {
             // instruction descriptor: D = F32, A = B = F16, both K-major, N = Npad, M = 128
             const uint32_t idesc = (1u << 4) | ((Npad >> 3) << 17) | ((PF_M >> 4) << 24);
+            const uint64_t desc0 = umma_desc(base);
             bool ok = true;
             for (uint32_t ks = 0; ks < nst; ++ks) {
                 ok = mbar_wait(&full_bar[ks % PF_STAGES], (ks / PF_STAGES) & 1, &abort_flag, status);
@@ -402,12 +421,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
                 const uint32_t bs = b_ring + (ks % PF_BS) * PF_B_BYTES;
                 const uint32_t acc = tmem_base + (ks % PF_ACC) * NMAT * Npad;
                 if (ks < G) {
-                    const uint32_t as = base + (ks % PF_STAGES) * S::A_STAGE;
+                    // descriptors differ from desc0 only in the start address field (bits 0-13, units of 16 bytes)
+                    const uint64_t adesc = desc0 + (((ks % PF_STAGES) * S::A_STAGE) >> 4), bdesc = desc0 + ((S::A_RING + (ks % PF_BS) * PF_B_BYTES) >> 4);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t bdesc = umma_desc(bs + kk * 256);
 #pragma unroll
-                        for (int m = 0; m < NMAT; ++m) umma_f16(acc + m * Npad, umma_desc(as + m * PF_A_BYTES + kk * 256), bdesc, idesc, kk != 0);
+                        for (int m = 0; m < NMAT; ++m) umma_f16(acc + m * Npad, adesc + ((m * PF_A_BYTES + kk * 256) >> 4), bdesc + ((kk * 256) >> 4), idesc, kk != 0);
                     }
                 } else {
                     const uint32_t blk = (ks - G) % nblk;
@@ -444,9 +463,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const Pf
             for (int m = 0; m < NMAT; ++m) {
                 scale[m] = 1.0f;
                 if (ks < G) {
-                    uint16_t bits;
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(bits) : "r"(meta_base + m * meta_tile + (r / 8) * meta_sbo + (ks / 8) * 128 + (r % 8) * 16 + (ks % 8) * 2));
-                    scale[m] = __half2float(__ushort_as_half(bits));
+                    scale[m] = __half2float(*reinterpret_cast<const __half*>(at(meta_base + m * meta_tile + (r / 8) * meta_sbo + (ks / 8) * 128 + (r % 8) * 16 + (ks % 8) * 2)));
                 }
             }
             ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[ks % PF_ACC], (ks / PF_ACC) & 1, &abort_flag, status));
