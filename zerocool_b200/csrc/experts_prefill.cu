@@ -234,7 +234,7 @@ struct PfSmem {
 // Grid: (weight-row tiles of 128, tiles of the list). See the file header for the roles.
 // bsrc: FP16 token rows [.., K]; bsum: their group sums [.., 4 G] (pf_sums_kernel).
 template <int NMAT, bool META_F16, int D>
-__global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(Call c, const PfTile* __restrict__ tiles, const int32_t* __restrict__ ntiles,
+__global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(Call c, const PfTile* __restrict__ tiles, const int32_t* __restrict__ ntiles,
                                                                  const __half* __restrict__ bsrc, const __half* __restrict__ bsum,
                                                                  __half* __restrict__ hdst) {
     using S = PfSmem<NMAT>;
@@ -542,6 +542,9 @@ int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* b
     if (N % PF_M) return fail(m, ZC_EINVAL, "prefill kernel: rows not a multiple of 128");
     if (G % 8) return fail(m, ZC_EINVAL, "prefill kernel: K must be a multiple of 512");
     const size_t limit = 227 * 1024;
+    // down: its K is short (ten stages per CTA), so the fixed cost of a CTA matters: a shallower ring lets two CTAs
+    // share an SM (shared memory and 256 TMEM columns each) and overlap one's set-up with the other's loop
+    if (NMAT == 1 && 2 * (PfSmem<NMAT>::total(G, 3) + 1024) <= limit) return launch_prefill_d<NMAT, META_F16, 3>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 3), s);
     if (PfSmem<NMAT>::total(G, 6) <= limit) return launch_prefill_d<NMAT, META_F16, 6>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 6), s);
     if (PfSmem<NMAT>::total(G, 3) <= limit) return launch_prefill_d<NMAT, META_F16, 3>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 3), s);
     return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
