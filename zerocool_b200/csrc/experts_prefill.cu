@@ -214,17 +214,17 @@ __device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-constexpr uint32_t PF_STAGES = 2;      // A stage buffers (written by the producers, read by the MMAs)
+constexpr uint32_t PF_STAGES = 3;      // A stage buffers (written by the producers, read by the MMAs): the producers may run two stages ahead
 // Prefetch distance D (template parameter of the kernel): the packed codes and the token rows of stage ks + D are
 // requested while stage ks is dequantised, so that D stages of work (a few thousand cycles) cover the memory
-// latency. Token-row (B) ring: D + 2 slots; per-thread ring of packed codes: D + 1 slots.
+// latency. Token-row (B) ring: D + PF_STAGES slots; per-thread ring of packed codes: D + 1 slots.
 
 // Shared memory of one CTA (dynamic, 1024-byte aligned for the tile buffers).
 template <int NMAT>
 struct PfSmem {
     static constexpr uint32_t A_STAGE = NMAT * PF_A_BYTES;
     static constexpr uint32_t A_RING = PF_STAGES * A_STAGE;
-    __host__ __device__ static uint32_t b_ring(uint32_t D) { return (D + 2) * PF_B_BYTES; }
+    __host__ __device__ static uint32_t b_ring(uint32_t D) { return (D + PF_STAGES) * PF_B_BYTES; }
     __host__ __device__ static uint32_t raw_bytes(uint32_t D) { return (D + 1) * NMAT * 128 * 32; }         // [slot][matrix][thread][32 B]
     // metadata tiles: per matrix 128 rows x 2 G halves in the A' layout (16 x 2 G / 8 core matrices of 128 B)
     static uint32_t meta_bytes(uint32_t G) { return NMAT * 128 * 2 * G * 2; }
@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
                                                                  const __half* __restrict__ bsrc, const __half* __restrict__ bsum,
                                                                  __half* __restrict__ hdst) {
     using S = PfSmem<NMAT>;
-    constexpr uint32_t PF_RAW = D + 1, PF_BS = D + 2;
+    constexpr uint32_t PF_RAW = D + 1, PF_BS = D + PF_STAGES;
     extern __shared__ uint8_t pf_raw_smem[];
     __shared__ __align__(8) uint64_t full_bar[PF_STAGES], done_bar[PF_STAGES], acc_full[PF_ACC], acc_free[PF_ACC], meta_bar;
     __shared__ uint32_t tmem_base_s;
@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
             // group ks (token rows and codes of this stage) is complete when at most D - 1 later groups are pending
             asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
             // the A buffer of this stage was last read by stage ks - PF_STAGES; MMAs complete in order, so every
-            // earlier stage has drained too and the B slot of stage ks + D (last used by stage ks - 2) is free
+            // earlier stage has drained too and the B slot of stage ks + D (last used by stage ks - PF_STAGES) is free
             if (ks >= PF_STAGES) ok = stage_done(ks - PF_STAGES);
             ok = __all_sync(0xffffffffu, ok);          // warp-uniform: the hand-over below synchronises the warp
             if (!ok) break;
@@ -544,9 +544,9 @@ int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* b
     const size_t limit = 227 * 1024;
     // down: its K is short (ten stages per CTA), so the fixed cost of a CTA matters: a shallower ring lets two CTAs
     // share an SM (shared memory and 256 TMEM columns each) and overlap one's set-up with the other's loop
-    if (NMAT == 1 && 2 * (PfSmem<NMAT>::total(G, 3) + 1024) <= limit) return launch_prefill_d<NMAT, META_F16, 3>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 3), s);
-    if (PfSmem<NMAT>::total(G, 6) <= limit) return launch_prefill_d<NMAT, META_F16, 6>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 6), s);
-    if (PfSmem<NMAT>::total(G, 3) <= limit) return launch_prefill_d<NMAT, META_F16, 3>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 3), s);
+    if (NMAT == 1 && 2 * (PfSmem<NMAT>::total(G, 2) + 1024) <= limit) return launch_prefill_d<NMAT, META_F16, 2>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 2), s);
+    if (PfSmem<NMAT>::total(G, 4) <= limit) return launch_prefill_d<NMAT, META_F16, 4>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 4), s);
+    if (PfSmem<NMAT>::total(G, 2) <= limit) return launch_prefill_d<NMAT, META_F16, 2>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 2), s);
     return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
 }
 
