@@ -164,7 +164,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     }
     Call& c = m->scratch;
     A(&c.logits, T * E * 4); A(&c.gate_logit, T * 4); A(&c.ids, T * K * 4); A(&c.weights, T * K * 4);
-    A(&c.offsets, (E + 1) * 4); A(&c.perm, T * K * 4); A(&c.active, E * 4); A(&c.counters, (16 + size_t(d.layers)) * 4);
+    A(&c.offsets, (E + 1) * 4); A(&c.perm, T * K * 4); A(&c.active, E * 4); A(&c.items, E * 16); A(&c.counters, (16 + size_t(d.layers)) * 4);
     A(&m->router_partial, 16 * T * size_t(router_rows_padded(d)) * 4);
     const size_t done_n = size_t(router_rows_padded(d) / 32) * ((T + 7) / 8);
     A(&m->router_done, done_n * 4);
@@ -177,6 +177,9 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         uint8_t* tl = nullptr; A(&tl, m->pf_max_tiles * prefill_tile_bytes()); m->pf_tiles = tl;
         A(&m->pf_ntiles, 16);
     } A(&c.expert_out, T * K * H * 4); A(&c.shared_out, T * H * 4); A(&c.status, 16);
+    A(&m->empty_items, E * 16);
+    if (rc == ZC_OK && (e = cudaMemset(m->empty_items, 0xff, E * 16)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+    if (rc == ZC_OK && (e = cudaMemset(c.items, 0xff, E * 16)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
     A(&m->zero_counters, (16 + size_t(d.layers)) * 4);
     if (rc == ZC_OK && (e = cudaMemset(m->zero_counters, 0, (16 + size_t(d.layers)) * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
     if (d.local_experts < d.experts) {
@@ -185,7 +188,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         const size_t R = T * K * ranks;
         m->ep_rows_cap = uint32_t(R);
         Call& q = m->ep;
-        A(&q.offsets, (E + 1) * 4); A(&q.perm, R * 4); A(&q.active, E * 4); A(&q.counters, (16 + size_t(d.layers)) * 4);
+        A(&q.offsets, (E + 1) * 4); A(&q.perm, R * 4); A(&q.active, E * 4); A(&q.items, E * 16); A(&q.counters, (16 + size_t(d.layers)) * 4);
         A(&q.hbuf, R * F * 4);
         if (rc == ZC_OK && (e = cudaMemset(q.counters, 0, (16 + size_t(d.layers)) * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
     }
@@ -207,7 +210,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         Call& q = m->ep;
         const Call keep = q;
         q = c;                                   // geometry and formats
-        q.offsets = keep.offsets; q.perm = keep.perm; q.active = keep.active; q.counters = keep.counters; q.hbuf = keep.hbuf;
+        q.offsets = keep.offsets; q.perm = keep.perm; q.active = keep.active; q.items = keep.items; q.counters = keep.counters; q.hbuf = keep.hbuf;
         q.K = 1; q.has_shared = 0;
     }
     *out = m;
@@ -374,6 +377,7 @@ int zc_moe_ep_combine(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens,
     if ((n = launch_ep_scatter(m, c, y_sorted, s)) < 0) return n; total += n;
     if (c.has_shared) {
         Call sh = c;
+        sh.items = m->empty_items;
         sh.counters = m->zero_counters;          // no routed items: only the shared expert's blocks find work
         if ((n = launch_experts_decode(m, sh, s)) < 0) return n; total += n;
     }

@@ -141,6 +141,7 @@ struct Call {
     int32_t* offsets;         // [E+1]
     int32_t* perm;            // [T*K]
     int32_t* active;          // [E] ascending ids of experts with work
+    int4* items;              // [E] the same list as {expert, first position in perm, rows, 0}; x = -1 past its end
     int32_t* counters;        // [0] number of active experts; [16 + layer] the same, kept per layer
     float* hbuf;              // [T*K + T, F]: rows in permuted slot order, then shared rows
     float* expert_out;        // [T*K, H] by original slot
@@ -171,6 +172,7 @@ struct zc_moe {
     uint32_t* router_done = nullptr;     // arrival counters of the router's (row tile, token tile) pairs
     zc::Call ep{};                       // second scratch set: the experts step of expert parallelism (rows from all ranks)
     uint32_t ep_rows_cap = 0;
+    int4* empty_items = nullptr;         // an item list with no entries (launches that run the shared expert only)
     int32_t* zero_counters = nullptr;    // an always-zero counter block (launches that run the shared expert only)
     float* router_partial = nullptr;     // [16, max_tokens, rows_padded] partition sums of the router
     void* act[2] = {nullptr, nullptr};   // stack ping-pong activations [max_tokens, H]

@@ -113,11 +113,12 @@ __device__ __forceinline__ bool decode_item(const Call& c, uint32_t item, ItemIn
         }
         item -= blocks;
     }
-    if (item >= uint32_t(c.counters[0])) return false;
-    const uint32_t e = uint32_t(c.active[item]);
+    const int4 entry = __ldcg(c.items + item);            // one load: {expert, first position, rows}; x = -1 past the list's end
+    if (entry.x < 0) return false;
+    const uint32_t e = uint32_t(entry.x);
     it.record = c.records + size_t(e - c.first_expert) * c.record_stride;
-    it.pos0 = uint32_t(c.offsets[e]);
-    it.count = uint32_t(c.offsets[e + 1]) - it.pos0;
+    it.pos0 = uint32_t(entry.y);
+    it.count = uint32_t(entry.z);
     it.hrow0 = it.pos0;
     it.shared = false;
     return true;

@@ -25,7 +25,7 @@ struct RouteArgs {
     uint32_t T, E, K;
     uint32_t* status;
     // permutation tail (run by the last CTA to finish when do_permute is set)
-    int32_t* offsets; int32_t* perm; int32_t* active; int32_t* counters; uint32_t* done;
+    int32_t* offsets; int32_t* perm; int32_t* active; int4* items; int32_t* counters; uint32_t* done;
     uint32_t first_expert, local_experts, layer, do_permute;
 };
 
@@ -154,13 +154,14 @@ template <int NT, bool CACHED>
 __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots, uint32_t E,
                                              uint32_t first_expert, uint32_t local_experts,
                                              int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
-                                             int32_t* __restrict__ active, int32_t* __restrict__ counters,
+                                             int32_t* __restrict__ active, int4* __restrict__ items, int32_t* __restrict__ counters,
                                              uint32_t layer, uint32_t* status, int32_t* hist, uint32_t range) {
     constexpr int NW = NT / 32;
     __shared__ unsigned long long warp_totals[33];
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t begin = min(slots, warp * range), end = min(slots, begin + range);
     int32_t* mine = hist + warp * E;
+    for (uint32_t i = threadIdx.x; i < E; i += NT) items[i].x = -1;        // entries past the end of the new list (ordered before the fill by the barriers below)
     int32_t cached[PERMUTE_CACHE];
     if constexpr (CACHED) {
 #pragma unroll
@@ -220,7 +221,11 @@ __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots,
             offsets[e] = offset;
 #pragma unroll
             for (int w = 0; w < NW; ++w) hist[w * E + e] += offset;
-            if (count[q] > 0 && e >= first_expert && e < first_expert + local_experts) active[slot++] = int32_t(e);
+            if (count[q] > 0 && e >= first_expert && e < first_expert + local_experts) {
+                active[slot] = int32_t(e);
+                items[slot] = make_int4(int(e), offset, count[q], 0);
+                ++slot;
+            }
             offset += count[q];
         }
     }
@@ -259,22 +264,22 @@ __host__ __device__ inline uint32_t permute_range(uint32_t slots, uint32_t warps
 
 template <int NT>
 __device__ __forceinline__ void permute_any(const int32_t* ids, uint32_t slots, uint32_t E, uint32_t first_expert, uint32_t local_experts,
-                                            int32_t* offsets, int32_t* perm, int32_t* active, int32_t* counters, uint32_t layer,
+                                            int32_t* offsets, int32_t* perm, int32_t* active, int4* items, int32_t* counters, uint32_t layer,
                                             uint32_t* status, int32_t* hist) {
     const uint32_t range = permute_range(slots, NT / 32);
-    if (range <= 32 * PERMUTE_CACHE) permute_body<NT, true>(ids, slots, E, first_expert, local_experts, offsets, perm, active, counters, layer, status, hist, range);
-    else permute_body<NT, false>(ids, slots, E, first_expert, local_experts, offsets, perm, active, counters, layer, status, hist, range);
+    if (range <= 32 * PERMUTE_CACHE) permute_body<NT, true>(ids, slots, E, first_expert, local_experts, offsets, perm, active, items, counters, layer, status, hist, range);
+    else permute_body<NT, false>(ids, slots, E, first_expert, local_experts, offsets, perm, active, items, counters, layer, status, hist, range);
 }
 
 __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const int32_t* __restrict__ ids, uint32_t slots, uint32_t E,
                                                                    uint32_t first_expert, uint32_t local_experts,
                                                                    int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
-                                                                   int32_t* __restrict__ active, int32_t* __restrict__ counters,
+                                                                   int32_t* __restrict__ active, int4* __restrict__ items, int32_t* __restrict__ counters,
                                                                    uint32_t layer, uint32_t* status) {
     extern __shared__ int32_t hist[];
     for (uint32_t i = threadIdx.x; i < (PERMUTE_THREADS / 32) * E; i += PERMUTE_THREADS) hist[i] = 0;
     __syncthreads();
-    permute_any<PERMUTE_THREADS>(ids, slots, E, first_expert, local_experts, offsets, perm, active, counters, layer, status, hist);
+    permute_any<PERMUTE_THREADS>(ids, slots, E, first_expert, local_experts, offsets, perm, active, items, counters, layer, status, hist);
 }
 
 // Route (one warp per token, eight tokens per CTA) and, when asked, the permutation as the tail of the
@@ -300,7 +305,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
     if (!last) return;
     __threadfence();
     if (threadIdx.x == 0) *a.done = 0;
-    permute_any<ROUTE_THREADS>(a.ids, a.T * a.K, a.E, a.first_expert, a.local_experts, a.offsets, a.perm, a.active, a.counters, a.layer, a.status, hist);
+    permute_any<ROUTE_THREADS>(a.ids, a.T * a.K, a.E, a.first_expert, a.local_experts, a.offsets, a.perm, a.active, a.items, a.counters, a.layer, a.status, hist);
 }
 
 }  // namespace
@@ -318,7 +323,7 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
         RouteArgs a{};
         a.logits = c.logits;
         a.ids = c.ids; a.weights = c.weights; a.T = c.T; a.E = c.E; a.K = c.K; a.status = c.status;
-        a.offsets = c.offsets; a.perm = c.perm; a.active = c.active; a.counters = c.counters; a.done = reinterpret_cast<uint32_t*>(c.counters + 1);
+        a.offsets = c.offsets; a.perm = c.perm; a.active = c.active; a.items = c.items; a.counters = c.counters; a.done = reinterpret_cast<uint32_t*>(c.counters + 1);
         a.first_expert = c.first_expert; a.local_experts = c.local_experts; a.layer = c.layer; a.do_permute = do_permute;
         const size_t smem = size_t(ROUTE_THREADS / 32) * c.E * sizeof(int32_t);
         const bool small = c.E <= 512;
@@ -351,7 +356,7 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
         {
             Timed t(m, s, KERNEL_PERMUTE);
             permute_kernel<<<1, PERMUTE_THREADS, hist_bytes, s>>>(c.ids, c.T * c.K, c.E, c.first_expert, c.local_experts, c.offsets, c.perm,
-                                                                 c.active, c.counters, c.layer, c.status);
+                                                                 c.active, c.items, c.counters, c.layer, c.status);
             rc = check_launch(m, "permute");
         }
         if (rc < 0) return rc;
