@@ -181,6 +181,7 @@ def run_reference(args):
         return
     from oracle import oracle
     oracle.build()
+    oracle.set_threads(len(os.sched_getaffinity(0)))      # a multi-rank launcher exports OMP_NUM_THREADS=1: use every host core anyway
     cfg = config(48, args.tokens)
     sample_layers = args.cpu_layers
     cache = {}

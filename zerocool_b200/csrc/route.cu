@@ -160,6 +160,7 @@ __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots,
     __shared__ unsigned long long warp_totals[33];
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t begin = min(slots, warp * range), end = min(slots, begin + range);
+    const int used = int(min(uint32_t(NW), (slots + range - 1) / max(range, 1u)));       // warps whose range is not empty: only their histograms count
     int32_t* mine = hist + warp * E;
     for (uint32_t i = threadIdx.x; i < E; i += NT) items[i].x = -1;        // entries past the end of the new list (ordered before the fill by the barriers below)
     int32_t cached[PERMUTE_CACHE];
@@ -204,8 +205,7 @@ __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots,
         count[q] = 0;
         if (uint32_t(q) < own && e < E) {
             int running = 0;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) { const int n = hist[w * E + e]; hist[w * E + e] = running; running += n; }
+            for (int w = 0; w < used; ++w) { const int n = hist[w * E + e]; hist[w * E + e] = running; running += n; }
             count[q] = running;
             const bool has_work = running > 0 && e >= first_expert && e < first_expert + local_experts;
             packed += (unsigned long long)(running) | ((unsigned long long)(has_work ? 1 : 0) << 32);
@@ -219,8 +219,7 @@ __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots,
         const uint32_t e = e_first + q;
         if (uint32_t(q) < own && e < E) {
             offsets[e] = offset;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) hist[w * E + e] += offset;
+            for (int w = 0; w < used; ++w) hist[w * E + e] += offset;
             if (count[q] > 0 && e >= first_expert && e < first_expert + local_experts) {
                 active[slot] = int32_t(e);
                 items[slot] = make_int4(int(e), offset, count[q], 0);
@@ -277,7 +276,8 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const int32_t*
                                                                    int32_t* __restrict__ active, int4* __restrict__ items, int32_t* __restrict__ counters,
                                                                    uint32_t layer, uint32_t* status) {
     extern __shared__ int32_t hist[];
-    for (uint32_t i = threadIdx.x; i < (PERMUTE_THREADS / 32) * E; i += PERMUTE_THREADS) hist[i] = 0;
+    const uint32_t used = min(uint32_t(PERMUTE_THREADS / 32), (slots + permute_range(slots, PERMUTE_THREADS / 32) - 1) / max(permute_range(slots, PERMUTE_THREADS / 32), 1u));
+    for (uint32_t i = threadIdx.x; i < used * E; i += PERMUTE_THREADS) hist[i] = 0;
     __syncthreads();
     permute_any<PERMUTE_THREADS>(ids, slots, E, first_expert, local_experts, offsets, perm, active, items, counters, layer, status, hist);
 }
@@ -300,7 +300,10 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) last = atomicAdd(a.done, 1u) == gridDim.x - 1;
-    for (uint32_t i = threadIdx.x; i < ROUTE_WARPS * a.E; i += ROUTE_THREADS) hist[i] = 0;      // overlaps the atomic's round trip
+    {
+        const uint32_t slots = a.T * a.K, range = permute_range(slots, ROUTE_WARPS), used = min(uint32_t(ROUTE_WARPS), (slots + range - 1) / max(range, 1u));
+        for (uint32_t i = threadIdx.x; i < used * a.E; i += ROUTE_THREADS) hist[i] = 0;      // overlaps the atomic's round trip
+    }
     __syncthreads();
     if (!last) return;
     __threadfence();
