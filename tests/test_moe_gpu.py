@@ -330,3 +330,35 @@ def test_stack_host_and_device_paths_agree(torch):
     m.stack_host(x_host, out_host)
     assert torch.equal(out_host, first.cpu())
     assert m.launches > 0
+
+
+@pytest.mark.parametrize("tokens", [3, 40])
+def test_dependent_launch_does_not_change_results(torch, tokens):
+    """The stack with programmatic dependent launch (kernels overlapping their predecessor's tail) returns the same
+    bytes as with plainly serialised launches, eagerly and as a replayed graph."""
+    cfg = util.cfg2(experts=64, layers=4, out_dtype=BF16, max_tokens=64)
+    m = make(cfg)
+    for l in range(cfg.layers):
+        m.synth_fill_layer(l, SEED)
+    x = device_x(m, synth.activations(cfg, SEED, 0, tokens))
+    m.set_option("pdl", 0)
+    plain = m.stack(x).clone()
+    m.set_option("pdl", 1)
+    overlapped = [m.stack(x).clone() for _ in range(3)]          # capture, then two replays
+    eager = m.stack_eager(x).clone()
+    assert all(torch.equal(plain, o) for o in overlapped) and torch.equal(plain, eager)
+    assert m.status() == 0
+    with pytest.raises(ValueError):
+        m.set_option("no such option", 1)
+
+
+def test_decode_token_order_invariance_at_full_shape(torch):
+    """Config 2 at full size, 64 tokens: a token's output does not depend on where it sits in the batch."""
+    cfg = util.cfg2(max_tokens=64)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    x = synth.activations(cfg, SEED, 0, 64)
+    out = m.decode(0, device_x(m, x)).clone()
+    order = np.random.default_rng(4).permutation(64)
+    out_p = m.decode(0, device_x(m, np.ascontiguousarray(x[order])))
+    assert torch.equal(out_p, out[torch.from_numpy(order).to(out.device)])

@@ -124,3 +124,33 @@ def test_forward_picks_the_family_by_token_count():
     assert m.launches - before == 5
     with pytest.raises(ValueError):
         make(util.cfg2(experts=64, max_tokens=16)).prefill(0, small)
+
+
+def test_full_shape_token_order_invariance():
+    """BASELINE config 3 at full size (512 experts, top-10 + shared, 2048 tokens, Zipf router bias): permuting the
+    tokens of the batch permutes the outputs bit for bit, for both kernel families' routing and for the grouped GEMM
+    (a token's result must not depend on its position in a tile or on its neighbours), and the first tokens agree
+    with the CPU checker."""
+    import torch
+    cfg = util.cfg2(max_tokens=2048)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    bias = synth.zipf_router_bias(cfg, SEED, 0)
+    m.set_router_bias(0, bias)
+    tokens = 2048
+    x = synth.activations(cfg, SEED, 0, tokens)
+    out = m.prefill(0, device_x(m, x)).clone()
+    ids = m.last_routing(tokens)["ids"].copy()
+    order = np.random.default_rng(3).permutation(tokens)
+    out_p = m.prefill(0, device_x(m, np.ascontiguousarray(x[order])))
+    assert m.status() == 0
+    assert np.array_equal(m.last_routing(tokens)["ids"], ids[order])
+    assert torch.equal(out_p, out[torch.from_numpy(order).to(out.device)])
+    counts = np.bincount(ids.reshape(-1), minlength=cfg.experts)
+    assert counts.max() > 512 and (counts == 0).sum() > 100          # the skew of the configuration
+    check = 16
+    want = oracle.moe_layer(cfg.as_dict(), util.selected_records(cfg, SEED, 0, ids[:check]), synth.router(cfg, SEED, 0), x[:check],
+                            shared_record=synth.record(cfg, SEED, 0, synth.SHARED_EXPERT), shared_gate_w=synth.shared_gate(cfg, SEED, 0),
+                            router_bias=bias)
+    assert np.array_equal(want["ids"], ids[:check])
+    assert util.rel_max_error(out[:check].float().cpu().numpy(), want["out"]) <= TOL
