@@ -407,8 +407,8 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (warp == 4) {
-        // ---- MMA issue: one lane of warp 4 ------------------------------------------------------------
-        if (lane == 0) {
+        // ---- MMA issue: the whole warp runs the loop (waits and addresses stay warp-uniform), one lane issues ----
+        {
             // instruction descriptor: D = F32, A = B = F16, both K-major, N = Npad, M = 128
             const uint32_t idesc = (1u << 4) | ((Npad >> 3) << 17) | ((PF_M >> 4) << 24);
             const uint64_t desc0 = umma_desc(base);
@@ -416,29 +416,33 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
             for (uint32_t ks = 0; ks < nst; ++ks) {
                 ok = mbar_wait(&full_bar[ks % PF_STAGES], (ks / PF_STAGES) & 1, &abort_flag, status);
                 if (ok && ks >= PF_ACC) ok = mbar_wait(&acc_free[ks % PF_ACC], ((ks / PF_ACC) - 1) & 1, &abort_flag, status);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t bs = b_ring + (ks % PF_BS) * PF_B_BYTES;
                 const uint32_t acc = tmem_base + (ks % PF_ACC) * NMAT * Npad;
-                if (ks < G) {
-                    // descriptors differ from desc0 only in the start address field (bits 0-13, units of 16 bytes)
-                    const uint64_t adesc = desc0 + (((ks % PF_STAGES) * S::A_STAGE) >> 4), bdesc = desc0 + ((S::A_RING + (ks % PF_BS) * PF_B_BYTES) >> 4);
+                // descriptors differ from desc0 only in the start address field (bits 0-13, units of 16 bytes)
+                const uint64_t adesc = desc0 + (((ks % PF_STAGES) * S::A_STAGE) >> 4), bdesc = desc0 + ((S::A_RING + (ks % PF_BS) * PF_B_BYTES) >> 4);
+                if (lane == 0) {
+                    if (ks < G) {
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
+                        for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
-                        for (int m = 0; m < NMAT; ++m) umma_f16(acc + m * Npad, adesc + ((m * PF_A_BYTES + kk * 256) >> 4), bdesc + ((kk * 256) >> 4), idesc, kk != 0);
+                            for (int m = 0; m < NMAT; ++m) umma_f16(acc + m * Npad, adesc + ((m * PF_A_BYTES + kk * 256) >> 4), bdesc + ((kk * 256) >> 4), idesc, kk != 0);
+                        }
+                    } else {
+                        const uint32_t blk = (ks - G) % nblk;
+                        for (uint32_t kk = 0; kk < kb / 16; ++kk) {
+                            const uint64_t bd = umma_desc(bs + kk * 256, (kb / 8) * 128);
+#pragma unroll
+                            for (int m = 0; m < NMAT; ++m)
+                                umma_f16(acc + m * Npad, umma_desc(meta_base + m * meta_tile + blk * (kb / 8) * 128 + kk * 256, meta_sbo), bd, idesc, kk != 0);
+                        }
                     }
-                } else {
-                    const uint32_t blk = (ks - G) % nblk;
-                    for (uint32_t kk = 0; kk < kb / 16; ++kk) {
-                        const uint64_t bdesc = umma_desc(bs + kk * 256, (kb / 8) * 128);
-#pragma unroll
-                        for (int m = 0; m < NMAT; ++m)
-                            umma_f16(acc + m * Npad, umma_desc(meta_base + m * meta_tile + blk * (kb / 8) * 128 + kk * 256, meta_sbo), bdesc, idesc, kk != 0);
-                    }
+                    umma_commit(&done_bar[ks % PF_STAGES]);
+                    umma_commit(&acc_full[ks % PF_ACC]);
                 }
-                umma_commit(&done_bar[ks % PF_STAGES]);
-                umma_commit(&acc_full[ks % PF_ACC]);
+                __syncwarp();
             }
         }
         __syncwarp();
