@@ -193,6 +193,8 @@ int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* ou
  *   "pdl" (default 1; environment ZC_MOE_PDL=0 at create time): the kernels of a layer are launched with
  *   programmatic stream serialization, so that each one's set-up and weight prefetch overlap the tail of the
  *   kernel before it; results are identical either way.
+ *   "exact_h" (default 0): the decode family's down product reads the FP32 SwiGLU rows as two FP16 terms (nothing
+ *   below FP32 is rounded) instead of one FP16 term (11 significant bits; the reference rounds these rows to BF16).
  * Changing an option drops the cached graphs of zc_moe_stack. */
 int zc_moe_set_option(zc_moe* moe, const char* name, int value);
 

@@ -144,10 +144,12 @@ def test_permute_is_bit_exact(torch, tokens, experts, k):
     assert int(offsets.cpu().numpy()[-1]) == tokens * k - 1
 
 
-def check_layer(torch, cfg, tokens, seed=SEED, tol=TOL, layer=0, fold=None):
+def check_layer(torch, cfg, tokens, seed=SEED, tol=TOL, layer=0, fold=None, exact_h=None):
     m = make(cfg)
     if fold is not None:
         m.set_option("fold_q4", fold)
+    if exact_h is not None:
+        m.set_option("exact_h", exact_h)
     m.synth_fill_layer(layer, seed)
     x = synth.activations(cfg, seed, layer, tokens)
     out = m.moe(layer, device_x(m, x))
@@ -362,3 +364,12 @@ def test_decode_token_order_invariance_at_full_shape(torch):
     order = np.random.default_rng(4).permutation(64)
     out_p = m.decode(0, device_x(m, np.ascontiguousarray(x[order])))
     assert torch.equal(out_p, out[torch.from_numpy(order).to(out.device)])
+
+
+@pytest.mark.parametrize("tokens", [4, 64])
+def test_exact_intermediate_option(torch, tokens):
+    """With "exact_h" nothing below FP32 is rounded between gate/up and down: the error drops from the FP16 rounding
+    of the SwiGLU rows (~1e-3 x RMS) to the tensor cores' accumulation error."""
+    out_exact, want, _ = check_layer(torch, util.cfg2(), tokens, exact_h=1, tol=5e-4)
+    out_fast, _, _ = check_layer(torch, util.cfg2(), tokens, exact_h=0)
+    assert util.rel_max_error(out_fast, out_exact) <= TOL

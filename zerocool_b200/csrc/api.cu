@@ -511,11 +511,12 @@ int zc_moe_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, voi
 
 int zc_moe_set_option(zc_moe* m, const char* name, int value) {
     if (!m || !name) return fail(m, ZC_EINVAL, "null handle or option name");
-    const bool fold = !std::strcmp(name, "fold_q4"), pdl = !std::strcmp(name, "pdl");
-    if (fold || pdl) {
+    const bool fold = !std::strcmp(name, "fold_q4"), pdl = !std::strcmp(name, "pdl"), exact_h = !std::strcmp(name, "exact_h");
+    if (fold || pdl || exact_h) {
         for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);      // captured launches hold the old choice
         m->graphs.clear();
-        if (fold) m->fold_q4 = value != 0; else m->pdl = value == 0 ? 0u : value == 1 ? 0xffffffffu : uint32_t(value);
+        if (exact_h) m->exact_h = value != 0;
+        else if (fold) m->fold_q4 = value != 0; else m->pdl = value == 0 ? 0u : value == 1 ? 0xffffffffu : uint32_t(value);
         return ZC_OK;
     }
     return fail(m, ZC_EINVAL, std::string("unknown option: ") + name);

@@ -20,8 +20,9 @@
 //    which is the reference's affine_dot form (qwen.metal:46-62) with an exact inner sum.
 //  * Q4 codes become FP16 with one logic operation per two weights: (w & 0x000f000f) | 0x6400 is the
 //    half2 (1024+q_lo, 1024+q_hi), and (w & 0x00f000f0) | 0x6400 is (1024+16 q, 1024+16 q). With FOLD
-//    those values go into the MMA as they are: the activation that meets a "16 q" slot is staged divided
-//    by 16 (exact), and the 1024 offset is removed from the FP32 group sum as 1024 * sum(x as staged).
+//    those values go into the MMA as they are: the activations that meet a "q" slot are staged multiplied by 16
+//    (exact; the finished sum is divided by 16), and the 1024 offset is removed from the FP32 group sum as
+//    1024 * sum(x as staged).
 //    Without FOLD the offset and the factor 16 are removed in FP16 before the MMA (exact, 4 more ops per
 //    word).
 //  * Weights reach the warp through a private cp.async ring in shared memory (no registers held
@@ -34,7 +35,7 @@
 //  * Lanes whose token row is absent (fewer than eight rows in the pass) skip the activation reads.
 //  * Because a dot product does not care about the order of k, the MMA's k slots are bound to whatever
 //    k values fall out of the cheapest extraction; the activations are staged in the matching order.
-// Activations must be finite FP16 magnitudes (|x| < 65504); hidden states after a norm are O(1..100).
+// Activations must stay inside FP16 after the factor 16 (|x| < 4096); hidden states after a norm are O(1..100).
 #include "common.cuh"
 
 namespace zc {
@@ -129,7 +130,7 @@ __device__ __forceinline__ bool decode_item(const Call& c, uint32_t item, ItemIn
 //   sums[grp][n] = (Sx, P):  Sx = sum of x over the group (REF: the reference's BF16 sum of four,
 //   qwen.metal:55), P = -1024 * sum of the values as staged: the MMA accumulator starts from P, which
 //   removes the folded 1024 offset of the codes (0 without FOLD).
-//   Q4 order inside each block of 8: (0,4,1,5,2,6,3,7), odd k staged / 16 when FOLD; Q8: natural order.
+//   Q4 order inside each block of 8: (0,4,1,5,2,6,3,7), even k staged x 16 when FOLD; Q8: natural order.
 // Rows n >= nvalid are left as they are: an MMA column only depends on its own B column.
 template <bool Q4ORDER, bool SPLIT, bool FOLD>
 __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const int* rows, uint32_t nvalid,
@@ -158,22 +159,30 @@ __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const 
         if (ref) sx = bf_round(bf_round(bf_round(v[0] + v[1]) + v[2]) + v[3]) + bf_round(bf_round(bf_round(v[4] + v[5]) + v[6]) + v[7]);
         else sx = (((v[0] + v[1]) + v[2]) + v[3]) + (((v[4] + v[5]) + v[6]) + v[7]);
         __half h[8], l[8];
-        float sf = 0.0f;
+        float sf = 0.0f, sn = 0.0f;        // sums of the values as fed to the MMA: as staged, and in natural scale
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float pre = (FOLD && Q4ORDER && (i & 1)) ? v[i] * 0.0625f : v[i];
+            // folded Q4 codes: the value that meets a "1024 + 16 q" slot must be 1/16 of its neighbours'. Even slots are
+            // staged x 16 rather than odd slots / 16, which keeps small activations out of FP16's subnormal range; the
+            // accumulated result is multiplied by 1/16 (exact) when it is finished.
+            const float pre = (FOLD && Q4ORDER && !(i & 1)) ? v[i] * 16.0f : v[i];
             h[i] = __float2half_rn(pre);
             float fed = __half2float(h[i]);
             if (SPLIT) { l[i] = __float2half_rn(pre - fed); fed += __half2float(l[i]); }
             sf += fed;
+            sn += (FOLD && Q4ORDER && !(i & 1)) ? fed * 0.0625f : fed;
         }
+        // The bias term multiplies the sum of the activations. Outside the reference arithmetic it uses the sum of
+        // the values the MMA really sees, so that a rounding of an activation to FP16 enters the result through the
+        // weight s q + b and not through s q alone.
+        if (!ref) sx = sn;
 #pragma unroll
         for (int off = 1; off <= 4; off <<= 1) {
             sx += __shfl_xor_sync(0xffffffffu, sx, off);
             sf += __shfl_xor_sync(0xffffffffu, sf, off);
         }
         if (!live) continue;
-        if ((q & 7) == 0) *reinterpret_cast<float2*>(sums + ((q / 8) * NTOK + n) * 2) = make_float2(sx, FOLD ? -1024.0f * sf : 0.0f);
+        if ((q & 7) == 0) *reinterpret_cast<float2*>(sums + ((q / 8) * NTOK + n) * 2) = make_float2((FOLD && Q4ORDER) ? 16.0f * sx : sx, FOLD ? -1024.0f * sf : 0.0f);
         constexpr int order_q4[8] = {0, 4, 1, 5, 2, 6, 3, 7};
         uint32_t ph[4], pl[4];
 #pragma unroll
@@ -394,6 +403,7 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
         auto finish = [&](uint32_t row, uint32_t n, float a0, float a1) {
             const long long d = dest[n];
             if (d < 0) return;
+            if constexpr (FOLDQ) { a0 *= 0.0625f; a1 *= 0.0625f; }          // the rows were staged x 16
             if constexpr (NMAT == 2) {
                 float h;
                 if (c.ref) {   // qwen.metal:71-81
@@ -570,7 +580,11 @@ int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s) {
     // A BF16 activation is exact as one FP16 term; an FP32 activation needs two, except under the
     // reference arithmetic, whose FP32 buffers hold BF16 values by contract.
     const bool split_x = c.act_dtype == ZC_F32 && !c.ref;
-    const bool split_h = !c.ref;      // h is FP32 unless the reference rounds it to BF16
+    // The SwiGLU rows h are FP32 in memory. By default the down product reads them as one FP16 term (11 significant
+    // bits, against the 8 of the BF16 the reference rounds h to; measured 1.2e-3 x RMS max-abs at 64 tokens, inside the
+    // 2e-3 bound); with the "exact_h" option as two FP16 terms, which costs a second MMA per fragment (73 us against
+    // 56 us for the down launch of the benchmark layer). The reference arithmetic's h is BF16: exact in one term.
+    const bool split_h = !c.ref && m->exact_h;
     const bool fold = m->fold_q4;
     // Few rows in flight: split K over all eight warps so that even one token fills the machine.
     const bool small = c.T * (c.K + (c.has_shared ? 1 : 0)) <= 64;
