@@ -46,7 +46,7 @@ def config(layers, max_tokens):
 def workload(cfg, tokens, n_gpus, kind="decode"):
     if kind == "prefill":
         return {
-            "workload": f"BASELINE config 3: prefill grouped GEMM, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
+            "workload": f"benchmark configuration 3: prefill grouped GEMM, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
                         f"top-{cfg.top_k} + 1 shared, ffn {cfg.ffn}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router with an additive "
                         f"Zipf(s=1.1) per-expert logit bias, sequence of {tokens} tokens per GPU, layers chained through bf16((out-mean)/std)",
             "tokens_per_gpu": tokens, "layers": cfg.layers,
@@ -55,7 +55,7 @@ def workload(cfg, tokens, n_gpus, kind="decode"):
             "accumulate": "f32", "weights": "q4_g64 fed to tcgen05.mma as two exact FP16 terms",
         }
     return {
-        "workload": f"BASELINE config 2: decode MoE stack, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
+        "workload": f"benchmark configuration 2: decode MoE stack, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
                     f"top-{cfg.top_k} + 1 shared, ffn {cfg.ffn}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router, "
                     f"batch of {tokens} tokens per GPU, layers chained through bf16((out-mean)/std)",
         "tokens_per_gpu": tokens, "layers": cfg.layers,
@@ -231,7 +231,7 @@ def layer_bytes(cfg, active, tokens):
 
 
 def run_ep(args):
-    """BASELINE config 5: expert-parallel stack on N GPUs (hidden 4096, 512 experts top-10 sharded 512/N per GPU,
+    """benchmark configuration 5: expert-parallel stack on N GPUs (hidden 4096, 512 experts top-10 sharded 512/N per GPU,
     ffn 512, Q4 g64), 256-token decode batch split over the ranks, NCCL all-to-all dispatch/combine."""
     import torch
     import torch.distributed as dist
@@ -284,7 +284,7 @@ def run_ep(args):
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"BASELINE config 5: expert-parallel stack, {cfg.layers} layers, hidden 4096, 512 experts top-10 ({per} per GPU), ffn 512, "
+            "config": {"workload": f"benchmark configuration 5: expert-parallel stack, {cfg.layers} layers, hidden 4096, 512 experts top-10 ({per} per GPU), ffn 512, "
                                    f"affine-Q4 g64, {total_tokens}-token decode batch ({t_local} per GPU), NCCL all-to-all dispatch/combine, "
                                    "layers chained through bf16((out-mean)/std)",
                        "parallelism": f"ep{world}", "tokens_total": total_tokens, "layers": cfg.layers,
@@ -485,7 +485,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep"],
-                    help="decode: BASELINE config 2 (the headline); prefill: config 3 (grouped GEMM, Zipf-skewed loads)")
+                    help="decode: benchmark configuration 2 (the headline); prefill: config 3 (grouped GEMM, Zipf-skewed loads)")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU: decode 1/4/16/64 (default 64), prefill 2048/8192 (default 2048)")
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--cpu-layers", type=int, default=8, help="layers of the stack the CPU baseline runs (scaled to 48)")

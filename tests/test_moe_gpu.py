@@ -169,13 +169,13 @@ def check_layer(torch, cfg, tokens, seed=SEED, tol=TOL, layer=0, fold=None, exac
 
 
 def test_config1_single_token_fp32(torch):
-    """BASELINE config 1: hidden 2048, 64 experts top-8, ffn 512, one fp32 token, no shared expert."""
+    """benchmark configuration 1: hidden 2048, 64 experts top-8, ffn 512, one fp32 token, no shared expert."""
     check_layer(torch, util.cfg1(), 1)
 
 
 @pytest.mark.parametrize("tokens", [1, 4, 16, 64])
 def test_config2_decode_batches(torch, tokens):
-    """BASELINE config 2 (one layer of it): 512 experts top-10 + shared, bf16 activations, token batches 1/4/16/64."""
+    """benchmark configuration 2 (one layer of it): 512 experts top-10 + shared, bf16 activations, token batches 1/4/16/64."""
     check_layer(torch, util.cfg2(), tokens)
 
 
@@ -203,12 +203,12 @@ def test_config2_ragged_batch_and_bf16_output(torch):
 
 
 def test_config5_hidden_4096(torch):
-    """BASELINE config 5 geometry on one GPU with a reduced expert count: hidden 4096, top-10, no shared expert."""
+    """benchmark configuration 5 geometry on one GPU with a reduced expert count: hidden 4096, top-10, no shared expert."""
     check_layer(torch, util.cfg2(hidden=4096, experts=64, has_shared=0, max_tokens=16), 9)
 
 
 def test_config4_mixed_q4_q8(torch):
-    """BASELINE config 4 geometry: gate/up Q4, down Q8 with signed int8 codes, a ragged 21-token batch."""
+    """benchmark configuration 4 geometry: gate/up Q4, down Q8 with signed int8 codes, a ragged 21-token batch."""
     check_layer(torch, util.cfg2(experts=64, has_shared=0, down_bits=8, q8_signed=1, max_tokens=32), 21)
 
 

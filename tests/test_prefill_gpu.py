@@ -127,7 +127,7 @@ def test_forward_picks_the_family_by_token_count():
 
 
 def test_full_shape_token_order_invariance():
-    """BASELINE config 3 at full size (512 experts, top-10 + shared, 2048 tokens, Zipf router bias): permuting the
+    """benchmark configuration 3 at full size (512 experts, top-10 + shared, 2048 tokens, Zipf router bias): permuting the
     tokens of the batch permutes the outputs bit for bit, for both kernel families' routing and for the grouped GEMM
     (a token's result must not depend on its position in a tile or on its neighbours), and the first tokens agree
     with the CPU checker."""

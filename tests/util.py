@@ -6,7 +6,7 @@ from zerocool_b200.records import ARITH_FP32, ARITH_REFERENCE, BF16, F16, F32, M
 
 
 def cfg1(**kw):
-    """BASELINE config 1: one layer, hidden 2048, 64 experts top-8, ffn 512, Q4 g64 fp16 metadata, fp32 activations."""
+    """benchmark configuration 1: one layer, hidden 2048, 64 experts top-8, ffn 512, Q4 g64 fp16 metadata, fp32 activations."""
     base = dict(hidden=2048, ffn=512, experts=64, top_k=8, layers=1, meta_dtype=F16, act_dtype=F32, out_dtype=F32,
                 router_dtype=F32, has_shared=0, arith=ARITH_FP32, max_tokens=8)
     base.update(kw)
@@ -14,7 +14,7 @@ def cfg1(**kw):
 
 
 def cfg2(**kw):
-    """BASELINE config 2 geometry: hidden 2048, 512 experts top-10 + shared, ffn 512, bf16 activations."""
+    """benchmark configuration 2 geometry: hidden 2048, 512 experts top-10 + shared, ffn 512, bf16 activations."""
     base = dict(hidden=2048, ffn=512, experts=512, top_k=10, layers=1, meta_dtype=F16, act_dtype=BF16, out_dtype=F32,
                 router_dtype=F32, has_shared=1, arith=ARITH_FP32, max_tokens=64)
     base.update(kw)
