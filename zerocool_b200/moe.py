@@ -248,7 +248,13 @@ class Moe:
         rows = torch.empty((tokens * self.cfg.top_k, self.cfg.hidden), dtype=self.act_torch, device=self.device)
         experts = torch.full((tokens * self.cfg.top_k,), -1, dtype=torch.int32, device=self.device)
         self._check(self.lib.zc_moe_ep_dispatch(self._h, layer, _ptr(x), tokens, _ptr(rows), _ptr(experts), self._stream()))
-        return rows, experts, self.last_routing(tokens)["offsets"]
+        return rows, experts, self.last_offsets()
+
+    def last_offsets(self):
+        """Host copy (numpy int32 [E + 1]) of the last call's expert offsets: one small device-to-host copy."""
+        ptrs = [ctypes.c_void_p() for _ in range(5)]
+        self._check(self.lib.zc_moe_last_routing(self._h, *[ctypes.byref(p) for p in ptrs]))
+        return self.read_device(ptrs[2].value, (self.cfg.experts + 1) * 4).view(np.int32)
 
     def ep_experts(self, layer, rows, row_experts):
         torch = self._torch
