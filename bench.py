@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Benchmark of the MoE-layer hot path: decode MoE stack at the Qwen3-Next-like shape.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload decode|prefill|mixed|ep]
 
 A step is one pass of the 48-layer MoE stack (hidden 2048, 512 routed experts top-10 + 1 shared expert,
 ffn 512, affine-Q4 group 64 with fp16 scale/bias, bf16 activations) over one batch of tokens, the layers
@@ -10,11 +10,15 @@ resident in HBM, so every step streams its weights from DRAM (inputs far larger 
 Inputs are seeded synthetic tensors with the shapes and value distributions of the benchmark
 specification; the real checkpoint is not available.
 
-Rank 0 prints ONE JSON line. `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same
-metric through the host-buffer entry point (pinned host activations copied in and out inside the timed
-region); `roofline` reports the dominant kernel against the measured HBM bandwidth; `cpu_baseline` is the
-CPU restatement of the reference's arithmetic (oracle/) timed on this machine's host cores on a bounded
-sample. With --impl reference the same CPU code is the thing timed.
+Rank 0 prints ONE JSON line. `value` is whole-job tokens/s of the decode stack (benchmark configuration 2) with
+inputs resident in HBM; `e2e` is the same metric through the host-buffer entry point (pinned host activations
+copied in and out inside the timed region); `roofline` reports the dominant kernel against the measured HBM
+bandwidth; `cpu_baseline` is the CPU restatement of the reference's arithmetic (oracle/) timed on this machine's
+host cores on a bounded sample. The same line carries the other configurations of the specification as
+sub-records: `prefill` (configuration 3: 2048 and 8192 tokens, Zipf-skewed loads, tensor roofline), `mixed`
+(configuration 4: gate/up Q4 + down Q8, ragged batch of 32 requests) and `ep` (configuration 5: hidden 4096,
+256-token batch; expert-parallel over the N ranks when N >= 2, one GPU holding all 87 GB when N = 1).
+With --impl reference the CPU code is the thing timed.
 """
 import argparse
 import json
@@ -36,47 +40,67 @@ from zerocool_b200.records import BF16, F16, F32, MoeConfig  # noqa: E402
 METRIC = "MoE-layer tokens/s at Qwen3-Next shape (decode, 48-layer MoE stack)"
 SEED = 20261125
 BATCHES = (1, 4, 16, 64)
+TOL = 2e-3            # max-abs error / output RMS, fp32 accumulation (the tolerance of the benchmark specification)
 
 
-def config(layers, max_tokens):
-    return MoeConfig(hidden=2048, ffn=512, experts=512, top_k=10, layers=layers, meta_dtype=F16, act_dtype=BF16,
-                     out_dtype=BF16, router_dtype=F32, has_shared=1, max_tokens=max_tokens)
+def config(layers, max_tokens, **kw):
+    base = dict(hidden=2048, ffn=512, experts=512, top_k=10, layers=layers, meta_dtype=F16, act_dtype=BF16,
+                out_dtype=BF16, router_dtype=F32, has_shared=1, max_tokens=max_tokens)
+    base.update(kw)
+    return MoeConfig(**base)
+
+
+def config5(layers, max_tokens, rank=0, world=1):
+    per = 512 // world
+    return MoeConfig(hidden=4096, ffn=512, experts=512, top_k=10, layers=layers, meta_dtype=F16, act_dtype=BF16, out_dtype=BF16,
+                     router_dtype=F32, has_shared=0, max_tokens=max_tokens, first_expert=rank * per if world > 1 else 0,
+                     local_experts=per if world > 1 else 0)
+
+
+def mixed_lengths():
+    """Configuration 4: 32 requests with seeded lengths U{1..512}, flattened to one ragged token batch."""
+    return np.random.default_rng(SEED).integers(1, 513, size=32)
 
 
 def workload(cfg, tokens, n_gpus, kind="decode"):
+    shape = (f"{cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts top-{cfg.top_k}" + (" + 1 shared" if cfg.has_shared else "") +
+             f", ffn {cfg.ffn}")
+    glue = "layers chained through bf16((out-mean)/std)"
+    replicas = f"dp{n_gpus}: independent replicas, tokens sharded, no data-path collective"
     if kind == "prefill":
-        return {
-            "workload": f"benchmark configuration 3: prefill grouped GEMM, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
-                        f"top-{cfg.top_k} + 1 shared, ffn {cfg.ffn}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router with an additive "
-                        f"Zipf(s=1.1) per-expert logit bias, sequence of {tokens} tokens per GPU, layers chained through bf16((out-mean)/std)",
-            "tokens_per_gpu": tokens, "layers": cfg.layers,
-            "parallelism": f"dp{n_gpus}: independent replicas, tokens sharded, no data-path collective",
-            "l2": "no flush needed: every layer streams its 906 MB of records (43.5 GB resident) through a 126 MB L2",
-            "accumulate": "f32", "weights": "q4_g64 fed to tcgen05.mma as two exact FP16 terms",
-        }
-    return {
-        "workload": f"benchmark configuration 2: decode MoE stack, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.experts} routed experts "
-                    f"top-{cfg.top_k} + 1 shared, ffn {cfg.ffn}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router, "
-                    f"batch of {tokens} tokens per GPU, layers chained through bf16((out-mean)/std)",
-        "tokens_per_gpu": tokens, "layers": cfg.layers,
-        "parallelism": f"dp{n_gpus}: independent replicas, tokens sharded, no data-path collective",
-        "l2": "no flush needed: each step streams the selected records of 48 different layers (GBs per step, 43.5 GB resident) through a 126 MB L2",
-        "accumulate": "f32", "weights": "q4_g64",
-    }
+        return {"workload": f"benchmark configuration 3: prefill grouped GEMM, {shape}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router with an "
+                            f"additive Zipf(s=1.1) per-expert logit bias, sequence of {tokens} tokens per GPU, {glue}",
+                "tokens_per_gpu": tokens, "layers": cfg.layers, "parallelism": replicas,
+                "l2": "no flush needed: every layer streams its active records (43.5 GB resident) through a 126 MB L2",
+                "accumulate": "f32", "weights": "q4_g64: exact integer codes on tcgen05.mma (FP16 operands, FP32 TMEM accumulators), scale and bias applied in FP32"}
+    if kind == "mixed":
+        return {"workload": f"benchmark configuration 4: mixed 4/8-bit continuous batching, {shape}, gate/up affine-Q4 g64 and down affine-Q8 g64 (int8), "
+                            f"fp16 scale/bias, ragged batch of 32 requests with seeded lengths 1..512 = {tokens} tokens, {glue}",
+                "tokens_per_gpu": tokens, "layers": cfg.layers, "parallelism": replicas,
+                "l2": "no flush needed: every layer streams its active records (56 GB resident) through a 126 MB L2",
+                "accumulate": "f32", "weights": "gate/up q4_g64, down q8_g64"}
+    return {"workload": f"benchmark configuration 2: decode MoE stack, {shape}, affine-Q4 g64 fp16 scale/bias, bf16 activations, fp32 router, "
+                        f"batch of {tokens} tokens per GPU, {glue}",
+            "tokens_per_gpu": tokens, "layers": cfg.layers, "parallelism": replicas,
+            "l2": "no flush needed: each step streams the selected records of 48 different layers (GBs per step, 43.5 GB resident) through a 126 MB L2",
+            "accumulate": "f32", "weights": "q4_g64"}
+
+
+def _peaks_file():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    return json.load(open(path)) if os.path.exists(path) else None
 
 
 def peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        p = json.load(open(path))
+    p = _peaks_file()
+    if p:
         return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
 def tensor_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        p = json.load(open(path))
+    p = _peaks_file()
+    if p:
         return float(p["bf16_tflops"]), float(p["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops burst / sustained)"
     return 1590.0, 1400.0, "fallback (1.59 PFLOP/s burst, earlier measurement on this pool)"
 
@@ -84,9 +108,7 @@ def tensor_peak():
 def ncu_traffic():
     """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if there is one."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(path):
-        return json.load(open(path))
-    return {}
+    return json.load(open(path)) if os.path.exists(path) else {}
 
 
 class ClockSampler:
@@ -128,6 +150,9 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+# ---------------------------------------------------------------------------------------------------------
+# CPU checker legs (parity gates and the CPU baseline): the only users of oracle/ in this file
+# ---------------------------------------------------------------------------------------------------------
 def rms_glue(out):
     """The inter-layer stand-in of the chained stack, on the CPU: bf16((out - mean) / std) per token."""
     from oracle import oracle
@@ -150,8 +175,10 @@ def cpu_layer(cfg, layer, x, cache, bias=None):
     for e in np.unique(ids):
         if e >= 0:
             records[e] = cache.setdefault(("record", layer, int(e)), synth.record(cfg, SEED, layer, int(e)))
-    shared = cache.setdefault(("shared", layer), synth.record(cfg, SEED, layer, synth.SHARED_EXPERT))
-    gate = cache.setdefault(("gate", layer), synth.shared_gate(cfg, SEED, layer))
+    shared = gate = None
+    if cfg.has_shared:
+        shared = cache.setdefault(("shared", layer), synth.record(cfg, SEED, layer, synth.SHARED_EXPERT))
+        gate = cache.setdefault(("gate", layer), synth.shared_gate(cfg, SEED, layer))
     t0 = time.perf_counter()
     res = oracle.moe_layer(cfg.as_dict(), records, router, x, shared_record=shared, shared_gate_w=gate, router_bias=bias)
     return res, time.perf_counter() - t0
@@ -159,22 +186,58 @@ def cpu_layer(cfg, layer, x, cache, bias=None):
 
 def cpu_sample(cfg, tokens, sample_layers, cache):
     """Chained CPU run over the first `sample_layers` layers; returns seconds of arithmetic (generation excluded)."""
+    from oracle import oracle
     x = synth.activations(cfg, SEED, 0, tokens)
     total = 0.0
     for layer in range(sample_layers):
         res, dt = cpu_layer(cfg, layer, x, cache)
         total += dt
-        x = rms_glue(oracle_bf(res["out"]))
+        x = rms_glue(oracle.bf(res["out"]))
     return total
 
 
-def oracle_bf(a):
+def parity_gate(torch, cfg, tokens, x_np, bias=None, out_bf16=None, checked=64, routing=None, runner=None):
+    """Layer 0 against the CPU checker, outside every timed region. The device result comes from a one-layer handle of
+    the same geometry and weights whose output dtype is FP32, so that the stated tolerance (max-abs error <= 2e-3 x
+    output RMS) is applied as it stands; the error of the benchmark handle's BF16 output is reported beside it.
+    `runner(x_dev) -> (out fp32 numpy, routing dict)` replaces the one-layer handle (expert-parallel runs)."""
     from oracle import oracle
-    return oracle.bf(a)
+    from zerocool_b200.moe import Moe
+    checked = min(tokens, checked)
+    if runner is None:
+        c32 = MoeConfig(**{**cfg.__dict__, "layers": 1, "out_dtype": F32, "max_tokens": tokens})
+        m32 = Moe(c32, torch.cuda.current_device())
+        m32.synth_fill_layer(0, SEED)
+        if bias is not None:
+            m32.set_router_bias(0, bias)
+        x_dev = torch.from_numpy(x_np).to(device="cuda", dtype=torch.bfloat16)
+        got = m32.moe(0, x_dev).float().cpu().numpy()
+        routing = m32.last_routing(tokens)
+        status = m32.status()
+        m32.close()
+    else:
+        got, routing, status = runner()
+    want, _ = cpu_layer(cfg, 0, x_np[:checked], {}, bias)
+    ids_all = routing["ids"]
+    offsets, perm = oracle.permute(want["ids"] if checked == tokens else ids_all, cfg.experts)    # long batches: from the device's own (checked) ids
+    rms = float(np.sqrt(np.mean(want["out"].astype(np.float64) ** 2)))
+    err = float(np.abs(got[:checked] - want["out"]).max() / rms)
+    parity = {
+        "layer": 0, "tokens": tokens, "tokens_checked_against_cpu": checked,
+        "ids_bit_exact": bool(np.array_equal(ids_all[:checked], want["ids"])),
+        "perm_bit_exact": bool(np.array_equal(routing["perm"], perm) and np.array_equal(routing["offsets"], offsets)),
+        "max_abs_err_over_rms": err, "within_tolerance": bool(err <= TOL), "device_status": int(status),
+        "tolerance": "max-abs error <= 2e-3 x output RMS on an FP32-output handle of the same geometry and weights",
+    }
+    if out_bf16 is not None:
+        parity["max_abs_err_over_rms_bf16_output"] = float(np.abs(out_bf16[:checked] - want["out"]).max() / rms)
+    if not (parity["ids_bit_exact"] and parity["perm_bit_exact"] and parity["within_tolerance"] and status == 0):
+        raise RuntimeError(f"parity gate failed: {parity}")
+    return parity
 
 
 def run_reference(args):
-    """The reference arm: the CPU implementation of the path (the port under oracle/ — the reference's native
+    """The reference arm: the CPU implementation of the path (the port under oracle/ - the reference's native
     code is Apple Metal and cannot be built here), all host threads, on a bounded sample of the same workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -204,6 +267,9 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------------------
+# Device-side measurement helpers
+# ---------------------------------------------------------------------------------------------------------
 def time_steps(torch, fn, steps, dist):
     if dist is not None:
         dist.barrier()
@@ -226,79 +292,194 @@ def time_steps(torch, fn, steps, dist):
 
 def layer_bytes(cfg, active, tokens):
     """Algorithmic bytes of one layer: (U + S) records + the router matrix + activations in and out."""
-    a = 2
-    return (active + cfg.has_shared) * cfg.record_bytes + cfg.experts * cfg.hidden * 4 + tokens * cfg.hidden * 2 * a
+    return (active + cfg.has_shared) * cfg.record_bytes + cfg.experts * cfg.hidden * 4 + tokens * cfg.hidden * 2 * 2
 
 
-def run_ep(args):
-    """benchmark configuration 5: expert-parallel stack on N GPUs (hidden 4096, 512 experts top-10 sharded 512/N per GPU,
-    ffn 512, Q4 g64), 256-token decode batch split over the ranks, NCCL all-to-all dispatch/combine."""
-    import torch
-    import torch.distributed as dist
-    from zerocool_b200.ep import ExpertParallel
-    from zerocool_b200.moe import Moe
-    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
-    if world < 2:
-        raise RuntimeError("--workload ep needs at least two ranks (torch.distributed.run --nproc-per-node N)")
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    total_tokens = args.tokens
-    t_local = total_tokens // world
-    per = 512 // world
-    cfg = MoeConfig(hidden=4096, ffn=512, experts=512, top_k=10, layers=args.layers, meta_dtype=F16, act_dtype=BF16, out_dtype=BF16,
-                    router_dtype=F32, has_shared=0, max_tokens=t_local, first_expert=rank * per, local_experts=per)
-    m = Moe(cfg, local)
+def kernel_profile(m, run, steps):
+    """Per-kernel device times over `steps` eager passes (event pairs around every launch)."""
+    run()
+    m._torch.cuda.synchronize()
+    m.profile_begin()
+    for _ in range(steps):
+        run()
+    prof = m.profile_end()
+    total = sum(v[0] for v in prof.values()) or 1.0
+    return {k: {"launches": n, "avg_us": 1e3 * t / max(n, 1), "share": t / total} for k, (t, n) in prof.items() if n}
+
+
+def fill(m, cfg, biased=False):
+    biases = {}
     for layer in range(cfg.layers):
         m.synth_fill_layer(layer, SEED)
-    torch.cuda.synchronize()
-    ep = ExpertParallel(m, cfg.experts, rank, world, dist)
-    x0 = torch.from_numpy(synth.activations(cfg, SEED + rank, 0, t_local)).to(device="cuda", dtype=torch.bfloat16)
-    rows_moved = [0]
+        if biased:
+            biases[layer] = synth.zipf_router_bias(cfg, SEED, layer)
+            m.set_router_bias(layer, biases[layer])
+    m._torch.cuda.synchronize()
+    return biases
 
-    def step():
-        x = x0
-        for layer in range(cfg.layers):
-            out = ep.moe(layer, x)
-            rows_moved[0] += ep.last_plan["rows_sent"]
-            if layer + 1 < cfg.layers:
-                f = out.float()
-                d = f - f.mean(-1, keepdim=True)
-                x = (d * torch.rsqrt((d * d).mean(-1, keepdim=True))).to(torch.bfloat16)
-        return out
 
-    for _ in range(args.warmup):
-        out = step()
-    before, rows_moved[0] = m.launches, 0
-    sampler = ClockSampler(local) if rank == 0 else None
-    ms = time_steps(torch, step, args.steps, dist)
-    clocks = sampler.stop() if sampler else None
-    launches = m.launches - before
-    finite = bool(torch.isfinite(out.float()).all())
+def make_inputs(torch, cfg, tokens, rank):
+    x = synth.activations(cfg, SEED + rank, 0, tokens)
+    host = torch.from_numpy(x).to(torch.bfloat16).pin_memory()
+    return x, host, host.cuda()
+
+
+def measure_long_batch(torch, m, cfg, tokens, steps, warmup, kind, biases, skip_parity):
+    """Configurations 3 and 4 on one GPU: the chained stack over one long batch (the tensor-core family)."""
     hbm_peak, peak_source = peaks()
-    active = torch.tensor([float(m.active_counts().mean())], device="cuda")
-    dist.all_reduce(active)
-    if rank == 0:
-        value = total_tokens / (ms * 1e-3)
-        # algorithmic bytes of the whole job per step: distinct experts touched on every rank x record bytes + router on every rank
-        step_bytes = cfg.layers * (float(active.item()) * cfg.record_bytes + world * cfg.experts * cfg.hidden * 4 + total_tokens * cfg.hidden * 4)
-        line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"benchmark configuration 5: expert-parallel stack, {cfg.layers} layers, hidden 4096, 512 experts top-10 ({per} per GPU), ffn 512, "
-                                   f"affine-Q4 g64, {total_tokens}-token decode batch ({t_local} per GPU), NCCL all-to-all dispatch/combine, "
-                                   "layers chained through bf16((out-mean)/std)",
-                       "parallelism": f"ep{world}", "tokens_total": total_tokens, "layers": cfg.layers,
-                       "l2": "no flush needed: each rank streams its selected records of 48 layers (GBs per step)"},
-            "gpu_launches": int(launches), "clocks": clocks, "finite": finite,
-            "roofline_step": {"bound": "hbm", "achieved": step_bytes / (ms * 1e-3) / 1e9 / world, "peak": hbm_peak, "unit": "GB/s per GPU",
-                              "frac": step_bytes / (ms * 1e-3) / 1e9 / world / hbm_peak, "peak_source": peak_source,
-                              "mean_active_experts_all_ranks": float(active.item())},
-            "nvlink_rows_per_step_rank0": rows_moved[0] / max(args.steps, 1),
-            "e2e": None, "cpu_baseline": None,
-        }
-        print(json.dumps(line), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
+    burst, sustained, tsource = tensor_peak()
+    x_np, _, x_dev = make_inputs(torch, cfg, tokens, 0)
+    out_dev = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device="cuda")
+    parity = None
+    if not skip_parity:
+        got16 = m.moe(0, x_dev).float().cpu().numpy()
+        parity = parity_gate(torch, cfg, tokens, x_np, biases.get(0), out_bf16=got16)
+    for _ in range(warmup):
+        m.stack(x_dev, out_dev)
+    before = m.launches
+    ms = time_steps(torch, lambda: m.stack(x_dev, out_dev), steps, None)
+    launches = m.launches - before
+    active = m.active_counts()
+    if not bool(torch.isfinite(out_dev.float()).all()):
+        raise RuntimeError("the chained stack produced non-finite values")
+    kernels = kernel_profile(m, lambda: m.stack_eager(x_dev, out_dev), min(steps, 3))
+    rows = tokens * (cfg.top_k + cfg.has_shared)
+    flops = {"prefill_gate_up": 2.0 * rows * 2 * cfg.ffn * cfg.hidden, "prefill_down": 2.0 * rows * cfg.hidden * cfg.ffn,
+             "gate_up": 2.0 * rows * 2 * cfg.ffn * cfg.hidden, "down": 2.0 * rows * cfg.hidden * cfg.ffn}
+    expert_kernels = [k for k in kernels if k in flops]
+    dominant = max(expert_kernels, key=lambda k: kernels[k]["share"])
+    tf = flops[dominant] / (kernels[dominant]["avg_us"] * 1e-6) / 1e12
+    step_flops = cfg.layers * 6.0 * rows * cfg.hidden * cfg.ffn
+    step_bytes = float(sum(layer_bytes(cfg, int(a), tokens) for a in active))
+    return {
+        "config": workload(cfg, tokens, 1, kind), "tokens": tokens, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+        "tokens_per_s": tokens / (ms * 1e-3), "gpu_launches": int(launches), "mean_active_experts": float(np.mean(active)),
+        "family": {k: ("tcgen05 grouped GEMM" if k.startswith("prefill") else "mma.sync GEMV family") for k in expert_kernels},
+        "roofline": {"bound": "tensor", "kernel": dominant, "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst,
+                     "frac_of_sustained": tf / sustained, "peak_source": tsource, "algorithmic_flops_per_launch": flops[dominant],
+                     "avg_launch_us": kernels[dominant]["avg_us"], "traffic": None,
+                     "definition": "2 x routed-and-shared rows x output columns x K of this launch (useful flops; padded token columns and the "
+                                   "bias-correction stages are not counted)"},
+        "roofline_step": {"tensor_tflops": step_flops / (ms * 1e-3) / 1e12, "frac_of_tensor_peak": step_flops / (ms * 1e-3) / 1e12 / burst,
+                          "hbm_gbs": step_bytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": step_bytes / (ms * 1e-3) / 1e9 / hbm_peak,
+                          "algorithmic_flops_per_step": step_flops, "algorithmic_bytes_per_step": step_bytes, "peak_source": peak_source},
+        "kernels": kernels, "parity": parity,
+    }
+
+
+def measure_ep(torch, dist, rank, world, local, layers, total_tokens, steps, warmup, skip_parity):
+    """Configuration 5: hidden 4096, 512 experts top-10 (512/N per GPU), ffn 512, Q4 g64, one 256-token decode batch.
+    N >= 2: expert parallel, rows and results exchanged by peer stores over NVLink (falls back to the NCCL all-to-all
+    with host-read split sizes if the windows cannot be mapped). N = 1: one GPU holds all 87 GB (the comparison point)."""
+    from zerocool_b200.moe import Moe
+    hbm_peak, peak_source = peaks()
+    t_local = total_tokens // world
+    cfg = config5(layers, t_local, rank, world)
+    m = Moe(cfg, local)
+    fill(m, cfg)
+    x_np, _, x_dev = make_inputs(torch, cfg, t_local, rank)
+    out_dev = torch.empty((t_local, cfg.hidden), dtype=torch.bfloat16, device="cuda")
+    transport, run, run_eager, layer0 = "none (one GPU holds every expert)", None, None, None
+    if world > 1:
+        from zerocool_b200.ep import ExpertParallel, PeerExpertParallel
+        try:
+            peer = PeerExpertParallel(m, dist)
+            attached = 1
+        except (RuntimeError, ValueError) as exc:
+            attached, why = 0, str(exc)
+        flag = torch.tensor([attached], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()):
+            transport = "peer stores into mapped windows (NVLink), flags with bounded waits, no host value per layer; 48 layers replayed from one CUDA graph"
+            run = lambda: m.ep_stack(x_dev, out_dev)                       # noqa: E731
+            run_eager = lambda: m.ep_stack(x_dev, out_dev, eager=True)     # noqa: E731
+            layer0 = lambda: m.ep_layer(0, x_dev)                          # noqa: E731
+        else:
+            transport = "NCCL all_to_all_single with split sizes read on the host (two host synchronisations per layer)" + (f"; peer windows unavailable: {why}" if not attached else "")
+            ep = ExpertParallel(m, cfg.experts, rank, world, dist)
+
+            def run():
+                x = x_dev
+                for layer in range(cfg.layers):
+                    out = ep.moe(layer, x)
+                    if layer + 1 < cfg.layers:
+                        f = out.float()
+                        d = f - f.mean(-1, keepdim=True)
+                        x = (d * torch.rsqrt((d * d).mean(-1, keepdim=True))).to(torch.bfloat16)
+                out_dev.copy_(out)
+            run_eager = None
+            layer0 = lambda: ep.moe(0, x_dev)                              # noqa: E731
+    else:
+        run = lambda: m.stack(x_dev, out_dev)                              # noqa: E731
+        run_eager = lambda: m.stack_eager(x_dev, out_dev)                  # noqa: E731
+        layer0 = lambda: m.moe(0, x_dev)                                   # noqa: E731
+
+    # ---- parity: layer 0 of this rank's tokens against the CPU checker (rank 0 checks; every rank runs the layer) ----
+    parity = None
+    if not skip_parity:
+        got16 = layer0().float().cpu().numpy()
+        routing = m.last_routing(t_local)
+        status = m.status()
+        if rank == 0:
+            from oracle import oracle
+            checked = min(t_local, 16)
+            want, _ = cpu_layer(cfg, 0, x_np[:checked], {})
+            rms = float(np.sqrt(np.mean(want["out"].astype(np.float64) ** 2)))
+            err = np.abs(got16[:checked] - want["out"])
+            offsets, perm = oracle.permute(routing["ids"], cfg.experts)
+            parity = {"layer": 0, "tokens_checked_against_cpu": checked,
+                      "ids_bit_exact": bool(np.array_equal(routing["ids"][:checked], want["ids"])),
+                      "perm_bit_exact": bool(np.array_equal(routing["perm"], perm) and np.array_equal(routing["offsets"], offsets)),
+                      "max_abs_err_over_rms_bf16_output": float(err.max() / rms),
+                      "within_tolerance": bool(np.all(err <= TOL * rms + np.abs(want["out"]) * 2.0 ** -8)), "device_status": int(status),
+                      "tolerance": "2e-3 x RMS + one bf16 rounding of this handle's bf16 output (the FP32-output bound is applied by the tests)"}
+            if not (parity["ids_bit_exact"] and parity["perm_bit_exact"] and parity["within_tolerance"] and status == 0):
+                raise RuntimeError(f"expert-parallel parity gate failed: {parity}")
+
+    for _ in range(warmup):
+        run()
+    before = m.launches
+    ms = time_steps(torch, run, steps, dist)
+    launches = m.launches - before
+    status = m.status()
+    finite = bool(torch.isfinite(out_dev.float()).all())
+    if not finite or status:
+        raise RuntimeError(f"expert-parallel stack: finite={finite}, device status {status}")
+    active = (m.ep_active_counts() if world > 1 else m.active_counts()).astype(np.float64)
+    ids_last = m.last_routing(t_local)["ids"]
+    per = cfg.experts // world
+    remote_rows = int(np.sum((ids_last // per) != rank)) if world > 1 else 0
+    kernels = kernel_profile(m, run_eager, min(steps, 3)) if run_eager is not None else {}
+    my_bytes = float(sum(a * cfg.record_bytes + cfg.experts * cfg.hidden * 4 + t_local * cfg.hidden * 4 for a in active))
+    stats = torch.tensor([my_bytes, float(active.mean()), float(remote_rows)], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(stats)
+    m.close()
+    if rank != 0:
+        return None
+    total_bytes, active_sum, remote_sum = (float(v) for v in stats.tolist())
+    row_bytes = cfg.hidden * 2
+    ep_kinds = {k: v for k, v in kernels.items() if k == "ep"}
+    return {
+        "config": {"workload": f"benchmark configuration 5: expert-parallel full stack, {cfg.layers} layers, hidden 4096, 512 experts top-10 ({per} per GPU), "
+                               f"ffn 512, affine-Q4 g64, {total_tokens}-token decode batch ({t_local} per GPU), layers chained through bf16((out-mean)/std)",
+                   "parallelism": f"ep{world}" if world > 1 else "one GPU, all 512 experts resident (87 GB)", "tokens_total": total_tokens,
+                   "layers": cfg.layers, "transport": transport,
+                   "l2": "no flush needed: each rank streams its selected records of 48 layers (GBs per step)"},
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms, "tokens_per_s": total_tokens / (ms * 1e-3), "scaling": "strong",
+        "gpu_launches_rank0": int(launches),
+        "roofline_step": {"bound": "hbm", "achieved": total_bytes / (ms * 1e-3) / 1e9 / world, "peak": hbm_peak, "unit": "GB/s per GPU",
+                          "frac": total_bytes / (ms * 1e-3) / 1e9 / world / hbm_peak, "peak_source": peak_source,
+                          "mean_active_experts_all_ranks": active_sum,
+                          "definition": "per rank: experts of its range that received rows x record bytes + its router matrix + its activations in/out, summed "
+                                        "over ranks and layers, divided by the step time and by N"},
+        "nvlink": {"remote_rows_per_layer_all_ranks": remote_sum, "bytes_per_layer_all_ranks": remote_sum * (row_bytes + cfg.hidden * 4 + 8),
+                   "definition": "rows whose expert lives on another rank (last layer's routing): bf16 row + 8-byte tag out, fp32 result row back"},
+        "kernels_rank0": kernels, "exchange_share_rank0": sum(v["share"] for v in ep_kinds.values()) if kernels else None,
+        "exchange_note": "kind 'ep' = send, receive (includes the wait for the slowest sender), return and the wait for results; event-timed "
+                         "eager launches on rank 0" if kernels else None,
+        "parity": parity,
+    }
 
 
 def run_ours(args):
@@ -315,51 +496,56 @@ def run_ours(args):
         d.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = d
     from zerocool_b200.moe import Moe
-    prefill = args.workload == "prefill"
-    cfg = config(args.layers, args.tokens if prefill else max(BATCHES + (args.tokens,)))
-    m = Moe(cfg, local)
-    biases = {}
-    for layer in range(cfg.layers):
-        m.synth_fill_layer(layer, SEED)
-        if prefill:
-            biases[layer] = synth.zipf_router_bias(cfg, SEED, layer)
-            m.set_router_bias(layer, biases[layer])
-    torch.cuda.synchronize()
     hbm_peak, peak_source = peaks()
 
+    if args.workload == "ep":
+        ep = measure_ep(torch, dist, rank, world, local, args.layers, args.tokens, args.steps, args.warmup, args.skip_parity)
+        if rank == 0:
+            line = {"metric": METRIC, "value": ep["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                    "ms_per_step": ep["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "config": ep["config"], "gpu_launches": ep["gpu_launches_rank0"], "ep": ep, "e2e": None, "cpu_baseline": None}
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    if args.workload in ("prefill", "mixed"):
+        if world > 1:
+            raise RuntimeError("--workload prefill / mixed run on one GPU")
+        if args.workload == "mixed":
+            tokens = int(mixed_lengths().sum())
+            cfg = config(args.layers, tokens, down_bits=8, q8_signed=1)
+        else:
+            tokens = args.tokens
+            cfg = config(args.layers, tokens)
+        m = Moe(cfg, local)
+        biases = fill(m, cfg, biased=args.workload == "prefill")
+        sampler = ClockSampler(local)
+        rec = measure_long_batch(torch, m, cfg, tokens, args.steps, args.warmup, args.workload, biases, args.skip_parity)
+        clocks = sampler.stop()
+        line = {"metric": METRIC, "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": rec["config"], "gpu_launches": rec["gpu_launches"], "clocks": clocks, "roofline": rec["roofline"],
+                "roofline_step": rec["roofline_step"], "kernels": rec["kernels"], "parity": rec["parity"], "e2e": None, "cpu_baseline": None}
+        print(json.dumps(line), flush=True)
+        return
+
+    # ---- default: benchmark configuration 2 (the headline) + the other configurations as sub-records -------------
+    extras = world == 1 and not args.skip_extras
+    cfg = config(args.layers, max(BATCHES + (args.tokens,) + ((8192,) if extras else ())))
+    m = Moe(cfg, local)
+    fill(m, cfg)
+
     def inputs(tokens):
-        x = synth.activations(cfg, SEED + rank, 0, tokens)
-        host = torch.from_numpy(x).to(torch.bfloat16).pin_memory()
-        return x, host, host.cuda()
+        return make_inputs(torch, cfg, tokens, rank)
 
     # ---- parity gate, outside every timed region: layer 0 against the CPU checker -------------------
     parity = None
     if rank == 0 and not args.skip_parity:
-        from oracle import oracle
         x_np, _, x_dev = inputs(args.tokens)
-        got = m.moe(0, x_dev).float().cpu().numpy()
-        routing = m.last_routing(args.tokens)
-        checked = min(args.tokens, 64)          # tokens are independent: the checker runs the first 64 of a long batch
-        want, _ = cpu_layer(cfg, 0, x_np[:checked], {}, biases.get(0))
-        got = got[:checked]
-        ids_all = routing["ids"]
-        routing = dict(routing, ids=ids_all[:checked])
-        if checked == args.tokens:
-            offsets, perm = oracle.permute(want["ids"], cfg.experts)
-        else:                                   # permutation of the whole batch from the device's own (checked below) ids
-            offsets, perm = oracle.permute(ids_all, cfg.experts)
-        rms = float(np.sqrt(np.mean(want["out"].astype(np.float64) ** 2)))
-        bound = 2e-3 * rms + np.abs(want["out"]) * 2.0 ** -8          # tolerance + one bf16 rounding of the output
-        parity = {
-            "layer": 0, "tokens": args.tokens, "tokens_checked_against_cpu": checked,
-            "ids_bit_exact": bool(np.array_equal(routing["ids"], want["ids"])),
-            "perm_bit_exact": bool(np.array_equal(routing["perm"], perm) and np.array_equal(routing["offsets"], offsets)),
-            "max_abs_err_over_rms": float(np.abs(got - want["out"]).max() / rms),
-            "within_tolerance": bool(np.all(np.abs(got - want["out"]) <= bound)),
-            "tolerance": "2e-3 x RMS + one bf16 rounding of the bf16 output",
-        }
-        if not (parity["ids_bit_exact"] and parity["perm_bit_exact"] and parity["within_tolerance"]):
-            raise RuntimeError(f"parity gate failed: {parity}")
+        got16 = m.moe(0, x_dev).float().cpu().numpy()
+        parity = parity_gate(torch, cfg, args.tokens, x_np, out_bf16=got16)
 
     # ---- timed region: K graph replays of the chained stack, inputs resident in HBM ------------------
     def measure(tokens, steps, warmup):
@@ -392,44 +578,47 @@ def run_ours(args):
            "h2d_bytes_per_step": host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
            "call": "zc_moe_stack_host (pinned host buffers; copies and the wait inside the timed region)"}
 
+    # ---- the same boundary called layer by layer, the way a per-layer binding of Model::moe would call it -----------
+    def per_layer_blocking():
+        for layer in range(cfg.layers):
+            m.moe_host(layer, host, out_host)
+            m.status()
+
+    def per_layer_async():
+        for layer in range(cfg.layers):
+            m.moe_host_async(layer, host, out_host)
+        m.status()
+
+    e2e_per_layer = {}
+    for name, fn in (("blocking", per_layer_blocking), ("async", per_layer_async)):
+        for _ in range(3):
+            fn()
+        t = time_steps(torch, fn, max(args.steps // 2, 5), dist)
+        e2e_per_layer[name] = {"ms_per_step": t, "tokens_per_s": tokens_total / (t * 1e-3)}
+    e2e_per_layer["definition"] = ("48 x zc_moe_forward_host (+ zc_moe_status) with pinned host activations in and out of every layer, no inter-layer glue: "
+                                   "'blocking' waits after every layer (96 host round trips per step); 'async' = zc_moe_forward_host_async with one wait at the end")
+    e2e_per_layer["h2d_bytes_per_step"] = host.numel() * 2 * cfg.layers
+    e2e_per_layer["d2h_bytes_per_step"] = out_host.numel() * 2 * cfg.layers
+
     # ---- per-kernel device times over the same K steps (eager launches bracketed by CUDA events) --------
-    m.stack_eager(x_dev, out_dev)
-    torch.cuda.synchronize()
-    m.profile_begin()
-    for _ in range(args.steps):
-        m.stack_eager(x_dev, out_dev)
-    prof = m.profile_end()
-    total_prof = sum(v[0] for v in prof.values()) or 1.0
-    kernels = {k: {"launches": n, "avg_us": 1e3 * t / max(n, 1), "share": t / total_prof} for k, (t, n) in prof.items() if n}
+    kernels = kernel_profile(m, lambda: m.stack_eager(x_dev, out_dev), args.steps)
     dominant = max(kernels, key=lambda k: kernels[k]["share"])
     active_eager = m.active_counts()
     mean_items = float(np.mean(active_eager)) + cfg.has_shared
     proj = {"gate_up": cfg.projection_bytes(0) + cfg.projection_bytes(1), "down": cfg.projection_bytes(2)}
     act_bytes = {"gate_up": args.tokens * cfg.hidden * 2, "down": args.tokens * cfg.hidden * 2}
-    if dominant in proj:
-        alg = mean_items * proj[dominant] + act_bytes[dominant]
-    else:
-        alg = step_bytes / cfg.layers
+    kernel_rooflines = {}
+    for k in proj:
+        if k in kernels:
+            alg = mean_items * proj[k] + act_bytes[k]
+            gbs = alg / (kernels[k]["avg_us"] * 1e-6) / 1e9
+            kernel_rooflines[k] = {"achieved": gbs, "frac": gbs / hbm_peak, "algorithmic_bytes_per_launch": alg, "avg_launch_us": kernels[k]["avg_us"]}
+    alg = mean_items * proj[dominant] + act_bytes[dominant] if dominant in proj else step_bytes / cfg.layers
     achieved = alg / (kernels[dominant]["avg_us"] * 1e-6) / 1e9
-    traffic = ncu_traffic().get(dominant)
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                "traffic": traffic, "peak_source": peak_source, "algorithmic_bytes_per_launch": alg,
-                "avg_launch_us": kernels[dominant]["avg_us"],
+                "traffic": ncu_traffic().get(dominant), "peak_source": peak_source, "algorithmic_bytes_per_launch": alg,
+                "avg_launch_us": kernels[dominant]["avg_us"], "other_kernels": {k: v for k, v in kernel_rooflines.items() if k != dominant},
                 "definition": "(distinct routed experts of the layer + shared) x projection bytes of this kernel + activation bytes, averaged over the layers"}
-    if prefill:
-        burst, sustained, tsource = tensor_peak()
-        rows = args.tokens * (cfg.top_k + cfg.has_shared)
-        flops = {"prefill_gate_up": 2.0 * rows * 2 * cfg.ffn * cfg.hidden, "prefill_down": 2.0 * rows * cfg.hidden * cfg.ffn}
-        if dominant in flops:
-            tf = flops[dominant] / (kernels[dominant]["avg_us"] * 1e-6) / 1e12
-            roofline = {"bound": "tensor", "kernel": dominant, "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst,
-                        "traffic": traffic, "peak_source": tsource, "algorithmic_flops_per_launch": flops[dominant],
-                        "avg_launch_us": kernels[dominant]["avg_us"], "frac_of_sustained": tf / sustained,
-                        "definition": "2 x routed-and-shared rows x output columns x K of this launch (useful flops; token tiles are "
-                                      "padded to 16 columns and two correction stages per tile are not counted)",
-                        "hbm_gbs_of_this_launch": mean_items * proj["gate_up" if dominant == "prefill_gate_up" else "down"] / (kernels[dominant]["avg_us"] * 1e-6) / 1e9,
-                        "hbm_note": "distinct active experts x projection bytes over the launch time: with the Zipf bias few experts are active, "
-                                    "so this launch is bound by the tensor / shared-memory pipeline, not by HBM"}
     step_achieved = step_bytes / (ms * 1e-3) / 1e9
     roofline_step = {"bound": "hbm", "achieved": step_achieved, "peak": hbm_peak, "unit": "GB/s", "frac": step_achieved / hbm_peak,
                      "algorithmic_bytes_per_step": step_bytes,
@@ -437,12 +626,7 @@ def run_ours(args):
 
     # ---- the other decode batch sizes of the configuration (same stack, fewer steps) -------------------
     batches = {}
-    if prefill:
-        burst, sustained, _ = tensor_peak()
-        step_flops = cfg.layers * 6.0 * args.tokens * (cfg.top_k + cfg.has_shared) * cfg.hidden * cfg.ffn
-        roofline_step.update({"tensor_tflops": step_flops / (ms * 1e-3) / 1e12, "frac_of_tensor_peak": step_flops / (ms * 1e-3) / 1e12 / burst,
-                              "algorithmic_flops_per_step": step_flops})
-    if not args.skip_batches and not prefill:
+    if not args.skip_batches:
         for t in BATCHES:
             if t == args.tokens:
                 bms, act = ms, active
@@ -454,7 +638,7 @@ def run_ours(args):
 
     # ---- CPU baseline on this machine's host cores, bounded sample ------------------------------------
     cpu = None
-    if rank == 0 and world == 1 and not args.skip_cpu and not prefill:
+    if rank == 0 and world == 1 and not args.skip_cpu:
         from oracle import oracle
         cache = {}
         cpu_sample(cfg, args.tokens, args.cpu_layers, cache)
@@ -464,14 +648,42 @@ def run_ours(args):
                "sample": f"layers 0..{args.cpu_layers - 1} of {cfg.layers} chained, {args.tokens} tokens, scaled by {cfg.layers}/{args.cpu_layers}; "
                          f"{seconds:.1f} s of CPU arithmetic"}
 
+    # ---- the other configurations of the specification, as sub-records of the same line ---------------------------
+    prefill = mixed = ep = None
+    if extras:
+        prefill = {}
+        biases = {}
+        for layer in range(cfg.layers):
+            biases[layer] = synth.zipf_router_bias(cfg, SEED, layer)
+            m.set_router_bias(layer, biases[layer])
+        for t in (2048, 8192):
+            prefill[str(t)] = measure_long_batch(torch, m, cfg, t, 3, 3, "prefill", biases, args.skip_parity)
+    m.close()
+    del m
+    if extras:
+        tokens4 = int(mixed_lengths().sum())
+        cfg4 = config(args.layers, tokens4, down_bits=8, q8_signed=1)
+        m4 = Moe(cfg4, local)
+        fill(m4, cfg4)
+        mixed = measure_long_batch(torch, m4, cfg4, tokens4, 3, 3, "mixed", {}, args.skip_parity)
+        mixed["request_lengths"] = [int(v) for v in mixed_lengths()]
+        m4.close()
+        del m4
+    if not args.skip_ep:
+        ep = measure_ep(torch, dist, rank, world, local, args.layers, 256, 10 if world > 1 else 5, 3, args.skip_parity)
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload(cfg, args.tokens, world, args.workload), "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "config": workload(cfg, args.tokens, world), "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "roofline": roofline, "roofline_step": roofline_step, "kernels": kernels, "cpu_baseline": cpu, "batches": batches,
-            "parity": parity, "mean_active_experts": float(np.mean(active)),
+            "parity": parity, "mean_active_experts": float(np.mean(active)), "e2e_per_layer": e2e_per_layer,
+            "prefill": prefill, "mixed": mixed, "ep": ep,
         }
+        if world > 1:
+            line["config"]["parallelism"] = (f"value / e2e: dp{world}, independent replicas of configuration 2, tokens sharded, no data-path collective; "
+                                             f"the `ep` record of this line is configuration 5 expert-parallel over the same {world} GPUs")
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -484,14 +696,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep"],
-                    help="decode: benchmark configuration 2 (the headline); prefill: config 3 (grouped GEMM, Zipf-skewed loads)")
-    ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU: decode 1/4/16/64 (default 64), prefill 2048/8192 (default 2048)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "mixed", "ep"],
+                    help="decode: benchmark configuration 2 (the headline) with configurations 3, 4 and 5 as sub-records; "
+                         "prefill / mixed / ep: configuration 3 / 4 / 5 alone")
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU: decode 1/4/16/64 (default 64), prefill 2048/8192 (default 2048); ep: total (256)")
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--cpu-layers", type=int, default=8, help="layers of the stack the CPU baseline runs (scaled to 48)")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-parity", action="store_true")
     ap.add_argument("--skip-batches", action="store_true")
+    ap.add_argument("--skip-extras", action="store_true", help="leave out the prefill and mixed sub-records (one-GPU runs)")
+    ap.add_argument("--skip-ep", action="store_true", help="leave out the configuration-5 sub-record")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -500,8 +715,6 @@ def main():
     if args.impl == "reference":
         args.cpu_layers = min(args.cpu_layers, 2)
         run_reference(args)
-    elif args.workload == "ep":
-        run_ep(args)
     else:
         run_ours(args)
 

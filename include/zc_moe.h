@@ -15,9 +15,20 @@
  *    passed as void* (NULL = the legacy default stream).
  *  - One host thread drives a handle at a time (the reference's single-coordinator rule,
  *    include/engine/metal.hpp:45-47).
- *  - All arguments are validated on the host before anything is launched. Conditions only the device
- *    can see (a token whose router scores select fewer than top_k experts) set a status word read by
- *    zc_moe_status(), like the reference's sparse_status_ (src/engine/model.cpp:118-120).
+ *  - All arguments are validated on the host before anything is launched: ranges, shapes, overlap of input
+ *    and output, and 16-byte alignment of every caller buffer (the kernels use 16-byte accesses; a misaligned
+ *    pointer is ZC_EINVAL, never a device fault). Conditions only the device can see (a token whose router
+ *    scores select fewer than top_k experts, a value outside the FP16 operand range, a peer that never
+ *    answered) set a status word read by zc_moe_status(), like the reference's sparse_status_
+ *    (src/engine/model.cpp:118-120).
+ *  - A handle belongs to the device given to zc_moe_create. Every call makes that device current for its own
+ *    duration and restores the caller's current device before it returns; x / out / stream must belong to the
+ *    handle's device. One process may own handles on several devices.
+ *  - Value range: activations and the internal SwiGLU rows enter the tensor-core products as FP16. For a Q4
+ *    projection of the short-batch kernels a value must satisfy |v| < 4094, otherwise |v| <= 65504; in the
+ *    long-batch kernels additionally the sum of 64 consecutive values must stay below 8188 in magnitude.
+ *    Beyond that the affected output rows are not meaningful and ZC_STATUS_RANGE is raised. Scales and biases
+ *    stored as BF16 must be representable in FP16 for the long-batch kernels (|s| >= 6.1e-5 or zero).
  *  - There is no CPU fallback: without a CUDA device zc_moe_create fails with ZC_EEXEC.
  */
 #ifndef ZC_MOE_H
@@ -50,7 +61,8 @@ extern "C" {
 
 /* Bits of the device status word. */
 #define ZC_STATUS_INVALID_ROUTE 1u   /* "invalid router output", src/engine/model.cpp:459 */
-#define ZC_STATUS_TIMEOUT       2u   /* a bounded device-side wait of the prefill kernels ran out */
+#define ZC_STATUS_TIMEOUT       2u   /* a bounded device-side wait (prefill pipeline, expert-parallel flags) ran out */
+#define ZC_STATUS_RANGE         4u   /* a value left the FP16 range of the tensor-core operands (see "Value range") */
 
 typedef struct zc_moe zc_moe;
 
@@ -124,7 +136,7 @@ int zc_moe_router(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, f
  * Same arithmetic and results as zc_moe_router. x [tokens, hidden] (act_dtype), router_w [experts, hidden]
  * (router_dtype) and logits [tokens, experts] fp32 are device memory of the current device.
  * Limits (rejected with ZC_EINVAL beyond them): tokens <= 64, experts <= 512 (multiple of 32), hidden <= 3072
- * (multiple of 128). The scratch is a 2 MiB + 4 KiB array inside the library image, held by every GPU that
+ * (multiple of 128); x, router_w and logits 16-byte aligned, logits overlapping neither input. The scratch is a 2 MiB + 4 KiB array inside the library image, held by every GPU that
  * loads the library until the process exits. The first call on a device looks up that array's device address
  * (cudaGetSymbolAddress); make that first call before any stream capture begins. All calls share the array,
  * which keeps the previous call's contents: the call clears the counters it needs at zero itself, and two
@@ -143,6 +155,19 @@ int zc_moe_route(zc_moe* moe, const float* logits, uint32_t tokens, int32_t* ids
  * the flat slots p = t*K + j by expert id. offsets [E+1], perm [tokens*K]; the tokens routed to expert e
  * are perm[offsets[e] .. offsets[e+1]) / K. Slots with an id outside [0, E) are dropped and flagged. */
 int zc_moe_permute(zc_moe* moe, const int32_t* ids, uint32_t tokens, int32_t* offsets, int32_t* perm, void* stream);
+
+/* Replaces the moe_sum dispatch (kernels/metal/qwen.metal:804-816, src/engine/model.cpp:553-555) on caller tensors
+ * (parity hook, like zc_moe_route): out[t, :] = sum over slots in the reference's fixed order of weights[t, j] *
+ * expert_out[t, j, :] (slots with ids[t, j] < 0 count as zero) + sigmoid(gate_logit[t]) * shared[t, :], with the
+ * handle's arithmetic mode and output dtype. expert_out [tokens, K, H] fp32, weights [tokens, K] fp32, ids
+ * [tokens, K] int32, shared [tokens, H] fp32 and gate_logit [tokens] fp32 (both or neither), device memory. */
+int zc_moe_combine(zc_moe* moe, const float* expert_out, const float* weights, const int32_t* ids, const float* shared,
+                   const float* gate_logit, uint32_t tokens, void* out, void* stream);
+
+/* The BF16-staged sigmoid and SiLU of the reference arithmetic (sigmoid_bf, kernels/metal/qwen.metal:33-35, and the
+ * activation of q4_gate_up :71-81), element by element on n fp32 device values (parity hook for the reference's
+ * 64-point activation tables, tests/test_qwen.cpp:876-897). Either output may be NULL. Runs on the current device. */
+int zc_activation_bf16(const float* x, uint32_t n, float* sigmoid_out, float* silu_out, void* stream);
 
 /* Replaces Buf Model::moe(x, layer, tokens, ...) (src/engine/model.cpp:431-557) for short batches —
  * the reference's decode / short-append branch (encode_expert_rows with q4_gate_mv_r2 / q4_mv_r*,
@@ -175,10 +200,51 @@ int zc_moe_ep_dispatch(zc_moe* moe, uint32_t layer, const void* x, uint32_t toke
 int zc_moe_ep_experts(zc_moe* moe, uint32_t layer, const void* rows, const int32_t* row_experts, uint32_t n_rows, float* y, void* stream);
 int zc_moe_ep_combine(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, const float* y_sorted, void* out, void* stream);
 
+/* Expert parallelism without a collective library and without any host value in the loop: every rank's handle
+ * owns a window of device memory that the other ranks of the node map over NVLink; rows, results and flags
+ * travel as plain peer stores issued by this library's kernels (no TMA, no multicast). No counterpart in the
+ * reference.
+ *   zc_moe_ep_export: the window's address (ranks inside one process) and / or its 64-byte inter-process handle
+ *     (cudaIpcGetMemHandle) — either output may be NULL.
+ *   zc_moe_ep_attach: peers = world x 64-byte handles (kind 0; the entry of `rank` is ignored) or world device
+ *     pointers (kind 1). world must equal experts / local_experts and rank first_expert / local_experts; every
+ *     rank uses the same descriptor apart from first_expert. All ranks must have attached (a host barrier)
+ *     before any of them issues a layer.
+ *   zc_moe_ep_layer: Model::moe for this rank's tokens: routing, rows to their owners, the local experts on
+ *     whatever arrived, results back to the router slots of their senders, fixed-order combine. Stream-ordered,
+ *     no host synchronisation. Every rank must issue the same sequence of expert-parallel layer calls (a layer
+ *     call on one rank waits for the matching call of every other rank). Device-side waits are bounded (option
+ *     "ep_wait_ms", default 2000): when a peer does not answer, ZC_STATUS_TIMEOUT is raised, the layer finishes
+ *     with whatever arrived, and later waits give up at once until zc_moe_status has cleared the word.
+ *   zc_moe_ep_send / _process / _finish: the three phases of zc_moe_ep_layer as separate calls (sender first
+ *     half, owner, sender second half), for hosts that emulate several ranks on one device: all ranks' sends,
+ *     then all ranks' processing, then all ranks' finishes.
+ *   zc_moe_ep_stack: the chained stack of zc_moe_stack with expert-parallel layers, replayed from a CUDA graph. */
+int zc_moe_ep_export(zc_moe* moe, void* handle64, void** window);
+int zc_moe_ep_attach(zc_moe* moe, uint32_t rank, uint32_t world, const void* peers, int kind);
+int zc_moe_ep_layer(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream);
+int zc_moe_ep_send(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* stream);
+int zc_moe_ep_process(zc_moe* moe, uint32_t layer, void* stream);
+int zc_moe_ep_finish(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream);
+int zc_moe_ep_stack(zc_moe* moe, const void* x, uint32_t tokens, void* out, void* stream);
+int zc_moe_ep_stack_eager(zc_moe* moe, const void* x, uint32_t tokens, void* out, void* stream);
+
 /* Model::moe for callers that hold HOST tensors (the reference's Buf is CPU-visible unified memory):
  * on `stream`, copies x in, runs zc_moe_forward, copies out back, then waits for the stream.
- * x_host/out_host: host memory (pinned memory makes the copies asynchronous to other streams). */
+ * x_host/out_host: host memory (pinned memory makes the copies asynchronous to other streams).
+ * The _async form returns after enqueueing; out_host is valid once the caller has waited for `stream`
+ * (cudaStreamSynchronize, an event, or zc_moe_status, which also returns the device status word) — the
+ * counterpart of the reference's asynchronous encode followed by one finish() (src/engine/metal.mm:442). */
 int zc_moe_forward_host(zc_moe* moe, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream);
+int zc_moe_forward_host_async(zc_moe* moe, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream);
+
+/* The reference's cancel flag (const std::atomic<bool>* cancel of Model::moe, include/engine/model.hpp:156; read at
+ * the stage boundaries of src/engine/pipeline.cpp:160-208). `flag` points to host memory another thread may set to
+ * non-zero (NULL removes it). It is read on the host when a layer call is validated, before every layer of a stack
+ * that is issued launch by launch, and once more by zc_moe_stack_host after its wait; the call then returns
+ * ZC_ECANCELLED ("generation cancelled", src/engine/model.cpp:15) and issues nothing further. Work already
+ * enqueued (a graph replay is one unit) runs to completion. */
+int zc_moe_set_cancel(zc_moe* moe, const int32_t* flag);
 
 /* The whole stack of `layers` MoE layers chained on one stream, layer l+1 reading
  * act_dtype((out_l - mean(out_l)) / std(out_l)) per token — the stand-in for the residual + norm between
@@ -195,6 +261,7 @@ int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* ou
  *   kernel before it; results are identical either way.
  *   "exact_h" (default 0): the decode family's down product reads the FP32 SwiGLU rows as two FP16 terms (nothing
  *   below FP32 is rounded) instead of one FP16 term (11 significant bits; the reference rounds these rows to BF16).
+ *   "ep_wait_ms" (default 2000): limit of one device-side wait for a peer's flag in the expert-parallel layer.
  * Changing an option drops the cached graphs of zc_moe_stack. */
 int zc_moe_set_option(zc_moe* moe, const char* name, int value);
 
@@ -217,6 +284,9 @@ int zc_moe_last_routing(zc_moe* moe, const int32_t** ids, const float** weights,
 /* Number of routed experts that received work in the most recent call of each layer, host_counts[layers]
  * (the reference reports the same through its route trace, include/engine/route_trace.hpp). Blocking. */
 int zc_moe_active_counts(zc_moe* moe, int32_t* host_counts);
+/* The same for the owner side of expert parallelism: experts of this handle's range that received rows (from any
+ * rank) in the most recent expert-parallel call of each layer. Blocking. */
+int zc_moe_ep_active_counts(zc_moe* moe, int32_t* host_counts);
 
 /* Blocking copy of handle-owned device memory (a resident tensor or the routing buffers above) to the host;
  * waits for all earlier work on the device. The reference reads the same tensors in place (unified memory). */

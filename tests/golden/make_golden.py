@@ -116,7 +116,10 @@ def numpy_moe(reference):
 
 
 def main():
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ZC_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: make_golden.py <reference tree>   (or set ZC_REFERENCE_ROOT)")
+    reference = Path(root)
     (HERE / "reference_known_answers.json").write_text(json.dumps(known_answers(reference), indent=1))
     np.savez_compressed(HERE / "numpy_moe_config0.npz", **numpy_moe(reference))
     print("wrote", HERE / "reference_known_answers.json", "and", HERE / "numpy_moe_config0.npz")

@@ -197,12 +197,15 @@ def test_reference_numpy_moe_anchor():
     assert rel < 2e-3, rel
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/scripts/qwen"), reason="reference tree not present")
+REFERENCE_ROOT = os.environ.get("ZC_REFERENCE_ROOT", "")
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_ROOT, "scripts", "qwen")), reason="ZC_REFERENCE_ROOT does not name a reference tree")
 def test_committed_numpy_fixture_is_reproducible():
-    """Where the reference tree is present, regenerating the fixture gives the committed bytes."""
+    """Where ZC_REFERENCE_ROOT names the reference tree, regenerating the fixture gives the committed bytes."""
     from pathlib import Path
     from tests.golden import make_golden
-    fresh = make_golden.numpy_moe(Path("/root/reference"))
+    fresh = make_golden.numpy_moe(Path(REFERENCE_ROOT))
     gold = np.load(os.path.join(GOLDEN, "numpy_moe_config0.npz"))
     for k in ("out", "ids", "logits"):
         assert np.array_equal(fresh[k], gold[k])

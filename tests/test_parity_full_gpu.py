@@ -1,0 +1,353 @@
+"""GPU parity at the full sizes of the benchmark configurations and on the inputs that stress the error margin:
+free biases, scaled activations, the mixed 4/8-bit ragged batch, 8192-token prefill, all 512 experts at hidden 4096,
+a chained stack against the CPU checker chained with the same glue, the reference's known-answer vectors fed to the
+device kernels, and the host-side contract (alignment, cancellation, graph cache, value-range status)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests import util
+from tests.test_moe_gpu import TOL, device_x, make, oracle_layer
+from zerocool_b200 import synth
+from zerocool_b200.records import ARITH_REFERENCE, BF16, F32, MoeConfig
+
+pytestmark = pytest.mark.gpu
+SEED = 4242
+KNOWN = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")))
+
+
+def glue(out):
+    """The stack's inter-layer stand-in on the CPU: bf16((out - mean) / std) per token."""
+    o = out.astype(np.float32)
+    d = o - o.mean(axis=-1, keepdims=True, dtype=np.float32)
+    scale = (1.0 / np.sqrt(np.mean(d * d, axis=-1, keepdims=True, dtype=np.float32))).astype(np.float32)
+    return oracle.bf(d * scale)
+
+
+def load_asymmetric(cfg, seed=SEED, spread=0.03):
+    rng = np.random.default_rng(11)
+    records = [util.asymmetric_record(cfg, seed, 0, e, rng, spread) for e in range(cfg.experts)]
+    shared = util.asymmetric_record(cfg, seed, 0, synth.SHARED_EXPERT, rng, spread) if cfg.has_shared else None
+    m = make(cfg)
+    m.load_layer(0, records=np.stack(records), router_w=synth.router(cfg, seed, 0), shared_record=shared,
+                 shared_gate_w=synth.shared_gate(cfg, seed, 0) if cfg.has_shared else None)
+    return m, records, shared
+
+
+@pytest.mark.parametrize("tokens", [3, 64])
+def test_decode_family_with_free_biases(tokens):
+    """bias != -8 scale: the bias term b * sum(x) no longer cancels against the codes' offset, so a rounding of an
+    activation to FP16 shows in the result unless it enters through the whole weight s q + b."""
+    cfg = util.cfg2(experts=32, top_k=4, max_tokens=64)
+    m, records, shared = load_asymmetric(cfg)
+    x = synth.activations(cfg, SEED, 0, tokens)
+    out = m.decode(0, device_x(m, x)).float().cpu().numpy()
+    assert m.status() == 0
+    want = oracle.moe_layer(cfg.as_dict(), records, synth.router(cfg, SEED, 0), x, shared_record=shared, shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    assert np.array_equal(m.last_routing(tokens)["ids"], want["ids"])
+    err = util.rel_max_error(out, want["out"])
+    print("decode family, free biases, max-abs error / RMS:", err)
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("family", ["decode", "prefill"])
+@pytest.mark.parametrize("scale", [8.0, 0.125])
+def test_scaled_activations_keep_the_margin(family, scale):
+    """Activations eight times larger and eight times smaller than N(0, 1) (exact scalings of the BF16 inputs): the
+    relative error must not depend on the input scale (no operand may drift towards FP16's limits)."""
+    cfg = util.cfg2(experts=64, max_tokens=256)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    tokens = 200 if family == "prefill" else 24
+    x = synth.activations(cfg, SEED, 0, tokens) * np.float32(scale)
+    out = getattr(m, family)(0, device_x(m, x)).float().cpu().numpy()
+    assert m.status() == 0
+    want = oracle_layer(cfg, SEED, 0, x, m.last_routing(tokens)["ids"])
+    assert np.array_equal(m.last_routing(tokens)["ids"], want["ids"])
+    err = util.rel_max_error(out, want["out"])
+    print(family, "x scaled by", scale, "max-abs error / RMS:", err)
+    assert err <= TOL, err
+
+
+def test_values_beyond_fp16_raise_the_range_bit():
+    """x scaled by 64 drives the SwiGLU rows past FP16's largest value: the status word says so instead of the
+    infinities passing silently; the next call on normal inputs is clean again."""
+    from zerocool_b200.moe import STATUS_RANGE
+    cfg = util.cfg2(experts=64, max_tokens=256)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    for family, tokens in (("decode", 16), ("prefill", 200)):
+        x = synth.activations(cfg, SEED, 0, tokens)
+        getattr(m, family)(0, device_x(m, x * np.float32(64.0)))
+        assert m.status() & STATUS_RANGE, family
+        getattr(m, family)(0, device_x(m, x))
+        assert m.status() == 0, family
+
+
+def test_config4_mixed_bits_ragged_batch_at_full_size():
+    """benchmark configuration 4, one layer at full size: 512 experts top-10 + shared, gate/up Q4 and down Q8 (int8),
+    32 requests of seeded lengths 1..512 flattened to one ragged batch. The first 64 tokens and the last 16 tokens of
+    the longest request against the CPU checker; permuting the whole batch permutes the outputs bit for bit; both
+    kernel families agree."""
+    import torch
+    lengths = np.random.default_rng(20261125).integers(1, 513, size=32)
+    tokens = int(lengths.sum())
+    cfg = util.cfg2(down_bits=8, q8_signed=1, max_tokens=tokens)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    x = synth.activations(cfg, SEED, 0, tokens)
+    before = m.launches
+    out = m.moe(0, device_x(m, x)).clone()
+    assert m.launches - before == 10                      # the tensor-core family took the batch: router, route, permute, 6 x grouped GEMM, combine
+    routing = m.last_routing(tokens)
+    ids = routing["ids"].copy()
+    assert m.status() == 0
+    offsets, perm = oracle.permute(ids, cfg.experts)
+    assert np.array_equal(routing["offsets"], offsets) and np.array_equal(routing["perm"], perm)
+    longest = int(np.argmax(lengths))
+    end = int(lengths[:longest + 1].sum())
+    for lo, hi in ((0, 64), (end - 16, end)):
+        want = oracle_layer(cfg, SEED, 0, x[lo:hi], ids[lo:hi])
+        assert np.array_equal(want["ids"], ids[lo:hi])
+        err = util.rel_max_error(out[lo:hi].float().cpu().numpy(), want["out"])
+        print("configuration 4, tokens", lo, hi, "max-abs error / RMS:", err)
+        assert err <= TOL, err
+    order = np.random.default_rng(8).permutation(tokens)
+    out_p = m.moe(0, device_x(m, np.ascontiguousarray(x[order])))
+    assert np.array_equal(m.last_routing(tokens)["ids"], ids[order])
+    assert torch.equal(out_p, out[torch.from_numpy(order).to(out.device)])
+    dec = m.decode(0, device_x(m, x[:96])).float().cpu().numpy()
+    assert util.rel_max_error(dec, out[:96].float().cpu().numpy()) <= TOL
+    assert m.status() == 0
+
+
+def test_prefill_q8_everywhere_and_free_biases():
+    """8-bit codes on all three projections through the tensor-core family (u8, the reference's Q8 form), with
+    free biases: against the CPU checker."""
+    cfg = util.cfg2(experts=32, top_k=4, gate_bits=8, up_bits=8, down_bits=8, q8_signed=0, max_tokens=256)
+    m, records, shared = load_asymmetric(cfg, spread=0.3)
+    x = synth.activations(cfg, SEED, 0, 150)
+    out = m.prefill(0, device_x(m, x)).float().cpu().numpy()
+    assert m.status() == 0
+    want = oracle.moe_layer(cfg.as_dict(), records, synth.router(cfg, SEED, 0), x, shared_record=shared, shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    assert np.array_equal(m.last_routing(150)["ids"], want["ids"])
+    err = util.rel_max_error(out, want["out"])
+    print("prefill family, Q8 everywhere, max-abs error / RMS:", err)
+    assert err <= TOL, err
+
+
+def test_config3_prefill_at_8192_tokens():
+    """benchmark configuration 3 at its long length: 8192 tokens, Zipf(1.1) router bias, 512 experts top-10 + shared.
+    Token-order invariance on the whole batch (bit for bit), the permutation against the checker, the first and the
+    last 16 tokens against the CPU checker."""
+    import torch
+    tokens = 8192
+    cfg = util.cfg2(max_tokens=tokens)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    bias = synth.zipf_router_bias(cfg, SEED, 0)
+    m.set_router_bias(0, bias)
+    x = synth.activations(cfg, SEED, 0, tokens)
+    out = m.prefill(0, device_x(m, x)).clone()
+    routing = m.last_routing(tokens)
+    ids = routing["ids"].copy()
+    assert m.status() == 0
+    offsets, perm = oracle.permute(ids, cfg.experts)
+    assert np.array_equal(routing["offsets"], offsets) and np.array_equal(routing["perm"], perm)
+    order = np.random.default_rng(3).permutation(tokens)
+    out_p = m.prefill(0, device_x(m, np.ascontiguousarray(x[order])))
+    assert m.status() == 0
+    assert np.array_equal(m.last_routing(tokens)["ids"], ids[order])
+    assert torch.equal(out_p, out[torch.from_numpy(order).to(out.device)])
+    for lo, hi in ((0, 16), (tokens - 16, tokens)):
+        want = oracle_layer(cfg, SEED, 0, x[lo:hi], ids[lo:hi], router_bias=bias)
+        assert np.array_equal(want["ids"], ids[lo:hi])
+        err = util.rel_max_error(out[lo:hi].float().cpu().numpy(), want["out"])
+        print("configuration 3 at 8192, tokens", lo, hi, "max-abs error / RMS:", err)
+        assert err <= TOL, err
+
+
+def test_config5_all_512_experts_on_one_handle():
+    """benchmark configuration 5's layer with every expert resident (hidden 4096, 512 experts top-10, no shared expert),
+    its 256-token batch: routing bit-exact on all tokens, the first 24 outputs against the CPU checker."""
+    cfg = util.cfg2(hidden=4096, has_shared=0, max_tokens=256)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    tokens = 256
+    x = synth.activations(cfg, SEED, 0, tokens)
+    out = m.moe(0, device_x(m, x)).float().cpu().numpy()
+    routing = m.last_routing(tokens)
+    assert m.status() == 0
+    logits = oracle.router_logits(x, synth.router(cfg, SEED, 0), cfg.router_dtype)
+    assert np.array_equal(routing["logits"].view(np.uint32), logits.view(np.uint32))
+    ids, _ = oracle.route(logits, cfg.top_k)
+    assert np.array_equal(routing["ids"], ids)
+    offsets, perm = oracle.permute(ids, cfg.experts)
+    assert np.array_equal(routing["offsets"], offsets) and np.array_equal(routing["perm"], perm)
+    want = oracle_layer(cfg, SEED, 0, x[:24], ids[:24])
+    err = util.rel_max_error(out[:24], want["out"])
+    print("configuration 5 layer, 512 experts, max-abs error / RMS:", err)
+    assert err <= TOL, err
+
+
+def test_four_layer_stack_against_the_chained_cpu_checker():
+    """Teacher forcing: layer l of the device gets the CPU chain's input of layer l; ids must be bit-exact and the
+    output within tolerance at every layer. Free running: the device's own two-layer chain (graph-replayed stack, glue
+    in the combine kernel) against the CPU chain after two layers."""
+    layers, tokens = 4, 12
+    cfg = util.cfg2(experts=64, layers=layers, max_tokens=16)
+    m = make(cfg)
+    for layer in range(layers):
+        m.synth_fill_layer(layer, SEED)
+    x = synth.activations(cfg, SEED, 0, tokens)
+    cpu_inputs, cpu_outputs = [], []
+    for layer in range(layers):
+        cpu_inputs.append(x)
+        logits = oracle.router_logits(x, synth.router(cfg, SEED, layer), cfg.router_dtype)
+        ids, _ = oracle.route(logits, cfg.top_k)
+        want = oracle_layer(cfg, SEED, layer, x, ids)
+        cpu_outputs.append(want)
+        x = glue(want["out"])
+    for layer in range(layers):
+        got = m.moe(layer, device_x(m, cpu_inputs[layer])).float().cpu().numpy()
+        assert m.status() == 0
+        assert np.array_equal(m.last_routing(tokens)["ids"], cpu_outputs[layer]["ids"]), layer
+        err = util.rel_max_error(got, cpu_outputs[layer]["out"])
+        print("teacher-forced layer", layer, "max-abs error / RMS:", err)
+        assert err <= TOL, (layer, err)
+    two = MoeConfig(**{**cfg.__dict__, "layers": 2})
+    m2 = make(two)
+    for layer in range(2):
+        m2.synth_fill_layer(layer, SEED)
+    free = m2.stack(device_x(m2, cpu_inputs[0])).float().cpu().numpy()
+    assert m2.status() == 0
+    assert np.array_equal(m2.last_routing(tokens)["ids"], cpu_outputs[1]["ids"])        # the second layer routed as the CPU chain did
+    # Layer 1 sees layer 0's error through the BF16 rounding of the glue (an input that moves by 1e-3 crosses a BF16
+    # boundary, 2^-7 apart near 1, in a few per cent of the coordinates) on top of its own: the bound on the chain is
+    # therefore on the relative L2 error, with a loose cap on the largest single deviation.
+    a, b = free.astype(np.float64).reshape(-1), cpu_outputs[1]["out"].astype(np.float64).reshape(-1)
+    rel_l2 = float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    err = util.rel_max_error(free, cpu_outputs[1]["out"])
+    print("free-running two-layer chain: relative L2", rel_l2, "max-abs error / RMS:", err)
+    assert rel_l2 <= 5e-3 and err <= 3e-2, (rel_l2, err)
+
+
+def test_moe_sum_midpoint_vector_through_the_combine_kernel():
+    """The reference's own known answer for the reduction order (tests/test_qwen.cpp:827-842): (p0 + p8) + (p1 + p9)
+    first decides a BF16 midpoint; expected 0.01190185546875. Fed to combine_kernel in reference arithmetic."""
+    import torch
+    g = KNOWN["moe_sum_midpoint"]
+    H = 128
+    cfg = util.cfg2(hidden=H, ffn=128, experts=32, top_k=10, has_shared=1, arith=ARITH_REFERENCE, act_dtype=F32, out_dtype=F32, max_tokens=4)
+    m = make(cfg)
+    eo = np.zeros((1, 10, H), np.float32)
+    eo[0, :, 0] = np.array(g["values"], np.float32)
+    w = np.array(g["weight_bits"], np.uint32).view(np.float32)[None].copy()
+    shared = np.zeros((1, H), np.float32)
+    shared[0, 0] = g["shared"]
+    gate = np.array([g["gate"]], np.float32)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()          # noqa: E731
+    out = m.combine(dev(eo), dev(w), dev(np.zeros((1, 10), np.int32)), dev(shared), dev(np.concatenate([gate, np.zeros(3, np.float32)]))).cpu().numpy()
+    assert out[0, 0] == np.float32(g["expected"])
+    assert np.all(out[0, 1:] == 0)
+    want = oracle.combine(cfg.as_dict(), eo, w, shared, gate)
+    assert np.array_equal(out, want)
+
+
+def test_activation_tables_on_the_device():
+    """The 64-point SiLU / sigmoid tables and the -6.84375 boundary the reference holds (tests/test_qwen.cpp:876-897),
+    through the device's sigmoid_bf."""
+    import torch
+    g = KNOWN["activations"]
+    m = make(util.cfg2(experts=32, top_k=4, max_tokens=4))
+    x = torch.tensor(g["x"] + [KNOWN["sigmoid_boundary"]["x"], -KNOWN["sigmoid_boundary"]["x"]], dtype=torch.float32, device="cuda")
+    sg, si = m.activation_bf16(x)
+    sg, si = sg.cpu().numpy(), si.cpu().numpy()
+    assert np.array_equal(sg[:64], np.array(g["sigmoid"], np.float32))
+    assert np.array_equal(si[:64], np.array(g["silu"], np.float32))
+    assert si[64] == np.float32(KNOWN["sigmoid_boundary"]["silu"]) and si[65] == np.float32(-KNOWN["sigmoid_boundary"]["x"])
+
+
+def test_misaligned_and_aliased_buffers_are_argument_errors():
+    """Every entry point that takes a caller buffer refuses a pointer off the 16-byte grid before anything is launched."""
+    import torch
+    from zerocool_b200.moe import ZC_EINVAL, _ptr
+    cfg = util.cfg2(experts=64, max_tokens=8)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    lib, h, s = m.lib, m._h, torch.cuda.current_stream().cuda_stream
+    T = 4
+    x = torch.zeros((T * cfg.hidden + 8,), dtype=torch.bfloat16, device="cuda")
+    f = torch.zeros((T * cfg.experts + 8,), dtype=torch.float32, device="cuda")
+    i32 = torch.zeros((T * cfg.top_k + 8,), dtype=torch.int32, device="cuda")
+    out = torch.zeros((T * cfg.hidden + 8,), dtype=torch.float32, device="cuda")
+    before = m.launches
+    assert lib.zc_moe_router(h, 0, _ptr(x) + 2, T, _ptr(f), s) == ZC_EINVAL
+    assert lib.zc_moe_router(h, 0, _ptr(x), T, _ptr(f) + 4, s) == ZC_EINVAL
+    assert lib.zc_moe_route(h, _ptr(f) + 4, T, _ptr(i32), _ptr(f), s) == ZC_EINVAL
+    assert lib.zc_moe_permute(h, _ptr(i32) + 4, T, _ptr(i32), _ptr(i32), s) == ZC_EINVAL
+    assert lib.zc_moe_forward(h, 0, _ptr(x) + 2, T, _ptr(out), s) == ZC_EINVAL
+    assert lib.zc_moe_forward(h, 0, _ptr(x), T, _ptr(out) + 4, s) == ZC_EINVAL
+    assert lib.zc_moe_ep_dispatch(h, 0, _ptr(x) + 2, T, _ptr(out), _ptr(i32), s) == ZC_EINVAL
+    w = torch.zeros((cfg.experts * cfg.hidden + 8,), dtype=torch.float32, device="cuda")
+    assert lib.zc_router_logits_noalloc(_ptr(x) + 2, BF16, _ptr(w), F32, T, cfg.hidden, cfg.experts, _ptr(f), s) == ZC_EINVAL
+    assert lib.zc_router_logits_noalloc(_ptr(x), BF16, _ptr(w) + 4, F32, T, cfg.hidden, cfg.experts, _ptr(f), s) == ZC_EINVAL
+    assert lib.zc_router_logits_noalloc(_ptr(x), BF16, _ptr(w), F32, T, cfg.hidden, cfg.experts, _ptr(w), s) == ZC_EINVAL      # logits over router_w
+    assert m.launches == before
+    torch.cuda.synchronize()
+    assert m.status() == 0
+
+
+def test_cancel_flag_stops_the_stack():
+    """The reference's cancel flag: set before a call -> "generation cancelled" and nothing is issued; cleared -> the
+    stack runs and returns the same bytes as before."""
+    import torch
+    from zerocool_b200.moe import Cancelled
+    cfg = util.cfg2(experts=64, layers=3, out_dtype=BF16, max_tokens=8)
+    m = make(cfg)
+    for layer in range(3):
+        m.synth_fill_layer(layer, SEED)
+    x = device_x(m, synth.activations(cfg, SEED, 0, 5))
+    want = m.stack(x).clone()
+    flag = np.zeros(1, np.int32)
+    m.set_cancel(flag)
+    flag[0] = 1
+    before = m.launches
+    for call in (lambda: m.stack(x), lambda: m.stack_eager(x), lambda: m.moe(0, x)):
+        with pytest.raises(Cancelled):
+            call()
+    assert m.launches == before
+    flag[0] = 0
+    assert torch.equal(m.stack(x), want)
+    m.set_cancel(None)
+
+
+def test_graph_cache_follows_bias_changes_and_stays_bounded():
+    """A captured stack must not outlive what it captured: removing a router bias drops the captures (the replay
+    equals the eager run again), and more distinct (x, out) pairs than the cache holds still give right answers."""
+    import torch
+    cfg = util.cfg2(experts=64, layers=2, out_dtype=BF16, max_tokens=8)
+    m = make(cfg)
+    for layer in range(2):
+        m.synth_fill_layer(layer, SEED)
+    x = device_x(m, synth.activations(cfg, SEED, 0, 6))
+    plain = m.stack(x).clone()
+    m.set_router_bias(0, synth.zipf_router_bias(cfg, SEED, 0))
+    biased = m.stack(x).clone()
+    assert not torch.equal(plain, biased)
+    m.set_router_bias(0, None)
+    assert torch.equal(m.stack(x), plain) and torch.equal(m.stack_eager(x), plain)
+    keep = []
+    for i in range(12):                                   # more captures than the cache holds
+        xi, oi = x.clone(), torch.empty_like(plain)
+        keep.append((xi, oi))
+        m.stack(xi, oi)
+        assert torch.equal(oi, plain), i
+    for xi, oi in keep[:3]:                               # evicted entries are captured again
+        oi.zero_()
+        m.stack(xi, oi)
+        assert torch.equal(oi, plain)
+    assert m.status() == 0

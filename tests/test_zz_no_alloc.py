@@ -9,6 +9,7 @@ import ctypes
 import numpy as np
 import pytest
 
+from oracle import oracle
 from tests import util
 from zerocool_b200 import synth
 from zerocool_b200.records import BF16, F32
@@ -45,3 +46,26 @@ def test_noalloc_router_matches_the_handle_router_on_two_calls():
     assert rc == ZC_EINVAL and b"tokens must be 1..64" in lib.zc_last_error()
     rc = lib.zc_router_logits_noalloc(big.data_ptr(), BF16, w_dev.data_ptr(), F32, 8, cfg.hidden, 1024, out.data_ptr(), stream)
     assert rc == ZC_EINVAL and b"at most 512" in lib.zc_last_error()
+
+
+@pytest.mark.parametrize("act,router_dtype,hidden,experts", [(F32, F32, 2560, 64), (BF16, BF16, 3072, 512), (F32, BF16, 2048, 64), (BF16, F32, 2560, 512)])
+def test_noalloc_router_at_its_documented_limits_against_the_cpu_checker(act, router_dtype, hidden, experts):
+    """Both activation and router dtypes, the largest hidden size the entry point takes (3072) and the reference's own
+    (2560), few and many experts: bit-exact against the CPU checker's pinned accumulation order, on two calls in a row
+    (a full batch, then a short one that runs on the first call's leftovers in the shared scratch)."""
+    import torch
+    from zerocool_b200.moe import load_library
+    lib = load_library()
+    cfg = util.cfg2(hidden=hidden, experts=experts, act_dtype=act, router_dtype=router_dtype, max_tokens=64)
+    w = synth.router(cfg, 99, 0)
+    w_dev = torch.from_numpy(w.view(np.int16) if router_dtype == BF16 else w).cuda()
+    stream = torch.cuda.current_stream().cuda_stream
+    for call, tokens in enumerate((64, 9)):
+        x = synth.activations(cfg, 99 + call, 0, tokens)
+        x_dev = torch.from_numpy(x).to(device="cuda", dtype=torch.bfloat16 if act == BF16 else torch.float32)
+        got = torch.full((tokens, experts), float("nan"), dtype=torch.float32, device="cuda")
+        rc = lib.zc_router_logits_noalloc(x_dev.data_ptr(), act, w_dev.data_ptr(), router_dtype, tokens, hidden, experts, got.data_ptr(), stream)
+        assert rc == 0, lib.zc_last_error()
+        torch.cuda.synchronize()
+        want = oracle.router_logits(x, w, router_dtype)
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32)), (call, tokens)

@@ -53,3 +53,17 @@ def rel_max_error(got, want):
     want = np.asarray(want, np.float64)
     got = np.asarray(got, np.float64)
     return float(np.abs(got - want).max() / np.sqrt(np.mean(want * want)))
+
+
+def asymmetric_record(cfg, seed, layer, expert, rng, spread=0.03):
+    """A record with the generator's codes and scales but free biases (bias = -8 scale + U(-spread, spread)): the
+    affine form's second term, (8 s + b) * sum(x), is then not zero."""
+    from zerocool_b200.records import build_record, float_to_meta, meta_to_float
+    parts = []
+    for p in range(3):
+        codes, sbits, bbits = synth.projection_parts(cfg, seed, layer, expert, p)
+        s = meta_to_float(sbits, cfg.meta_dtype)
+        offset = -8.0 if cfg.bits(p) == 4 else 0.0
+        b = offset * s + rng.uniform(-spread, spread, size=s.shape).astype(np.float32)
+        parts.append((codes, sbits, float_to_meta(b, cfg.meta_dtype).reshape(bbits.shape)))
+    return build_record(cfg, parts)

@@ -9,6 +9,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <initializer_list>
 
 namespace zc {
 
@@ -77,15 +78,32 @@ Call make_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* 
     return c;
 }
 
+// Every caller buffer is read or written with 16-byte accesses: a misaligned pointer is an argument error here,
+// not a misaligned-address fault on the device.
+bool aligned16(std::initializer_list<const void*> ptrs) {
+    for (const void* p : ptrs) if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+    return true;
+}
+bool overlaps(const void* a, size_t a_bytes, const void* b, size_t b_bytes) {
+    const char* p = static_cast<const char*>(a); const char* q = static_cast<const char*>(b);
+    return p < q + b_bytes && q < p + a_bytes;
+}
+// The reference's cancel flag (const std::atomic<bool>* cancel, include/engine/model.hpp:156): read on the host.
+bool cancelled(const zc_moe* m) { return m->cancel && *static_cast<const volatile int32_t*>(m->cancel) != 0; }
+void drop_graphs(zc_moe* m) {
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);
+    m->graphs.clear();
+}
+
 int check_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const void* out) {
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
     if (!tokens || tokens > m->d.max_tokens) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens");
     if (!x || !out) return fail(m, ZC_EINVAL, "missing input or output buffer");
     const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), ob = size_t(tokens) * m->d.hidden * elem_bytes(m->d.out_dtype);
-    const char* a = static_cast<const char*>(x); const char* b = static_cast<const char*>(out);
-    if (a < b + ob && b < a + xb) return fail(m, ZC_EINVAL, "invalid or overlapping output");
-    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    if (overlaps(x, xb, out, ob)) return fail(m, ZC_EINVAL, "invalid or overlapping output");
+    if (!aligned16({x, out})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    if (cancelled(m)) return fail(m, ZC_ECANCELLED, "generation cancelled");
     return ZC_OK;
 }
 
@@ -94,7 +112,9 @@ int check_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const 
 // family: 0 = decode kernels, 1 = prefill kernels (tensor-core grouped GEMM), -1 = by token count.
 int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next = nullptr, int family = -1) {
     const Call c = make_call(m, layer, x, tokens, out);
-    if (family < 0) family = tokens >= 256 ? 1 : 0;
+    // The tensor-core family pays from about sixteen rows per expert on (a tile of an expert's rows is one pass over
+    // its weights through shared memory); below that the streaming kernels, which take eight rows per pass, are faster.
+    if (family < 0) family = (tokens >= 64 && uint64_t(tokens) * m->d.top_k >= 16ull * m->d.local_experts) ? 1 : 0;
     if (family == 1 && !m->pf_tiles) family = 0;      // formats the prefill kernels do not take, or a decode-sized handle
     int n, total = 0;
     if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
@@ -139,8 +159,10 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     int count = 0;
     cudaError_t e = cudaGetDeviceCount(&count);
     if (e != cudaSuccess || count == 0) return fail(nullptr, ZC_EEXEC, "no CUDA device: this library has no CPU path");
-    if (device < 0 || device >= count) return fail(nullptr, ZC_EINVAL, "device index outside the visible devices");
-    if ((e = cudaSetDevice(device)) != cudaSuccess) return cuda_fail(nullptr, e, "cudaSetDevice");
+    if (device < 0 || device >= count || device >= MAX_DEVICES) return fail(nullptr, ZC_EINVAL, "device index outside the visible devices");
+    DeviceGuard guard(device);          // the caller's current device is restored on return
+    int current = -1;
+    if (cudaGetDevice(&current) != cudaSuccess || current != device) return fail(nullptr, ZC_EEXEC, "cudaSetDevice failed");
     cudaDeviceProp prop{};
     cudaGetDeviceProperties(&prop, device);
     if (prop.major < 10) return fail(nullptr, ZC_EEXEC, "this library is built for sm_100a (B200) only");
@@ -176,6 +198,8 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         m->pf_max_tiles = uint32_t(prefill_tile_capacity(d));
         uint8_t* tl = nullptr; A(&tl, m->pf_max_tiles * prefill_tile_bytes()); m->pf_tiles = tl;
         A(&m->pf_ntiles, 16);
+        // rows of dropped slots are never written: start from zeros so that the range check of the group sums only ever sees values a kernel stored
+        if (rc == ZC_OK && (e = cudaMemset(m->hbuf16, 0, (T * K + T) * F * 2)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
     } A(&c.expert_out, T * K * H * 4); A(&c.shared_out, T * H * 4); A(&c.status, 16);
     A(&m->empty_items, E * 16);
     if (rc == ZC_OK && (e = cudaMemset(m->empty_items, 0xff, E * 16)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
@@ -191,6 +215,15 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         A(&q.offsets, (E + 1) * 4); A(&q.perm, R * 4); A(&q.active, E * 4); A(&q.items, E * 16); A(&q.counters, (16 + size_t(d.layers)) * 4);
         A(&q.hbuf, R * F * 4);
         if (rc == ZC_OK && (e = cudaMemset(q.counters, 0, (16 + size_t(d.layers)) * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+        // peer transport: the window other ranks store into, and what the owner side needs around it
+        if (d.experts % d.local_experts == 0 && d.first_expert % d.local_experts == 0 && ranks <= size_t(EP_MAX_RANKS)) {
+            m->ep_layout = ep_window_layout(d);
+            A(&m->ep_window, m->ep_layout.bytes);
+            if (rc == ZC_OK && (e = cudaMemset(m->ep_window, 0, m->ep_layout.bytes)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+            A(&m->ep_ctl, 64); A(&m->ep_counts, EP_MAX_RANKS * 4); A(&m->ep_row_ids, R * 4); A(&q.expert_out, R * H * 4);
+            if (rc == ZC_OK && (e = cudaMemset(m->ep_ctl, 0, 64)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+            if (rc == ZC_OK && (e = cudaMemset(m->ep_counts, 0, EP_MAX_RANKS * 4)) != cudaSuccess) rc = cuda_fail(m, e, "cudaMemset");
+        }
     }
     uint8_t* p0 = nullptr; uint8_t* p1 = nullptr; uint8_t* dx = nullptr; uint8_t* dout = nullptr; uint8_t* dfin = nullptr;
     A(&p0, T * H * 4); A(&p1, T * H * 4); A(&dx, T * H * 4); A(&dout, T * H * 4); A(&dfin, T * H * 4);
@@ -211,6 +244,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         const Call keep = q;
         q = c;                                   // geometry and formats
         q.offsets = keep.offsets; q.perm = keep.perm; q.active = keep.active; q.items = keep.items; q.counters = keep.counters; q.hbuf = keep.hbuf;
+        q.expert_out = keep.expert_out;
         q.K = 1; q.has_shared = 0;
     }
     *out = m;
@@ -219,9 +253,10 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
 
 void zc_moe_destroy(zc_moe* m) {
     if (!m) return;
-    cudaSetDevice(m->device);
+    DeviceGuard guard(m->device);
     cudaDeviceSynchronize();
-    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);
+    drop_graphs(m);
+    for (void* p : m->ep_opened) if (p) cudaIpcCloseMemHandle(p);
     for (void* p : m->allocations) cudaFree(p);
     if (m->host_x) cudaFreeHost(m->host_x);
     if (m->host_out) cudaFreeHost(m->host_out);
@@ -235,6 +270,7 @@ int zc_moe_load_layer(zc_moe* m, uint32_t layer, const void* records, uint32_t f
     if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
     const zc_moe_desc& d = m->d;
     LayerMem& L = m->layers[layer];
+    DeviceGuard guard(m->device);
     cudaError_t e;
     if (records) {
         if (first_expert < d.first_expert || uint64_t(first_expert) + count > uint64_t(d.first_expert) + d.local_experts)
@@ -256,12 +292,12 @@ int zc_moe_set_router_bias(zc_moe* m, uint32_t layer, const float* bias) {
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
     LayerMem& L = m->layers[layer];
+    DeviceGuard guard(m->device);
+    drop_graphs(m);                      // captured launches hold the old argument (bias pointer or none)
     if (!bias) { L.bias_set = false; return ZC_OK; }
     const cudaError_t e = cudaMemcpy(L.router_bias, bias, size_t(m->d.experts) * 4, cudaMemcpyDefault);
     if (e != cudaSuccess) return cuda_fail(m, e, "copy of router bias");
     L.bias_set = true;
-    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);   // captured launches hold the old argument
-    m->graphs.clear();
     return ZC_OK;
 }
 
@@ -280,6 +316,8 @@ int zc_moe_router(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, flo
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
     if (!tokens || tokens > m->d.max_tokens || !x || !logits) return fail(m, ZC_EINVAL, "linear input shape");
+    if (!aligned16({x, logits})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
     Call c = make_call(m, layer, x, tokens, nullptr);
     c.logits = logits;
     const int n = launch_router(m, c, static_cast<cudaStream_t>(stream));
@@ -292,6 +330,8 @@ int zc_moe_route(zc_moe* m, const float* logits, uint32_t tokens, int32_t* ids, 
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     // Metal::route: "invalid route selection buffers" (src/engine/metal.mm:262-264)
     if (!tokens || tokens > m->d.max_tokens || !logits || !ids || !weights) return fail(m, ZC_EINVAL, "invalid route selection buffers");
+    if (!aligned16({logits, ids, weights})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
     Call c = m->scratch;
     c.T = tokens; c.logits = const_cast<float*>(logits); c.ids = ids; c.weights = weights;
     const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), true, false);
@@ -303,6 +343,8 @@ int zc_moe_route(zc_moe* m, const float* logits, uint32_t tokens, int32_t* ids, 
 int zc_moe_permute(zc_moe* m, const int32_t* ids, uint32_t tokens, int32_t* offsets, int32_t* perm, void* stream) {
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (!tokens || tokens > m->d.max_tokens || !ids || !offsets || !perm) return fail(m, ZC_EINVAL, "invalid permutation buffers");
+    if (!aligned16({ids, offsets, perm})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
     Call c = m->scratch;
     c.T = tokens; c.ids = const_cast<int32_t*>(ids); c.offsets = offsets; c.perm = perm;
     const int n = launch_route_permute(m, c, static_cast<cudaStream_t>(stream), false, true);
@@ -311,9 +353,32 @@ int zc_moe_permute(zc_moe* m, const int32_t* ids, uint32_t tokens, int32_t* offs
     return ZC_OK;
 }
 
+int zc_moe_combine(zc_moe* m, const float* expert_out, const float* weights, const int32_t* ids, const float* shared, const float* gate_logit,
+                   uint32_t tokens, void* out, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (!tokens || tokens > m->d.max_tokens || !expert_out || !weights || !ids || !out) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
+    if ((shared == nullptr) != (gate_logit == nullptr)) return fail(m, ZC_EINVAL, "shared rows and gate values come together");
+    if (!aligned16({expert_out, weights, ids, shared, gate_logit, out})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
+    Call c = m->scratch;
+    c.T = tokens; c.out = out;
+    c.expert_out = const_cast<float*>(expert_out); c.weights = const_cast<float*>(weights); c.ids = const_cast<int32_t*>(ids);
+    c.shared_out = const_cast<float*>(shared); c.gate_logit = const_cast<float*>(gate_logit); c.has_shared = shared != nullptr;
+    const int n = launch_combine(m, c, static_cast<cudaStream_t>(stream));
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_activation_bf16(const float* x, uint32_t n, float* sigmoid_out, float* silu_out, void* stream) {
+    if (!x || !n || (!sigmoid_out && !silu_out)) return fail(nullptr, ZC_EINVAL, "missing buffer");
+    return launch_activation_table(x, n, sigmoid_out, silu_out, static_cast<cudaStream_t>(stream));
+}
+
 static int forward_family(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream, int family) {
     int rc = check_call(m, layer, x, tokens, out);
     if (rc != ZC_OK) return rc;
+    DeviceGuard guard(m->device);
     const int n = run_layer(m, layer, x, tokens, out, static_cast<cudaStream_t>(stream), nullptr, family);
     if (n < 0) return n;
     m->launches += n;
@@ -325,7 +390,7 @@ int zc_moe_decode(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, voi
 }
 
 int zc_moe_prefill(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
-    if (m && !m->pf_tiles) return fail(m, ZC_EINVAL, "prefill kernels need Q4 projections, BF16 activations, FP32 arithmetic and max_tokens above 64");
+    if (m && !m->pf_tiles) return fail(m, ZC_EINVAL, "prefill kernels need BF16 activations, FP32 arithmetic, hidden and ffn multiples of 512 and max_tokens above 64");
     return forward_family(m, layer, x, tokens, out, stream, 1);
 }
 
@@ -338,6 +403,8 @@ int zc_moe_ep_dispatch(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
     if (!tokens || tokens > m->d.max_tokens || !x || !rows || !row_experts) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
+    if (!aligned16({x, rows, row_experts})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const Call c = make_call(m, layer, x, tokens, nullptr);
     int n, total = 0;
@@ -355,6 +422,8 @@ int zc_moe_ep_experts(zc_moe* m, uint32_t layer, const void* rows, const int32_t
     if (n_rows > m->ep_rows_cap) return fail(m, ZC_EINVAL, "more rows than max_tokens x top_k x ranks");
     if (!n_rows) return ZC_OK;
     if (!rows || !row_experts || !y) return fail(m, ZC_EINVAL, "missing buffer");
+    if (!aligned16({rows, row_experts, y})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     Call c = m->ep;
     const LayerMem& L = m->layers[layer];
@@ -371,6 +440,8 @@ int zc_moe_ep_combine(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens,
     int rc = check_call(m, layer, x, tokens, out);
     if (rc != ZC_OK) return rc;
     if (!y_sorted) return fail(m, ZC_EINVAL, "missing buffer");
+    if (!aligned16({y_sorted})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     Call c = make_call(m, layer, x, tokens, out);
     int n, total = 0;
@@ -386,29 +457,188 @@ int zc_moe_ep_combine(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens,
     return ZC_OK;
 }
 
-int zc_moe_forward_host(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream) {
+// ---- expert parallelism over peer memory ------------------------------------------------------------
+namespace {
+
+int ep_ready(zc_moe* m, uint32_t layer) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    if (!m->ep_window) return fail(m, ZC_EINVAL, "the handle has no expert-parallel window: it needs local_experts < experts, dividing experts evenly");
+    if (!m->ep_world) return fail(m, ZC_EINVAL, "zc_moe_ep_attach has not been called");
+    return ZC_OK;
+}
+
+// Sender side, first half: routing of the local tokens, rows and tags into the owners' windows, flags; then the
+// shared expert (it depends on nothing that travels, so it runs while the rows are in flight).
+int ep_send_phase(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, cudaStream_t s) {
+    const Call c = make_call(m, layer, x, tokens, nullptr);
+    int n, total = 0;
+    if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
+    if ((n = launch_route_permute(m, c, s, true, true)) < 0) return n; total += n;
+    if ((n = launch_ep_send(m, c, s)) < 0) return n; total += n;
+    if (c.has_shared) {
+        Call sh = c;
+        sh.items = m->empty_items;
+        sh.counters = m->zero_counters;          // no routed items: only the shared expert's blocks find work
+        if ((n = launch_experts_decode(m, sh, s)) < 0) return n; total += n;
+    }
+    return total;
+}
+
+// Owner side: wait for every source's rows, regroup them by expert, run the experts in place, store the results
+// into the senders' windows and publish the return flags.
+int ep_process_phase(zc_moe* m, uint32_t layer, cudaStream_t s) {
+    int n, total = 0;
+    if ((n = launch_ep_receive(m, s)) < 0) return n; total += n;
+    Call q = m->ep;
+    const LayerMem& L = m->layers[layer];
+    q.x = m->ep_window + m->ep_layout.rows; q.records = L.records; q.ids = m->ep_row_ids;
+    q.T = m->ep_world * m->ep_layout.cap; q.layer = layer; q.status = m->scratch.status; q.quiet_drop = 1;
+    if ((n = launch_route_permute(m, q, s, false, true)) < 0) return n; total += n;
+    if ((n = launch_experts_decode(m, q, s)) < 0) return n; total += n;
+    if ((n = launch_ep_return(m, s)) < 0) return n; total += n;
+    return total;
+}
+
+// Sender side, second half: wait for every owner's results (they sit at their router slots in this rank's
+// window), then the fixed-order combine; with `next` also the normalised input of the following layer.
+int ep_finish_phase(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next) {
+    int n, total = 0;
+    if ((n = launch_ep_returned(m, s)) < 0) return n; total += n;
+    Call c = make_call(m, layer, x, tokens, out);
+    c.expert_out = reinterpret_cast<float*>(m->ep_window + m->ep_layout.out);
+    n = next ? launch_combine_norm(m, c, next, m->d.act_dtype, s) : launch_combine(m, c, s);
+    if (n < 0) return n; total += n;
+    return total;
+}
+
+int ep_layer_launches(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next) {
+    int n, total = 0;
+    if ((n = ep_send_phase(m, layer, x, tokens, s)) < 0) return n; total += n;
+    if ((n = ep_process_phase(m, layer, s)) < 0) return n; total += n;
+    if ((n = ep_finish_phase(m, layer, x, tokens, out, s, next)) < 0) return n; total += n;
+    return total;
+}
+
+}  // namespace
+
+int zc_moe_ep_export(zc_moe* m, void* handle64, void** window) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (!m->ep_window) return fail(m, ZC_EINVAL, "the handle has no expert-parallel window: it needs local_experts < experts, dividing experts evenly");
+    DeviceGuard guard(m->device);
+    if (window) *window = m->ep_window;
+    if (handle64) {
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the IPC handle is exchanged as 64 bytes");
+        cudaIpcMemHandle_t h;
+        const cudaError_t e = cudaIpcGetMemHandle(&h, m->ep_window);
+        if (e != cudaSuccess) return cuda_fail(m, e, "cudaIpcGetMemHandle");
+        std::memcpy(handle64, &h, 64);
+    }
+    return ZC_OK;
+}
+
+int zc_moe_ep_attach(zc_moe* m, uint32_t rank, uint32_t world, const void* peers, int kind) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (!m->ep_window) return fail(m, ZC_EINVAL, "the handle has no expert-parallel window: it needs local_experts < experts, dividing experts evenly");
+    if (world != m->ep_layout.world || rank >= world || rank != m->d.first_expert / m->d.local_experts)
+        return fail(m, ZC_EINVAL, "rank / world do not match the handle's expert range (world = experts / local_experts, rank = first_expert / local_experts)");
+    if (!peers || (kind != 0 && kind != 1)) return fail(m, ZC_EINVAL, "missing peer table");
+    DeviceGuard guard(m->device);
+    for (uint32_t r = 0; r < world; ++r) {
+        if (r == rank) { m->ep_peers.base[r] = m->ep_window; continue; }
+        if (kind == 1) { m->ep_peers.base[r] = static_cast<uint8_t* const*>(peers)[r]; continue; }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, static_cast<const uint8_t*>(peers) + size_t(r) * 64, 64);
+        void* p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess || !p) { cudaGetLastError(); return cuda_fail(m, e, "cudaIpcOpenMemHandle (peer access between the GPUs of this node is required)"); }
+        m->ep_opened[r] = p;
+        m->ep_peers.base[r] = static_cast<uint8_t*>(p);
+    }
+    m->ep_rank = rank; m->ep_world = world;
+    drop_graphs(m);
+    return ZC_OK;
+}
+
+int zc_moe_ep_send(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* stream) {
+    int rc = ep_ready(m, layer);
+    if (rc != ZC_OK) return rc;
+    if (!tokens || tokens > m->d.max_tokens || !x) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
+    if (!aligned16({x})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
+    const int n = ep_send_phase(m, layer, x, tokens, static_cast<cudaStream_t>(stream));
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_ep_process(zc_moe* m, uint32_t layer, void* stream) {
+    int rc = ep_ready(m, layer);
+    if (rc != ZC_OK) return rc;
+    DeviceGuard guard(m->device);
+    const int n = ep_process_phase(m, layer, static_cast<cudaStream_t>(stream));
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_ep_finish(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
+    int rc = ep_ready(m, layer);
+    if (rc != ZC_OK) return rc;
+    if ((rc = check_call(m, layer, x, tokens, out)) != ZC_OK) return rc;
+    DeviceGuard guard(m->device);
+    const int n = ep_finish_phase(m, layer, x, tokens, out, static_cast<cudaStream_t>(stream), nullptr);
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_ep_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream) {
+    int rc = ep_ready(m, layer);
+    if (rc != ZC_OK) return rc;
+    if ((rc = check_call(m, layer, x, tokens, out)) != ZC_OK) return rc;
+    DeviceGuard guard(m->device);
+    const int n = ep_layer_launches(m, layer, x, tokens, out, static_cast<cudaStream_t>(stream), nullptr);
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+// ---- host-buffer entry points and the chained stack ----------------------------------------------------
+static int forward_host(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream, bool wait) {
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (!tokens || tokens > m->d.max_tokens || !x_host || !out_host) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
     const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), ob = size_t(tokens) * m->d.hidden * elem_bytes(m->d.out_dtype);
+    DeviceGuard guard(m->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if ((e = cudaMemcpyAsync(m->dev_x, x_host, xb, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(m, e, "host to device copy");
     int rc = zc_moe_forward(m, layer, m->dev_x, tokens, m->dev_out, s);
     if (rc != ZC_OK) return rc;
     if ((e = cudaMemcpyAsync(out_host, m->dev_out, ob, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return cuda_fail(m, e, "device to host copy");
-    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(m, e, "MoE execution");
+    if (wait && (e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(m, e, "MoE execution");
     return ZC_OK;
 }
 
-// Launches the chained stack on `s`: layer l reads `in` (l = 0) or the normalised previous output.
-static int stack_launches(zc_moe* m, const void* x, uint32_t tokens, void* out, cudaStream_t s) {
+int zc_moe_forward_host(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream) {
+    return forward_host(m, layer, x_host, tokens, out_host, stream, true);
+}
+
+int zc_moe_forward_host_async(zc_moe* m, uint32_t layer, const void* x_host, uint32_t tokens, void* out_host, void* stream) {
+    return forward_host(m, layer, x_host, tokens, out_host, stream, false);
+}
+
+// Launches the chained stack on `s`: layer l reads `in` (l = 0) or the normalised previous output. With `ep` the
+// layers are expert-parallel layers over peer memory. The cancel flag is read before every layer.
+static int stack_launches(zc_moe* m, const void* x, uint32_t tokens, void* out, cudaStream_t s, bool ep = false) {
     const zc_moe_desc& d = m->d;
     int total = 0;
     const void* in = x;
     for (uint32_t l = 0; l < d.layers; ++l) {
+        if (cancelled(m)) return fail(m, ZC_ECANCELLED, "generation cancelled");
         const bool last = l + 1 == d.layers;
         void* next = last ? nullptr : m->act[l & 1];
-        int n = run_layer(m, l, in, tokens, last ? out : m->dev_out, s, next);
+        int n = ep ? ep_layer_launches(m, l, in, tokens, last ? out : m->dev_out, s, next) : run_layer(m, l, in, tokens, last ? out : m->dev_out, s, next);
         if (n < 0) return n;
         total += n;
         in = next;
@@ -416,13 +646,10 @@ static int stack_launches(zc_moe* m, const void* x, uint32_t tokens, void* out, 
     return total;
 }
 
-int zc_moe_stack(zc_moe* m, const void* x, uint32_t tokens, void* out, void* stream) {
-    int rc = check_call(m, 0, x, tokens, out);
-    if (rc != ZC_OK) return rc;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // One CUDA graph per (tokens, x, out): the launch sequence is fixed — routing only changes which
-    // blocks find work — so replaying the graph removes the per-launch host cost of ~6 kernels a layer.
-    const uint64_t key = (uint64_t(tokens) * 0x9E3779B97F4A7C15ull) ^ reinterpret_cast<uint64_t>(x) ^ (reinterpret_cast<uint64_t>(out) << 1);
+// One CUDA graph per (kind of stack, tokens, x, out): the launch sequence is fixed - routing only changes which
+// blocks find work - so replaying the graph removes the per-launch host cost of ~6 kernels a layer.
+static int stack_graph(zc_moe* m, const void* x, uint32_t tokens, void* out, cudaStream_t s, bool ep) {
+    const auto key = std::make_tuple(ep ? 1 : 0, tokens, x, static_cast<const void*>(out));
     auto found = m->graphs.find(key);
     if (found == m->graphs.end()) {
         cudaStream_t cs = m->own_stream;
@@ -430,11 +657,11 @@ int zc_moe_stack(zc_moe* m, const void* x, uint32_t tokens, void* out, void* str
         // First use of each kernel outside capture, so that function attributes are set once. The input
         // may still be in flight on the caller's stream, so wait for that stream first.
         if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(m, e, "MoE stack execution");
-        int n = stack_launches(m, x, tokens, out, cs);
+        int n = stack_launches(m, x, tokens, out, cs, ep);
         if (n < 0) return n;
         if ((e = cudaStreamSynchronize(cs)) != cudaSuccess) return cuda_fail(m, e, "MoE stack execution");
         if ((e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal)) != cudaSuccess) return cuda_fail(m, e, "graph capture");
-        n = stack_launches(m, x, tokens, out, cs);
+        n = stack_launches(m, x, tokens, out, cs, ep);
         cudaGraph_t graph = nullptr;
         e = cudaStreamEndCapture(cs, &graph);
         if (n < 0) { if (graph) cudaGraphDestroy(graph); return n; }
@@ -443,11 +670,44 @@ int zc_moe_stack(zc_moe* m, const void* x, uint32_t tokens, void* out, void* str
         e = cudaGraphInstantiate(&exec, graph, 0);
         cudaGraphDestroy(graph);
         if (e != cudaSuccess) return cuda_fail(m, e, "graph instantiation");
-        found = m->graphs.emplace(key, zc_moe::Graph{exec, uint64_t(n)}).first;
+        if (m->graphs.size() >= zc_moe::GRAPH_CACHE) {              // drop the least recently used capture
+            auto oldest = m->graphs.begin();
+            for (auto it = m->graphs.begin(); it != m->graphs.end(); ++it) if (it->second.last_use < oldest->second.last_use) oldest = it;
+            cudaGraphExecDestroy(oldest->second.exec);
+            m->graphs.erase(oldest);
+        }
+        found = m->graphs.emplace(key, zc_moe::Graph{exec, uint64_t(n), 0}).first;
     }
+    found->second.last_use = ++m->graph_clock;
     const cudaError_t e = cudaGraphLaunch(found->second.exec, s);
     if (e != cudaSuccess) return cuda_fail(m, e, "graph launch");
     m->launches += found->second.nodes;
+    return ZC_OK;
+}
+
+int zc_moe_stack(zc_moe* m, const void* x, uint32_t tokens, void* out, void* stream) {
+    int rc = check_call(m, 0, x, tokens, out);
+    if (rc != ZC_OK) return rc;
+    DeviceGuard guard(m->device);
+    return stack_graph(m, x, tokens, out, static_cast<cudaStream_t>(stream), false);
+}
+
+int zc_moe_ep_stack(zc_moe* m, const void* x, uint32_t tokens, void* out, void* stream) {
+    int rc = ep_ready(m, 0);
+    if (rc != ZC_OK) return rc;
+    if ((rc = check_call(m, 0, x, tokens, out)) != ZC_OK) return rc;
+    DeviceGuard guard(m->device);
+    return stack_graph(m, x, tokens, out, static_cast<cudaStream_t>(stream), true);
+}
+
+int zc_moe_ep_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, void* stream) {
+    int rc = ep_ready(m, 0);
+    if (rc != ZC_OK) return rc;
+    if ((rc = check_call(m, 0, x, tokens, out)) != ZC_OK) return rc;
+    DeviceGuard guard(m->device);
+    const int n = stack_launches(m, x, tokens, out, static_cast<cudaStream_t>(stream), true);
+    if (n < 0) return n;
+    m->launches += n;
     return ZC_OK;
 }
 
@@ -455,6 +715,7 @@ int zc_moe_stack_host(zc_moe* m, const void* x_host, uint32_t tokens, void* out_
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (!tokens || tokens > m->d.max_tokens || !x_host || !out_host) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
     const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), ob = size_t(tokens) * m->d.hidden * elem_bytes(m->d.out_dtype);
+    DeviceGuard guard(m->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if ((e = cudaMemcpyAsync(m->dev_x, x_host, xb, cudaMemcpyHostToDevice, s)) != cudaSuccess) return cuda_fail(m, e, "host to device copy");
@@ -462,6 +723,13 @@ int zc_moe_stack_host(zc_moe* m, const void* x_host, uint32_t tokens, void* out_
     if (rc != ZC_OK) return rc;
     if ((e = cudaMemcpyAsync(out_host, m->dev_final, ob, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return cuda_fail(m, e, "device to host copy");
     if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(m, e, "MoE stack execution");
+    if (cancelled(m)) return fail(m, ZC_ECANCELLED, "generation cancelled");
+    return ZC_OK;
+}
+
+int zc_moe_set_cancel(zc_moe* m, const int32_t* flag) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    m->cancel = flag;
     return ZC_OK;
 }
 
@@ -477,13 +745,24 @@ int zc_moe_last_routing(zc_moe* m, const int32_t** ids, const float** weights, c
 
 int zc_moe_active_counts(zc_moe* m, int32_t* host_counts) {
     if (!m || !host_counts) return fail(m, ZC_EINVAL, "null handle or buffer");
+    DeviceGuard guard(m->device);
     const cudaError_t e = cudaMemcpy(host_counts, m->scratch.counters + 16, size_t(m->d.layers) * 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(m, e, "device read");
+    return ZC_OK;
+}
+
+int zc_moe_ep_active_counts(zc_moe* m, int32_t* host_counts) {
+    if (!m || !host_counts) return fail(m, ZC_EINVAL, "null handle or buffer");
+    if (!m->ep.counters) return fail(m, ZC_EINVAL, "the handle holds every expert: expert parallelism needs local_experts < experts");
+    DeviceGuard guard(m->device);
+    const cudaError_t e = cudaMemcpy(host_counts, m->ep.counters + 16, size_t(m->d.layers) * 4, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_fail(m, e, "device read");
     return ZC_OK;
 }
 
 int zc_moe_read_device(zc_moe* m, void* host_dst, const void* device_src, uint64_t bytes) {
     if (!m || !host_dst || !device_src) return fail(m, ZC_EINVAL, "null handle or buffer");
+    DeviceGuard guard(m->device);
     const cudaError_t e = cudaMemcpy(host_dst, device_src, bytes, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_fail(m, e, "device read");
     return ZC_OK;
@@ -491,6 +770,7 @@ int zc_moe_read_device(zc_moe* m, void* host_dst, const void* device_src, uint64
 
 int zc_moe_status(zc_moe* m, void* stream, uint32_t* status) {
     if (!m || !status) return fail(m, ZC_EINVAL, "null handle or status");
+    DeviceGuard guard(m->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaStreamSynchronize(s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->own_stream);
@@ -503,6 +783,7 @@ int zc_moe_status(zc_moe* m, void* stream, uint32_t* status) {
 int zc_moe_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, void* stream) {
     int rc = check_call(m, 0, x, tokens, out);
     if (rc != ZC_OK) return rc;
+    DeviceGuard guard(m->device);
     const int n = stack_launches(m, x, tokens, out, static_cast<cudaStream_t>(stream));
     if (n < 0) return n;
     m->launches += n;
@@ -512,9 +793,16 @@ int zc_moe_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, voi
 int zc_moe_set_option(zc_moe* m, const char* name, int value) {
     if (!m || !name) return fail(m, ZC_EINVAL, "null handle or option name");
     const bool fold = !std::strcmp(name, "fold_q4"), pdl = !std::strcmp(name, "pdl"), exact_h = !std::strcmp(name, "exact_h");
+    if (!std::strcmp(name, "ep_wait_ms")) {
+        if (value < 1 || value > 60000) return fail(m, ZC_EINVAL, "ep_wait_ms must be 1..60000");
+        DeviceGuard guard(m->device);
+        drop_graphs(m);
+        m->ep_wait_ms = uint32_t(value);
+        return ZC_OK;
+    }
     if (fold || pdl || exact_h) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);      // captured launches hold the old choice
-        m->graphs.clear();
+        DeviceGuard guard(m->device);
+        drop_graphs(m);                                                      // captured launches hold the old choice
         if (exact_h) m->exact_h = value != 0;
         else if (fold) m->fold_q4 = value != 0; else m->pdl = value == 0 ? 0u : value == 1 ? 0xffffffffu : uint32_t(value);
         return ZC_OK;
@@ -523,7 +811,7 @@ int zc_moe_set_option(zc_moe* m, const char* name, int value) {
 }
 
 const char* zc_moe_kernel_name(int kind) {
-    static const char* names[KERNEL_KINDS] = {"router", "route", "permute", "gate_up", "down", "combine", "norm_act",
+    static const char* names[KERNEL_KINDS] = {"router", "route", "permute", "gate_up", "down", "combine", "ep",
                                               "prefill_prep", "prefill_gate_up", "prefill_down"};
     return kind >= 0 && kind < KERNEL_KINDS ? names[kind] : nullptr;
 }
@@ -537,6 +825,7 @@ int zc_moe_profile_begin(zc_moe* m) {
 int zc_moe_profile_end(zc_moe* m, double* ms_per_kind, uint64_t* launches_per_kind) {
     if (!m || !ms_per_kind || !launches_per_kind) return fail(m, ZC_EINVAL, "null handle or output");
     m->profiling = false;
+    DeviceGuard guard(m->device);
     cudaError_t e = cudaDeviceSynchronize();
     for (int k = 0; k < KERNEL_KINDS; ++k) { ms_per_kind[k] = 0; launches_per_kind[k] = 0; }
     for (auto& sp : m->spans) {
@@ -552,6 +841,7 @@ int zc_moe_profile_end(zc_moe* m, double* ms_per_kind, uint64_t* launches_per_ki
 int zc_synth_fill_layer(zc_moe* m, uint32_t layer, uint64_t seed, void* stream) {
     if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
     if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    DeviceGuard guard(m->device);
     const int n = launch_synth_layer(m, layer, seed, static_cast<cudaStream_t>(stream));
     if (n < 0) return n;
     m->launches += n;

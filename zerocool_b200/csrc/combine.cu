@@ -103,7 +103,11 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(Call c) {
 
 // combine + the inter-layer stand-in of the chained stack in one launch: one CTA per token computes the
 // layer output (rounded to the output dtype, as a separate combine launch would have stored it), keeps it
-// in shared memory, and writes next[t, :] = act_dtype((out - mean) / std). See norm_act_kernel.
+// in shared memory, and writes next[t, :] = act_dtype((out - mean) / std): the stand-in for the residual + norm
+// between MoE layers used when the stack is timed as one dependent chain. The mean is removed because the
+// synthetic weights have a non-zero mean (codes 0..15 with bias -8 scale): without centring, that common
+// component is amplified layer after layer until every token carries the same vector and routes to the same
+// ten experts, which a real model's hidden states do not do.
 constexpr int CN_THREADS = 512;
 template <int KMAX>
 __global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(Call c, void* next, int next_dtype) {
@@ -145,46 +149,21 @@ __global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(Call c, void* 
     }
 }
 
-// x_next[t, :] = act_dtype((in[t, :] - mean) / std): the stand-in for the residual + norm between MoE
-// layers used when the stack is timed as one dependent chain. The mean is removed because the synthetic
-// weights have a non-zero mean (codes 0..15 with bias -8 scale): without centring, that common component
-// is amplified layer after layer until every token carries the same vector and routes to the same ten
-// experts, which a real model's hidden states do not do. One CTA per token.
-constexpr int RMS_THREADS = 256;
-__device__ __forceinline__ float block_sum(float v, float* partial) {
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    __syncthreads();
-    if (threadIdx.x % 32 == 0) partial[threadIdx.x / 32] = v;
-    __syncthreads();
-    float total = 0.0f;
-    for (int i = 0; i < RMS_THREADS / 32; ++i) total += partial[i];
-    return total;
-}
-__device__ __forceinline__ float load_as_float(const void* in, int dtype, size_t i) {
-    return dtype == ZC_F32 ? static_cast<const float*>(in)[i] : bf_to_float(static_cast<const uint16_t*>(in)[i]);
-}
-__global__ void __launch_bounds__(RMS_THREADS) norm_act_kernel(const void* in, int in_dtype, void* out, int out_dtype, uint32_t H) {
-    const uint32_t t = blockIdx.x;
-    __shared__ float partial[RMS_THREADS / 32];
-    float sum = 0.0f;
-    for (uint32_t k = threadIdx.x; k < H; k += RMS_THREADS) sum += load_as_float(in, in_dtype, size_t(t) * H + k);
-    const float mean = block_sum(sum, partial) / float(H);
-    float sq = 0.0f;
-    for (uint32_t k = threadIdx.x; k < H; k += RMS_THREADS) {
-        const float d = load_as_float(in, in_dtype, size_t(t) * H + k) - mean;
-        sq = __fmaf_rn(d, d, sq);
-    }
-    const float var = block_sum(sq, partial) / float(H);
-    const float scale = var > 0.0f ? __fdiv_rn(1.0f, sqrtf(var)) : 0.0f;
-    for (uint32_t k = threadIdx.x; k < H; k += RMS_THREADS) {
-        const float r = __fmul_rn(load_as_float(in, in_dtype, size_t(t) * H + k) - mean, scale);
-        if (out_dtype == ZC_F32) static_cast<float*>(out)[size_t(t) * H + k] = r;
-        else static_cast<uint16_t*>(out)[size_t(t) * H + k] = bf_bits(r);
-    }
+// The BF16-staged activations of the reference arithmetic, element by element (parity hook).
+__global__ void activation_table_kernel(const float* __restrict__ x, uint32_t n, float* __restrict__ sigmoid_out, float* __restrict__ silu_out) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = x[i], sg = sigmoid_bf(v);
+    if (sigmoid_out) sigmoid_out[i] = bf_round(sg);
+    if (silu_out) silu_out[i] = bf_round(__fmul_rn(v, sg));
 }
 
 }  // namespace
+
+int launch_activation_table(const float* x, uint32_t n, float* sigmoid_out, float* silu_out, cudaStream_t s) {
+    activation_table_kernel<<<(n + 127) / 128, 128, 0, s>>>(x, n, sigmoid_out, silu_out);
+    return check_launch(nullptr, "activation table");
+}
 
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s) {
     if (c.K > MAX_K) return fail(m, ZC_EINVAL, "top_k above 32");
@@ -203,12 +182,6 @@ int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cu
       auto k = c.K <= 8 ? combine_norm_kernel<8> : c.K <= 16 ? combine_norm_kernel<16> : combine_norm_kernel<32>;
       launch_chained(m, KERNEL_COMBINE, k, dim3(c.T), dim3(CN_THREADS), smem, s, nullptr, 0, c, next, next_dtype);
       rc = check_launch(m, "combine_norm"); }
-    return rc < 0 ? rc : 1;
-}
-
-int launch_norm_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s) {
-    int rc;
-    { Timed t(m, s, KERNEL_NORM_ACT); norm_act_kernel<<<T, RMS_THREADS, 0, s>>>(in, in_dtype, out, out_dtype, H); rc = check_launch(m, "norm_act"); }
     return rc < 0 ? rc : 1;
 }
 

@@ -6,7 +6,8 @@
 #include <cstdint>
 #include <string>
 #include <vector>
-#include <unordered_map>
+#include <map>
+#include <tuple>
 
 #include "../../include/zc_moe.h"
 
@@ -39,54 +40,6 @@ __device__ __forceinline__ float sigmoid_bf(float x) {
     float e = float(exp(double(fabsf(x))));
     float y = bf_round(__fdiv_rn(1.0f, bf_round(1.0f + bf_round(e))));
     return x < 0 ? y : bf_round(1.0f - y);
-}
-
-__device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
-// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col). Lane (g = lane/4, c = lane%4) holds
-//   a0: A[g][2c,2c+1]   a1: A[g+8][2c,2c+1]   a2: A[g][2c+8,2c+9]   a3: A[g+8][2c+8,2c+9]
-//   b0: B[2c,2c+1][g]   b1: B[2c+8,2c+9][g]
-//   d0,d1: D[g][2c,2c+1]   d2,d3: D[g+8][2c,2c+1]
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// Eight 4-bit codes of one little-endian word -> four bf16x2 registers holding the integer values
-// (k0,k4) (k1,k5) (k2,k6) (k3,k7); low half first. 0x4300 is bf16 128.0, whose ulp is 1, so
-// (0x4300 | q) is exactly 128+q and the subtraction is exact.
-__device__ __forceinline__ void dequant_q4_word(uint32_t w, uint32_t (&p)[4]) {
-    const uint32_t magic = 0x43004300u, mask = 0x000f000fu;
-    const __nv_bfloat162 off = __floats2bfloat162_rn(128.0f, 128.0f);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t v = ((w >> (4 * i)) & mask) | magic;
-        __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), off);
-        p[i] = *reinterpret_cast<uint32_t*>(&r);
-    }
-}
-// Four 8-bit codes of one word -> two bf16x2 registers (k0,k1) (k2,k3). Every integer in
-// [-128, 255] is exact in bf16. is_signed reads the byte as int8.
-__device__ __forceinline__ void dequant_q8_word(uint32_t w, bool is_signed, uint32_t (&p)[2]) {
-    if (is_signed) w ^= 0x80808080u;
-    const float off = is_signed ? 8388608.0f + 128.0f : 8388608.0f;
-    float f[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(0x4b000000u | ((w >> (8 * i)) & 0xffu)) - off;
-    __nv_bfloat162 lo = __floats2bfloat162_rn(f[0], f[1]), hi = __floats2bfloat162_rn(f[2], f[3]);
-    p[0] = *reinterpret_cast<uint32_t*>(&lo);
-    p[1] = *reinterpret_cast<uint32_t*>(&hi);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -152,7 +105,23 @@ struct Call {
     uint64_t record_stride;
     Projection gate, up, down;
     uint8_t act_dtype, out_dtype, meta_f16, router_dtype, has_shared, ref, q8_signed;
+    uint8_t quiet_drop;       // the permutation drops ids outside [0, E) without raising the status bit (unused row slots of a receive area)
 };
+
+// Expert parallelism over peer memory (csrc/ep.cu). Every rank owns one window with this layout (byte offsets).
+constexpr int EP_MAX_RANKS = 16;
+struct EpWindow {
+    uint64_t rows;        // [world][cap][row bytes]  token rows received from each source rank
+    uint64_t tags;        // [world][cap] int2 {expert id, router slot on the source}
+    uint64_t in_flags;    // [EP_MAX_RANKS] u64 {epoch << 32 | rows sent}, written by each source
+    uint64_t ret_flags;   // [EP_MAX_RANKS] u64 {epoch << 32}, written by each owner when its results are stored
+    uint64_t out;         // [cap][H] fp32: results by router slot, written by the owners (the combine's expert_out)
+    uint64_t bytes;
+    uint32_t cap;         // rows one source can send to one owner: max_tokens x top_k
+    uint32_t world;
+};
+struct EpPeers { uint8_t* base[EP_MAX_RANKS]; };
+EpWindow ep_window_layout(const zc_moe_desc& d);
 
 }  // namespace zc
 
@@ -172,6 +141,17 @@ struct zc_moe {
     uint32_t* router_done = nullptr;     // arrival counters of the router's (row tile, token tile) pairs
     zc::Call ep{};                       // second scratch set: the experts step of expert parallelism (rows from all ranks)
     uint32_t ep_rows_cap = 0;
+    // peer transport of expert parallelism (allocated when local_experts < experts; usable after zc_moe_ep_attach)
+    uint8_t* ep_window = nullptr;
+    zc::EpWindow ep_layout{};
+    zc::EpPeers ep_peers{};
+    void* ep_opened[zc::EP_MAX_RANKS] = {};   // mappings opened from IPC handles (closed at destroy)
+    uint32_t ep_rank = 0, ep_world = 0;   // world = 0: not attached
+    uint32_t* ep_ctl = nullptr;           // [0] epoch, [1] send arrivals, [2] return arrivals
+    int32_t* ep_row_ids = nullptr;        // [world x cap] expert id of every row slot of the receive area (-1: unused)
+    uint32_t* ep_counts = nullptr;        // [EP_MAX_RANKS] rows received from each source in the current epoch
+    uint32_t ep_wait_ms = 2000;           // limit of one device-side wait for a peer's flag
+    const int32_t* cancel = nullptr;      // host flag read before a layer is issued (zc_moe_set_cancel)
     int4* empty_items = nullptr;         // an item list with no entries (launches that run the shared expert only)
     int32_t* zero_counters = nullptr;    // an always-zero counter block (launches that run the shared expert only)
     float* router_partial = nullptr;     // [16, max_tokens, rows_padded] partition sums of the router
@@ -184,8 +164,12 @@ struct zc_moe {
     cudaStream_t own_stream = nullptr;
     std::string error;
     uint64_t launches = 0;
-    struct Graph { cudaGraphExec_t exec; uint64_t nodes; };
-    std::unordered_map<uint64_t, Graph> graphs;
+    // Captured stacks, keyed by everything a capture bakes in (kind of stack, token count, input and output address);
+    // at most GRAPH_CACHE entries, the least recently used one is dropped.
+    struct Graph { cudaGraphExec_t exec; uint64_t nodes; uint64_t last_use; };
+    static constexpr size_t GRAPH_CACHE = 8;
+    std::map<std::tuple<int, uint32_t, const void*, const void*>, Graph> graphs;
+    uint64_t graph_clock = 0;
     // Optional per-kernel timing (zc_moe_profile_begin/end): one event pair per launch.
     uint32_t pdl = 0xffffffffu;   // bit per KernelKind: that kernel launches with programmatic stream serialization (see launch_chained)
     bool exact_h = false;         // down reads the FP32 SwiGLU rows as two FP16 terms instead of one
@@ -209,10 +193,14 @@ size_t prefill_tile_bytes();
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_ep_gather(zc_moe* m, const Call& c, void* rows, int32_t* row_experts, cudaStream_t s);
 int launch_ep_scatter(zc_moe* m, const Call& c, const float* y, cudaStream_t s);
+int launch_ep_send(zc_moe* m, const Call& c, cudaStream_t s);
+int launch_ep_receive(zc_moe* m, cudaStream_t s);
+int launch_ep_return(zc_moe* m, cudaStream_t s);
+int launch_ep_returned(zc_moe* m, cudaStream_t s);
+int launch_activation_table(const float* x, uint32_t n, float* sigmoid_out, float* silu_out, cudaStream_t s);
 int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cudaStream_t s);
-int launch_norm_act(zc_moe* m, const void* in, int in_dtype, void* out, int out_dtype, uint32_t T, uint32_t H, cudaStream_t s);
 int launch_synth_layer(zc_moe* m, uint32_t layer, uint64_t seed, cudaStream_t s);
-enum KernelKind { KERNEL_ROUTER = 0, KERNEL_ROUTE, KERNEL_PERMUTE, KERNEL_GATE_UP, KERNEL_DOWN, KERNEL_COMBINE, KERNEL_NORM_ACT,
+enum KernelKind { KERNEL_ROUTER = 0, KERNEL_ROUTE, KERNEL_PERMUTE, KERNEL_GATE_UP, KERNEL_DOWN, KERNEL_COMBINE, KERNEL_EP,
                   KERNEL_PREFILL_PREP, KERNEL_PREFILL_GATE_UP, KERNEL_PREFILL_DOWN, KERNEL_KINDS };
 // Brackets one kernel launch with events when profiling is enabled.
 struct Timed {
@@ -228,6 +216,31 @@ struct Timed {
 };
 int fail(zc_moe* m, int code, const std::string& text);
 int check_launch(zc_moe* m, const char* what);
+
+// cudaFuncSetAttribute is a per-device setting: the largest dynamic shared-memory size a kernel has been opted
+// into is remembered per device, so that a process that owns handles on several GPUs configures each of them.
+constexpr int MAX_DEVICES = 64;
+struct SmemOptIn { size_t bytes[MAX_DEVICES] = {}; };
+template <typename Kernel>
+inline cudaError_t opt_in_smem(Kernel kernel, SmemOptIn& state, int device, size_t smem) {
+    if (device < 0 || device >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    if (smem <= state.bytes[device]) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e == cudaSuccess) state.bytes[device] = smem;
+    return e;
+}
+
+// Makes the handle's device current for the duration of an entry point and restores the caller's device.
+struct DeviceGuard {
+    int previous = -1;
+    bool changed = false;
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&previous) == cudaSuccess && previous != device) changed = cudaSetDevice(device) == cudaSuccess;
+    }
+    ~DeviceGuard() { if (changed) cudaSetDevice(previous); }
+    DeviceGuard(const DeviceGuard&) = delete;
+    DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
 
 // Programmatic dependent launch. The kernels of a layer form a chain on one stream; each is launched with
 // "programmatic stream serialization", which lets its CTAs be placed on SMs that the previous kernel no longer

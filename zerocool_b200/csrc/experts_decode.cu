@@ -35,7 +35,9 @@
 //  * Lanes whose token row is absent (fewer than eight rows in the pass) skip the activation reads.
 //  * Because a dot product does not care about the order of k, the MMA's k slots are bound to whatever
 //    k values fall out of the cheapest extraction; the activations are staged in the matching order.
-// Activations must stay inside FP16 after the factor 16 (|x| < 4096); hidden states after a norm are O(1..100).
+// Activations must stay inside FP16 after the factor 16 (|x| < 4094 for Q4 projections, < 65504 for Q8); hidden
+// states after a norm are O(1..100). A value beyond that raises ZC_STATUS_RANGE in the status word (the output of
+// that row is then not meaningful); the same holds for the SwiGLU rows the down projection reads.
 #include "common.cuh"
 
 namespace zc {
@@ -134,8 +136,9 @@ __device__ __forceinline__ bool decode_item(const Call& c, uint32_t item, ItemIn
 // Rows n >= nvalid are left as they are: an MMA column only depends on its own B column.
 template <bool Q4ORDER, bool SPLIT, bool FOLD>
 __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const int* rows, uint32_t nvalid,
-                                           uint32_t K, bool ref, __half* hi, __half* lo, float* sums) {
+                                           uint32_t K, bool ref, __half* hi, __half* lo, float* sums, uint32_t* status) {
     const uint32_t RS = K + ROW_PAD, blocks = K / 8, total = nvalid * blocks;
+    bool out_of_range = false;
     // The trip count is uniform per warp (the shuffles below need all 32 lanes); lanes past the end carry zeros.
     for (uint32_t idx = threadIdx.x; (idx & ~31u) < total; idx += EXPERT_THREADS) {
         const bool live = idx < total;
@@ -166,6 +169,7 @@ __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const 
             // staged x 16 rather than odd slots / 16, which keeps small activations out of FP16's subnormal range; the
             // accumulated result is multiplied by 1/16 (exact) when it is finished.
             const float pre = (FOLD && Q4ORDER && !(i & 1)) ? v[i] * 16.0f : v[i];
+            out_of_range |= fabsf(pre) > 65504.0f;          // would become an FP16 infinity: reported, not hidden
             h[i] = __float2half_rn(pre);
             float fed = __half2float(h[i]);
             if (SPLIT) { l[i] = __float2half_rn(pre - fed); fed += __half2float(l[i]); }
@@ -194,6 +198,7 @@ __device__ __forceinline__ void stage_rows(const void* src, bool src_f32, const 
         *reinterpret_cast<uint4*>(hi + n * RS + q * 8) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
         if (SPLIT) *reinterpret_cast<uint4*>(lo + n * RS + q * 8) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
     }
+    if (out_of_range) atomicOr(status, ZC_STATUS_RANGE);
 }
 
 // Source of one matrix for this lane's cp.async copies. A pass of the warp copies ROWS_PER_PASS rows: the
@@ -396,7 +401,7 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
         __syncthreads();
         if constexpr (NMAT == 1) { pdl_wait(); pdl_launch_dependents(); }
         stage_rows<BITS == 4, SPLIT, FOLDQ>(NMAT == 2 ? c.x : static_cast<const void*>(c.hbuf), NMAT == 2 ? c.act_dtype == ZC_F32 : true,
-                                            rows, nvalid, K, c.ref && BITS == 4, xhi, xlo, sums);
+                                            rows, nvalid, K, c.ref && BITS == 4, xhi, xlo, sums, c.status);
         __syncthreads();
 
         // The lane holds rows g, g+8 of its tile for tokens 2cq, 2cq+1.
@@ -535,11 +540,8 @@ int launch_expert_ch(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_pe
     while (tiles_per_warp > 1 && N % (16 * RT * tiles_per_warp)) --tiles_per_warp;
     if (N % (16 * RT * tiles_per_warp)) return fail(m, ZC_EINVAL, "expert kernel: rows not a multiple of the CTA tile");
     auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH>;
-    static size_t configured = 0;       // one per instantiation of this function template
-    if (smem > configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return check_launch(m, "expert kernel attribute");
-        configured = smem;
-    }
+    static SmemOptIn configured;        // one per instantiation of this function template
+    if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) return check_launch(m, "expert kernel attribute");
     Timed t(m, s, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN);
     const cudaError_t e = launch_chained(m, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN, kernel, dim3(N / (16 * RT * tiles_per_warp), items), dim3(EXPERT_THREADS), smem, s, nullptr, 0, c, tiles_per_warp);
     if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("expert kernel launch: ") + cudaGetErrorString(e));

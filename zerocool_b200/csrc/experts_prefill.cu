@@ -21,6 +21,9 @@
 //     own FP16 metadata) times B' = [8 S_0.. | S_0..] with S_g = sum of the token's activations in group g,
 //     carried as two FP16 terms (hi, lo). It runs as extra stages after the K loop (K' in blocks of 64, hi then lo)
 //     and is added with scale 1.
+//   8-bit codes (u8 as in the reference's affine8_dot, qwen.metal:112-125, or int8) take the same path with the
+//   codes themselves as the exact FP16 integers (no offset: the correction term is b_g * sum_k x_k alone) and the
+//   token rows in natural k order.
 //   NMAT = 2: gate and up tiles of the same 128 rows sit side by side in TMEM; the final epilogue applies
 //             SwiGLU and stores h as FP16 in the k order the second launch consumes.
 //   NMAT = 1: the down projection; the final epilogue writes FP32 rows at the slots' router positions.
@@ -131,6 +134,16 @@ __device__ __forceinline__ uint4 pf_dequant_word(uint32_t w) {
     return make_uint4(p[0], p[1], p[2], p[3]);
 }
 
+// Four 8-bit codes of one word -> two half2 (k0,k1) (k2,k3) holding the integers exactly: the byte b next to 0x64 is
+// the FP16 value 1024 + b; int8 codes are biased by 128 first (b ^ 0x80) and lose 1152.
+__device__ __forceinline__ uint2 pf_dequant_q8_word(uint32_t w, bool is_signed) {
+    if (is_signed) w ^= 0x80808080u;
+    const __half2 off = is_signed ? __floats2half2_rn(1152.0f, 1152.0f) : __floats2half2_rn(1024.0f, 1024.0f);
+    uint32_t lo = __byte_perm(w, 0x64646464u, 0x4140), hi = __byte_perm(w, 0x64646464u, 0x4342);
+    __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo), off), b = __hsub2(*reinterpret_cast<__half2*>(&hi), off);
+    return make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+
 // Tile list: one entry per (expert with work, block of PF_NMAX of its rows), the shared expert's token
 // blocks first. One CTA of 1024 threads; experts <= 1024.
 __global__ void __launch_bounds__(1024) pf_tiles_kernel(const int32_t* __restrict__ offsets, uint32_t E, uint32_t first_expert, uint32_t local_experts,
@@ -162,7 +175,7 @@ __global__ void __launch_bounds__(1024) pf_tiles_kernel(const int32_t* __restric
 
 // x [T, H] (bf16 or fp32) -> FP16 [T, H] with every block of eight k values stored in pf_pos8 order: the
 // B operand of the gate/up launch, copied into shared memory with plain 16-byte cp.async.
-__global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, __half* __restrict__ xp, size_t blocks) {
+__global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, __half* __restrict__ xp, size_t blocks, uint32_t* __restrict__ status, bool natural) {
     const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= blocks) return;
     float v[8];
@@ -177,15 +190,17 @@ __global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, _
         for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(r[j] << 16); v[2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u); }
     }
     __half h[8];
+    bool out_of_range = false;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) h[pf_pos8(j)] = __float2half_rn(v[j]);
+    for (int j = 0; j < 8; ++j) { out_of_range |= fabsf(v[j]) > 65504.0f; h[natural ? j : pf_pos8(j)] = __float2half_rn(v[j]); }
     *reinterpret_cast<uint4*>(xp + i * 8) = *reinterpret_cast<uint4*>(h);
+    if (out_of_range) atomicOr(status, ZC_STATUS_RANGE);
 }
 
 // Per row of an FP16 matrix [rows, K] and per 64-wide group g: S_g = sum of the row's values in the group (FP32 sum),
-// stored as the B' operand of the correction stages, [8 hi_0.. | hi_0.. | 8 lo_0.. | lo_0..] with hi = fp16(S),
-// lo = fp16(S - hi) (4 G halves per row). One warp per row.
-__global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, uint32_t K, __half* __restrict__ sums) {
+// stored as the B' operand of the correction stages, [c hi_0.. | hi_0.. | c lo_0.. | lo_0..] with hi = fp16(S),
+// lo = fp16(S - hi) (4 G halves per row) and c = the code offset the K loop removed (8 for Q4, 0 for Q8). One warp per row.
+__global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, uint32_t K, __half* __restrict__ sums, uint32_t* __restrict__ status, float offset) {
     const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
     if (row >= rows) return;
     const uint32_t G = K / 64;
@@ -202,10 +217,11 @@ __global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, ui
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         sum += __shfl_xor_sync(0xffffffffu, sum, 4);
         if (g < G && lane % 8 == 0) {
+            if (!(fabsf(sum) <= 8188.0f)) atomicOr(status, ZC_STATUS_RANGE);       // 8 S (or an infinite input) leaves FP16
             const __half hi = __float2half_rn(sum), lo = __float2half_rn(sum - __half2float(hi));
             __half* dst = sums + size_t(row) * 4 * G;
-            dst[g] = __float2half_rn(8.0f * __half2float(hi)); dst[G + g] = hi;
-            dst[2 * G + g] = __float2half_rn(8.0f * __half2float(lo)); dst[3 * G + g] = lo;
+            dst[g] = __float2half_rn(offset * __half2float(hi)); dst[G + g] = hi;
+            dst[2 * G + g] = __float2half_rn(offset * __half2float(lo)); dst[3 * G + g] = lo;
         }
     }
 }
@@ -220,12 +236,13 @@ constexpr uint32_t PF_STAGES = 3;      // A stage buffers (written by the produc
 // latency. Token-row (B) ring: D + PF_STAGES slots; per-thread ring of packed codes: D + 1 slots.
 
 // Shared memory of one CTA (dynamic, 1024-byte aligned for the tile buffers).
-template <int NMAT>
+template <int NMAT, int BITS>
 struct PfSmem {
     static constexpr uint32_t A_STAGE = NMAT * PF_A_BYTES;
     static constexpr uint32_t A_RING = PF_STAGES * A_STAGE;
+    static constexpr uint32_t RAWB = BITS * 8;                 // packed code bytes of one weight row of one group
     __host__ __device__ static uint32_t b_ring(uint32_t D) { return (D + PF_STAGES) * PF_B_BYTES; }
-    __host__ __device__ static uint32_t raw_bytes(uint32_t D) { return (D + 1) * NMAT * 128 * 32; }         // [slot][matrix][thread][32 B]
+    __host__ __device__ static uint32_t raw_bytes(uint32_t D) { return (D + 1) * NMAT * 128 * RAWB; }       // [slot][matrix][thread][RAWB]
     // metadata tiles: per matrix 128 rows x 2 G halves in the A' layout (16 x 2 G / 8 core matrices of 128 B)
     static uint32_t meta_bytes(uint32_t G) { return NMAT * 128 * 2 * G * 2; }
     static uint32_t total(uint32_t G, uint32_t D) { return A_RING + b_ring(D) + raw_bytes(D) + meta_bytes(G) + 1024; }   // + alignment slack
@@ -233,11 +250,11 @@ struct PfSmem {
 
 // Grid: (weight-row tiles of 128, tiles of the list). See the file header for the roles.
 // bsrc: FP16 token rows [.., K]; bsum: their group sums [.., 4 G] (pf_sums_kernel).
-template <int NMAT, bool META_F16, int D>
+template <int NMAT, int BITS, bool META_F16, int D>
 __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(Call c, const PfTile* __restrict__ tiles, const int32_t* __restrict__ ntiles,
                                                                  const __half* __restrict__ bsrc, const __half* __restrict__ bsum,
-                                                                 __half* __restrict__ hdst) {
-    using S = PfSmem<NMAT>;
+                                                                 __half* __restrict__ hdst, uint32_t h_natural) {
+    using S = PfSmem<NMAT, BITS>;
     constexpr uint32_t PF_RAW = D + 1, PF_BS = D + PF_STAGES;
     extern __shared__ uint8_t pf_raw_smem[];
     __shared__ __align__(8) uint64_t full_bar[PF_STAGES], done_bar[PF_STAGES], acc_full[PF_ACC], acc_free[PF_ACC], meta_bar;
@@ -297,7 +314,7 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
         const uint32_t r = tid;                                   // weight row of the tile
         const uint8_t* codes[NMAT];
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m) codes[m] = record + pr[m].codes + size_t(r0 + r) * (K / 2);
+        for (int m = 0; m < NMAT; ++m) codes[m] = record + pr[m].codes + size_t(r0 + r) * (K * BITS / 8);
         // metadata of row r -> A' tiles [s_0..s_G-1 | b_0..b_G-1] as FP16, core-matrix layout
 #pragma unroll
         for (int m = 0; m < NMAT; ++m) {
@@ -337,9 +354,9 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
             const uint32_t slot = ks % PF_RAW;
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
-                const uint32_t dst = raw_base + ((slot * NMAT + m) * 128 + r) * 32;
-                pf_cp16(dst, codes[m] + ks * 32);
-                pf_cp16(dst + 16, codes[m] + ks * 32 + 16);
+                const uint32_t dst = raw_base + ((slot * NMAT + m) * 128 + r) * S::RAWB;
+#pragma unroll
+                for (uint32_t piece = 0; piece < S::RAWB; piece += 16) pf_cp16(dst + piece, codes[m] + ks * S::RAWB + piece);
             }
         };
         // token rows of stage ks, 16-byte pieces straight into the tile: 64 k of the rows for a K stage, the 2 G
@@ -386,14 +403,26 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
                 const uint32_t as = base + (ks % PF_STAGES) * S::A_STAGE;
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
-                    const uint32_t src = raw_base + (((ks % PF_RAW) * NMAT + m) * 128 + r) * 32;
-                    const uint4 w0 = *reinterpret_cast<const uint4*>(at(src)), w1 = *reinterpret_cast<const uint4*>(at(src + 16));
-                    const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                    const uint32_t src = raw_base + (((ks % PF_RAW) * NMAT + m) * 128 + r) * S::RAWB;
                     const uint32_t dst = as + m * PF_A_BYTES + (r / 8) * 1024 + (r % 8) * 16;
+                    if constexpr (BITS == 4) {
+                        const uint4 w0 = *reinterpret_cast<const uint4*>(at(src)), w1 = *reinterpret_cast<const uint4*>(at(src + 16));
+                        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint4 v = pf_dequant_word(words[i]);
-                        *reinterpret_cast<uint4*>(at(dst + i * 128)) = v;
+                        for (int i = 0; i < 8; ++i) {
+                            const uint4 v = pf_dequant_word(words[i]);
+                            *reinterpret_cast<uint4*>(at(dst + i * 128)) = v;
+                        }
+                    } else {
+                        const bool q8s = c.q8_signed;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {             // 16 bytes = 16 codes = two k chunks of eight
+                            const uint4 w = *reinterpret_cast<const uint4*>(at(src + i * 16));
+                            const uint2 a = pf_dequant_q8_word(w.x, q8s), b = pf_dequant_q8_word(w.y, q8s);
+                            const uint2 e = pf_dequant_q8_word(w.z, q8s), f = pf_dequant_q8_word(w.w, q8s);
+                            *reinterpret_cast<uint4*>(at(dst + (2 * i) * 128)) = make_uint4(a.x, a.y, b.x, b.y);
+                            *reinterpret_cast<uint4*>(at(dst + (2 * i + 1) * 128)) = make_uint4(e.x, e.y, f.x, f.y);
+                        }
                     }
                 }
             }
@@ -509,7 +538,7 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
                         if constexpr (NMAT == 2) {
                             const float u = acc[NMAT - 1][h][j];
                             const float hv = (g * sigmoid_f(g)) * u;
-                            hdst[drow[t] + (row & ~7u) + pf_pos8(row & 7)] = __float2half_rn(hv);
+                            hdst[drow[t] + (h_natural ? row : (row & ~7u) + pf_pos8(row & 7))] = __float2half_rn(hv);
                         } else {
                             out_base[drow[t] + row] = g;
                         }
@@ -525,32 +554,30 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
     }
 }
 
-template <int NMAT, bool META_F16, int D>
+template <int NMAT, int BITS, bool META_F16, int D>
 int launch_prefill_d(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, size_t smem, cudaStream_t s) {
     const uint32_t N = NMAT == 2 ? c.F : c.H;
-    auto kernel = prefill_kernel<NMAT, META_F16, D>;
-    static size_t configured = 0;
-    if (smem > configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
-            return check_launch(m, "prefill kernel attribute");
-        configured = smem;
-    }
+    auto kernel = prefill_kernel<NMAT, BITS, META_F16, D>;
+    static SmemOptIn configured;
+    if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) return check_launch(m, "prefill kernel attribute");
     Timed t(m, s, NMAT == 2 ? KERNEL_PREFILL_GATE_UP : KERNEL_PREFILL_DOWN);
-    kernel<<<dim3(N / PF_M, m->pf_max_tiles), PF_THREADS, smem, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, bsum, m->hbuf16);
+    kernel<<<dim3(N / PF_M, m->pf_max_tiles), PF_THREADS, smem, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, bsum, m->hbuf16,
+                                                                     c.down.bits == 8 ? 1u : 0u);
     return check_launch(m, NMAT == 2 ? "prefill gate_up" : "prefill down");
 }
 
-template <int NMAT, bool META_F16>
+template <int NMAT, int BITS, bool META_F16>
 int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, cudaStream_t s) {
+    using P = PfSmem<NMAT, BITS>;
     const uint32_t N = NMAT == 2 ? c.F : c.H, K = NMAT == 2 ? c.H : c.F, G = K / 64;
     if (N % PF_M) return fail(m, ZC_EINVAL, "prefill kernel: rows not a multiple of 128");
     if (G % 8) return fail(m, ZC_EINVAL, "prefill kernel: K must be a multiple of 512");
     const size_t limit = 227 * 1024;
     // down: its K is short (ten stages per CTA), so the fixed cost of a CTA matters: a shallower ring lets two CTAs
     // share an SM (shared memory and 256 TMEM columns each) and overlap one's set-up with the other's loop
-    if (NMAT == 1 && 2 * (PfSmem<NMAT>::total(G, 2) + 1024) <= limit) return launch_prefill_d<NMAT, META_F16, 2>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 2), s);
-    if (PfSmem<NMAT>::total(G, 4) <= limit) return launch_prefill_d<NMAT, META_F16, 4>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 4), s);
-    if (PfSmem<NMAT>::total(G, 2) <= limit) return launch_prefill_d<NMAT, META_F16, 2>(m, c, bsrc, bsum, PfSmem<NMAT>::total(G, 2), s);
+    if (NMAT == 1 && 2 * (P::total(G, 2) + 1024) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 2>(m, c, bsrc, bsum, P::total(G, 2), s);
+    if (P::total(G, 4) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 4>(m, c, bsrc, bsum, P::total(G, 4), s);
+    if (P::total(G, 2) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 2>(m, c, bsrc, bsum, P::total(G, 2), s);
     return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
 }
 
@@ -564,8 +591,7 @@ size_t prefill_tile_bytes() { return sizeof(PfTile); }
 
 bool prefill_supported(const zc_moe_desc& d) {
     // BF16 activations convert to FP16 exactly; an FP32 activation would need a second FP16 term.
-    return d.gate_bits == 4 && d.up_bits == 4 && d.down_bits == 4 && d.arith == ZC_ARITH_FP32 && d.act_dtype == ZC_BF16 &&
-           d.ffn % 512 == 0 && d.hidden % 512 == 0 && d.hidden <= 4096;
+    return d.arith == ZC_ARITH_FP32 && d.act_dtype == ZC_BF16 && d.ffn % 512 == 0 && d.hidden % 512 == 0 && d.hidden <= 4096;
 }
 
 // tile list -> FP16 activations -> gate/up (+SwiGLU) -> down. Routing must already be in place.
@@ -580,23 +606,25 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
         const size_t blocks = size_t(c.T) * c.H / 8;
-        pf_prepare_x_kernel<<<unsigned((blocks + 255) / 256), 256, 0, s>>>(c.x, c.act_dtype, m->xp, blocks);
+        pf_prepare_x_kernel<<<unsigned((blocks + 255) / 256), 256, 0, s>>>(c.x, c.act_dtype, m->xp, blocks, c.status, c.gate.bits == 8);
         if ((rc = check_launch(m, "prefill activations")) < 0) return rc;
     }
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
-        pf_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(m->xp, c.T, c.H, m->xsum);
+        pf_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(m->xp, c.T, c.H, m->xsum, c.status, c.gate.bits == 4 ? 8.0f : 0.0f);
         if ((rc = check_launch(m, "prefill activation sums")) < 0) return rc;
     }
-    rc = c.meta_f16 ? launch_prefill<2, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, false>(m, c, m->xp, m->xsum, s);
+    if (c.gate.bits == 4) rc = c.meta_f16 ? launch_prefill<2, 4, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, 4, false>(m, c, m->xp, m->xsum, s);
+    else rc = c.meta_f16 ? launch_prefill<2, 8, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, 8, false>(m, c, m->xp, m->xsum, s);
     if (rc < 0) return rc;
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
         const uint32_t rows = c.T * c.K + c.T;
-        pf_sums_kernel<<<(rows * 32 + 255) / 256, 256, 0, s>>>(m->hbuf16, rows, c.F, m->hsum);
+        pf_sums_kernel<<<(rows * 32 + 255) / 256, 256, 0, s>>>(m->hbuf16, rows, c.F, m->hsum, c.status, c.down.bits == 4 ? 8.0f : 0.0f);
         if ((rc = check_launch(m, "prefill intermediate sums")) < 0) return rc;
     }
-    rc = c.meta_f16 ? launch_prefill<1, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, false>(m, c, m->hbuf16, m->hsum, s);
+    if (c.down.bits == 4) rc = c.meta_f16 ? launch_prefill<1, 4, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, 4, false>(m, c, m->hbuf16, m->hsum, s);
+    else rc = c.meta_f16 ? launch_prefill<1, 8, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, 8, false>(m, c, m->hbuf16, m->hsum, s);
     if (rc < 0) return rc;
     return 6;
 }

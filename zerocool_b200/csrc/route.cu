@@ -192,7 +192,7 @@ __device__ __forceinline__ void permute_body(const int32_t* ids, uint32_t slots,
             for (int q = 0; q < PERMUTE_CACHE; ++q) if (blk + 32 * q < end) count_chunk(blk + 32 * q + lane, v[q]);
         }
     }
-    if (bad) atomicOr(status, ZC_STATUS_INVALID_ROUTE);
+    if (bad && status) atomicOr(status, ZC_STATUS_INVALID_ROUTE);
     __syncthreads();
     // Per-warp counts become per-warp starting ranks inside the expert; the scan gives the expert's first position.
     const uint32_t own = (E + NT - 1) / NT;                        // <= PERMUTE_OWN, checked at launch
@@ -330,12 +330,11 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
         a.first_expert = c.first_expert; a.local_experts = c.local_experts; a.layer = c.layer; a.do_permute = do_permute;
         const size_t smem = size_t(ROUTE_THREADS / 32) * c.E * sizeof(int32_t);
         const bool small = c.E <= 512;
-        static size_t configured[2] = {0, 0};
-        if (smem > configured[small]) {
-            cudaError_t e = small ? cudaFuncSetAttribute(route_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
-                                  : cudaFuncSetAttribute(route_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        static SmemOptIn configured[2];
+        {
+            const cudaError_t e = small ? opt_in_smem(route_kernel<16>, configured[1], m->device, smem)
+                                        : opt_in_smem(route_kernel<32>, configured[0], m->device, smem);
             if (e != cudaSuccess) return check_launch(m, "route attribute");
-            configured[small] = smem;
         }
         const uint32_t grid = (c.T + ROUTE_WARPS - 1) / ROUTE_WARPS;
         int rc;
@@ -350,16 +349,13 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
         ++launched;
     }
     if (separate || (!do_route && do_permute)) {
-        static bool configured = false;
-        if (!configured) {
-            cudaFuncSetAttribute(permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-            configured = true;
-        }
+        static SmemOptIn configured;
+        if (opt_in_smem(permute_kernel, configured, m->device, 160 * 1024) != cudaSuccess) return check_launch(m, "permute attribute");
         int rc;
         {
             Timed t(m, s, KERNEL_PERMUTE);
             permute_kernel<<<1, PERMUTE_THREADS, hist_bytes, s>>>(c.ids, c.T * c.K, c.E, c.first_expert, c.local_experts, c.offsets, c.perm,
-                                                                 c.active, c.items, c.counters, c.layer, c.status);
+                                                                 c.active, c.items, c.counters, c.layer, c.quiet_drop ? nullptr : c.status);
             rc = check_launch(m, "permute");
         }
         if (rc < 0) return rc;

@@ -387,21 +387,20 @@ int launch_router_cluster(zc_moe* m, const Call& c, cudaStream_t s) {
     cudaLaunchConfig_t cfg{};           // for the occupancy query
     cfg.gridDim = grid; cfg.blockDim = dim3(ROUTER_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    static size_t configured = 0;       // per instantiation
-    static int usable = -1;             // -1 unknown, 0 the device cannot host a cluster of this shape, 1 yes
-    if (smem > 200 * 1024) return 0;
-    if (smem > configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) { cudaGetLastError(); return 0; }
-        configured = smem;
-        usable = -1;
+    static SmemOptIn configured;        // per instantiation, per device
+    static int8_t usable[MAX_DEVICES];  // per device: 0 unknown, 1 the device hosts a cluster of this shape, 2 it cannot
+    if (smem > 200 * 1024 || m->device < 0 || m->device >= MAX_DEVICES) return 0;
+    if (smem > configured.bytes[m->device]) {
+        if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
+        usable[m->device] = 0;
     }
-    if (usable < 0) {
+    if (usable[m->device] == 0) {
         int clusters = 0;
         const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
         if (e != cudaSuccess) cudaGetLastError();
-        usable = (e == cudaSuccess && clusters > 0) ? 1 : 0;
+        usable[m->device] = (e == cudaSuccess && clusters > 0) ? 1 : 2;
     }
-    if (!usable) return 0;
+    if (usable[m->device] != 1) return 0;
     int rc;
     {
         Timed t(m, s, KERNEL_ROUTER);
@@ -438,13 +437,12 @@ int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s) {
     const uint32_t TT = which == 0 ? 8 : which == 1 ? 32 : 64;
     const uint32_t row_tile = which == 1 ? 64 : 32;
     const size_t smem = size_t(part) * (TT + row_tile) * sizeof(float);
-    static size_t configured[3] = {0, 0, 0};
-    if (smem > configured[which]) {
-        cudaError_t e = which == 0 ? cudaFuncSetAttribute(router_partial_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
-                      : which == 1 ? cudaFuncSetAttribute(router_partial_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
-                                   : cudaFuncSetAttribute(router_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    static SmemOptIn configured[3];
+    {
+        const cudaError_t e = which == 0 ? opt_in_smem(router_partial_kernel<8>, configured[0], m->device, smem)
+                            : which == 1 ? opt_in_smem(router_partial_kernel<32>, configured[1], m->device, smem)
+                                         : opt_in_smem(router_partial_kernel<64>, configured[2], m->device, smem);
         if (e != cudaSuccess) return check_launch(m, "router attribute");
-        configured[which] = smem;
     }
     const uint32_t rows_total = c.E + (c.has_shared ? 1 : 0);
     const dim3 grid((rows_total + row_tile - 1) / row_tile, 16, (c.T + TT - 1) / TT);
@@ -499,6 +497,18 @@ extern "C" int zc_router_logits_noalloc(const void* x, int act_dtype, const void
         return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: hidden must be a multiple of 128, at most 3072");
     if ((act_dtype != ZC_BF16 && act_dtype != ZC_F32) || (router_dtype != ZC_BF16 && router_dtype != ZC_F32))
         return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: dtypes must be BF16 or F32");
+    // The kernel reads x and router_w and writes logits with 16-byte accesses: a misaligned or aliased buffer is an
+    // argument error here, not a device fault.
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(router_w) | reinterpret_cast<uintptr_t>(logits)) & 15)
+        return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: x, router_w and logits must be 16-byte aligned");
+    {
+        const size_t xb = size_t(tokens) * hidden * (act_dtype == ZC_F32 ? 4 : 2), wb = size_t(experts) * hidden * (router_dtype == ZC_F32 ? 4 : 2);
+        const size_t lb = size_t(tokens) * experts * 4;
+        const char* lo = reinterpret_cast<const char*>(logits);
+        const char* xa = static_cast<const char*>(x); const char* wa = static_cast<const char*>(router_w);
+        if ((lo < xa + xb && xa < lo + lb) || (lo < wa + wb && wa < lo + lb))
+            return fail(nullptr, ZC_EINVAL, "zc_router_logits_noalloc: logits overlaps an input");
+    }
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return fail(nullptr, ZC_EEXEC, std::string("cudaGetDevice: ") + cudaGetErrorString(e));

@@ -7,10 +7,18 @@ and tokens start data parallel. Per layer each rank runs
     dispatch (local)  ->  all-to-all of token rows + expert ids  ->  experts (local)
                       ->  all-to-all of the results back          ->  combine (local)
 
-The exchange is `torch.distributed.all_to_all_single` (NCCL over NVLink on GPUs; gloo in the CPU tests). The
-three local steps come from a backend: a `zerocool_b200.moe.Moe` handle on a GPU, or any object with the same
-`ep_dispatch / ep_experts / ep_combine` methods. Results do not depend on arrival order: every contribution is
-stored at its router slot and reduced in fixed slot order by the combine step.
+Two transports:
+
+* `ExpertParallel`: the exchange is `torch.distributed.all_to_all_single` (NCCL over NVLink on GPUs; gloo in the
+  CPU tests). The three local steps come from a backend: a `zerocool_b200.moe.Moe` handle on a GPU, or any object
+  with the same `ep_dispatch / ep_experts / ep_combine` methods. The split sizes are read on the host, so every
+  layer costs two host synchronisations.
+* `PeerExpertParallel`: rows, results and flags travel as peer stores issued by the library's own kernels into
+  windows the ranks map from each other (`zc_moe_ep_layer`, `zc_moe_ep_stack`); the process group is used once,
+  to exchange the window handles. Nothing is read on the host per layer and a whole stack replays from a graph.
+
+Results do not depend on arrival order: every contribution is stored at its router slot and reduced in fixed
+slot order by the combine step.
 """
 import numpy as np
 
@@ -58,6 +66,41 @@ class ExpertParallel:
             y_back = torch.cat([y_back, pad])
         self.last_plan = dict(send=send, recv=recv, rows_sent=int(send.sum()), rows_received=int(recv.sum()))
         return self.backend.ep_combine(layer, x, y_back, out)
+
+
+class PeerExpertParallel:
+    """One rank's view of the peer-store transport. `moe` is a `zerocool_b200.moe.Moe` holding this rank's expert
+    range; `dist` is torch.distributed (initialised), used only to exchange the window handles."""
+
+    def __init__(self, moe, dist, group=None):
+        self.handle = moe
+        moe.ep_attach_group(dist, group)
+
+    def moe(self, layer, x, out=None):
+        """x: this rank's tokens [T_local, H] -> out [T_local, H]; stream-ordered, no host synchronisation."""
+        return self.handle.ep_layer(layer, x, out)
+
+    def stack(self, x, out=None, eager=False):
+        """All layers chained through act((out - mean) / std), replayed from one CUDA graph."""
+        return self.handle.ep_stack(x, out, eager=eager)
+
+
+def emulate_peer(handles, layer, xs):
+    """The peer-store transport with every rank in this process on one device: all sends, then all owners, then
+    all finishes, in stream order - no kernel ever has to wait for a later launch. handles[r] must already be
+    attached to each other (attach_local)."""
+    for h, x in zip(handles, xs):
+        h.ep_send(layer, x)
+    for h in handles:
+        h.ep_process(layer)
+    return [h.ep_finish(layer, x) for h, x in zip(handles, xs)]
+
+
+def attach_local(handles):
+    """Attaches handles that live in one process on one device to each other by window address."""
+    windows = [h.ep_export()[1] for h in handles]
+    for r, h in enumerate(handles):
+        h.ep_attach(r, len(handles), pointers=windows)
 
 
 def emulate(backends, experts, layer, xs):

@@ -19,14 +19,20 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libzc_moe.so")
 
 ZC_OK, ZC_EINVAL, ZC_ERANGE, ZC_EEXEC, ZC_ECANCELLED, ZC_ENOMEM = 0, -1, -2, -3, -4, -5
-STATUS_INVALID_ROUTE = 1
+STATUS_INVALID_ROUTE, STATUS_TIMEOUT, STATUS_RANGE = 1, 2, 4
+
+
+class Cancelled(RuntimeError):
+    """The reference's "generation cancelled" (src/engine/model.cpp:15)."""
 
 EXPORTS = [
     "zc_moe_desc_finalize", "zc_moe_create", "zc_moe_destroy", "zc_moe_last_error", "zc_last_error",
     "zc_moe_load_layer", "zc_moe_set_router_bias", "zc_moe_layer_buffers", "zc_moe_router", "zc_router_logits_noalloc", "zc_moe_route", "zc_moe_permute",
-    "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_ep_dispatch", "zc_moe_ep_experts", "zc_moe_ep_combine", "zc_moe_forward_host", "zc_moe_stack",
+    "zc_moe_combine", "zc_activation_bf16", "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_ep_dispatch", "zc_moe_ep_experts", "zc_moe_ep_combine",
+    "zc_moe_ep_export", "zc_moe_ep_attach", "zc_moe_ep_layer", "zc_moe_ep_send", "zc_moe_ep_process", "zc_moe_ep_finish", "zc_moe_ep_stack", "zc_moe_ep_stack_eager",
+    "zc_moe_forward_host", "zc_moe_forward_host_async", "zc_moe_set_cancel", "zc_moe_stack",
     "zc_moe_stack_host", "zc_moe_set_option", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
-    "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
+    "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_ep_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
 ]
 
 
@@ -71,15 +77,28 @@ def load_library():
     lib.zc_router_logits_noalloc.argtypes = [vp, i32, vp, i32, u32, u32, u32, vp, vp]
     lib.zc_moe_route.argtypes = [vp, vp, u32, vp, vp, vp]
     lib.zc_moe_permute.argtypes = [vp, vp, u32, vp, vp, vp]
+    lib.zc_moe_combine.argtypes = [vp, vp, vp, vp, vp, vp, u32, vp, vp]
+    lib.zc_activation_bf16.argtypes = [vp, u32, vp, vp, vp]
     for name in ("zc_moe_decode", "zc_moe_prefill", "zc_moe_forward"):
         getattr(lib, name).argtypes = [vp, u32, vp, u32, vp, vp]
     lib.zc_moe_ep_dispatch.argtypes = [vp, u32, vp, u32, vp, vp, vp]
     lib.zc_moe_ep_experts.argtypes = [vp, u32, vp, vp, u32, vp, vp]
     lib.zc_moe_ep_combine.argtypes = [vp, u32, vp, u32, vp, vp, vp]
+    lib.zc_moe_ep_export.argtypes = [vp, vp, ctypes.POINTER(vp)]
+    lib.zc_moe_ep_attach.argtypes = [vp, u32, u32, vp, i32]
+    lib.zc_moe_ep_layer.argtypes = [vp, u32, vp, u32, vp, vp]
+    lib.zc_moe_ep_send.argtypes = [vp, u32, vp, u32, vp]
+    lib.zc_moe_ep_process.argtypes = [vp, u32, vp]
+    lib.zc_moe_ep_finish.argtypes = [vp, u32, vp, u32, vp, vp]
+    lib.zc_moe_ep_stack.argtypes = [vp, vp, u32, vp, vp]
+    lib.zc_moe_ep_stack_eager.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_forward_host.argtypes = [vp, u32, vp, u32, vp, vp]
+    lib.zc_moe_forward_host_async.argtypes = [vp, u32, vp, u32, vp, vp]
+    lib.zc_moe_set_cancel.argtypes = [vp, vp]
     lib.zc_moe_stack.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_stack_host.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_active_counts.argtypes = [vp, vp]
+    lib.zc_moe_ep_active_counts.argtypes = [vp, vp]
     lib.zc_moe_set_option.argtypes = [vp, ctypes.c_char_p, i32]
     lib.zc_moe_stack_eager.argtypes = [vp, vp, u32, vp, vp]
     lib.zc_moe_profile_begin.argtypes = [vp]
@@ -111,6 +130,8 @@ def _raise(code, text):
         raise IndexError(text)
     if code == ZC_ENOMEM:
         raise MemoryError(text)
+    if code == ZC_ECANCELLED:
+        raise Cancelled(text)
     raise RuntimeError(text)
 
 
@@ -222,6 +243,25 @@ class Moe:
         self._check(self.lib.zc_moe_permute(self._h, _ptr(ids), tokens, _ptr(offsets), _ptr(perm), self._stream()))
         return offsets, perm
 
+    def combine(self, expert_out, weights, ids, shared=None, gate_logit=None, out=None):
+        """moe_sum on caller tensors: expert_out [T,K,H] fp32, weights [T,K] fp32, ids [T,K] int32, shared [T,H] / gate_logit [T]."""
+        torch = self._torch
+        tokens = weights.shape[0]
+        if out is None:
+            out = torch.empty((tokens, self.cfg.hidden), dtype=self.out_torch, device=self.device)
+        self._check(self.lib.zc_moe_combine(self._h, _ptr(expert_out), _ptr(weights), _ptr(ids), _ptr(shared), _ptr(gate_logit), tokens,
+                                            _ptr(out), self._stream()))
+        return out
+
+    def activation_bf16(self, x):
+        """(sigmoid, silu) of the reference's BF16-staged activation on an fp32 device tensor."""
+        torch = self._torch
+        sg, si = torch.empty_like(x), torch.empty_like(x)
+        rc = self.lib.zc_activation_bf16(_ptr(x), x.numel(), _ptr(sg), _ptr(si), self._stream())
+        if rc != ZC_OK:
+            _raise(rc, self.lib.zc_last_error())
+        return sg, si
+
     def _run(self, fn, layer, x, out):
         torch = self._torch
         tokens = x.shape[0]
@@ -271,6 +311,80 @@ class Moe:
             out = torch.empty((tokens, self.cfg.hidden), dtype=self.out_torch, device=self.device)
         self._check(self.lib.zc_moe_ep_combine(self._h, layer, _ptr(x), tokens, _ptr(y_sorted), _ptr(out), self._stream()))
         return out
+
+    # -- expert parallelism over peer memory (no collective library, no host value per layer) ------------
+    def ep_export(self):
+        """-> (64-byte inter-process handle of this rank's window, its device address)."""
+        handle = (ctypes.c_uint8 * 64)()
+        window = ctypes.c_void_p()
+        self._check(self.lib.zc_moe_ep_export(self._h, handle, ctypes.byref(window)))
+        return bytes(handle), window.value
+
+    def ep_attach(self, rank, world, handles=None, pointers=None):
+        """handles: list of `world` 64-byte handles (ranks in other processes); pointers: list of `world` window
+        addresses (ranks in this process)."""
+        if pointers is not None:
+            table = (ctypes.c_void_p * world)(*[int(p) for p in pointers])
+            self._check(self.lib.zc_moe_ep_attach(self._h, rank, world, table, 1))
+        else:
+            blob = b"".join(handles)
+            if len(blob) != 64 * world:
+                raise ValueError("one 64-byte handle per rank is needed")
+            self._check(self.lib.zc_moe_ep_attach(self._h, rank, world, blob, 0))
+
+    def ep_attach_group(self, dist, group=None):
+        """Exchanges the window handles over the (already initialised) process group and attaches; ends with a barrier,
+        after which every rank may issue expert-parallel layers."""
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        try:
+            handle, error = self.ep_export()[0], None
+        except (RuntimeError, ValueError) as exc:
+            handle, error = b"\0" * 64, str(exc)
+        handles = [None] * world
+        dist.all_gather_object(handles, (handle, error), group=group)
+        if error is None and all(e is None for _, e in handles):
+            try:
+                self.ep_attach(rank, world, handles=[h for h, _ in handles])
+            except (RuntimeError, ValueError) as exc:
+                error = str(exc)
+        # every rank learns whether every rank attached (this exchange is also the barrier before the first layer)
+        errors = [None] * world
+        dist.all_gather_object(errors, error, group=group)
+        failed = [f"rank {r}: {e}" for r, e in enumerate(errors) if e is not None] + \
+                 [f"rank {r}: {e}" for r, (_, e) in enumerate(handles) if e is not None]
+        if failed:
+            raise RuntimeError("expert-parallel windows could not be attached: " + "; ".join(sorted(set(failed))))
+
+    def ep_layer(self, layer, x, out=None):
+        return self._run(self.lib.zc_moe_ep_layer, layer, x, out)
+
+    def ep_send(self, layer, x):
+        self._check(self.lib.zc_moe_ep_send(self._h, layer, _ptr(x), x.shape[0], self._stream()))
+
+    def ep_process(self, layer):
+        self._check(self.lib.zc_moe_ep_process(self._h, layer, self._stream()))
+
+    def ep_finish(self, layer, x, out=None):
+        return self._run(self.lib.zc_moe_ep_finish, layer, x, out)
+
+    def ep_stack(self, x, out=None, eager=False):
+        torch = self._torch
+        if out is None:
+            out = torch.empty((x.shape[0], self.cfg.hidden), dtype=self.out_torch, device=self.device)
+        fn = self.lib.zc_moe_ep_stack_eager if eager else self.lib.zc_moe_ep_stack
+        self._check(fn(self._h, _ptr(x), x.shape[0], _ptr(out), self._stream()))
+        return out
+
+    def set_cancel(self, flag):
+        """flag: numpy int32 array of one element another thread may set to non-zero (None removes it). The caller
+        keeps the array alive while it is registered."""
+        self._cancel_keep = flag
+        self._check(self.lib.zc_moe_set_cancel(self._h, None if flag is None else flag.ctypes.data))
+
+    def moe_host_async(self, layer, x_host, out_host):
+        """moe_host without the wait: out_host is valid after the stream has been waited for (status() does)."""
+        self._check(self.lib.zc_moe_forward_host_async(self._h, layer, _ptr(x_host), x_host.shape[0], _ptr(out_host), self._stream()))
+        return out_host
 
     def moe_host(self, layer, x_host, out_host):
         """Model::moe for host tensors (pinned numpy/torch CPU memory): copies in, runs, copies out, waits."""
@@ -332,6 +446,12 @@ class Moe:
         """Routed experts with work in the latest call of each layer (numpy int32 [layers])."""
         out = np.zeros(self.cfg.layers, np.int32)
         self._check(self.lib.zc_moe_active_counts(self._h, out.ctypes.data))
+        return out
+
+    def ep_active_counts(self):
+        """Experts of this handle's range that received rows in the latest expert-parallel call of each layer."""
+        out = np.zeros(self.cfg.layers, np.int32)
+        self._check(self.lib.zc_moe_ep_active_counts(self._h, out.ctypes.data))
         return out
 
     def status(self):
