@@ -436,6 +436,8 @@ def measure_ep(torch, dist, rank, world, local, layers, total_tokens, steps, war
             if not (parity["ids_bit_exact"] and parity["perm_bit_exact"] and parity["within_tolerance"] and status == 0):
                 raise RuntimeError(f"expert-parallel parity gate failed: {parity}")
 
+    if dist is not None:
+        dist.barrier()            # rank 0 spent seconds in the CPU checker: a device-side wait for its rows must not start before it is back
     for _ in range(warmup):
         run()
     before = m.launches
@@ -449,6 +451,8 @@ def measure_ep(torch, dist, rank, world, local, layers, total_tokens, steps, war
     ids_last = m.last_routing(t_local)["ids"]
     per = cfg.experts // world
     remote_rows = int(np.sum((ids_last // per) != rank)) if world > 1 else 0
+    if dist is not None:
+        dist.barrier()
     kernels = kernel_profile(m, run_eager, min(steps, 3)) if run_eager is not None else {}
     my_bytes = float(sum(a * cfg.record_bytes + cfg.experts * cfg.hidden * 4 + t_local * cfg.hidden * 4 for a in active))
     stats = torch.tensor([my_bytes, float(active.mean()), float(remote_rows)], dtype=torch.float64, device="cuda")

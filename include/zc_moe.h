@@ -26,7 +26,7 @@
  *    handle's device. One process may own handles on several devices.
  *  - Value range: activations and the internal SwiGLU rows enter the tensor-core products as FP16. For a Q4
  *    projection of the short-batch kernels a value must satisfy |v| < 4094, otherwise |v| <= 65504; in the
- *    long-batch kernels additionally the sum of 64 consecutive values must stay below 8188 in magnitude.
+ *    long-batch kernels additionally the sum of 64 consecutive values must stay within 65504 in magnitude.
  *    Beyond that the affected output rows are not meaningful and ZC_STATUS_RANGE is raised. Scales and biases
  *    stored as BF16 must be representable in FP16 for the long-batch kernels (|s| >= 6.1e-5 or zero).
  *  - There is no CPU fallback: without a CUDA device zc_moe_create fails with ZC_EEXEC.

@@ -56,14 +56,14 @@ def rel_max_error(got, want):
 
 
 def asymmetric_record(cfg, seed, layer, expert, rng, spread=0.03):
-    """A record with the generator's codes and scales but free biases (bias = -8 scale + U(-spread, spread)): the
-    affine form's second term, (8 s + b) * sum(x), is then not zero."""
+    """A record with the generator's codes and scales but free biases: bias = -(mean code) * scale + U(-spread, spread),
+    so the weights stay roughly centred while the affine form's bias term no longer cancels against the codes."""
     from zerocool_b200.records import build_record, float_to_meta, meta_to_float
     parts = []
     for p in range(3):
         codes, sbits, bbits = synth.projection_parts(cfg, seed, layer, expert, p)
         s = meta_to_float(sbits, cfg.meta_dtype)
-        offset = -8.0 if cfg.bits(p) == 4 else 0.0
+        offset = -8.0 if cfg.bits(p) == 4 else (0.0 if cfg.q8_signed else -127.5)
         b = offset * s + rng.uniform(-spread, spread, size=s.shape).astype(np.float32)
         parts.append((codes, sbits, float_to_meta(b, cfg.meta_dtype).reshape(bbits.shape)))
     return build_record(cfg, parts)

@@ -112,9 +112,9 @@ int check_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const 
 // family: 0 = decode kernels, 1 = prefill kernels (tensor-core grouped GEMM), -1 = by token count.
 int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next = nullptr, int family = -1) {
     const Call c = make_call(m, layer, x, tokens, out);
-    // The tensor-core family pays from about sixteen rows per expert on (a tile of an expert's rows is one pass over
-    // its weights through shared memory); below that the streaming kernels, which take eight rows per pass, are faster.
-    if (family < 0) family = (tokens >= 64 && uint64_t(tokens) * m->d.top_k >= 16ull * m->d.local_experts) ? 1 : 0;
+    // The tensor-core family pays from about 24 rows per expert on (measured crossover with every expert active:
+    // 30 rows per expert at hidden 2048, 20 at hidden 4096); below that the streaming kernels are faster.
+    if (family < 0) family = (tokens >= 64 && uint64_t(tokens) * m->d.top_k >= 24ull * m->d.local_experts) ? 1 : 0;
     if (family == 1 && !m->pf_tiles) family = 0;      // formats the prefill kernels do not take, or a decode-sized handle
     int n, total = 0;
     if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;

@@ -12,17 +12,16 @@
 // the dequantisation cheap and many bytes in flight.
 //
 // Arithmetic (the reference's affine form, qwen.metal:46-62, regrouped):
-//     sum_k (s_g q_k + b_g) x_k  =  s_g * sum_k (q_k - 8) x_k  +  (8 s_g + b_g) * sum_k x_k      per 64-wide group g
-//   * the tensor cores multiply the exact integers q - 8 (FP16) with the FP16 activations, one fresh TMEM
+//     sum_k (s_g q_k + b_g) x_k  =  s_g * sum_k q_k x_k  +  b_g * sum_k x_k      per 64-wide group g
+//   * the tensor cores multiply the exact integer codes q (FP16) with the FP16 activations, one fresh TMEM
 //     accumulator per group (four buffers rotate);
 //   * the epilogue warps read each group's accumulator (tcgen05.ld) and add it into FP32 registers scaled by
 //     s_g - the scale never enters an FP16 product, so no weight is rounded;
 //   * the second term is itself a small product over the groups: A' = [s_0..s_G-1 | b_0..b_G-1] (the record's
-//     own FP16 metadata) times B' = [8 S_0.. | S_0..] with S_g = sum of the token's activations in group g,
-//     carried as two FP16 terms (hi, lo). It runs as extra stages after the K loop (K' in blocks of 64, hi then lo)
+//     own FP16 metadata) times B' = [0 .. | S_0..] with S_g = sum of the token's activations in group g,
+//     carried as two FP16 terms (hi, lo); the zero half meets the scales, so the tile is used as it lies in the record. It runs as extra stages after the K loop (K' in blocks of 64, hi then lo)
 //     and is added with scale 1.
 //   8-bit codes (u8 as in the reference's affine8_dot, qwen.metal:112-125, or int8) take the same path with the
-//   codes themselves as the exact FP16 integers (no offset: the correction term is b_g * sum_k x_k alone) and the
 //   token rows in natural k order.
 //   NMAT = 2: gate and up tiles of the same 128 rows sit side by side in TMEM; the final epilogue applies
 //             SwiGLU and stores h as FP16 in the k order the second launch consumes.
@@ -118,17 +117,17 @@ __device__ __forceinline__ uint32_t pf_and_or(uint32_t a, uint32_t b, uint32_t c
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-// Eight Q4 codes of one word -> the integers q - 8 as FP16, in the order (k0,k4) (k1,k5) (k2,k6) (k3,k7).
+// Eight Q4 codes of one word -> the integers q as FP16, in the order (k0,k4) (k1,k5) (k2,k6) (k3,k7).
 // (w & 0x000f000f) | 0x6400 is the half2 (1024 + q, 1024 + q'); the nibbles one position up give 1024 + 16 q.
 __device__ __forceinline__ uint4 pf_dequant_word(uint32_t w) {
     const uint32_t mlo = 0x000f000fu, mhi = 0x00f000f0u, magic = 0x64006400u;
-    const __half2 k1032 = __floats2half2_rn(1032.0f, 1032.0f), k16 = __floats2half2_rn(0.0625f, 0.0625f), k72 = __floats2half2_rn(-72.0f, -72.0f);
+    const __half2 k1024 = __floats2half2_rn(1024.0f, 1024.0f), k16 = __floats2half2_rn(0.0625f, 0.0625f), k64 = __floats2half2_rn(-64.0f, -64.0f);
     const uint32_t w8 = w >> 8;
     uint32_t p[4] = {pf_and_or(w, mlo, magic), pf_and_or(w, mhi, magic), pf_and_or(w8, mlo, magic), pf_and_or(w8, mhi, magic)};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         __half2 q = *reinterpret_cast<__half2*>(&p[i]);
-        q = (i & 1) ? __hfma2(q, k16, k72) : __hsub2(q, k1032);      // exact
+        q = (i & 1) ? __hfma2(q, k16, k64) : __hsub2(q, k1024);      // exact
         p[i] = *reinterpret_cast<const uint32_t*>(&q);
     }
     return make_uint4(p[0], p[1], p[2], p[3]);
@@ -198,9 +197,9 @@ __global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, _
 }
 
 // Per row of an FP16 matrix [rows, K] and per 64-wide group g: S_g = sum of the row's values in the group (FP32 sum),
-// stored as the B' operand of the correction stages, [c hi_0.. | hi_0.. | c lo_0.. | lo_0..] with hi = fp16(S),
-// lo = fp16(S - hi) (4 G halves per row) and c = the code offset the K loop removed (8 for Q4, 0 for Q8). One warp per row.
-__global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, uint32_t K, __half* __restrict__ sums, uint32_t* __restrict__ status, float offset) {
+// stored as the B' operand of the correction stages, [0 .. | hi_0.. | 0 .. | lo_0..] with hi = fp16(S),
+// lo = fp16(S - hi) (4 G halves per row; the zeros meet the scale half of the metadata tile). One warp per row.
+__global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, uint32_t K, __half* __restrict__ sums, uint32_t* __restrict__ status) {
     const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
     if (row >= rows) return;
     const uint32_t G = K / 64;
@@ -217,11 +216,12 @@ __global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, ui
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         sum += __shfl_xor_sync(0xffffffffu, sum, 4);
         if (g < G && lane % 8 == 0) {
-            if (!(fabsf(sum) <= 8188.0f)) atomicOr(status, ZC_STATUS_RANGE);       // 8 S (or an infinite input) leaves FP16
+            if (!(fabsf(sum) <= 65504.0f)) atomicOr(status, ZC_STATUS_RANGE);      // S (or an infinite input) leaves FP16
             const __half hi = __float2half_rn(sum), lo = __float2half_rn(sum - __half2float(hi));
             __half* dst = sums + size_t(row) * 4 * G;
-            dst[g] = __float2half_rn(offset * __half2float(hi)); dst[G + g] = hi;
-            dst[2 * G + g] = __float2half_rn(offset * __half2float(lo)); dst[3 * G + g] = lo;
+            const __half zero = __float2half_rn(0.0f);
+            dst[g] = zero; dst[G + g] = hi;
+            dst[2 * G + g] = zero; dst[3 * G + g] = lo;
         }
     }
 }
@@ -611,7 +611,7 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
     }
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
-        pf_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(m->xp, c.T, c.H, m->xsum, c.status, c.gate.bits == 4 ? 8.0f : 0.0f);
+        pf_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(m->xp, c.T, c.H, m->xsum, c.status);
         if ((rc = check_launch(m, "prefill activation sums")) < 0) return rc;
     }
     if (c.gate.bits == 4) rc = c.meta_f16 ? launch_prefill<2, 4, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, 4, false>(m, c, m->xp, m->xsum, s);
@@ -620,7 +620,7 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
         const uint32_t rows = c.T * c.K + c.T;
-        pf_sums_kernel<<<(rows * 32 + 255) / 256, 256, 0, s>>>(m->hbuf16, rows, c.F, m->hsum, c.status, c.down.bits == 4 ? 8.0f : 0.0f);
+        pf_sums_kernel<<<(rows * 32 + 255) / 256, 256, 0, s>>>(m->hbuf16, rows, c.F, m->hsum, c.status);
         if ((rc = check_launch(m, "prefill intermediate sums")) < 0) return rc;
     }
     if (c.down.bits == 4) rc = c.meta_f16 ? launch_prefill<1, 4, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, 4, false>(m, c, m->hbuf16, m->hsum, s);
