@@ -793,6 +793,7 @@ int zc_moe_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, voi
 int zc_moe_set_option(zc_moe* m, const char* name, int value) {
     if (!m || !name) return fail(m, ZC_EINVAL, "null handle or option name");
     const bool fold = !std::strcmp(name, "fold_q4"), pdl = !std::strcmp(name, "pdl"), exact_h = !std::strcmp(name, "exact_h");
+    const bool wide = !std::strcmp(name, "prefill_wide");
     if (!std::strcmp(name, "ep_wait_ms")) {
         if (value < 1 || value > 60000) return fail(m, ZC_EINVAL, "ep_wait_ms must be 1..60000");
         DeviceGuard guard(m->device);
@@ -800,10 +801,11 @@ int zc_moe_set_option(zc_moe* m, const char* name, int value) {
         m->ep_wait_ms = uint32_t(value);
         return ZC_OK;
     }
-    if (fold || pdl || exact_h) {
+    if (fold || pdl || exact_h || wide) {
         DeviceGuard guard(m->device);
         drop_graphs(m);                                                      // captured launches hold the old choice
-        if (exact_h) m->exact_h = value != 0;
+        if (wide) m->prefill_wide = value != 0;
+        else if (exact_h) m->exact_h = value != 0;
         else if (fold) m->fold_q4 = value != 0; else m->pdl = value == 0 ? 0u : value == 1 ? 0xffffffffu : uint32_t(value);
         return ZC_OK;
     }

@@ -173,6 +173,7 @@ struct zc_moe {
     // Optional per-kernel timing (zc_moe_profile_begin/end): one event pair per launch.
     uint32_t pdl = 0xffffffffu;   // bit per KernelKind: that kernel launches with programmatic stream serialization (see launch_chained)
     bool exact_h = false;         // down reads the FP32 SwiGLU rows as two FP16 terms instead of one
+    bool prefill_wide = true;     // long batches: wide-tile kernel with accumulators resident in TMEM (false: per-group drain kernel)
     bool fold_q4 = true;          // Q4 codes enter the MMA with their 1024 offset (removed from the FP32 group sum)
     bool profiling = false;
     struct Span { int kind; cudaEvent_t start, stop; };

@@ -89,6 +89,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// The same for the lane that feeds the tensor cores: it has nothing else to do, and the wake-up of a suspended wait
+// (a few hundred clocks) is idle tensor time, so it polls without suspending. Still bounded.
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
+    for (uint32_t i = 0; i < (PF_POLL_LIMIT << 4); ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicOr(status, ZC_STATUS_TIMEOUT);
+    return false;
+}
+
 // K-major, no swizzle: start address, LBO = 128 B (next k chunk), SBO = sbo bytes (next 8 rows), version 1.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t sbo = 1024) {
     return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(128 >> 4) << 16) | (uint64_t(sbo >> 4) << 32) | (1ull << 46);
@@ -554,6 +566,372 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
     }
 }
 
+// =================================================================================================
+// Wide-tile kernel: accumulators that stay in TMEM for the whole K, weights fed to the tensor cores from TMEM.
+//
+// The kernel above hands every 64-wide group from the tensor cores to the epilogue warps (one TMEM drain per
+// group), and its token tile is at most 64 columns: per stage it offers 128-256 cycles of tensor work against a
+// hand-over chain of well over a thousand. This kernel removes the per-group drain. The per-group scale rides in
+// the A operand instead, without rounding any weight: the product s_g * q of an FP16 scale (11 significant bits) and
+// an integer code needs up to 19 bits, so it is written as two FP16 terms, hi = fl(s q) and lo = s q - hi (the error
+// of a rounded product is itself representable: one fused multiply-add gives it exactly), and both terms are
+// multiplied into the same accumulator. Every product the tensor cores form is then exact and they accumulate in
+// FP32, as before; the bias term b_g * sum_k x_k still runs as correction stages after the K loop.
+//   tile   : 128 weight rows x up to 128 tokens (N padded to 16) x two matrices - gate and up of the same rows
+//            (NMAT = 2, SwiGLU in the final epilogue) or two 128-row blocks of the down projection (NMAT = 1) -
+//            so each staged token tile meets 256 weight rows; two FP32 accumulators of N columns in TMEM.
+//   A      : the dequantised weights never touch shared memory. A first version staged them there (two terms x two
+//            matrices = 32 KB written and read per 32 k) and measured shared-memory bound: 112 KB per stage through a
+//            128 B/clock pipe is 860 clocks against 512 of tensor work. Producer thread r now writes its row's FP16
+//            pairs straight into TMEM lane r (tcgen05.st, eight 32-bit columns per 16 k) and the MMAs take A from
+//            tensor memory; a ring of two or three stages (128 columns each) sits beside the accumulators.
+//   B      : [N x 64] FP16 per stage in shared memory (K-major core-matrix layout without swizzle: LBO 128 B, SBO 1024 B).
+//   stage  : one 64-wide quantisation group = 16 MMAs (4 k steps x 2 matrices x 2 terms). Clock stamps showed the MMAs
+//            issuing at the tensor rate (64 clocks each at N = 128) and every wait, fence and commit of the issuing
+//            warp as idle tensor time, so a stage carries as much tensor work as TMEM allows and costs that warp one
+//            wait and one commit.
+//   roles  : warps 0-7 producers (warp w: matrix w / 4, TMEM lane quadrant w mod 4). Packed codes and token rows both
+//            arrive through the producers' cp.async stream, DR stages ahead: the token-row ring has DR + NA slots, so
+//            the slot a producer refills was released by the same completed-stage barrier it waits on for its TMEM
+//            columns. The same warps then run the final epilogue on their quadrant. One lane each of warps 8 and 9 issue
+//            the MMAs of alternate stages and release a stage with one tcgen05.commit.
+// Every wait is bounded as above.
+constexpr int PW_NMAX = 128;
+constexpr uint32_t PW_K = 64;
+constexpr uint32_t PW_B_STAGE = PW_NMAX * PW_K * 2;       // 16 KB
+constexpr uint32_t PW_A_COLS = 128;                       // TMEM columns of one A stage: [matrix][term][16-k block][8]
+constexpr uint32_t PW_TMEM_COLS = 512;
+constexpr uint32_t PW_NA_MAX = 3;
+constexpr int PW_THREADS = 320;                           // producers / epilogue 0-7, MMA issue 8-9
+
+// Development aid (build with -DZC_PW_STAMPS): the first CTA of a launch records clock64() at fixed points of each
+// role's loop, read back through zc_dbg_prefill_stamps. Compiled out otherwise.
+#ifdef ZC_PW_STAMPS
+__device__ unsigned long long pw_stamps[4][96][8];
+#define PW_STAMP(role, stage, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (stage) < 96 && lane == 0 && (warp == 0 || warp >= 8)) pw_stamps[role][stage][slot] = clock64(); } while (0)
+#else
+#define PW_STAMP(role, stage, slot) do {} while (0)
+#endif
+
+struct PwSmem {
+    uint32_t b_ring, raw, meta, total;
+    __host__ __device__ PwSmem(uint32_t G, uint32_t DR, uint32_t bits) {
+        b_ring = 0;
+        raw = b_ring + (DR + PW_NA_MAX) * PW_B_STAGE;
+        meta = raw + (DR + 1) * 2 * 128 * (bits * 8);     // [slot][matrix][row][bytes of 64 codes]
+        total = meta + 2 * 128 * 2 * G * 2 + 1024;        // two metadata tiles [128 x 2 G] FP16, + alignment slack
+        if (total < 116 * 1024) total = 116 * 1024;       // one CTA per SM: a CTA takes all 512 TMEM columns
+    }
+};
+
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+// D (TMEM) += A (TMEM, lane = row, two FP16 per 32-bit column) * B (shared memory descriptor).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int NMAT, int BITS, int DR>
+__global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, const PfTile* __restrict__ tiles, const int32_t* __restrict__ ntiles,
+                                                                    const __half* __restrict__ bsrc, const __half* __restrict__ bsum,
+                                                                    __half* __restrict__ hdst, uint32_t h_natural) {
+    constexpr uint32_t RAWB = BITS * 8;                   // packed bytes of one weight row of one stage
+    constexpr uint32_t NRAW = DR + 1;
+    extern __shared__ uint8_t pf_raw_smem[];
+    __shared__ __align__(8) uint64_t full[PW_NA_MAX], done[PW_NA_MAX], turn[2], meta_bar, acc_done, drain_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile uint32_t abort_flag;
+    __shared__ uint32_t brow[PW_NMAX];
+    __shared__ long long drow[PW_NMAX];
+    if (blockIdx.y >= uint32_t(*ntiles)) return;
+    const PfTile tile = tiles[blockIdx.y];
+    const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
+    const uint32_t nmain = G;
+    const uint32_t kb = 2 * G < PW_K ? 2 * G : PW_K, nblk = 2 * G / kb, ncorr = 2 * nblk, nst = nmain + ncorr;
+    const uint32_t N = uint32_t(tile.rows), Npad = (N + 15) & ~15u;
+    const uint32_t NA = Npad > 64 ? 2u : 3u;               // A stages beside two accumulators of Npad columns
+    const uint32_t NB = DR + NA;                           // token-row slots
+    const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t r0 = blockIdx.x * (NMAT == 2 ? 128u : 256u);
+    const PwSmem L(G, DR, BITS);
+    const uint32_t base = (pf_smem(pf_raw_smem) + 1023) & ~1023u;
+    uint8_t* const sm = pf_raw_smem + (base - pf_smem(pf_raw_smem));
+    auto at = [&](uint32_t shared_addr) { return sm + (shared_addr - base); };
+    const uint32_t b_ring = base + L.b_ring, raw_base = base + L.raw, meta_base = base + L.meta;
+    const uint32_t meta_sbo = (2 * G / 8) * 128, meta_tile = 128 * 2 * G * 2;
+    const uint8_t* record = tile.shared ? c.shared_record : c.records + size_t(uint32_t(tile.expert) - c.first_expert) * c.record_stride;
+    uint32_t* status = c.status;
+
+    if (tid == 0) {
+        for (uint32_t i = 0; i < PW_NA_MAX; ++i) { mbar_init(&full[i], 8); mbar_init(&done[i], 1); }
+        mbar_init(&meta_bar, 8); mbar_init(&acc_done, 1); mbar_init(&drain_bar, 2); mbar_init(&turn[0], 1); mbar_init(&turn[1], 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid < N) {
+        const uint32_t i = uint32_t(tile.row0) + tid;
+        if (tile.shared) {
+            brow[tid] = NMAT == 2 ? i : c.T * c.K + i;
+            drow[tid] = NMAT == 2 ? (long long)(size_t(c.T) * c.K + i) * c.F : (long long)i * c.H;
+        } else {
+            const uint32_t pos = uint32_t(c.offsets[tile.expert]) + i, slot = uint32_t(c.perm[pos]);
+            brow[tid] = NMAT == 2 ? slot / c.K : pos;
+            drow[tid] = NMAT == 2 ? (long long)pos * c.F : (long long)slot * c.H;
+        }
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pf_smem(&tmem_base_s)), "r"(PW_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    const uint32_t tmem_a = tmem_base + 2 * Npad;           // A ring: stage s at columns s * PW_A_COLS, then [matrix][term][block][8]
+
+    if (warp < 8) {
+        // ---- producers: thread (m, r) owns weight row r of matrix m ---------------------------------------
+        const uint32_t m = warp / 4, quad = warp % 4, r = quad * 32 + lane;
+        const Projection pr = NMAT == 2 ? (m == 0 ? c.gate : c.up) : c.down;
+        const uint32_t mrow = r0 + (NMAT == 1 ? m * 128u : 0u) + r;
+        const uint8_t* codes = record + pr.codes + size_t(mrow) * (K * BITS / 8);
+        const uint32_t lane_base = (quad * 32) << 16;
+        // metadata of the row -> A' tile [s_0..s_G-1 | b_0..b_G-1] as FP16 (the correction stages' A operand, and where
+        // this thread reads its scales)
+        {
+            const uint8_t* sc = record + pr.scales + size_t(mrow) * G * 2;
+            const uint8_t* bi = record + pr.biases + size_t(mrow) * G * 2;
+            const uint32_t dst = meta_base + m * meta_tile + (r / 8) * meta_sbo + (r % 8) * 16;
+            for (uint32_t ch = 0; ch < G / 8; ++ch) {
+                if (c.meta_f16) {
+                    pf_cp16(dst + ch * 128, sc + ch * 16);
+                    pf_cp16(dst + (G / 8 + ch) * 128, bi + ch * 16);
+                } else {
+                    const uint4 a = *reinterpret_cast<const uint4*>(sc + ch * 16), b = *reinterpret_cast<const uint4*>(bi + ch * 16);
+                    const uint32_t ra[4] = {a.x, a.y, a.z, a.w}, rb[4] = {b.x, b.y, b.z, b.w};
+                    uint32_t ha[4], hb[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __half2 x = __floats2half2_rn(__uint_as_float(ra[i] << 16), __uint_as_float(ra[i] & 0xffff0000u));
+                        const __half2 y = __floats2half2_rn(__uint_as_float(rb[i] << 16), __uint_as_float(rb[i] & 0xffff0000u));
+                        ha[i] = *reinterpret_cast<const uint32_t*>(&x); hb[i] = *reinterpret_cast<const uint32_t*>(&y);
+                    }
+                    *reinterpret_cast<uint4*>(at(dst + ch * 128)) = make_uint4(ha[0], ha[1], ha[2], ha[3]);
+                    *reinterpret_cast<uint4*>(at(dst + (G / 8 + ch) * 128)) = make_uint4(hb[0], hb[1], hb[2], hb[3]);
+                }
+            }
+        }
+        // Token rows of a main stage: 128 bytes per row = 8 pieces; thread t copies piece (row t / 8 + 32 i, chunk t mod 8)
+        // for i < 4. The row pointers are prepared once; a stage adds 128 bytes.
+        const __half* src_i[PW_NMAX / 32];
+#pragma unroll
+        for (int i = 0; i < PW_NMAX / 32; ++i) {
+            const uint32_t row = tid / 8 + 32 * i;
+            src_i[i] = row < N ? bsrc + size_t(brow[row]) * K + (tid % 8) * 8 : nullptr;
+        }
+        const uint32_t dst_piece = (tid / 64) * 1024 + (tid % 8) * 128 + ((tid / 8) % 8) * 16;     // + i * 4096
+        auto issue_stage = [&](uint32_t j) {             // everything stage j needs from memory, into slot j of the rings
+            if (j >= nst) return;
+            const uint32_t bs = b_ring + (j % NB) * PW_B_STAGE;
+            if (j < nmain) {
+                const uint32_t dst = raw_base + (((j % NRAW) * 2 + m) * 128 + r) * RAWB;
+#pragma unroll
+                for (uint32_t piece = 0; piece < RAWB; piece += 16) pf_cp16(dst + piece, codes + size_t(j) * RAWB + piece);
+#pragma unroll
+                for (int i = 0; i < PW_NMAX / 32; ++i) if (src_i[i]) pf_cp16(bs + i * 4096 + dst_piece, src_i[i] + j * PW_K);
+            } else {
+                const uint32_t chunks = kb / 8, term = (j - nmain) / nblk, blk = (j - nmain) % nblk;
+                for (uint32_t q = tid; q < N * chunks; q += 256) {
+                    const uint32_t row = q / chunks, kc = q % chunks;
+                    pf_cp16(bs + (row / 8) * (chunks * 128) + kc * 128 + (row % 8) * 16, bsum + size_t(brow[row]) * 4 * G + term * 2 * G + blk * kb + kc * 8);
+                }
+            }
+        };
+#pragma unroll 1
+        for (uint32_t j = 0; j < uint32_t(DR); ++j) {
+            issue_stage(j);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        bool ok = true;
+        const bool q8s = c.q8_signed;
+        const uint32_t scale_at = meta_base + m * meta_tile + (r / 8) * meta_sbo + (r % 8) * 16;
+        for (uint32_t ks = 0; ks < nst && ok; ++ks) {
+            PW_STAMP(0, ks, 0);
+            asm volatile("cp.async.wait_group %0;" ::"n"(DR - 1) : "memory");       // this thread's copies for stage ks (and, at ks = 0, the metadata) have landed
+            PW_STAMP(0, ks, 1);
+            // stage ks - NA has drained: its TMEM columns, and the token-row slot that stage ks + DR will use, are free
+            if (ks >= NA) ok = mbar_wait(&done[ks % NA], ((ks / NA) - 1) & 1, &abort_flag, status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            PW_STAMP(0, ks, 2);
+            issue_stage(ks + DR);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (ks < nmain) {
+                const __half sh = *reinterpret_cast<const __half*>(at(scale_at + (ks / 8) * 128 + (ks % 8) * 2));
+                const __half2 s2 = __half2half2(sh);
+                const uint32_t src = raw_base + (((ks % NRAW) * 2 + m) * 128 + r) * RAWB;
+                const uint32_t ta = tmem_a + lane_base + (ks % NA) * PW_A_COLS + m * 64;       // this row's columns: [term][block][8]
+                auto two_terms = [&](uint32_t q_bits, uint32_t& hi, uint32_t& lo) {      // q exact -> fl(s q), s q - fl(s q)
+                    const __half2 q = *reinterpret_cast<const __half2*>(&q_bits);
+                    const __half2 h = __hmul2(q, s2);
+                    const __half2 l = __hfma2(q, s2, __hneg2(h));
+                    hi = *reinterpret_cast<const uint32_t*>(&h); lo = *reinterpret_cast<const uint32_t*>(&l);
+                };
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");      // the MMAs that read these columns have completed
+#pragma unroll
+                for (int blk = 0; blk < 4; ++blk) {                // 16 k per block: eight packed columns per term
+                    uint32_t hi[8], lo[8];
+                    if constexpr (BITS == 4) {
+                        const uint2 w = *reinterpret_cast<const uint2*>(at(src + blk * 8));
+                        const uint4 qa = pf_dequant_word(w.x), qb = pf_dequant_word(w.y);
+                        two_terms(qa.x, hi[0], lo[0]); two_terms(qa.y, hi[1], lo[1]); two_terms(qa.z, hi[2], lo[2]); two_terms(qa.w, hi[3], lo[3]);
+                        two_terms(qb.x, hi[4], lo[4]); two_terms(qb.y, hi[5], lo[5]); two_terms(qb.z, hi[6], lo[6]); two_terms(qb.w, hi[7], lo[7]);
+                    } else {
+                        const uint4 w = *reinterpret_cast<const uint4*>(at(src + blk * 16));
+                        const uint2 a = pf_dequant_q8_word(w.x, q8s), b = pf_dequant_q8_word(w.y, q8s);
+                        const uint2 e = pf_dequant_q8_word(w.z, q8s), f = pf_dequant_q8_word(w.w, q8s);
+                        two_terms(a.x, hi[0], lo[0]); two_terms(a.y, hi[1], lo[1]); two_terms(b.x, hi[2], lo[2]); two_terms(b.y, hi[3], lo[3]);
+                        two_terms(e.x, hi[4], lo[4]); two_terms(e.y, hi[5], lo[5]); two_terms(f.x, hi[6], lo[6]); two_terms(f.y, hi[7], lo[7]);
+                    }
+                    tmem_st8(ta + 0 * 32 + blk * 8, hi);
+                    tmem_st8(ta + 1 * 32 + blk * 8, lo);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            PW_STAMP(0, ks, 3);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the token rows (and at ks = 0 the metadata tile) for the MMAs
+            __syncwarp();
+            if (lane == 0) {
+                if (ks == 0) mbar_arrive(&meta_bar);      // one-shot: the metadata tiles are in place
+                mbar_arrive(&full[ks % NA]);
+            }
+            PW_STAMP(0, ks, 4);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // ---- final epilogue on this warp's lane quadrant: TMEM lane r is weight row r; the two warps of a quadrant
+        // (m = 0, 1) take alternate 16-column chunks ---------------------------------------------------------
+        PW_STAMP(3, 0, 0);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&acc_done, 0, &abort_flag, status));
+        PW_STAMP(3, 0, 1);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float* out_base = tile.shared ? c.shared_out : c.expert_out;
+            const uint32_t row = r0 + r;
+            for (uint32_t chunk = m; chunk * 16 < Npad; chunk += 2) {
+                uint32_t d0[16], d1[16];
+                tmem_ld16(tmem_base + lane_base + chunk * 16, d0);
+                tmem_ld16(tmem_base + lane_base + Npad + chunk * 16, d1);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint32_t t = chunk * 16 + j;
+                    if (t < N) {
+                        const float a = __uint_as_float(d0[j]), b = __uint_as_float(d1[j]);
+                        if constexpr (NMAT == 2) {
+                            const float hv = (a * sigmoid_f(a)) * b;
+                            hdst[drow[t] + (h_natural ? row : (row & ~7u) + pf_pos8(row & 7))] = __float2half_rn(hv);
+                        } else {
+                            out_base[drow[t] + row] = a;
+                            out_base[drow[t] + row + 128] = b;
+                        }
+                    }
+                }
+            }
+        }
+        PW_STAMP(3, 0, 2);
+    } else {
+        // ---- MMA issue (warps 8 and 9): whatever the issuing lane does besides issuing is idle tensor time - the MMAs
+        // leave at the tensor rate, so the queue behind the lane is shallow. Two lanes therefore alternate: warp 8 takes
+        // the even stages, warp 9 the odd ones; a lane waits for its stage's operands while the other one issues, takes
+        // the turn (one mbarrier hand-over, ordered by the tcgen05 fences), issues, passes the turn on and only then
+        // commits. All MMAs of the tile still reach the tensor pipe in stage order.
+        const uint32_t idesc = (1u << 4) | ((Npad >> 3) << 17) | ((PF_M >> 4) << 24);       // D = F32, A = B = F16, K-major, N = Npad, M = 128
+        const uint32_t me = warp - 8;
+        if (lane == 0) {
+            bool ok = true;
+            for (uint32_t j = me; j < nst; j += 2) {
+                const bool main = j < nmain;
+                PW_STAMP(2, j, 0);
+                if (j >= nmain) ok = mbar_spin(&meta_bar, 0, &abort_flag, status);
+                if (ok) ok = mbar_spin(&full[j % NA], (j / NA) & 1, &abort_flag, status);
+                if (ok && j > 0) ok = mbar_spin(&turn[(j - 1) & 1], ((j - 1) / 2) & 1, &abort_flag, status);      // stage j - 1 has been issued
+                if (!ok) break;
+                PW_STAMP(2, j, 1);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t bs = b_ring + (j % NB) * PW_B_STAGE;
+                if (main) {
+                    const uint32_t ta = tmem_a + (j % NA) * PW_A_COLS;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t bd = umma_desc(bs + kk * 256, 1024);
+#pragma unroll
+                        for (int m = 0; m < 2; ++m)
+#pragma unroll
+                            for (int term = 0; term < 2; ++term)
+                                umma_f16_ts(tmem_base + m * Npad, ta + m * 64 + term * 32 + kk * 8, bd, idesc, (j | kk | term) != 0);
+                    }
+                } else {
+                    const uint32_t blk = (j - nmain) % nblk;
+                    for (uint32_t kk = 0; kk < kb / 16; ++kk) {
+                        const uint64_t bd = umma_desc(bs + kk * 256, (kb / 8) * 128);
+#pragma unroll
+                        for (int m = 0; m < 2; ++m)
+                            umma_f16(tmem_base + m * Npad, umma_desc(meta_base + m * meta_tile + blk * (kb / 8) * 128 + kk * 256, meta_sbo), bd, idesc, 1);
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(&turn[j & 1]);
+                PW_STAMP(2, j, 2);
+                umma_commit(&done[j % NA]);
+                if (j + 1 == nst) umma_commit(&acc_done);
+                PW_STAMP(2, j, 3);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp >= 8) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // After an aborted run MMAs may still be in flight: both issuing lanes commit, and the columns are returned only
+        // after everything issued has drained (bounded).
+        if (abort_flag) {
+            if (lane == 0) umma_commit(&drain_bar);
+            __syncwarp();
+            if (warp == 8) for (uint32_t i = 0; i < PF_POLL_LIMIT && !mbar_try(&drain_bar, 0); ++i) {}
+            __syncwarp();
+        }
+        if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(PW_TMEM_COLS) : "memory");
+    }
+}
+
+template <int NMAT, int BITS, int DR>
+int launch_prefill_wide_d(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, size_t smem, cudaStream_t s) {
+    auto kernel = prefill_wide_kernel<NMAT, BITS, DR>;
+    static SmemOptIn configured;
+    if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) return check_launch(m, "prefill kernel attribute");
+    Timed t(m, s, NMAT == 2 ? KERNEL_PREFILL_GATE_UP : KERNEL_PREFILL_DOWN);
+    const uint32_t row_tiles = NMAT == 2 ? c.F / 128 : c.H / 256;
+    kernel<<<dim3(row_tiles, m->pf_max_tiles), PW_THREADS, smem, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, bsum, m->hbuf16,
+                                                                    c.down.bits == 8 ? 1u : 0u);
+    return check_launch(m, NMAT == 2 ? "prefill gate_up" : "prefill down");
+}
+
+// Deepest weight prefetch that fits beside the metadata tiles.
+template <int NMAT, int BITS>
+int launch_prefill_wide(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, cudaStream_t s) {
+    const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
+    const size_t limit = 227 * 1024 - 2048;             // dynamic shared memory beside the kernel's static arrays
+    if (PwSmem(G, 5, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 5>(m, c, bsrc, bsum, PwSmem(G, 5, BITS).total, s);
+    if (PwSmem(G, 4, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 4>(m, c, bsrc, bsum, PwSmem(G, 4, BITS).total, s);
+    if (PwSmem(G, 2, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 2>(m, c, bsrc, bsum, PwSmem(G, 2, BITS).total, s);
+    return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
+}
+
 template <int NMAT, int BITS, bool META_F16, int D>
 int launch_prefill_d(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, size_t smem, cudaStream_t s) {
     const uint32_t N = NMAT == 2 ? c.F : c.H;
@@ -583,6 +961,10 @@ int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* b
 
 }  // namespace
 
+#ifdef ZC_PW_STAMPS
+extern "C" int zc_dbg_prefill_stamps(void* host) { return cudaMemcpyFromSymbol(host, pw_stamps, sizeof(pw_stamps)) == cudaSuccess ? 0 : -1; }
+#endif
+
 size_t prefill_tile_capacity(const zc_moe_desc& d) {
     const size_t local = d.local_experts ? d.local_experts : d.experts;
     return local + (size_t(d.max_tokens) * d.top_k + d.max_tokens) / PF_NMAX + 2;
@@ -597,9 +979,10 @@ bool prefill_supported(const zc_moe_desc& d) {
 // tile list -> FP16 activations -> gate/up (+SwiGLU) -> down. Routing must already be in place.
 int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
     int rc;
+    const bool wide = m->prefill_wide;
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
-        pf_tiles_kernel<<<1, 1024, 0, s>>>(c.offsets, c.E, c.first_expert, c.local_experts, c.T, c.has_shared, PF_NMAX,
+        pf_tiles_kernel<<<1, 1024, 0, s>>>(c.offsets, c.E, c.first_expert, c.local_experts, c.T, c.has_shared, wide ? PW_NMAX : PF_NMAX,
                                            static_cast<PfTile*>(m->pf_tiles), m->pf_ntiles);
         if ((rc = check_launch(m, "prefill tiles")) < 0) return rc;
     }
@@ -614,7 +997,8 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
         pf_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(m->xp, c.T, c.H, m->xsum, c.status);
         if ((rc = check_launch(m, "prefill activation sums")) < 0) return rc;
     }
-    if (c.gate.bits == 4) rc = c.meta_f16 ? launch_prefill<2, 4, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, 4, false>(m, c, m->xp, m->xsum, s);
+    if (wide) rc = c.gate.bits == 4 ? launch_prefill_wide<2, 4>(m, c, m->xp, m->xsum, s) : launch_prefill_wide<2, 8>(m, c, m->xp, m->xsum, s);
+    else if (c.gate.bits == 4) rc = c.meta_f16 ? launch_prefill<2, 4, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, 4, false>(m, c, m->xp, m->xsum, s);
     else rc = c.meta_f16 ? launch_prefill<2, 8, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, 8, false>(m, c, m->xp, m->xsum, s);
     if (rc < 0) return rc;
     {
@@ -623,7 +1007,8 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
         pf_sums_kernel<<<(rows * 32 + 255) / 256, 256, 0, s>>>(m->hbuf16, rows, c.F, m->hsum, c.status);
         if ((rc = check_launch(m, "prefill intermediate sums")) < 0) return rc;
     }
-    if (c.down.bits == 4) rc = c.meta_f16 ? launch_prefill<1, 4, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, 4, false>(m, c, m->hbuf16, m->hsum, s);
+    if (wide) rc = c.down.bits == 4 ? launch_prefill_wide<1, 4>(m, c, m->hbuf16, m->hsum, s) : launch_prefill_wide<1, 8>(m, c, m->hbuf16, m->hsum, s);
+    else if (c.down.bits == 4) rc = c.meta_f16 ? launch_prefill<1, 4, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, 4, false>(m, c, m->hbuf16, m->hsum, s);
     else rc = c.meta_f16 ? launch_prefill<1, 8, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, 8, false>(m, c, m->hbuf16, m->hsum, s);
     if (rc < 0) return rc;
     return 6;

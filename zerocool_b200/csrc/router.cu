@@ -206,6 +206,9 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_partial_kernel(Call c, 
 // Thread (tx = lane, ty = warp) owns rows tx (and tx + 32) x tokens ty*TPT.. x both partitions: up to 32
 // independent chains, each still the k-ascending fused multiply-add chain of its partition.
 namespace cg = cooperative_groups;
+#ifndef ZC_ROUTER_SMALL_T
+#define ZC_ROUTER_SMALL_T 128
+#endif
 constexpr int CLUSTER_PARTS = 2;                      // partitions per CTA
 constexpr int CLUSTER_SIZE = 16 / CLUSTER_PARTS;
 
@@ -389,7 +392,7 @@ int launch_router_cluster(zc_moe* m, const Call& c, cudaStream_t s) {
     cfg.attrs = attr; cfg.numAttrs = 1;
     static SmemOptIn configured;        // per instantiation, per device
     static int8_t usable[MAX_DEVICES];  // per device: 0 unknown, 1 the device hosts a cluster of this shape, 2 it cannot
-    if (smem > 200 * 1024 || m->device < 0 || m->device >= MAX_DEVICES) return 0;
+    if (smem > 224 * 1024 || m->device < 0 || m->device >= MAX_DEVICES) return 0;
     if (smem > configured.bytes[m->device]) {
         if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
         usable[m->device] = 0;
@@ -413,19 +416,147 @@ int launch_router_cluster(zc_moe* m, const Call& c, cudaStream_t s) {
     return rc < 0 ? rc : 1;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Long batches: one CTA owns a 64-token x 64-row tile of the logits for the whole of K. It walks the sixteen
+// partitions in order; inside a partition every (token, row) pair is the k-ascending chain of fused multiply-adds,
+// and the finished partial is added to the pair's running total - the same additions in the same order as the
+// partition kernels above ("partials added 0..15 starting from zero"), but nothing leaves the registers: no partial
+// store, no arrival counter, no ordered re-read. Thread (tx, ty) holds rows tx + 16 i and tokens 4 ty + j (i, j < 4):
+// sixteen independent chains, fed by four row reads and four broadcast token reads per four k, which keeps the
+// kernel bound by the FP32 pipe and not by shared memory. Tiles keep the row-major [row][k] layout (leading
+// dimension part + 4 floats), so FP32 router rows are copied with 16-byte cp.async.
+constexpr int LONG_TT = 64, LONG_RT = 64;
+__global__ void __launch_bounds__(ROUTER_THREADS, 3) router_long_kernel(Call c) {
+    extern __shared__ __align__(16) float smem[];
+    const uint32_t H = c.H, part = H / 16, LD = part + 4;
+    float* ws = smem;                       // [LONG_RT][LD]
+    float* xs = ws + LONG_RT * LD;          // [LONG_TT][LD]
+    const uint32_t e0 = blockIdx.x * LONG_RT, t0 = blockIdx.y * LONG_TT;
+    const uint32_t rows_total = c.E + (c.has_shared ? 1u : 0u);
+    const uint32_t tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+    const bool x32 = c.act_dtype == ZC_F32, w32 = c.router_dtype == ZC_F32;
+    float total[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) total[i][j] = 0.0f;
+    pdl_wait();
+    for (uint32_t p = 0; p < 16; ++p) {
+        const uint32_t k0 = p * part;
+        __syncthreads();                     // the previous partition's tiles have been consumed
+        for (uint32_t task = tid; task < LONG_RT * (part / 4); task += ROUTER_THREADS) {
+            const uint32_t el = task / (part / 4), kq = task % (part / 4), e = e0 + el;
+            float* dst = ws + el * LD + kq * 4;
+            if (e >= rows_total) { *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0); continue; }
+            if (w32) {
+                const float* base = e < c.E ? static_cast<const float*>(c.router_w) + size_t(e) * H : static_cast<const float*>(c.shared_gate_w);
+                cp_async16(dst, base + k0 + kq * 4);
+            } else {
+                const uint16_t* base = e < c.E ? static_cast<const uint16_t*>(c.router_w) + size_t(e) * H : static_cast<const uint16_t*>(c.shared_gate_w);
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(base + k0 + kq * 4));
+                *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                                              __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+            }
+        }
+        if (x32) {
+            for (uint32_t task = tid; task < LONG_TT * (part / 4); task += ROUTER_THREADS) {
+                const uint32_t tt = task / (part / 4), kq = task % (part / 4), t = t0 + tt;
+                float* dst = xs + tt * LD + kq * 4;
+                if (t < c.T) cp_async16(dst, static_cast<const float*>(c.x) + size_t(t) * H + k0 + kq * 4);
+                else *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0);
+            }
+        } else {
+            for (uint32_t task = tid; task < LONG_TT * (part / 8); task += ROUTER_THREADS) {
+                const uint32_t tt = task / (part / 8), kb = task % (part / 8), t = t0 + tt;
+                uint4 raw = make_uint4(0, 0, 0, 0);
+                if (t < c.T) raw = __ldcg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(c.x) + size_t(t) * H + k0 + kb * 8));
+                const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+                float4* dst = reinterpret_cast<float4*>(xs + tt * LD + kb * 8);
+                dst[0] = make_float4(__uint_as_float(r[0] << 16), __uint_as_float(r[0] & 0xffff0000u), __uint_as_float(r[1] << 16), __uint_as_float(r[1] & 0xffff0000u));
+                dst[1] = make_float4(__uint_as_float(r[2] << 16), __uint_as_float(r[2] & 0xffff0000u), __uint_as_float(r[3] << 16), __uint_as_float(r[3] & 0xffff0000u));
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        float acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+        const float* wrow = ws + tx * LD;
+        const float* xrow = xs + ty * 4 * LD;
+#pragma unroll 2
+        for (uint32_t k = 0; k < part; k += 4) {
+            float4 wv[4], xv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) wv[i] = *reinterpret_cast<const float4*>(wrow + i * 16 * LD + k);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xv[j] = *reinterpret_cast<const float4*>(xrow + j * LD + k);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float a = acc[i][j];
+                    a = __fmaf_rn(xv[j].x, wv[i].x, a);
+                    a = __fmaf_rn(xv[j].y, wv[i].y, a);
+                    a = __fmaf_rn(xv[j].z, wv[i].z, a);
+                    a = __fmaf_rn(xv[j].w, wv[i].w, a);
+                    acc[i][j] = a;
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) total[i][j] = __fadd_rn(total[i][j], acc[i][j]);      // partial p joins the ordered sum
+    }
+    pdl_launch_dependents();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t e = e0 + tx + 16 * i;
+        if (e >= rows_total) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t t = t0 + ty * 4 + j;
+            if (t >= c.T) continue;
+            if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(total[i][j], c.router_bias[e]) : total[i][j];
+            else c.gate_logit[t] = total[i][j];
+        }
+    }
+}
+
+int launch_router_long(zc_moe* m, const Call& c, cudaStream_t s) {
+    const uint32_t part = c.H / 16, LD = part + 4;
+    const size_t smem = size_t(LONG_RT + LONG_TT) * LD * sizeof(float);
+    if (smem > 200 * 1024) return 0;
+    static SmemOptIn configured;
+    if (opt_in_smem(router_long_kernel, configured, m->device, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
+    const uint32_t rows_total = c.E + (c.has_shared ? 1 : 0);
+    const dim3 grid((rows_total + LONG_RT - 1) / LONG_RT, (c.T + LONG_TT - 1) / LONG_TT);
+    int rc;
+    {
+        Timed t(m, s, KERNEL_ROUTER);
+        const cudaError_t e = launch_chained(m, -1, router_long_kernel, grid, dim3(ROUTER_THREADS), smem, s, nullptr, 0, c);
+        if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("router (long) launch: ") + cudaGetErrorString(e));
+        rc = check_launch(m, "router");
+    }
+    return rc < 0 ? rc : 1;
+}
+
 }  // namespace
 
 uint32_t router_rows_padded(const zc_moe_desc& d) { return (d.experts + (d.has_shared ? 1 : 0) + ROW_TILE_PAD - 1) / ROW_TILE_PAD * ROW_TILE_PAD; }
 
 int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s) {
-    // Cluster form for short batches (returns 0 when the device cannot host it: fall through to the global-memory form).
+    // Cluster form for short batches, whole-K tiles for long ones (either returns 0 when the device cannot host it or
+    // the tile does not fit: fall through to the global-memory form).
     {
-        int n;
-        // Small tiles up to 128 tokens: at 64 tokens, 544 CTAs of 16 tokens x 32 rows measured 19 us against 21 us
-        // (32 x 32) and 25 us (32 x 64, whose 144 large CTAs do not all find a cluster slot in the first wave).
+        int n = 0;
+        // Up to 128 tokens small tiles win on latency: at 64 tokens, 544 CTAs of 16 tokens x 32 rows measured 19 us
+        // against 21 us (32 x 32) and 25 us (32 x 64, whose 144 large CTAs do not all find a cluster slot in the first wave).
         if (c.T <= 8) n = launch_router_cluster<8, 1>(m, c, s);
-        else if (c.T <= 128) n = launch_router_cluster<16, 1>(m, c, s);
-        else n = 0;       // long batches: the 64-token tiles of the global-memory form re-read the rows least (237 us against 307-381 us at 2048 tokens)
+        else if (c.T <= ZC_ROUTER_SMALL_T) n = launch_router_cluster<16, 1>(m, c, s);
+        else n = launch_router_long(m, c, s);      // long batches: whole-K tiles, partials never leave the registers
         if (n != 0) return n;
     }
     const uint32_t part = c.H / 16;
