@@ -486,6 +486,68 @@ def measure_ep(torch, dist, rank, world, local, layers, total_tokens, steps, war
     }
 
 
+def route_trace_run(torch, local, args):
+    """--record-routes: one pass of the chained decode stack, layer by layer, writing every layer's selections as a route
+    trace. --replay-routes: the recorded selections forced into the layers (the router still scores, the top-k search is
+    skipped), timed per pass with CUDA events; the counterpart of the reference's dependency replay
+    (src/engine/bench.cpp:43-104), with the whole layer - router scores, shared expert, combine - inside the timed region."""
+    import hashlib
+    from zerocool_b200.moe import Moe
+    from zerocool_b200.route_trace import RouteTrace, read_route_trace
+    cfg = config(args.layers, max(args.tokens, 64))
+
+    def glue(out):
+        f = out.float()
+        d = f - f.mean(-1, keepdim=True)
+        return (d * torch.rsqrt((d * d).mean(-1, keepdim=True))).to(torch.bfloat16)
+
+    if args.record_routes:
+        m = Moe(cfg, local)
+        fill(m, cfg)
+        _, _, x = make_inputs(torch, cfg, args.tokens, 0)
+        with RouteTrace(args.record_routes, {"generator": "bench.py", "seed": SEED, "layers": cfg.layers, "experts": cfg.experts, "top_k": cfg.top_k},
+                        cfg.layers, cfg.top_k) as trace:
+            trace.request_begin("synthetic", [], args.tokens)
+            trace.begin(1, 0, args.tokens, phase="decode")
+            for layer in range(cfg.layers):
+                out = m.moe(layer, x)
+                trace.routes(layer, 0, args.tokens, m.last_routing(args.tokens)["ids"])
+                x = glue(out)
+            trace.commit(args.tokens)
+            trace.request_end([], "stop")
+            trace.finish()
+        return {"recorded": args.record_routes, "tokens": args.tokens, "layers": cfg.layers, "output_sha256": hashlib.sha256(out.cpu().view(torch.int16).numpy().tobytes()).hexdigest()}
+    passes = read_route_trace(args.replay_routes, cfg.layers, cfg.top_k, cfg.experts)
+    cfg = config(args.layers, max(64, max(p["tokens"] for p in passes)))
+    m = Moe(cfg, local)
+    fill(m, cfg)
+    hbm_peak, peak_source = peaks()
+    runs = []
+    for index, recorded in enumerate(passes):
+        tokens = recorded["tokens"]
+        ids = [torch.from_numpy(r).cuda() for r in recorded["routes"]]
+        _, _, x0 = make_inputs(torch, cfg, tokens, 0)
+
+        def one_pass():
+            x = x0
+            for layer in range(cfg.layers):
+                out = m.moe_routed(layer, x, ids[layer])
+                x = glue(out)
+            return out
+
+        for _ in range(args.warmup):
+            out = one_pass()
+        ms = time_steps(torch, one_pass, args.steps, None)
+        active = [len(np.unique(r)) for r in recorded["routes"]]
+        step_bytes = float(sum(layer_bytes(cfg, a, tokens) for a in active))
+        runs.append({"recorded_pass": index, "tokens": tokens, "offset": recorded["offset"], "phase": recorded["phase"], "ms_per_pass": ms,
+                     "tokens_per_s": tokens / (ms * 1e-3), "mean_active_experts": float(np.mean(active)),
+                     "hbm_gbs": step_bytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": step_bytes / (ms * 1e-3) / 1e9 / hbm_peak,
+                     "device_status": m.status(), "output_sha256": hashlib.sha256(out.cpu().view(torch.int16).numpy().tobytes()).hexdigest()})
+    return {"kind": "route_replay", "route_source": args.replay_routes, "steps": args.steps, "warmup": args.warmup, "peak_source": peak_source, "runs": runs,
+            "note": "launch by launch with the inter-layer glue in PyTorch (no graph): a harness for recorded routing distributions, not the headline path"}
+
+
 def run_ours(args):
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -501,6 +563,12 @@ def run_ours(args):
         dist = d
     from zerocool_b200.moe import Moe
     hbm_peak, peak_source = peaks()
+
+    if args.record_routes or args.replay_routes:
+        if world > 1:
+            raise RuntimeError("route traces are recorded and replayed on one GPU")
+        print(json.dumps(route_trace_run(torch, local, args)), flush=True)
+        return
 
     if args.workload == "ep":
         ep = measure_ep(torch, dist, rank, world, local, args.layers, args.tokens, args.steps, args.warmup, args.skip_parity)
@@ -711,6 +779,8 @@ def main():
     ap.add_argument("--skip-batches", action="store_true")
     ap.add_argument("--skip-extras", action="store_true", help="leave out the prefill and mixed sub-records (one-GPU runs)")
     ap.add_argument("--skip-ep", action="store_true", help="leave out the configuration-5 sub-record")
+    ap.add_argument("--record-routes", default="", help="write the expert selections of one decode pass as a route trace (JSON lines) and exit")
+    ap.add_argument("--replay-routes", default="", help="time the decode stack with the expert selections of a recorded route trace forced into every layer")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -183,6 +183,26 @@ int zc_moe_prefill(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, 
 /* Model::moe with the family chosen from `tokens`. */
 int zc_moe_forward(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, void* out, void* stream);
 
+/* The steps either side of Model::moe in the layer loop (src/engine/model.cpp:653, 659-662): the reference keeps four
+ * residual streams of width H ("hyper connections").
+ *   zc_moe_hc_mix replaces the hc_mix dispatch of Model::hyper (src/engine/model.cpp:343, kernels/metal/qwen.metal:582-588):
+ *     x[t, d] = bf(bf(bf(bf(p0 + p1) + p2) + p3) / 4) with p_h = bf(normed[t, h, d] * mix[t, h, d]); normed and mix are
+ *     fp32 [tokens, 4, H] device memory, x [tokens, H] is written in the handle's activation dtype (what zc_moe_forward reads).
+ *   zc_moe_forward_hc is zc_moe_forward with hc_add (qwen.metal:589-595, dispatched at model.cpp:660-662) as the combine's
+ *     epilogue: hyper_out[t, h, d] = bf(hyper[t, h, d] + bf(m[t, d] * inject[t, h])), m = the layer's output, which is not
+ *     written anywhere (the roundings apply under ZC_ARITH_REFERENCE; otherwise the sum is plain fp32 on m rounded to the
+ *     handle's output dtype). hyper, hyper_out: fp32 [tokens, 4, H] (may be the same buffer); inject: fp32 [tokens, 4]. */
+int zc_moe_hc_mix(zc_moe* moe, const float* normed, const float* mix, uint32_t tokens, void* x, void* stream);
+int zc_moe_forward_hc(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, const float* hyper, const float* inject,
+                      float* hyper_out, void* stream);
+
+/* Model::moe with the expert selection given instead of searched: the replay of a recorded route
+ * (include/engine/route_trace.hpp:44-49 records the ids of every layer; src/engine/bench.cpp:43-104 replays them).
+ * ids [tokens, K] int32 device memory, in rank order; the router still runs (its scores of the given experts give
+ * the weights, renormalised over the selection exactly as Metal::route does; row E gives the shared gate), the top-k
+ * search does not. With the ids a normal call selected, the output equals that call's bit for bit. */
+int zc_moe_forward_routed(zc_moe* moe, uint32_t layer, const void* x, uint32_t tokens, const int32_t* ids, void* out, void* stream);
+
 /* Expert parallelism over the ranks of one node (no counterpart in the reference, a single-GPU engine).
  * A handle created with first_expert / local_experts holds one contiguous range of every layer's experts;
  * router, shared expert and shared gate are replicated. Per layer and rank:

@@ -208,3 +208,21 @@ def bf(x):
     u = x.view(np.uint32)
     r = ((u + np.uint32(0x7FFF) + ((u >> 16) & 1)) & np.uint32(0xFFFF0000)).view(np.float32)
     return np.where(np.isnan(x), np.float32(np.nan), r)
+
+
+def hc_mix(normed, mix):
+    """hc_mix (kernels/metal/qwen.metal:582-588): normed, mix fp32 [T, 4, H] -> [T, H];
+    sum = bf(sum + bf(n * w)) over the four streams from zero, then bf(sum / 4)."""
+    normed, mix = _f32(normed), _f32(mix)
+    total = np.zeros(normed[:, 0].shape, np.float32)
+    for h in range(normed.shape[1]):
+        total = bf(total + bf(normed[:, h] * mix[:, h]))
+    return bf(total / np.float32(4))
+
+
+def hc_add(hyper, x, inject, ref=True):
+    """hc_add (kernels/metal/qwen.metal:589-595): hyper fp32 [T, 4, H], x fp32 [T, H], inject fp32 [T, 4] ->
+    bf(hyper + bf(x * inject)); ref=False drops both roundings (plain fp32)."""
+    hyper, x, inject = _f32(hyper), _f32(x), _f32(inject)
+    p = x[:, None, :] * inject[:, :, None]
+    return bf(hyper + bf(p)) if ref else (hyper + p).astype(np.float32)

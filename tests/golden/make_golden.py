@@ -13,6 +13,9 @@ It writes
                                 (function ``moe``, imported unmodified) on a seeded synthetic layer at
                                 the reference's native shape (hidden 2560, ffn 640, top-10, BF16
                                 metadata, shared expert), E = 32 experts, T = 5 tokens.
+  hyper_connection.npz          the reference CPU oracle's hyper-connection arithmetic either side of the MoE layer
+                                (``hyper``, reference_numpy.py:99-106, called unmodified through a stand-in weights
+                                object, and the residual update of its layer loop, :237) on seeded inputs, T = 2.
 The inputs of the second fixture are regenerated from the seed by zerocool_b200.synth, so only the
 outputs are stored.
 """
@@ -115,6 +118,43 @@ def numpy_moe(reference):
     return dict(out=out.astype(np.float32), ids=idx.astype(np.int32), logits=logits.astype(np.float32))
 
 
+def load_reference_numpy(reference):
+    spec = importlib.util.spec_from_file_location("reference_numpy", reference / "scripts" / "qwen" / "reference_numpy.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def hyper_connection(reference):
+    """``hyper`` of the reference oracle with a stand-in weights object: unit norm weight, and seeded arrays in place of
+    the three small projections (their products are not part of the MoE path). Stored: the normalised streams, the
+    mixing gate (both recomputed with the module's own norm / sigmoid / bf), ``hyper``'s two outputs, and the residual
+    update bf(h + bf(out x injection)) of the layer loop evaluated with the module's bf."""
+    module = load_reference_numpy(reference)
+    rng = np.random.default_rng(20261125)
+    T, H = 2, 2560
+    streams = module.bf(rng.standard_normal((T, 4 * H)).astype(np.float32))
+    pre_gate = module.bf(rng.standard_normal((T, 4 * H)).astype(np.float32) * 2)
+    pre_inject = module.bf(rng.standard_normal((T, 4)).astype(np.float32) * 3)
+    low = module.bf(rng.standard_normal((T, 64)).astype(np.float32))
+
+    class Weights:
+        def get(self, name):
+            return np.ones(4 * H, np.float32)
+
+        def linear(self, name, x, floating=False):
+            return {"input_mix_weight_down": low, "input_mix_weight_up": pre_gate, "block_inject_weight": pre_inject}[name.rsplit(".", 1)[-1]]
+
+    w = Weights()
+    mixed, injection = module.hyper(w, "h", streams)
+    normed = module.norm(w, "h.hc_norm", streams, True)
+    gate = module.bf(module.sigmoid(pre_gate))
+    out = module.bf(rng.standard_normal((T, H)).astype(np.float32))
+    updated = module.bf(streams + module.bf(out[:, None, :] * injection[:, :, None]).reshape(T, 4 * H))
+    return dict(streams=streams, normed=normed.astype(np.float32), gate=gate.astype(np.float32), mixed=mixed.astype(np.float32),
+                injection=injection.astype(np.float32), out=out, updated=updated.astype(np.float32))
+
+
 def main():
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ZC_REFERENCE_ROOT")
     if not root:
@@ -122,7 +162,8 @@ def main():
     reference = Path(root)
     (HERE / "reference_known_answers.json").write_text(json.dumps(known_answers(reference), indent=1))
     np.savez_compressed(HERE / "numpy_moe_config0.npz", **numpy_moe(reference))
-    print("wrote", HERE / "reference_known_answers.json", "and", HERE / "numpy_moe_config0.npz")
+    np.savez_compressed(HERE / "hyper_connection.npz", **hyper_connection(reference))
+    print("wrote", HERE / "reference_known_answers.json", HERE / "numpy_moe_config0.npz", "and", HERE / "hyper_connection.npz")
 
 
 if __name__ == "__main__":

@@ -20,6 +20,9 @@ def round_bf16(v):
     return bf16_to_float(bf16_bits(np.asarray(v, np.float32)))
 
 
+REFERENCE_ROOT = os.environ.get("ZC_REFERENCE_ROOT", "")
+
+
 def test_router_matches_mlx_bit_patterns():
     """tests/test_qwen.cpp:798-826 — synthetic W/x formulas (:801-806), 16 captured fp32 bit patterns, chunk invariance."""
     g = KNOWN["router_mlx"]
@@ -197,9 +200,6 @@ def test_reference_numpy_moe_anchor():
     assert rel < 2e-3, rel
 
 
-REFERENCE_ROOT = os.environ.get("ZC_REFERENCE_ROOT", "")
-
-
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_ROOT, "scripts", "qwen")), reason="ZC_REFERENCE_ROOT does not name a reference tree")
 def test_committed_numpy_fixture_is_reproducible():
     """Where ZC_REFERENCE_ROOT names the reference tree, regenerating the fixture gives the committed bytes."""
@@ -209,6 +209,20 @@ def test_committed_numpy_fixture_is_reproducible():
     gold = np.load(os.path.join(GOLDEN, "numpy_moe_config0.npz"))
     for k in ("out", "ids", "logits"):
         assert np.array_equal(fresh[k], gold[k])
+
+
+def test_hyper_connection_steps_match_the_reference_numpy_oracle():
+    """hc_mix and hc_add (kernels/metal/qwen.metal:582-595) against the reference CPU oracle's hyper() and its residual
+    update (scripts/qwen/reference_numpy.py:99-106, :237), fixture tests/golden/hyper_connection.npz: bit for bit."""
+    g = np.load(os.path.join(GOLDEN, "hyper_connection.npz"))
+    T, H = g["out"].shape
+    assert np.array_equal(oracle.hc_mix(g["normed"].reshape(T, 4, H), g["gate"].reshape(T, 4, H)), g["mixed"])
+    assert np.array_equal(oracle.hc_add(g["streams"].reshape(T, 4, H), g["out"], g["injection"]).reshape(T, 4 * H), g["updated"])
+    if os.path.isdir(os.path.join(REFERENCE_ROOT, "scripts", "qwen")):
+        from pathlib import Path
+        from tests.golden import make_golden
+        fresh = make_golden.hyper_connection(Path(REFERENCE_ROOT))
+        assert all(np.array_equal(fresh[k], g[k]) for k in g.files)
 
 
 def test_permute_is_a_stable_counting_sort():

@@ -356,3 +356,77 @@ def test_graph_cache_follows_bias_changes_and_stays_bounded():
         m.stack(xi, oi)
         assert torch.equal(oi, plain)
     assert m.status() == 0
+
+
+def test_replay_of_a_traced_run_reproduces_it_bit_for_bit(tmp_path):
+    """Route trace -> replay: the ids of a three-layer run are written as a route trace, read back, and forced into
+    the layers (router for the scores, no top-k search): same bytes out. A foreign selection is honoured too."""
+    import torch
+    from zerocool_b200.route_trace import RouteTrace, read_route_trace
+    cfg = util.cfg2(experts=64, layers=3, max_tokens=16)
+    m = make(cfg)
+    for layer in range(cfg.layers):
+        m.synth_fill_layer(layer, SEED)
+    tokens = 7
+    xs = [device_x(m, synth.activations(cfg, SEED, layer, tokens)) for layer in range(cfg.layers)]
+    path = tmp_path / "routes.jsonl"
+    outs = []
+    with RouteTrace(path, {"test": "replay"}, cfg.layers, cfg.top_k) as trace:
+        trace.request_begin("r0", [], tokens)
+        trace.begin(1, 0, tokens, phase="prefill")
+        for layer in range(cfg.layers):
+            outs.append(m.moe(layer, xs[layer]).clone())
+            trace.routes(layer, 0, tokens, m.last_routing(tokens)["ids"])
+        trace.commit(tokens)
+        trace.request_end([], "stop")
+        trace.finish()
+    (recorded,) = read_route_trace(path, cfg.layers, cfg.top_k, cfg.experts)
+    for layer in range(cfg.layers):
+        ids = torch.from_numpy(recorded["routes"][layer]).cuda()
+        again = m.moe_routed(layer, xs[layer], ids)
+        assert torch.equal(again, outs[layer]), layer
+        assert np.array_equal(m.last_routing(tokens)["ids"], recorded["routes"][layer])
+    assert m.status() == 0
+    foreign = torch.from_numpy(np.stack([np.arange(t, t + cfg.top_k) % cfg.experts for t in range(tokens)]).astype(np.int32)).cuda()
+    other = m.moe_routed(0, xs[0], foreign)
+    routing = m.last_routing(tokens)
+    assert m.status() == 0 and bool(torch.isfinite(other).all()) and not torch.equal(other, outs[0])
+    assert np.allclose(routing["weights"].sum(-1), 1.0, atol=1e-5) and np.array_equal(routing["ids"], foreign.cpu().numpy())
+    logits = oracle.router_logits(synth.activations(cfg, SEED, 0, tokens), synth.router(cfg, SEED, 0), cfg.router_dtype)
+    picked = np.take_along_axis(logits, foreign.cpu().numpy().astype(np.int64), axis=1).astype(np.float64)
+    want_w = np.exp(picked - picked[:, :1])
+    assert np.allclose(routing["weights"], want_w / want_w.sum(-1, keepdims=True), rtol=1e-5)
+    bad = foreign.clone()
+    bad[0, 0] = cfg.experts + 3
+    m.moe_routed(0, xs[0], bad)
+    assert m.status() & 1
+
+
+def test_hyper_connection_mix_and_fused_residual_update():
+    """The steps either side of the layer. hc_mix on the device against the reference oracle's fixture, bit for bit; the
+    combine with hc_add as its epilogue against combine followed by the CPU hc_add - in reference arithmetic (BF16
+    boundaries) and in FP32 arithmetic, where the fused and the two-step results must be equal to the last bit."""
+    import torch
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "hyper_connection.npz"))
+    T, H = g["out"].shape
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).cuda()          # noqa: E731
+    for arith in (ARITH_REFERENCE, 0):
+        cfg = util.cfg0(arith=arith, act_dtype=F32, max_tokens=4)
+        m = make(cfg)
+        m.synth_fill_layer(0, SEED)
+        x = m.hc_mix(dev(g["normed"]), dev(g["gate"]))
+        assert np.array_equal(x.cpu().numpy(), g["mixed"])
+        streams, inject = dev(g["streams"]), dev(g["injection"])
+        fused = m.moe_hc(0, x, streams, inject).cpu().numpy().reshape(T, 4, H)
+        plain = m.moe(0, x).cpu().numpy()
+        assert m.status() == 0
+        want = oracle.hc_add(g["streams"].reshape(T, 4, H), plain, g["injection"], ref=arith == ARITH_REFERENCE)
+        assert np.array_equal(fused, want), arith
+    # against the CPU checker end to end (reference arithmetic): layer on the mixed input, then hc_add
+    cfg = util.cfg0(act_dtype=F32, max_tokens=4)
+    layer = oracle_layer(cfg, SEED, 0, g["mixed"], m.last_routing(T)["ids"])
+    want = oracle.hc_add(g["streams"].reshape(T, 4, H), layer["out"], g["injection"]).reshape(-1).astype(np.float64)
+    mref = make(cfg)
+    mref.synth_fill_layer(0, SEED)
+    got = mref.moe_hc(0, dev(g["mixed"]), streams, inject).cpu().numpy().reshape(-1).astype(np.float64)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-3

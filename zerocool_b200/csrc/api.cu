@@ -110,7 +110,9 @@ int check_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const 
 // One layer: router partials -> route + permutation (one launch) -> gate/up -> down -> combine.
 // With `next` set the combine also writes the normalised input of the following layer (the chained stack).
 // family: 0 = decode kernels, 1 = prefill kernels (tensor-core grouped GEMM), -1 = by token count.
-int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next = nullptr, int family = -1) {
+struct HcEpilogue { const float* hyper; const float* inject; float* out; };
+int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next = nullptr, int family = -1,
+              const HcEpilogue* hc = nullptr) {
     const Call c = make_call(m, layer, x, tokens, out);
     // The tensor-core family pays from about 24 rows per expert on (measured crossover with every expert active:
     // 30 rows per expert at hidden 2048, 20 at hidden 4096); below that the streaming kernels are faster.
@@ -120,7 +122,8 @@ int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* o
     if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
     if ((n = launch_route_permute(m, c, s, true, true)) < 0) return n; total += n;
     if ((n = family == 1 ? launch_experts_prefill(m, c, s) : launch_experts_decode(m, c, s)) < 0) return n; total += n;
-    if (next) n = launch_combine_norm(m, c, next, m->d.act_dtype, s);
+    if (hc) n = launch_combine_hc(m, c, hc->hyper, hc->inject, hc->out, s);
+    else if (next) n = launch_combine_norm(m, c, next, m->d.act_dtype, s);
     else n = launch_combine(m, c, s);
     if (n < 0) return n; total += n;
     return total;
@@ -382,6 +385,52 @@ static int forward_family(zc_moe* m, uint32_t layer, const void* x, uint32_t tok
     const int n = run_layer(m, layer, x, tokens, out, static_cast<cudaStream_t>(stream), nullptr, family);
     if (n < 0) return n;
     m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_hc_mix(zc_moe* m, const float* normed, const float* mix, uint32_t tokens, void* x, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (!tokens || tokens > m->d.max_tokens || !normed || !mix || !x) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
+    if (!aligned16({normed, mix, x})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
+    const int n = launch_hc_mix(m, normed, mix, tokens, m->d.hidden, x, m->d.act_dtype, static_cast<cudaStream_t>(stream));
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_forward_hc(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const float* hyper, const float* inject, float* hyper_out, void* stream) {
+    if (!m) return fail(nullptr, ZC_EINVAL, "null handle");
+    if (layer >= m->d.layers) return fail(m, ZC_ERANGE, "layer outside the model");
+    if (!tokens || tokens > m->d.max_tokens || !x || !hyper || !inject || !hyper_out) return fail(m, ZC_EINVAL, "token count outside 1..max_tokens or missing buffer");
+    if (!aligned16({x, hyper, inject, hyper_out})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    const size_t xb = size_t(tokens) * m->d.hidden * elem_bytes(m->d.act_dtype), hb = size_t(tokens) * 4 * m->d.hidden * 4;
+    if (overlaps(x, xb, hyper_out, hb)) return fail(m, ZC_EINVAL, "invalid or overlapping output");
+    if (cancelled(m)) return fail(m, ZC_ECANCELLED, "generation cancelled");
+    DeviceGuard guard(m->device);
+    const HcEpilogue hc{hyper, inject, hyper_out};
+    const int n = run_layer(m, layer, x, tokens, nullptr, static_cast<cudaStream_t>(stream), nullptr, -1, &hc);
+    if (n < 0) return n;
+    m->launches += n;
+    return ZC_OK;
+}
+
+int zc_moe_forward_routed(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const int32_t* ids, void* out, void* stream) {
+    int rc = check_call(m, layer, x, tokens, out);
+    if (rc != ZC_OK) return rc;
+    if (!ids) return fail(m, ZC_EINVAL, "invalid route selection buffers");
+    if (!aligned16({ids})) return fail(m, ZC_EINVAL, "buffers must be 16-byte aligned");
+    DeviceGuard guard(m->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const Call c = make_call(m, layer, x, tokens, out);
+    int n, total = 0;
+    if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;          // the scores of the recorded experts, and the shared gate
+    if ((n = launch_forced_weights(m, c, ids, s)) < 0) return n; total += n;
+    if ((n = launch_route_permute(m, c, s, false, true)) < 0) return n; total += n;
+    const bool wide = tokens >= 64 && uint64_t(tokens) * m->d.top_k >= 24ull * m->d.local_experts && m->pf_tiles;
+    if ((n = wide ? launch_experts_prefill(m, c, s) : launch_experts_decode(m, c, s)) < 0) return n; total += n;
+    if ((n = launch_combine(m, c, s)) < 0) return n; total += n;
+    m->launches += total;
     return ZC_OK;
 }
 

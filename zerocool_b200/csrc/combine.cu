@@ -149,6 +149,63 @@ __global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(Call c, void* 
     }
 }
 
+// Hyper-connection glue either side of the layer (the reference keeps four residual streams of width H).
+// hc_mix_kernel replaces hc_mix (kernels/metal/qwen.metal:582-588, dispatched by Model::hyper, src/engine/model.cpp:343):
+//   x[t, d] = bf( bf(bf(bf(p0 + p1) + p2) + p3) / 4 ),  p_h = bf(n[t, h, d] * mix[t, h, d])
+// - the layer's input, written in the activation dtype the router and the expert kernels read (a BF16 value either way).
+constexpr int HC_STREAMS = 4;
+__global__ void __launch_bounds__(256) hc_mix_kernel(const float* __restrict__ n, const float* __restrict__ mix, uint32_t H, void* __restrict__ x, int x_dtype) {
+    const uint32_t t = blockIdx.y, d = (blockIdx.x * 256 + threadIdx.x) * 4;
+    if (d >= H) return;
+    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int h = 0; h < HC_STREAMS; ++h) {
+        const size_t k = (size_t(t) * HC_STREAMS + h) * H + d;
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(n + k)), b = __ldcg(reinterpret_cast<const float4*>(mix + k));
+        sum[0] = bf_round(__fadd_rn(sum[0], bf_round(__fmul_rn(a.x, b.x))));
+        sum[1] = bf_round(__fadd_rn(sum[1], bf_round(__fmul_rn(a.y, b.y))));
+        sum[2] = bf_round(__fadd_rn(sum[2], bf_round(__fmul_rn(a.z, b.z))));
+        sum[3] = bf_round(__fadd_rn(sum[3], bf_round(__fmul_rn(a.w, b.w))));
+    }
+    float r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r[i] = bf_round(__fmul_rn(sum[i], 0.25f));
+    store4(x, x_dtype, size_t(t) * H + d, r);
+}
+
+// combine_hc_kernel: the combine with hc_add (qwen.metal:589-595, dispatched at src/engine/model.cpp:660-662) as its
+// epilogue: the layer output m[t, :] never goes to memory, the four residual streams are updated directly,
+//   out[t, h, d] = bf( hyper[t, h, d] + bf( m[t, d] * inject[t, h] ) )
+// (without the roundings outside the reference arithmetic; m is first rounded as the handle's output dtype would have stored it).
+template <int KMAX>
+__global__ void __launch_bounds__(COMBINE_THREADS) combine_hc_kernel(Call c, const float* __restrict__ hyper, const float* __restrict__ inject, float* __restrict__ out) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t col = (blockIdx.x * COMBINE_THREADS + threadIdx.x) * 4;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (col >= c.H) return;
+    float m[4];
+    combine_columns<KMAX>(c, t, col, m);
+    if (c.out_dtype != ZC_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) m[i] = bf_round(m[i]);
+    }
+#pragma unroll
+    for (int h = 0; h < HC_STREAMS; ++h) {
+        const size_t k = (size_t(t) * HC_STREAMS + h) * c.H + col;
+        const float4 o = __ldcg(reinterpret_cast<const float4*>(hyper + k));
+        const float inj = __ldcg(inject + size_t(t) * HC_STREAMS + h);
+        const float base[4] = {o.x, o.y, o.z, o.w};
+        float r[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float p = __fmul_rn(m[i], inj);
+            r[i] = c.ref ? bf_round(__fadd_rn(base[i], bf_round(p))) : __fadd_rn(base[i], p);
+        }
+        *reinterpret_cast<float4*>(out + k) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+}
+
 // The BF16-staged activations of the reference arithmetic, element by element (parity hook).
 __global__ void activation_table_kernel(const float* __restrict__ x, uint32_t n, float* __restrict__ sigmoid_out, float* __restrict__ silu_out) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -163,6 +220,23 @@ __global__ void activation_table_kernel(const float* __restrict__ x, uint32_t n,
 int launch_activation_table(const float* x, uint32_t n, float* sigmoid_out, float* silu_out, cudaStream_t s) {
     activation_table_kernel<<<(n + 127) / 128, 128, 0, s>>>(x, n, sigmoid_out, silu_out);
     return check_launch(nullptr, "activation table");
+}
+
+int launch_hc_mix(zc_moe* m, const float* n, const float* mix, uint32_t T, uint32_t H, void* x, int x_dtype, cudaStream_t s) {
+    Timed t(m, s, KERNEL_COMBINE);
+    hc_mix_kernel<<<dim3((H / 4 + 255) / 256, T), 256, 0, s>>>(n, mix, H, x, x_dtype);
+    const int rc = check_launch(m, "hc_mix");
+    return rc < 0 ? rc : 1;
+}
+
+int launch_combine_hc(zc_moe* m, const Call& c, const float* hyper, const float* inject, float* out, cudaStream_t s) {
+    if (c.K > MAX_K) return fail(m, ZC_EINVAL, "top_k above 32");
+    const dim3 grid((c.H / 4 + COMBINE_THREADS - 1) / COMBINE_THREADS, c.T);
+    int rc;
+    { Timed t(m, s, KERNEL_COMBINE); auto k = c.K <= 8 ? combine_hc_kernel<8> : c.K <= 16 ? combine_hc_kernel<16> : combine_hc_kernel<32>;
+      launch_chained(m, KERNEL_COMBINE, k, grid, dim3(COMBINE_THREADS), 0, s, nullptr, 0, c, hyper, inject, out);
+      rc = check_launch(m, "combine + hc_add"); }
+    return rc < 0 ? rc : 1;
 }
 
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s) {

@@ -186,6 +186,7 @@ int launch_router(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s);
 uint32_t router_rows_padded(const zc_moe_desc& d);
 int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute);
+int launch_forced_weights(zc_moe* m, const Call& c, const int32_t* forced, cudaStream_t s);
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s);
 bool prefill_supported(const zc_moe_desc& d);
@@ -198,6 +199,8 @@ int launch_ep_send(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_ep_receive(zc_moe* m, cudaStream_t s);
 int launch_ep_return(zc_moe* m, cudaStream_t s);
 int launch_ep_returned(zc_moe* m, cudaStream_t s);
+int launch_hc_mix(zc_moe* m, const float* n, const float* mix, uint32_t T, uint32_t H, void* x, int x_dtype, cudaStream_t s);
+int launch_combine_hc(zc_moe* m, const Call& c, const float* hyper, const float* inject, float* out, cudaStream_t s);
 int launch_activation_table(const float* x, uint32_t n, float* sigmoid_out, float* silu_out, cudaStream_t s);
 int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cudaStream_t s);
 int launch_synth_layer(zc_moe* m, uint32_t layer, uint64_t seed, cudaStream_t s);

@@ -112,6 +112,45 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, uint32_t t, uint
     if (bad) atomicOr(a.status, ZC_STATUS_INVALID_ROUTE);
 }
 
+// Weights for a selection that is given, not searched (replay of a recorded route): the same renormalised softmax
+// over the K selected scores, with the same lane layout and summation order as route_token. The first id of a token
+// plays the role of rank 0 (its score is subtracted before the exponential). ids outside [0, E) get weight 0 and
+// raise the status bit.
+__global__ void __launch_bounds__(ROUTE_THREADS) forced_weights_kernel(const float* __restrict__ logits, const int32_t* __restrict__ forced,
+                                                                        int32_t* __restrict__ ids, float* __restrict__ weights,
+                                                                        uint32_t T, uint32_t E, uint32_t K, uint32_t* status) {
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32, t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= T) return;
+    const float ninf = __int_as_float(0xff800000);
+    const int32_t top_id = forced[size_t(t) * K];
+    const float top = top_id >= 0 && uint32_t(top_id) < E ? __ldcg(logits + size_t(t) * E + top_id) : ninf;
+    float values[4], sum = 0.0f;
+    int32_t id[4];
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t j = lane * 4 + i;
+        values[i] = 0.0f; id[i] = -1;
+        if (j < K) {
+            id[i] = forced[size_t(t) * K + j];
+            const bool valid = id[i] >= 0 && uint32_t(id[i]) < E;
+            bad |= !valid;
+            if (!valid) id[i] = -1;
+            values[i] = valid ? expf(__ldcg(logits + size_t(t) * E + id[i]) - top) : 0.0f;
+        }
+        sum = __fadd_rn(sum, values[i]);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, off));
+    const float inverse = __fdiv_rn(1.0f, sum);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t j = lane * 4 + i;
+        if (j < K) { ids[size_t(t) * K + j] = id[i]; weights[size_t(t) * K + j] = __fmul_rn(values[i], inverse); }
+    }
+    if (bad) atomicOr(status, ZC_STATUS_INVALID_ROUTE);
+}
+
 constexpr int PERMUTE_THREADS = 1024;
 constexpr int PERMUTE_CACHE = 4;          // 32-slot chunks of a warp's range kept in registers between the two passes
 constexpr int PERMUTE_OWN = 4;            // consecutive experts owned by one thread in the scan (E <= 4 x threads)
@@ -312,6 +351,14 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
 }
 
 }  // namespace
+
+int launch_forced_weights(zc_moe* m, const Call& c, const int32_t* forced, cudaStream_t s) {
+    if (c.K > 32) return fail(m, ZC_EINVAL, "route: top_k above 32");
+    Timed t(m, s, KERNEL_ROUTE);
+    forced_weights_kernel<<<(c.T + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_THREADS, 0, s>>>(c.logits, forced, c.ids, c.weights, c.T, c.E, c.K, c.status);
+    const int rc = check_launch(m, "forced route weights");
+    return rc < 0 ? rc : 1;
+}
 
 int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute) {
     int launched = 0;

@@ -28,7 +28,7 @@ class Cancelled(RuntimeError):
 EXPORTS = [
     "zc_moe_desc_finalize", "zc_moe_create", "zc_moe_destroy", "zc_moe_last_error", "zc_last_error",
     "zc_moe_load_layer", "zc_moe_set_router_bias", "zc_moe_layer_buffers", "zc_moe_router", "zc_router_logits_noalloc", "zc_moe_route", "zc_moe_permute",
-    "zc_moe_combine", "zc_activation_bf16", "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_ep_dispatch", "zc_moe_ep_experts", "zc_moe_ep_combine",
+    "zc_moe_combine", "zc_activation_bf16", "zc_moe_decode", "zc_moe_prefill", "zc_moe_forward", "zc_moe_forward_routed", "zc_moe_hc_mix", "zc_moe_forward_hc", "zc_moe_ep_dispatch", "zc_moe_ep_experts", "zc_moe_ep_combine",
     "zc_moe_ep_export", "zc_moe_ep_attach", "zc_moe_ep_layer", "zc_moe_ep_send", "zc_moe_ep_process", "zc_moe_ep_finish", "zc_moe_ep_stack", "zc_moe_ep_stack_eager",
     "zc_moe_forward_host", "zc_moe_forward_host_async", "zc_moe_set_cancel", "zc_moe_stack",
     "zc_moe_stack_host", "zc_moe_set_option", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
@@ -81,6 +81,9 @@ def load_library():
     lib.zc_activation_bf16.argtypes = [vp, u32, vp, vp, vp]
     for name in ("zc_moe_decode", "zc_moe_prefill", "zc_moe_forward"):
         getattr(lib, name).argtypes = [vp, u32, vp, u32, vp, vp]
+    lib.zc_moe_forward_routed.argtypes = [vp, u32, vp, u32, vp, vp, vp]
+    lib.zc_moe_hc_mix.argtypes = [vp, vp, vp, u32, vp, vp]
+    lib.zc_moe_forward_hc.argtypes = [vp, u32, vp, u32, vp, vp, vp, vp]
     lib.zc_moe_ep_dispatch.argtypes = [vp, u32, vp, u32, vp, vp, vp]
     lib.zc_moe_ep_experts.argtypes = [vp, u32, vp, vp, u32, vp, vp]
     lib.zc_moe_ep_combine.argtypes = [vp, u32, vp, u32, vp, vp, vp]
@@ -273,6 +276,33 @@ class Moe:
     def moe(self, layer, x, out=None):
         """Model::moe(x, layer, tokens): out [T, H]."""
         return self._run(self.lib.zc_moe_forward, layer, x, out)
+
+    def hc_mix(self, normed, mix):
+        """Model::hyper's hc_mix: normed, mix fp32 [T, 4, H] -> the layer input x [T, H] in the activation dtype."""
+        torch = self._torch
+        tokens = normed.shape[0]
+        x = torch.empty((tokens, self.cfg.hidden), dtype=self.act_torch, device=self.device)
+        self._check(self.lib.zc_moe_hc_mix(self._h, _ptr(normed), _ptr(mix), tokens, _ptr(x), self._stream()))
+        return x
+
+    def moe_hc(self, layer, x, hyper, inject, out=None):
+        """Model::moe followed by hc_add in one pass: hyper fp32 [T, 4, H], inject fp32 [T, 4] -> the updated streams."""
+        torch = self._torch
+        if out is None:
+            out = torch.empty_like(hyper)
+        self._check(self.lib.zc_moe_forward_hc(self._h, layer, _ptr(x), x.shape[0], _ptr(hyper), _ptr(inject), _ptr(out), self._stream()))
+        return out
+
+    def moe_routed(self, layer, x, ids, out=None):
+        """Model::moe with a recorded expert selection (ids int32 [T, K] on the device) instead of the top-k search."""
+        torch = self._torch
+        tokens = x.shape[0]
+        if ids.shape != (tokens, self.cfg.top_k) or ids.dtype != torch.int32:
+            raise ValueError("invalid route selection buffers")
+        if out is None:
+            out = torch.empty((tokens, self.cfg.hidden), dtype=self.out_torch, device=self.device)
+        self._check(self.lib.zc_moe_forward_routed(self._h, layer, _ptr(x), tokens, _ptr(ids), _ptr(out), self._stream()))
+        return out
 
     def decode(self, layer, x, out=None):
         return self._run(self.lib.zc_moe_decode, layer, x, out)
