@@ -548,15 +548,16 @@ int launch_router_long(zc_moe* m, const Call& c, cudaStream_t s) {
 uint32_t router_rows_padded(const zc_moe_desc& d) { return (d.experts + (d.has_shared ? 1 : 0) + ROW_TILE_PAD - 1) / ROW_TILE_PAD * ROW_TILE_PAD; }
 
 int launch_router_partial(zc_moe* m, const Call& c, cudaStream_t s) {
-    // Cluster form for short batches, whole-K tiles for long ones (either returns 0 when the device cannot host it or
-    // the tile does not fit: fall through to the global-memory form).
+    // Cluster form for short batches, whole-K tiles for long ones (2048 tokens: 178 us against 237 us for the
+    // global-memory form; 8192: 650 against 893), the global-memory form in between (256 tokens at hidden 4096: 77 us
+    // against 205 us for 36 whole-K tiles) and whenever the device cannot host the others.
     {
         int n = 0;
         // Up to 128 tokens small tiles win on latency: at 64 tokens, 544 CTAs of 16 tokens x 32 rows measured 19 us
         // against 21 us (32 x 32) and 25 us (32 x 64, whose 144 large CTAs do not all find a cluster slot in the first wave).
         if (c.T <= 8) n = launch_router_cluster<8, 1>(m, c, s);
         else if (c.T <= ZC_ROUTER_SMALL_T) n = launch_router_cluster<16, 1>(m, c, s);
-        else n = launch_router_long(m, c, s);      // long batches: whole-K tiles, partials never leave the registers
+        else if (size_t((c.T + 63) / 64) * ((c.E + 64) / 64) >= 144) n = launch_router_long(m, c, s);      // enough whole-K tiles to fill the SMs
         if (n != 0) return n;
     }
     const uint32_t part = c.H / 16;

@@ -16,7 +16,7 @@ import numpy as np
 from .records import ARITH_FP32, ARITH_REFERENCE, BF16, F16, F32, MoeConfig
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libzc_moe.so")
+LIB_PATH = os.environ.get("ZC_MOE_LIB") or os.path.join(_HERE, "libzc_moe.so")      # ZC_MOE_LIB: another build of the library
 
 ZC_OK, ZC_EINVAL, ZC_ERANGE, ZC_EEXEC, ZC_ECANCELLED, ZC_ENOMEM = 0, -1, -2, -3, -4, -5
 STATUS_INVALID_ROUTE, STATUS_TIMEOUT, STATUS_RANGE = 1, 2, 4
