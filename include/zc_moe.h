@@ -88,7 +88,10 @@ typedef struct zc_moe_desc {
     uint8_t  router_dtype;   /* router weight and shared-gate vector: ZC_F32 or ZC_BF16 */
     uint8_t  has_shared;     /* layer has a shared expert with a sigmoid gate */
     uint8_t  arith;          /* ZC_ARITH_* */
-    uint8_t  reserved[6];
+    uint8_t  shared_gate_bits, shared_up_bits, shared_down_bits;   /* shared expert's record: 4 or 8 per projection; 0 = as the routed
+                                * experts. The reference's mixed artifact keeps routed experts Q4 and the shared expert Q8
+                                * (src/engine/metal.mm:1103-1123, docs/qwen_engine.md:261-266). */
+    uint8_t  reserved[3];
     uint64_t record_bytes;   /* payload of one record = sum over projections of codes+scales+biases */
     uint64_t record_stride;  /* distance between records in a layer file (>= record_bytes) */
 } zc_moe_desc;
@@ -111,7 +114,8 @@ const char* zc_last_error(void);
  * Record layout (expert_linear, src/engine/metal.mm:1124-1129, generalised): projections gate, up, down
  * in that order, each [codes | scales | biases]; codes row-major [N, K*bits/8] (Q4: uint32 words of 8
  * nibbles, k ascending from the least significant nibble); scales/biases [N, K/group] 16-bit.
- * router_w: [E, H]; shared_record: one record or NULL; shared_gate_w: [1, H] or NULL.
+ * router_w: [E, H]; shared_record: one record in the same layout with the shared expert's own bit widths
+ * (shared_*_bits) or NULL; shared_gate_w: [1, H] or NULL.
  * Any pointer may be NULL to leave that tensor as it is. */
 int zc_moe_load_layer(zc_moe* moe, uint32_t layer, const void* records, uint32_t first_expert, uint32_t count,
                       const void* router_w, const void* shared_record, const void* shared_gate_w);

@@ -26,7 +26,8 @@ class Desc(ctypes.Structure):
         ("gate_bits", ctypes.c_uint8), ("up_bits", ctypes.c_uint8), ("down_bits", ctypes.c_uint8),
         ("q8_signed", ctypes.c_uint8), ("meta_dtype", ctypes.c_uint8), ("act_dtype", ctypes.c_uint8),
         ("out_dtype", ctypes.c_uint8), ("router_dtype", ctypes.c_uint8), ("has_shared", ctypes.c_uint8),
-        ("arith", ctypes.c_uint8), ("reserved", ctypes.c_uint8 * 6),
+        ("arith", ctypes.c_uint8),
+        ("shared_gate_bits", ctypes.c_uint8), ("shared_up_bits", ctypes.c_uint8), ("shared_down_bits", ctypes.c_uint8), ("reserved", ctypes.c_uint8 * 3),
         ("record_bytes", ctypes.c_uint64), ("record_stride", ctypes.c_uint64),
     ]
 
@@ -161,6 +162,8 @@ def set_router_bias(bias):
 def moe_layer(cfg, records, router_w, x, shared_record=None, shared_gate_w=None, want_intermediates=False, router_bias=None):
     """Whole layer. ``records``: sequence of E uint8 arrays (or None for experts known to be unselected),
     or one [E, stride] uint8 array. x: fp32 [T,H]. Returns dict(out, ids, weights[, logits, expert_out, shared, gate])."""
+    if cfg.get("has_shared") and any(cfg.get(k) for k in ("shared_gate_bits", "shared_up_bits", "shared_down_bits")):
+        return _moe_layer_mixed(cfg, records, router_w, x, shared_record, shared_gate_w, want_intermediates, router_bias)
     d = make_desc(cfg)
     x = _f32(x).reshape(-1, d.hidden)
     T = x.shape[0]
@@ -226,3 +229,23 @@ def hc_add(hyper, x, inject, ref=True):
     hyper, x, inject = _f32(hyper), _f32(x), _f32(inject)
     p = x[:, None, :] * inject[:, :, None]
     return bf(hyper + bf(p)) if ref else (hyper + p).astype(np.float32)
+
+
+def _moe_layer_mixed(cfg, records, router_w, x, shared_record, shared_gate_w, want_intermediates, router_bias):
+    """A layer whose shared expert's record has its own bit widths (the reference's mixed artifact, src/engine/metal.mm:1103-1123):
+    the routed part as a layer without shared expert, the shared expert through `expert` with the shared bit widths, the
+    gate scalar as router row E (src/engine/model.cpp:482-485), then the fixed-order combine."""
+    routed_cfg = dict(cfg, has_shared=0, shared_gate_bits=0, shared_up_bits=0, shared_down_bits=0)
+    res = moe_layer(routed_cfg, records, router_w, x, want_intermediates=True, router_bias=router_bias)
+    shared_cfg = dict(routed_cfg, gate_bits=cfg.get("shared_gate_bits") or cfg["gate_bits"], up_bits=cfg.get("shared_up_bits") or cfg["up_bits"],
+                      down_bits=cfg.get("shared_down_bits") or cfg["down_bits"])
+    x = _f32(x).reshape(-1, cfg["hidden"])
+    shared = expert(shared_cfg, shared_record, x)[1]
+    gate = router_logits(x, np.ascontiguousarray(shared_gate_w), cfg.get("router_dtype", F32))[:, 0]
+    if cfg.get("arith", 0) == ARITH_REFERENCE:
+        gate = bf(gate)
+    out = combine(dict(cfg, has_shared=1), res["expert_out"], res["weights"], shared, gate)
+    full = dict(out=out, ids=res["ids"], weights=res["weights"])
+    if want_intermediates:
+        full.update(logits=res["logits"], expert_out=res["expert_out"], shared=shared, gate=gate)
+    return full

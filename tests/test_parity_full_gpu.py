@@ -430,3 +430,27 @@ def test_hyper_connection_mix_and_fused_residual_update():
     mref.synth_fill_layer(0, SEED)
     got = mref.moe_hc(0, dev(g["mixed"]), streams, inject).cpu().numpy().reshape(-1).astype(np.float64)
     assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-3
+
+
+@pytest.mark.parametrize("family,tokens", [("decode", 9), ("prefill", 200)])
+def test_mixed_artifact_routed_q4_shared_q8_in_one_handle(family, tokens):
+    """The reference's mixed artifact (src/engine/metal.mm:1103-1123): routed experts Q4, the layer's shared expert Q8
+    with unsigned codes, one handle (shared_*_bits). Both kernel families against the CPU checker."""
+    cfg = util.cfg2(experts=64, shared_gate_bits=8, shared_up_bits=8, shared_down_bits=8, q8_signed=0, max_tokens=256)
+    assert cfg.shared_cfg().record_bytes > cfg.record_bytes
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    got = m.read_layer_tensor(0, "shared_record", cfg.shared_cfg().record_bytes)
+    assert np.array_equal(got, synth.record(cfg, SEED, 0, synth.SHARED_EXPERT)[:cfg.shared_cfg().record_bytes])      # generator twins agree on the Q8 layout
+    shared = util.asymmetric_record(cfg.shared_cfg(), SEED, 0, synth.SHARED_EXPERT, np.random.default_rng(3), spread=0.3)    # centred u8 weights
+    m.load_layer(0, shared_record=shared)
+    x = synth.activations(cfg, SEED, 0, tokens)
+    out = getattr(m, family)(0, device_x(m, x)).float().cpu().numpy()
+    ids = m.last_routing(tokens)["ids"]
+    assert m.status() == 0
+    want = oracle.moe_layer(cfg.as_dict(), util.selected_records(cfg, SEED, 0, ids), synth.router(cfg, SEED, 0), x,
+                            shared_record=shared, shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    assert np.array_equal(ids, want["ids"])
+    err = util.rel_max_error(out, want["out"])
+    print("mixed artifact,", family, "max-abs error / RMS:", err)
+    assert err <= TOL, err

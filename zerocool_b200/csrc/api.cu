@@ -54,6 +54,8 @@ int validate_desc(const zc_moe_desc& d, std::string& why) {
     if (d.top_k > 32 || d.top_k > d.experts) return bad("top_k must be at most 32 and at most experts");
     for (uint8_t b : {d.gate_bits, d.up_bits, d.down_bits}) if (b != 4 && b != 8) return bad("unsupported affine matrix geometry: bits must be 4 or 8");
     if (d.gate_bits != d.up_bits) return bad("fused gate/up requires matching affine matrices");
+    for (uint8_t b : {d.shared_gate_bits, d.shared_up_bits, d.shared_down_bits}) if (b != 0 && b != 4 && b != 8) return bad("unsupported affine matrix geometry: shared bits must be 0, 4 or 8");
+    { const zc_moe_desc sd = shared_desc_of(d); if (sd.gate_bits != sd.up_bits) return bad("fused gate/up requires matching affine matrices (shared expert)"); }
     if (d.meta_dtype != ZC_BF16 && d.meta_dtype != ZC_F16) return bad("metadata dtype must be BF16 or F16");
     if (d.act_dtype != ZC_BF16 && d.act_dtype != ZC_F32) return bad("activation dtype must be BF16 or F32");
     if (d.out_dtype != ZC_BF16 && d.out_dtype != ZC_F32) return bad("output dtype must be BF16 or F32");
@@ -183,7 +185,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
         uint8_t* rw = nullptr; A(&rw, E * H * elem_bytes(d.router_dtype)); L.router_w = rw;
         A(&L.router_bias, E * 4);
         if (d.has_shared) {
-            A(&L.shared_record, d.record_stride);
+            A(&L.shared_record, (record_bytes_of(shared_desc_of(d)) + 16383) / 16384 * 16384);
             uint8_t* gw = nullptr; A(&gw, H * elem_bytes(d.router_dtype)); L.shared_gate_w = gw;
         }
     }
@@ -240,6 +242,11 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     c.H = d.hidden; c.F = d.ffn; c.E = d.experts; c.K = d.top_k;
     c.first_expert = d.first_expert; c.local_experts = d.local_experts; c.record_stride = d.record_stride;
     c.gate = projection_of(d, 0); c.up = projection_of(d, 1); c.down = projection_of(d, 2);
+    {
+        const zc_moe_desc sd = shared_desc_of(d);
+        c.sgate = projection_of(sd, 0); c.sup = projection_of(sd, 1); c.sdown = projection_of(sd, 2);
+        c.shared_split = d.has_shared && (sd.gate_bits != d.gate_bits || sd.up_bits != d.up_bits || sd.down_bits != d.down_bits);
+    }
     c.act_dtype = d.act_dtype; c.out_dtype = d.out_dtype; c.meta_f16 = d.meta_dtype == ZC_F16; c.router_dtype = d.router_dtype;
     c.has_shared = d.has_shared; c.ref = d.arith == ZC_ARITH_REFERENCE; c.q8_signed = d.q8_signed;
     if (m->ep_rows_cap) {
@@ -284,7 +291,7 @@ int zc_moe_load_layer(zc_moe* m, uint32_t layer, const void* records, uint32_t f
     if (router_w && (e = cudaMemcpy(L.router_w, router_w, size_t(d.experts) * d.hidden * elem_bytes(d.router_dtype), cudaMemcpyDefault)) != cudaSuccess)
         return cuda_fail(m, e, "copy of router weight");
     if ((shared_record || shared_gate_w) && !d.has_shared) return fail(m, ZC_EINVAL, "layer has no shared expert");
-    if (shared_record && (e = cudaMemcpy(L.shared_record, shared_record, d.record_bytes, cudaMemcpyDefault)) != cudaSuccess)
+    if (shared_record && (e = cudaMemcpy(L.shared_record, shared_record, record_bytes_of(shared_desc_of(d)), cudaMemcpyDefault)) != cudaSuccess)
         return cuda_fail(m, e, "copy of shared expert record");
     if (shared_gate_w && (e = cudaMemcpy(L.shared_gate_w, shared_gate_w, size_t(d.hidden) * elem_bytes(d.router_dtype), cudaMemcpyDefault)) != cudaSuccess)
         return cuda_fail(m, e, "copy of shared gate weight");

@@ -66,6 +66,19 @@ inline Projection projection_of(const zc_moe_desc& d, int p) {
     return r;
 }
 
+// The descriptor of the shared expert's record: the routed geometry with the shared expert's own bit widths.
+inline zc_moe_desc shared_desc_of(const zc_moe_desc& d) {
+    zc_moe_desc s = d;
+    if (d.shared_gate_bits) s.gate_bits = d.shared_gate_bits;
+    if (d.shared_up_bits) s.up_bits = d.shared_up_bits;
+    if (d.shared_down_bits) s.down_bits = d.shared_down_bits;
+    return s;
+}
+inline uint64_t record_bytes_of(const zc_moe_desc& d) {
+    const Projection pr = projection_of(d, 2);
+    return pr.biases + uint64_t(pr.N) * (pr.K / d.group) * 2;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Handle
 // ---------------------------------------------------------------------------------------------
@@ -104,6 +117,8 @@ struct Call {
     uint32_t first_expert, local_experts;
     uint64_t record_stride;
     Projection gate, up, down;
+    Projection sgate, sup, sdown;   // the shared expert's record (equal to gate, up, down unless shared_split)
+    uint8_t shared_split;           // the shared record has other bit widths: it runs as launches of its own
     uint8_t act_dtype, out_dtype, meta_f16, router_dtype, has_shared, ref, q8_signed;
     uint8_t quiet_drop;       // the permutation drops ids outside [0, E) without raising the status bit (unused row slots of a receive area)
 };

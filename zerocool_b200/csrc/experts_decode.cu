@@ -576,7 +576,28 @@ int dispatch_expert(zc_moe* m, const Call& c, uint32_t items, uint32_t tpw, bool
 
 }  // namespace
 
+static int launch_experts_decode_one(zc_moe* m, const Call& c, cudaStream_t s);
+
+// A shared expert whose record has other bit widths than the routed experts' (the reference's mixed artifact: routed Q4,
+// shared Q8) cannot share a launch with them - the code width is a template parameter - so it runs as launches of its
+// own over the same buffers (its rows of hbuf and shared_out are disjoint from the routed ones).
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s) {
+    if (!(c.has_shared && c.shared_split)) return launch_experts_decode_one(m, c, s);
+    int total = 0, n;
+    if (c.items != m->empty_items) {
+        Call routed = c;
+        routed.has_shared = 0;
+        if ((n = launch_experts_decode_one(m, routed, s)) < 0) return n;
+        total += n;
+    }
+    Call shared = c;
+    shared.gate = c.sgate; shared.up = c.sup; shared.down = c.sdown; shared.shared_split = 0;
+    shared.items = m->empty_items; shared.counters = m->zero_counters;
+    if ((n = launch_experts_decode_one(m, shared, s)) < 0) return n;
+    return total + n;
+}
+
+static int launch_experts_decode_one(zc_moe* m, const Call& c, cudaStream_t s) {
     const uint32_t routed = c.T * c.K < c.local_experts ? c.T * c.K : c.local_experts;
     const uint32_t items = routed + (c.has_shared ? (c.T + NTOK - 1) / NTOK : 0);
     // A BF16 activation is exact as one FP16 term; an FP32 activation needs two, except under the

@@ -21,8 +21,8 @@
 //     own FP16 metadata) times B' = [0 .. | S_0..] with S_g = sum of the token's activations in group g,
 //     carried as two FP16 terms (hi, lo); the zero half meets the scales, so the tile is used as it lies in the record. It runs as extra stages after the K loop (K' in blocks of 64, hi then lo)
 //     and is added with scale 1.
-//   8-bit codes (u8 as in the reference's affine8_dot, qwen.metal:112-125, or int8) take the same path with the
-//   token rows in natural k order.
+//   8-bit codes (u8 as in the reference's affine8_dot, qwen.metal:112-125, or int8) take the same path: two byte
+//   permutes bring them into the k order the token rows are stored in.
 //   NMAT = 2: gate and up tiles of the same 128 rows sit side by side in TMEM; the final epilogue applies
 //             SwiGLU and stores h as FP16 in the k order the second launch consumes.
 //   NMAT = 1: the down projection; the final epilogue writes FP32 rows at the slots' router positions.
@@ -41,6 +41,7 @@
 // Every wait is bounded: after ~2^22 polls a role sets ZC_STATUS_TIMEOUT, raises the CTA's abort flag and
 // leaves its loop; the CTA then frees its TMEM and exits.
 #include "common.cuh"
+#include <type_traits>
 
 namespace zc {
 namespace {
@@ -155,6 +156,14 @@ __device__ __forceinline__ uint2 pf_dequant_q8_word(uint32_t w, bool is_signed) 
     return make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
 }
 
+// Eight 8-bit codes (two words, k0..k3 and k4..k7) -> four half2 in the order every B tile of this file uses:
+// (k0,k4) (k1,k5) (k2,k6) (k3,k7). Two byte permutes interleave the words first.
+__device__ __forceinline__ uint4 pf_dequant_q8_block(uint32_t lo, uint32_t hi, bool is_signed) {
+    const uint2 a = pf_dequant_q8_word(__byte_perm(lo, hi, 0x5140), is_signed);      // bytes k0, k4, k1, k5
+    const uint2 b = pf_dequant_q8_word(__byte_perm(lo, hi, 0x7362), is_signed);      // bytes k2, k6, k3, k7
+    return make_uint4(a.x, a.y, b.x, b.y);
+}
+
 // Tile list: one entry per (expert with work, block of PF_NMAX of its rows), the shared expert's token
 // blocks first. One CTA of 1024 threads; experts <= 1024.
 __global__ void __launch_bounds__(1024) pf_tiles_kernel(const int32_t* __restrict__ offsets, uint32_t E, uint32_t first_expert, uint32_t local_experts,
@@ -186,7 +195,7 @@ __global__ void __launch_bounds__(1024) pf_tiles_kernel(const int32_t* __restric
 
 // x [T, H] (bf16 or fp32) -> FP16 [T, H] with every block of eight k values stored in pf_pos8 order: the
 // B operand of the gate/up launch, copied into shared memory with plain 16-byte cp.async.
-__global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, __half* __restrict__ xp, size_t blocks, uint32_t* __restrict__ status, bool natural) {
+__global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, __half* __restrict__ xp, size_t blocks, uint32_t* __restrict__ status) {
     const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= blocks) return;
     float v[8];
@@ -203,7 +212,7 @@ __global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, _
     __half h[8];
     bool out_of_range = false;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { out_of_range |= fabsf(v[j]) > 65504.0f; h[natural ? j : pf_pos8(j)] = __float2half_rn(v[j]); }
+    for (int j = 0; j < 8; ++j) { out_of_range |= fabsf(v[j]) > 65504.0f; h[pf_pos8(j)] = __float2half_rn(v[j]); }
     *reinterpret_cast<uint4*>(xp + i * 8) = *reinterpret_cast<uint4*>(h);
     if (out_of_range) atomicOr(status, ZC_STATUS_RANGE);
 }
@@ -265,7 +274,7 @@ struct PfSmem {
 template <int NMAT, int BITS, bool META_F16, int D>
 __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(Call c, const PfTile* __restrict__ tiles, const int32_t* __restrict__ ntiles,
                                                                  const __half* __restrict__ bsrc, const __half* __restrict__ bsum,
-                                                                 __half* __restrict__ hdst, uint32_t h_natural) {
+                                                                 __half* __restrict__ hdst, uint32_t tile_filter) {
     using S = PfSmem<NMAT, BITS>;
     constexpr uint32_t PF_RAW = D + 1, PF_BS = D + PF_STAGES;
     extern __shared__ uint8_t pf_raw_smem[];
@@ -276,6 +285,7 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
     __shared__ long long drow[PF_NMAX];           // destination element offset of each token row
     if (blockIdx.y >= uint32_t(*ntiles)) return;
     const PfTile tile = tiles[blockIdx.y];
+    if ((tile_filter == 1 && tile.shared) || (tile_filter == 2 && !tile.shared)) return;
     const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
     // K stages, then the correction stages: K' = 2 G in blocks of at most 64, each as a hi and a lo term
     const uint32_t kb = 2 * G < 64 ? 2 * G : 64, nblk = 2 * G / kb, nst = G + 2 * nblk;
@@ -430,10 +440,8 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {             // 16 bytes = 16 codes = two k chunks of eight
                             const uint4 w = *reinterpret_cast<const uint4*>(at(src + i * 16));
-                            const uint2 a = pf_dequant_q8_word(w.x, q8s), b = pf_dequant_q8_word(w.y, q8s);
-                            const uint2 e = pf_dequant_q8_word(w.z, q8s), f = pf_dequant_q8_word(w.w, q8s);
-                            *reinterpret_cast<uint4*>(at(dst + (2 * i) * 128)) = make_uint4(a.x, a.y, b.x, b.y);
-                            *reinterpret_cast<uint4*>(at(dst + (2 * i + 1) * 128)) = make_uint4(e.x, e.y, f.x, f.y);
+                            *reinterpret_cast<uint4*>(at(dst + (2 * i) * 128)) = pf_dequant_q8_block(w.x, w.y, q8s);
+                            *reinterpret_cast<uint4*>(at(dst + (2 * i + 1) * 128)) = pf_dequant_q8_block(w.z, w.w, q8s);
                         }
                     }
                 }
@@ -550,7 +558,7 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
                         if constexpr (NMAT == 2) {
                             const float u = acc[NMAT - 1][h][j];
                             const float hv = (g * sigmoid_f(g)) * u;
-                            hdst[drow[t] + (h_natural ? row : (row & ~7u) + pf_pos8(row & 7))] = __float2half_rn(hv);
+                            hdst[drow[t] + (row & ~7u) + pf_pos8(row & 7)] = __float2half_rn(hv);
                         } else {
                             out_base[drow[t] + row] = g;
                         }
@@ -638,7 +646,7 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
 template <int NMAT, int BITS, int DR>
 __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, const PfTile* __restrict__ tiles, const int32_t* __restrict__ ntiles,
                                                                     const __half* __restrict__ bsrc, const __half* __restrict__ bsum,
-                                                                    __half* __restrict__ hdst, uint32_t h_natural) {
+                                                                    __half* __restrict__ hdst, uint32_t tile_filter) {
     constexpr uint32_t RAWB = BITS * 8;                   // packed bytes of one weight row of one stage
     constexpr uint32_t NRAW = DR + 1;
     extern __shared__ uint8_t pf_raw_smem[];
@@ -649,6 +657,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
     __shared__ long long drow[PW_NMAX];
     if (blockIdx.y >= uint32_t(*ntiles)) return;
     const PfTile tile = tiles[blockIdx.y];
+    if ((tile_filter == 1 && tile.shared) || (tile_filter == 2 && !tile.shared)) return;      // 1: routed tiles only, 2: shared tiles only
     const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
     const uint32_t nmain = G;
     const uint32_t kb = 2 * G < PW_K ? 2 * G : PW_K, nblk = 2 * G / kb, ncorr = 2 * nblk, nst = nmain + ncorr;
@@ -792,10 +801,9 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                         two_terms(qb.x, hi[4], lo[4]); two_terms(qb.y, hi[5], lo[5]); two_terms(qb.z, hi[6], lo[6]); two_terms(qb.w, hi[7], lo[7]);
                     } else {
                         const uint4 w = *reinterpret_cast<const uint4*>(at(src + blk * 16));
-                        const uint2 a = pf_dequant_q8_word(w.x, q8s), b = pf_dequant_q8_word(w.y, q8s);
-                        const uint2 e = pf_dequant_q8_word(w.z, q8s), f = pf_dequant_q8_word(w.w, q8s);
-                        two_terms(a.x, hi[0], lo[0]); two_terms(a.y, hi[1], lo[1]); two_terms(b.x, hi[2], lo[2]); two_terms(b.y, hi[3], lo[3]);
-                        two_terms(e.x, hi[4], lo[4]); two_terms(e.y, hi[5], lo[5]); two_terms(f.x, hi[6], lo[6]); two_terms(f.y, hi[7], lo[7]);
+                        const uint4 qa = pf_dequant_q8_block(w.x, w.y, q8s), qb = pf_dequant_q8_block(w.z, w.w, q8s);
+                        two_terms(qa.x, hi[0], lo[0]); two_terms(qa.y, hi[1], lo[1]); two_terms(qa.z, hi[2], lo[2]); two_terms(qa.w, hi[3], lo[3]);
+                        two_terms(qb.x, hi[4], lo[4]); two_terms(qb.y, hi[5], lo[5]); two_terms(qb.z, hi[6], lo[6]); two_terms(qb.w, hi[7], lo[7]);
                     }
                     tmem_st8(ta + 0 * 32 + blk * 8, hi);
                     tmem_st8(ta + 1 * 32 + blk * 8, lo);
@@ -834,7 +842,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                         const float a = __uint_as_float(d0[j]), b = __uint_as_float(d1[j]);
                         if constexpr (NMAT == 2) {
                             const float hv = (a * sigmoid_f(a)) * b;
-                            hdst[drow[t] + (h_natural ? row : (row & ~7u) + pf_pos8(row & 7))] = __float2half_rn(hv);
+                            hdst[drow[t] + (row & ~7u) + pf_pos8(row & 7)] = __float2half_rn(hv);
                         } else {
                             out_base[drow[t] + row] = a;
                             out_base[drow[t] + row + 128] = b;
@@ -910,42 +918,40 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
 }
 
 template <int NMAT, int BITS, int DR>
-int launch_prefill_wide_d(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, size_t smem, cudaStream_t s) {
+int launch_prefill_wide_d(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, size_t smem, uint32_t filter, cudaStream_t s) {
     auto kernel = prefill_wide_kernel<NMAT, BITS, DR>;
     static SmemOptIn configured;
     if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) return check_launch(m, "prefill kernel attribute");
     Timed t(m, s, NMAT == 2 ? KERNEL_PREFILL_GATE_UP : KERNEL_PREFILL_DOWN);
     const uint32_t row_tiles = NMAT == 2 ? c.F / 128 : c.H / 256;
-    kernel<<<dim3(row_tiles, m->pf_max_tiles), PW_THREADS, smem, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, bsum, m->hbuf16,
-                                                                    c.down.bits == 8 ? 1u : 0u);
+    kernel<<<dim3(row_tiles, m->pf_max_tiles), PW_THREADS, smem, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, bsum, m->hbuf16, filter);
     return check_launch(m, NMAT == 2 ? "prefill gate_up" : "prefill down");
 }
 
 // Deepest weight prefetch that fits beside the metadata tiles.
 template <int NMAT, int BITS>
-int launch_prefill_wide(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, cudaStream_t s) {
+int launch_prefill_wide(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, uint32_t filter, cudaStream_t s) {
     const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
     const size_t limit = 227 * 1024 - 2048;             // dynamic shared memory beside the kernel's static arrays
-    if (PwSmem(G, 5, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 5>(m, c, bsrc, bsum, PwSmem(G, 5, BITS).total, s);
-    if (PwSmem(G, 4, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 4>(m, c, bsrc, bsum, PwSmem(G, 4, BITS).total, s);
-    if (PwSmem(G, 2, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 2>(m, c, bsrc, bsum, PwSmem(G, 2, BITS).total, s);
+    if (PwSmem(G, 5, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 5>(m, c, bsrc, bsum, PwSmem(G, 5, BITS).total, filter, s);
+    if (PwSmem(G, 4, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 4>(m, c, bsrc, bsum, PwSmem(G, 4, BITS).total, filter, s);
+    if (PwSmem(G, 2, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 2>(m, c, bsrc, bsum, PwSmem(G, 2, BITS).total, filter, s);
     return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
 }
 
 template <int NMAT, int BITS, bool META_F16, int D>
-int launch_prefill_d(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, size_t smem, cudaStream_t s) {
+int launch_prefill_d(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, size_t smem, uint32_t filter, cudaStream_t s) {
     const uint32_t N = NMAT == 2 ? c.F : c.H;
     auto kernel = prefill_kernel<NMAT, BITS, META_F16, D>;
     static SmemOptIn configured;
     if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) return check_launch(m, "prefill kernel attribute");
     Timed t(m, s, NMAT == 2 ? KERNEL_PREFILL_GATE_UP : KERNEL_PREFILL_DOWN);
-    kernel<<<dim3(N / PF_M, m->pf_max_tiles), PF_THREADS, smem, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, bsum, m->hbuf16,
-                                                                     c.down.bits == 8 ? 1u : 0u);
+    kernel<<<dim3(N / PF_M, m->pf_max_tiles), PF_THREADS, smem, s>>>(c, static_cast<const PfTile*>(m->pf_tiles), m->pf_ntiles, bsrc, bsum, m->hbuf16, filter);
     return check_launch(m, NMAT == 2 ? "prefill gate_up" : "prefill down");
 }
 
 template <int NMAT, int BITS, bool META_F16>
-int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, cudaStream_t s) {
+int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, uint32_t filter, cudaStream_t s) {
     using P = PfSmem<NMAT, BITS>;
     const uint32_t N = NMAT == 2 ? c.F : c.H, K = NMAT == 2 ? c.H : c.F, G = K / 64;
     if (N % PF_M) return fail(m, ZC_EINVAL, "prefill kernel: rows not a multiple of 128");
@@ -953,9 +959,9 @@ int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* b
     const size_t limit = 227 * 1024;
     // down: its K is short (ten stages per CTA), so the fixed cost of a CTA matters: a shallower ring lets two CTAs
     // share an SM (shared memory and 256 TMEM columns each) and overlap one's set-up with the other's loop
-    if (NMAT == 1 && 2 * (P::total(G, 2) + 1024) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 2>(m, c, bsrc, bsum, P::total(G, 2), s);
-    if (P::total(G, 4) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 4>(m, c, bsrc, bsum, P::total(G, 4), s);
-    if (P::total(G, 2) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 2>(m, c, bsrc, bsum, P::total(G, 2), s);
+    if (NMAT == 1 && 2 * (P::total(G, 2) + 1024) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 2>(m, c, bsrc, bsum, P::total(G, 2), filter, s);
+    if (P::total(G, 4) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 4>(m, c, bsrc, bsum, P::total(G, 4), filter, s);
+    if (P::total(G, 2) <= limit) return launch_prefill_d<NMAT, BITS, META_F16, 2>(m, c, bsrc, bsum, P::total(G, 2), filter, s);
     return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
 }
 
@@ -989,7 +995,7 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
         const size_t blocks = size_t(c.T) * c.H / 8;
-        pf_prepare_x_kernel<<<unsigned((blocks + 255) / 256), 256, 0, s>>>(c.x, c.act_dtype, m->xp, blocks, c.status, c.gate.bits == 8);
+        pf_prepare_x_kernel<<<unsigned((blocks + 255) / 256), 256, 0, s>>>(c.x, c.act_dtype, m->xp, blocks, c.status);
         if ((rc = check_launch(m, "prefill activations")) < 0) return rc;
     }
     {
@@ -997,9 +1003,20 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
         pf_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(m->xp, c.T, c.H, m->xsum, c.status);
         if ((rc = check_launch(m, "prefill activation sums")) < 0) return rc;
     }
-    if (wide) rc = c.gate.bits == 4 ? launch_prefill_wide<2, 4>(m, c, m->xp, m->xsum, s) : launch_prefill_wide<2, 8>(m, c, m->xp, m->xsum, s);
-    else if (c.gate.bits == 4) rc = c.meta_f16 ? launch_prefill<2, 4, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, 4, false>(m, c, m->xp, m->xsum, s);
-    else rc = c.meta_f16 ? launch_prefill<2, 8, true>(m, c, m->xp, m->xsum, s) : launch_prefill<2, 8, false>(m, c, m->xp, m->xsum, s);
+    // The code width is a template parameter: a shared expert with other bit widths than the routed experts' takes the
+    // shared tiles in launches of its own (filter 2) while the routed launch skips them (filter 1).
+    auto gemm = [&](auto nmat_tag, const Call& q, uint32_t bits, const __half* bsrc, const __half* bsum, uint32_t filter) {
+        constexpr int NM = decltype(nmat_tag)::value;
+        if (wide) return bits == 4 ? launch_prefill_wide<NM, 4>(m, q, bsrc, bsum, filter, s) : launch_prefill_wide<NM, 8>(m, q, bsrc, bsum, filter, s);
+        if (bits == 4) return q.meta_f16 ? launch_prefill<NM, 4, true>(m, q, bsrc, bsum, filter, s) : launch_prefill<NM, 4, false>(m, q, bsrc, bsum, filter, s);
+        return q.meta_f16 ? launch_prefill<NM, 8, true>(m, q, bsrc, bsum, filter, s) : launch_prefill<NM, 8, false>(m, q, bsrc, bsum, filter, s);
+    };
+    const bool split = c.has_shared && c.shared_split;
+    Call shared = c;
+    shared.gate = c.sgate; shared.up = c.sup; shared.down = c.sdown;
+    int extra = 0;
+    rc = gemm(std::integral_constant<int, 2>{}, c, c.gate.bits, m->xp, m->xsum, split ? 1u : 0u);
+    if (rc >= 0 && split) { rc = gemm(std::integral_constant<int, 2>{}, shared, shared.gate.bits, m->xp, m->xsum, 2u); ++extra; }
     if (rc < 0) return rc;
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
@@ -1007,11 +1024,10 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
         pf_sums_kernel<<<(rows * 32 + 255) / 256, 256, 0, s>>>(m->hbuf16, rows, c.F, m->hsum, c.status);
         if ((rc = check_launch(m, "prefill intermediate sums")) < 0) return rc;
     }
-    if (wide) rc = c.down.bits == 4 ? launch_prefill_wide<1, 4>(m, c, m->hbuf16, m->hsum, s) : launch_prefill_wide<1, 8>(m, c, m->hbuf16, m->hsum, s);
-    else if (c.down.bits == 4) rc = c.meta_f16 ? launch_prefill<1, 4, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, 4, false>(m, c, m->hbuf16, m->hsum, s);
-    else rc = c.meta_f16 ? launch_prefill<1, 8, true>(m, c, m->hbuf16, m->hsum, s) : launch_prefill<1, 8, false>(m, c, m->hbuf16, m->hsum, s);
+    rc = gemm(std::integral_constant<int, 1>{}, c, c.down.bits, m->hbuf16, m->hsum, split ? 1u : 0u);
+    if (rc >= 0 && split) { rc = gemm(std::integral_constant<int, 1>{}, shared, shared.down.bits, m->hbuf16, m->hsum, 2u); ++extra; }
     if (rc < 0) return rc;
-    return 6;
+    return 6 + extra;
 }
 
 }  // namespace zc

@@ -30,7 +30,7 @@ struct SynthArgs {
     uint8_t* records; uint8_t* shared_record;
     uint64_t record_stride, seed;
     uint32_t layer, first_expert, local_experts, group;
-    Projection proj[3];
+    Projection proj[3], shared_proj[3];
     uint8_t meta_f16, q8_signed, has_shared;
 };
 
@@ -40,7 +40,7 @@ __global__ void fill_records_kernel(SynthArgs a) {
     const bool shared = slot >= a.local_experts;
     uint8_t* record = shared ? a.shared_record : a.records + size_t(slot) * a.record_stride;
     const uint64_t expert = shared ? SHARED_EXPERT : uint64_t(a.first_expert + slot);
-    const Projection pr = a.proj[p];
+    const Projection pr = shared ? a.shared_proj[p] : a.proj[p];
     const uint64_t ck = stream_key(a.seed, a.layer, expert, p, KIND_CODES), sk = stream_key(a.seed, a.layer, expert, p, KIND_SCALES);
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x, first = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (pr.bits == 4) {
@@ -94,7 +94,8 @@ int launch_synth_layer(zc_moe* m, uint32_t layer, uint64_t seed, cudaStream_t s)
     a.records = L.records; a.shared_record = L.shared_record;
     a.record_stride = d.record_stride; a.seed = seed; a.layer = layer;
     a.first_expert = d.first_expert; a.local_experts = d.local_experts; a.group = d.group;
-    for (int p = 0; p < 3; ++p) a.proj[p] = projection_of(d, p);
+    const zc_moe_desc sd = shared_desc_of(d);
+    for (int p = 0; p < 3; ++p) { a.proj[p] = projection_of(d, p); a.shared_proj[p] = projection_of(sd, p); }
     a.meta_f16 = d.meta_dtype == ZC_F16; a.q8_signed = d.q8_signed; a.has_shared = d.has_shared;
     int launched = 0;
     fill_records_kernel<<<dim3(32, d.local_experts + (d.has_shared ? 1 : 0), 3), 256, 0, s>>>(a);

@@ -46,7 +46,8 @@ class Desc(ctypes.Structure):
         ("gate_bits", ctypes.c_uint8), ("up_bits", ctypes.c_uint8), ("down_bits", ctypes.c_uint8),
         ("q8_signed", ctypes.c_uint8), ("meta_dtype", ctypes.c_uint8), ("act_dtype", ctypes.c_uint8),
         ("out_dtype", ctypes.c_uint8), ("router_dtype", ctypes.c_uint8), ("has_shared", ctypes.c_uint8),
-        ("arith", ctypes.c_uint8), ("reserved", ctypes.c_uint8 * 6),
+        ("arith", ctypes.c_uint8),
+        ("shared_gate_bits", ctypes.c_uint8), ("shared_up_bits", ctypes.c_uint8), ("shared_down_bits", ctypes.c_uint8), ("reserved", ctypes.c_uint8 * 3),
         ("record_bytes", ctypes.c_uint64), ("record_stride", ctypes.c_uint64),
     ]
 

@@ -41,6 +41,9 @@ class MoeConfig:
     router_dtype: int = F32
     has_shared: int = 0
     arith: int = ARITH_FP32
+    shared_gate_bits: int = 0       # the shared expert's record: 4 or 8 per projection, 0 = as the routed experts
+    shared_up_bits: int = 0
+    shared_down_bits: int = 0
 
     def bits(self, projection):
         return (self.gate_bits, self.up_bits, self.down_bits)[projection]
@@ -70,6 +73,13 @@ class MoeConfig:
     def record_stride(self):
         return (self.record_bytes + RECORD_ALIGN - 1) // RECORD_ALIGN * RECORD_ALIGN
 
+    def shared_cfg(self):
+        """The configuration that describes the shared expert's record (the reference's mixed artifact keeps routed experts
+        Q4 and the shared expert Q8, src/engine/metal.mm:1103-1123): same geometry, the shared bit widths."""
+        from dataclasses import replace
+        return replace(self, gate_bits=self.shared_gate_bits or self.gate_bits, up_bits=self.shared_up_bits or self.up_bits,
+                       down_bits=self.shared_down_bits or self.down_bits, shared_gate_bits=0, shared_up_bits=0, shared_down_bits=0)
+
     @property
     def n_local(self):
         return self.local_experts or self.experts
@@ -88,6 +98,8 @@ class MoeConfig:
         for p in range(3):
             if self.bits(p) not in (4, 8):
                 raise ValueError("projection bits must be 4 or 8")
+        if any(b not in (0, 4, 8) for b in (self.shared_gate_bits, self.shared_up_bits, self.shared_down_bits)):
+            raise ValueError("shared projection bits must be 0, 4 or 8")
         if not 0 < self.top_k <= min(self.experts, 128):
             raise ValueError("top_k must be in 1..min(experts,128)")
 

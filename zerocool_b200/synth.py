@@ -94,8 +94,11 @@ def projection_parts(cfg: MoeConfig, seed, layer, expert, projection):
 
 
 def record(cfg: MoeConfig, seed, layer, expert):
-    """One expert record (uint8 [record_stride]); ``expert=SHARED_EXPERT`` gives the shared expert."""
+    """One expert record (uint8 [record_stride]); ``expert=SHARED_EXPERT`` gives the shared expert, in the layout of
+    ``cfg.shared_cfg()`` (its own bit widths)."""
     from .records import build_record
+    if expert == SHARED_EXPERT:
+        cfg = cfg.shared_cfg()
     return build_record(cfg, [projection_parts(cfg, seed, layer, expert, p) for p in range(3)])
 
 
