@@ -40,6 +40,7 @@ from zerocool_b200.records import BF16, F16, F32, MoeConfig  # noqa: E402
 METRIC = "MoE-layer tokens/s at Qwen3-Next shape (decode, 48-layer MoE stack)"
 SEED = 20261125
 BATCHES = (1, 4, 16, 64)
+SMALL_ROWS = 16       # long batches: experts with at most this many rows take the streaming kernels (option prefill_small_rows)
 TOL = 2e-3            # max-abs error / output RMS, fp32 accumulation (the tolerance of the benchmark specification)
 
 
@@ -330,6 +331,7 @@ def measure_long_batch(torch, m, cfg, tokens, steps, warmup, kind, biases, skip_
     burst, sustained, tsource = tensor_peak()
     x_np, _, x_dev = make_inputs(torch, cfg, tokens, 0)
     out_dev = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device="cuda")
+    m.set_option("prefill_small_rows", SMALL_ROWS)
     parity = None
     if not skip_parity:
         got16 = m.moe(0, x_dev).float().cpu().numpy()
@@ -344,8 +346,14 @@ def measure_long_batch(torch, m, cfg, tokens, steps, warmup, kind, biases, skip_
         raise RuntimeError("the chained stack produced non-finite values")
     kernels = kernel_profile(m, lambda: m.stack_eager(x_dev, out_dev), min(steps, 3))
     rows = tokens * (cfg.top_k + cfg.has_shared)
-    flops = {"prefill_gate_up": 2.0 * rows * 2 * cfg.ffn * cfg.hidden, "prefill_down": 2.0 * rows * cfg.hidden * cfg.ffn,
-             "gate_up": 2.0 * rows * 2 * cfg.ffn * cfg.hidden, "down": 2.0 * rows * cfg.hidden * cfg.ffn}
+    # Rows per kernel family: experts with at most SMALL_ROWS rows run on the streaming kernels, the grouped GEMM takes the
+    # rest and the shared expert (counted on the last layer's routing, which the handle still holds).
+    counts = np.diff(m.last_routing(tokens)["offsets"])
+    rows_small = int(counts[counts <= SMALL_ROWS].sum())
+    rows_big = int(counts[counts > SMALL_ROWS].sum()) + tokens * cfg.has_shared
+    per_row = {"gate_up": 2.0 * 2 * cfg.ffn * cfg.hidden, "down": 2.0 * cfg.hidden * cfg.ffn}
+    flops = {"prefill_gate_up": rows_big * per_row["gate_up"], "prefill_down": rows_big * per_row["down"],
+             "gate_up": rows_small * per_row["gate_up"], "down": rows_small * per_row["down"]}
     expert_kernels = [k for k in kernels if k in flops]
     dominant = max(expert_kernels, key=lambda k: kernels[k]["share"])
     tf = flops[dominant] / (kernels[dominant]["avg_us"] * 1e-6) / 1e12
@@ -354,12 +362,13 @@ def measure_long_batch(torch, m, cfg, tokens, steps, warmup, kind, biases, skip_
     return {
         "config": workload(cfg, tokens, 1, kind), "tokens": tokens, "steps": steps, "warmup": warmup, "ms_per_step": ms,
         "tokens_per_s": tokens / (ms * 1e-3), "gpu_launches": int(launches), "mean_active_experts": float(np.mean(active)),
-        "family": {k: ("tcgen05 grouped GEMM" if k.startswith("prefill") else "mma.sync GEMV family") for k in expert_kernels},
+        "family": {k: ("tcgen05 grouped GEMM" if k.startswith("prefill") else f"mma.sync streaming kernels (experts with at most {SMALL_ROWS} rows)") for k in expert_kernels},
+        "rows_last_layer": {"tensor_core_family": rows_big, "streaming_family": rows_small},
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst,
                      "frac_of_sustained": tf / sustained, "peak_source": tsource, "algorithmic_flops_per_launch": flops[dominant],
                      "avg_launch_us": kernels[dominant]["avg_us"], "traffic": None,
-                     "definition": "2 x routed-and-shared rows x output columns x K of this launch (useful flops; padded token columns and the "
-                                   "bias-correction stages are not counted)"},
+                     "definition": "2 x rows this kernel family processed (last layer's routing) x output columns x K of this launch (useful flops; "
+                                   "padded token columns, the second FP16 term of the exact weights and the bias-correction stages are not counted)"},
         "roofline_step": {"tensor_tflops": step_flops / (ms * 1e-3) / 1e12, "frac_of_tensor_peak": step_flops / (ms * 1e-3) / 1e12 / burst,
                           "hbm_gbs": step_bytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": step_bytes / (ms * 1e-3) / 1e9 / hbm_peak,
                           "algorithmic_flops_per_step": step_flops, "algorithmic_bytes_per_step": step_bytes, "peak_source": peak_source},
@@ -779,9 +788,11 @@ def main():
     ap.add_argument("--skip-batches", action="store_true")
     ap.add_argument("--skip-extras", action="store_true", help="leave out the prefill and mixed sub-records (one-GPU runs)")
     ap.add_argument("--skip-ep", action="store_true", help="leave out the configuration-5 sub-record")
+    ap.add_argument("--small-rows", type=int, default=SMALL_ROWS, help="long batches: experts with at most this many rows take the streaming kernels (0: none)")
     ap.add_argument("--record-routes", default="", help="write the expert selections of one decode pass as a route trace (JSON lines) and exit")
     ap.add_argument("--replay-routes", default="", help="time the decode stack with the expert selections of a recorded route trace forced into every layer")
     args = ap.parse_args()
+    globals()["SMALL_ROWS"] = args.small_rows
     if args.warmup < 3:
         args.warmup = 3
     if not args.tokens:

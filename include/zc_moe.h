@@ -286,6 +286,10 @@ int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* ou
  *   "exact_h" (default 0): the decode family's down product reads the FP32 SwiGLU rows as two FP16 terms (nothing
  *   below FP32 is rounded) instead of one FP16 term (11 significant bits; the reference rounds these rows to BF16).
  *   "ep_wait_ms" (default 2000): limit of one device-side wait for a peer's flag in the expert-parallel layer.
+ *   "prefill_wide" (default 1): long batches use the wide-tile grouped GEMM (accumulators and weights in tensor memory);
+ *   0 selects the earlier per-group-drain kernel.
+ *   "prefill_small_rows" (default 16, 0..64): in a long batch, experts with at most this many rows run on the streaming
+ *   kernels and the grouped GEMM takes the others (0: the grouped GEMM takes every expert).
  * Changing an option drops the cached graphs of zc_moe_stack. */
 int zc_moe_set_option(zc_moe* moe, const char* name, int value);
 

@@ -101,7 +101,7 @@ def test_config4_mixed_bits_ragged_batch_at_full_size():
     x = synth.activations(cfg, SEED, 0, tokens)
     before = m.launches
     out = m.moe(0, device_x(m, x)).clone()
-    assert m.launches - before == 10                      # the tensor-core family took the batch: router, route, permute, 6 x grouped GEMM, combine
+    assert m.launches - before == 12                      # the tensor-core family took the batch: router, route, permute, 2 x few-row experts, 6 x grouped GEMM, combine
     routing = m.last_routing(tokens)
     ids = routing["ids"].copy()
     assert m.status() == 0
@@ -454,3 +454,34 @@ def test_mixed_artifact_routed_q4_shared_q8_in_one_handle(family, tokens):
     err = util.rel_max_error(out, want["out"])
     print("mixed artifact,", family, "max-abs error / RMS:", err)
     assert err <= TOL, err
+
+
+def test_few_row_experts_take_the_streaming_kernels_in_a_long_batch():
+    """In a long batch, experts with at most `prefill_small_rows` rows run on the streaming kernels and the grouped GEMM
+    takes the others. Every setting of the threshold (none, some, all experts small) must agree with the CPU checker, and
+    with each other within the tolerance."""
+    cfg = util.cfg2(experts=128, max_tokens=512)
+    router = synth.router(cfg, SEED, 0).copy()
+    router *= (1.0 + 40.0 / (1.0 + np.arange(cfg.experts, dtype=np.float32)))[:, None]       # skewed: a few hot experts, many with a handful of rows
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    m.load_layer(0, router_w=router)
+    tokens = 400
+    x = synth.activations(cfg, SEED, 0, tokens)
+    outs = {}
+    for small in (0, 16, 64):
+        m.set_option("prefill_small_rows", small)
+        outs[small] = m.prefill(0, device_x(m, x)).float().cpu().numpy()
+        assert m.status() == 0
+    routing = m.last_routing(tokens)
+    counts = np.diff(routing["offsets"])
+    assert (counts > 64).sum() >= 2 and ((counts > 0) & (counts <= 16)).sum() >= 8      # both kinds of expert are present
+    want = oracle.moe_layer(cfg.as_dict(), util.selected_records(cfg, SEED, 0, routing["ids"][:48]), router, x[:48],
+                            shared_record=synth.record(cfg, SEED, 0, synth.SHARED_EXPERT), shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    assert np.array_equal(want["ids"], routing["ids"][:48])
+    for small, out in outs.items():
+        err = util.rel_max_error(out[:48], want["out"])
+        print("few-row threshold", small, "max-abs error / RMS:", err)
+        assert err <= TOL, (small, err)
+    with pytest.raises(ValueError):
+        m.set_option("prefill_small_rows", 65)

@@ -109,6 +109,24 @@ int check_call(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, const 
     return ZC_OK;
 }
 
+// The experts of a layer. Long batches run on the tensor-core family, whose tile costs about the same whether it holds
+// 128 token rows or 8 (the dequantisation of its 128 x K weights sets the pace): experts with only a few rows therefore
+// go to the streaming kernels (eight rows per pass at HBM speed) first, and the grouped GEMM takes the rest. Which
+// family an expert takes depends on its row count only, so a token's result does not depend on its place in the batch.
+int launch_experts(zc_moe* m, const Call& c, cudaStream_t s, int family) {
+    if (family != 1) return launch_experts_decode(m, c, s);
+    int n, total = 0;
+    const uint32_t small = m->prefill_small_rows;
+    if (small) {
+        Call few = c;
+        few.has_shared = 0;                 // the shared expert sees every token: its rows stay with the grouped GEMM
+        few.item_rows_max = small;
+        if ((n = launch_experts_decode(m, few, s)) < 0) return n; total += n;
+    }
+    if ((n = launch_experts_prefill(m, c, s, small)) < 0) return n; total += n;
+    return total;
+}
+
 // One layer: router partials -> route + permutation (one launch) -> gate/up -> down -> combine.
 // With `next` set the combine also writes the normalised input of the following layer (the chained stack).
 // family: 0 = decode kernels, 1 = prefill kernels (tensor-core grouped GEMM), -1 = by token count.
@@ -123,7 +141,7 @@ int run_layer(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* o
     int n, total = 0;
     if ((n = launch_router_partial(m, c, s)) < 0) return n; total += n;
     if ((n = launch_route_permute(m, c, s, true, true)) < 0) return n; total += n;
-    if ((n = family == 1 ? launch_experts_prefill(m, c, s) : launch_experts_decode(m, c, s)) < 0) return n; total += n;
+    if ((n = launch_experts(m, c, s, family)) < 0) return n; total += n;
     if (hc) n = launch_combine_hc(m, c, hc->hyper, hc->inject, hc->out, s);
     else if (next) n = launch_combine_norm(m, c, next, m->d.act_dtype, s);
     else n = launch_combine(m, c, s);
@@ -435,7 +453,7 @@ int zc_moe_forward_routed(zc_moe* m, uint32_t layer, const void* x, uint32_t tok
     if ((n = launch_forced_weights(m, c, ids, s)) < 0) return n; total += n;
     if ((n = launch_route_permute(m, c, s, false, true)) < 0) return n; total += n;
     const bool wide = tokens >= 64 && uint64_t(tokens) * m->d.top_k >= 24ull * m->d.local_experts && m->pf_tiles;
-    if ((n = wide ? launch_experts_prefill(m, c, s) : launch_experts_decode(m, c, s)) < 0) return n; total += n;
+    if ((n = launch_experts(m, c, s, wide ? 1 : 0)) < 0) return n; total += n;
     if ((n = launch_combine(m, c, s)) < 0) return n; total += n;
     m->launches += total;
     return ZC_OK;
@@ -850,6 +868,13 @@ int zc_moe_set_option(zc_moe* m, const char* name, int value) {
     if (!m || !name) return fail(m, ZC_EINVAL, "null handle or option name");
     const bool fold = !std::strcmp(name, "fold_q4"), pdl = !std::strcmp(name, "pdl"), exact_h = !std::strcmp(name, "exact_h");
     const bool wide = !std::strcmp(name, "prefill_wide");
+    if (!std::strcmp(name, "prefill_small_rows")) {
+        if (value < 0 || value > 64) return fail(m, ZC_EINVAL, "prefill_small_rows must be 0..64");
+        DeviceGuard guard(m->device);
+        drop_graphs(m);
+        m->prefill_small_rows = uint32_t(value);
+        return ZC_OK;
+    }
     if (!std::strcmp(name, "ep_wait_ms")) {
         if (value < 1 || value > 60000) return fail(m, ZC_EINVAL, "ep_wait_ms must be 1..60000");
         DeviceGuard guard(m->device);

@@ -120,6 +120,7 @@ struct Call {
     Projection sgate, sup, sdown;   // the shared expert's record (equal to gate, up, down unless shared_split)
     uint8_t shared_split;           // the shared record has other bit widths: it runs as launches of its own
     uint8_t act_dtype, out_dtype, meta_f16, router_dtype, has_shared, ref, q8_signed;
+    uint32_t item_rows_max;   // decode family: items with more rows than this are left to the tensor-core family (0 = no limit)
     uint8_t quiet_drop;       // the permutation drops ids outside [0, E) without raising the status bit (unused row slots of a receive area)
 };
 
@@ -188,6 +189,7 @@ struct zc_moe {
     // Optional per-kernel timing (zc_moe_profile_begin/end): one event pair per launch.
     uint32_t pdl = 0xffffffffu;   // bit per KernelKind: that kernel launches with programmatic stream serialization (see launch_chained)
     bool exact_h = false;         // down reads the FP32 SwiGLU rows as two FP16 terms instead of one
+    uint32_t prefill_small_rows = 16;   // long batches: experts with at most this many rows run on the streaming kernels (0 = none)
     bool prefill_wide = true;     // long batches: wide-tile kernel with accumulators resident in TMEM (false: per-group drain kernel)
     bool fold_q4 = true;          // Q4 codes enter the MMA with their 1024 offset (removed from the FP32 group sum)
     bool profiling = false;
@@ -203,7 +205,7 @@ uint32_t router_rows_padded(const zc_moe_desc& d);
 int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route, bool do_permute);
 int launch_forced_weights(zc_moe* m, const Call& c, const int32_t* forced, cudaStream_t s);
 int launch_experts_decode(zc_moe* m, const Call& c, cudaStream_t s);
-int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s);
+int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s, uint32_t skip_rows_upto = 0);
 bool prefill_supported(const zc_moe_desc& d);
 size_t prefill_tile_capacity(const zc_moe_desc& d);
 size_t prefill_tile_bytes();

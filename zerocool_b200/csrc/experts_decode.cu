@@ -118,6 +118,7 @@ __device__ __forceinline__ bool decode_item(const Call& c, uint32_t item, ItemIn
     }
     const int4 entry = __ldcg(c.items + item);            // one load: {expert, first position, rows}; x = -1 past the list's end
     if (entry.x < 0) return false;
+    if (c.item_rows_max && uint32_t(entry.z) > c.item_rows_max) return false;      // this expert's rows go to the tensor-core family
     const uint32_t e = uint32_t(entry.x);
     it.record = c.records + size_t(e - c.first_expert) * c.record_stride;
     it.pos0 = uint32_t(entry.y);

@@ -167,12 +167,14 @@ __device__ __forceinline__ uint4 pf_dequant_q8_block(uint32_t lo, uint32_t hi, b
 // Tile list: one entry per (expert with work, block of PF_NMAX of its rows), the shared expert's token
 // blocks first. One CTA of 1024 threads; experts <= 1024.
 __global__ void __launch_bounds__(1024) pf_tiles_kernel(const int32_t* __restrict__ offsets, uint32_t E, uint32_t first_expert, uint32_t local_experts,
-                                                        uint32_t T, uint32_t has_shared, uint32_t nmax, PfTile* __restrict__ tiles, int32_t* __restrict__ ntiles) {
+                                                        uint32_t T, uint32_t has_shared, uint32_t nmax, uint32_t skip_rows_upto,
+                                                        PfTile* __restrict__ tiles, int32_t* __restrict__ ntiles) {
     __shared__ int warp_totals[33];
     const uint32_t e = threadIdx.x, lane = threadIdx.x % 32, warp = threadIdx.x / 32;
     const uint32_t shared_tiles = has_shared ? (T + nmax - 1) / nmax : 0;
     int rows = 0;
     if (e < E && e >= first_expert && e < first_expert + local_experts) rows = offsets[e + 1] - offsets[e];
+    if (uint32_t(rows) <= skip_rows_upto) rows = 0;          // few rows: the streaming kernels take this expert
     const int mine = (rows + int(nmax) - 1) / int(nmax);
     int inclusive = mine;
 #pragma unroll
@@ -598,8 +600,9 @@ __global__ void __launch_bounds__(PF_THREADS, NMAT == 1 ? 2 : 1) prefill_kernel(
 //            issuing at the tensor rate (64 clocks each at N = 128) and every wait, fence and commit of the issuing
 //            warp as idle tensor time, so a stage carries as much tensor work as TMEM allows and costs that warp one
 //            wait and one commit.
-//   roles  : warps 0-7 producers (warp w: matrix w / 4, TMEM lane quadrant w mod 4). Packed codes and token rows both
-//            arrive through the producers' cp.async stream, DR stages ahead: the token-row ring has DR + NA slots, so
+//   roles  : warps 0-7 producers (warp w: matrix w / 4, TMEM lane quadrant w mod 4). Packed codes (whole 128-byte lines
+//            of the warp's 32 rows, double-buffered) and token rows (DR stages ahead) both arrive through the producers'
+//            cp.async stream: the token-row ring has DR + NA slots, so
 //            the slot a producer refills was released by the same completed-stage barrier it waits on for its TMEM
 //            columns. The same warps then run the final epilogue on their quadrant. One lane each of warps 8 and 9 issue
 //            the MMAs of alternate stages and release a stage with one tcgen05.commit.
@@ -626,7 +629,7 @@ struct PwSmem {
     __host__ __device__ PwSmem(uint32_t G, uint32_t DR, uint32_t bits) {
         b_ring = 0;
         raw = b_ring + (DR + PW_NA_MAX) * PW_B_STAGE;
-        meta = raw + (DR + 1) * 2 * 128 * (bits * 8);     // [slot][matrix][row][bytes of 64 codes]
+        meta = raw + 2 * 8 * 32 * 128;                    // packed codes: [slot 0..1][producer warp][row of the warp][128 B]
         total = meta + 2 * 128 * 2 * G * 2 + 1024;        // two metadata tiles [128 x 2 G] FP16, + alignment slack
         if (total < 116 * 1024) total = 116 * 1024;       // one CTA per SM: a CTA takes all 512 TMEM columns
     }
@@ -648,7 +651,8 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                                                                     const __half* __restrict__ bsrc, const __half* __restrict__ bsum,
                                                                     __half* __restrict__ hdst, uint32_t tile_filter) {
     constexpr uint32_t RAWB = BITS * 8;                   // packed bytes of one weight row of one stage
-    constexpr uint32_t NRAW = DR + 1;
+    constexpr uint32_t SUPER = 128 / RAWB;                // stages whose packed codes arrive in one 128-byte line per row: 4 (Q4), 2 (Q8)
+    static_assert(DR <= int(SUPER), "the line of the next stages must have landed when its first stage begins");
     extern __shared__ uint8_t pf_raw_smem[];
     __shared__ __align__(8) uint64_t full[PW_NA_MAX], done[PW_NA_MAX], turn[2], meta_bar, acc_done, drain_bar;
     __shared__ uint32_t tmem_base_s;
@@ -658,6 +662,9 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
     if (blockIdx.y >= uint32_t(*ntiles)) return;
     const PfTile tile = tiles[blockIdx.y];
     if ((tile_filter == 1 && tile.shared) || (tile_filter == 2 && !tile.shared)) return;      // 1: routed tiles only, 2: shared tiles only
+#ifdef ZC_PW_STAMPS
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) pw_stamps[1][2][0] = clock64();
+#endif
     const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
     const uint32_t nmain = G;
     const uint32_t kb = 2 * G < PW_K ? 2 * G : PW_K, nblk = 2 * G / kb, ncorr = 2 * nblk, nst = nmain + ncorr;
@@ -700,14 +707,25 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+#ifdef ZC_PW_STAMPS
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) pw_stamps[1][2][1] = clock64();
+#endif
     const uint32_t tmem_a = tmem_base + 2 * Npad;           // A ring: stage s at columns s * PW_A_COLS, then [matrix][term][block][8]
 
     if (warp < 8) {
         // ---- producers: thread (m, r) owns weight row r of matrix m ---------------------------------------
+        PW_STAMP(1, 0, 0);
         const uint32_t m = warp / 4, quad = warp % 4, r = quad * 32 + lane;
         const Projection pr = NMAT == 2 ? (m == 0 ? c.gate : c.up) : c.down;
         const uint32_t mrow = r0 + (NMAT == 1 ? m * 128u : 0u) + r;
-        const uint8_t* codes = record + pr.codes + size_t(mrow) * (K * BITS / 8);
+        const uint32_t row_bytes = K * BITS / 8;
+        // Packed codes: the warp fetches the lines of its own 32 rows together - eight lanes take the eight 16-byte pieces
+        // of one row's 128-byte line, four rows per instruction - so that every request is a whole line (one 16-byte piece
+        // per thread from 32 different rows, as the first version had it, costs 32 tag look-ups per instruction and made
+        // the issue of a stage take ~1,500 clocks). A line holds the codes of SUPER stages. In shared memory the pieces of a
+        // row are xor-swizzled by the row so that the per-row reads below spread over the banks.
+        const uint8_t* code_lines = record + pr.codes + size_t(mrow - lane + lane / 8) * row_bytes + (lane % 8) * 16;      // row (lane / 8) of the warp, piece lane % 8
+        const uint32_t raw_warp = raw_base + warp * (32 * 128);
         const uint32_t lane_base = (quad * 32) << 16;
         // metadata of the row -> A' tile [s_0..s_G-1 | b_0..b_G-1] as FP16 (the correction stages' A operand, and where
         // this thread reads its scales)
@@ -734,6 +752,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                 }
             }
         }
+        PW_STAMP(1, 0, 1);
         // Token rows of a main stage: 128 bytes per row = 8 pieces; thread t copies piece (row t / 8 + 32 i, chunk t mod 8)
         // for i < 4. The row pointers are prepared once; a stage adds 128 bytes.
         const __half* src_i[PW_NMAX / 32];
@@ -743,13 +762,19 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
             src_i[i] = row < N ? bsrc + size_t(brow[row]) * K + (tid % 8) * 8 : nullptr;
         }
         const uint32_t dst_piece = (tid / 64) * 1024 + (tid % 8) * 128 + ((tid / 8) % 8) * 16;     // + i * 4096
-        auto issue_stage = [&](uint32_t j) {             // everything stage j needs from memory, into slot j of the rings
+        auto issue_codes = [&](uint32_t line) {          // the 128-byte lines holding stages line * SUPER .. of this warp's rows
+            if (line * SUPER >= nmain) return;
+            const uint32_t slot = raw_warp + (line & 1) * (8 * 32 * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t row = uint32_t(i) * 4 + lane / 8;
+                pf_cp16(slot + row * 128 + (((lane % 8) ^ (row & 7)) * 16), code_lines + size_t(i) * 4 * row_bytes + size_t(line) * 128);
+            }
+        };
+        auto issue_stage = [&](uint32_t j) {             // the token rows (or group sums) of stage j, into slot j of their ring
             if (j >= nst) return;
             const uint32_t bs = b_ring + (j % NB) * PW_B_STAGE;
             if (j < nmain) {
-                const uint32_t dst = raw_base + (((j % NRAW) * 2 + m) * 128 + r) * RAWB;
-#pragma unroll
-                for (uint32_t piece = 0; piece < RAWB; piece += 16) pf_cp16(dst + piece, codes + size_t(j) * RAWB + piece);
 #pragma unroll
                 for (int i = 0; i < PW_NMAX / 32; ++i) if (src_i[i]) pf_cp16(bs + i * 4096 + dst_piece, src_i[i] + j * PW_K);
             } else {
@@ -760,10 +785,13 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                 }
             }
         };
+        PW_STAMP(1, 0, 2);
+        issue_codes(0);
 #pragma unroll 1
         for (uint32_t j = 0; j < uint32_t(DR); ++j) {
             issue_stage(j);
             asm volatile("cp.async.commit_group;" ::: "memory");
+            PW_STAMP(1, 1, j);
         }
         bool ok = true;
         const bool q8s = c.q8_signed;
@@ -778,11 +806,14 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
             if (!ok) break;
             PW_STAMP(0, ks, 2);
             issue_stage(ks + DR);
+            if (ks % SUPER == 0) issue_codes(ks / SUPER + 1);       // into the slot whose stages this warp finished reading an iteration ago
             asm volatile("cp.async.commit_group;" ::: "memory");
+            __syncwarp();                                           // the other lanes' pieces of this row's line have landed too
             if (ks < nmain) {
                 const __half sh = *reinterpret_cast<const __half*>(at(scale_at + (ks / 8) * 128 + (ks % 8) * 2));
                 const __half2 s2 = __half2half2(sh);
-                const uint32_t src = raw_base + (((ks % NRAW) * 2 + m) * 128 + r) * RAWB;
+                const uint32_t src = raw_warp + ((ks / SUPER) & 1) * (8 * 32 * 128) + lane * 128;      // this row's line
+                const uint32_t sub = ks % SUPER;
                 const uint32_t ta = tmem_a + lane_base + (ks % NA) * PW_A_COLS + m * 64;       // this row's columns: [term][block][8]
                 auto two_terms = [&](uint32_t q_bits, uint32_t& hi, uint32_t& lo) {      // q exact -> fl(s q), s q - fl(s q)
                     const __half2 q = *reinterpret_cast<const __half2*>(&q_bits);
@@ -795,12 +826,14 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                 for (int blk = 0; blk < 4; ++blk) {                // 16 k per block: eight packed columns per term
                     uint32_t hi[8], lo[8];
                     if constexpr (BITS == 4) {
-                        const uint2 w = *reinterpret_cast<const uint2*>(at(src + blk * 8));
+                        const uint32_t piece = sub * 2 + blk / 2;
+                        const uint2 w = *reinterpret_cast<const uint2*>(at(src + ((piece ^ (lane & 7)) * 16) + (blk % 2) * 8));
                         const uint4 qa = pf_dequant_word(w.x), qb = pf_dequant_word(w.y);
                         two_terms(qa.x, hi[0], lo[0]); two_terms(qa.y, hi[1], lo[1]); two_terms(qa.z, hi[2], lo[2]); two_terms(qa.w, hi[3], lo[3]);
                         two_terms(qb.x, hi[4], lo[4]); two_terms(qb.y, hi[5], lo[5]); two_terms(qb.z, hi[6], lo[6]); two_terms(qb.w, hi[7], lo[7]);
                     } else {
-                        const uint4 w = *reinterpret_cast<const uint4*>(at(src + blk * 16));
+                        const uint32_t piece = sub * 4 + blk;
+                        const uint4 w = *reinterpret_cast<const uint4*>(at(src + ((piece ^ (lane & 7)) * 16)));
                         const uint4 qa = pf_dequant_q8_block(w.x, w.y, q8s), qb = pf_dequant_q8_block(w.z, w.w, q8s);
                         two_terms(qa.x, hi[0], lo[0]); two_terms(qa.y, hi[1], lo[1]); two_terms(qa.z, hi[2], lo[2]); two_terms(qa.w, hi[3], lo[3]);
                         two_terms(qb.x, hi[4], lo[4]); two_terms(qb.y, hi[5], lo[5]); two_terms(qb.z, hi[6], lo[6]); two_terms(qb.w, hi[7], lo[7]);
@@ -933,8 +966,9 @@ template <int NMAT, int BITS>
 int launch_prefill_wide(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, uint32_t filter, cudaStream_t s) {
     const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
     const size_t limit = 227 * 1024 - 2048;             // dynamic shared memory beside the kernel's static arrays
-    if (PwSmem(G, 5, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 5>(m, c, bsrc, bsum, PwSmem(G, 5, BITS).total, filter, s);
-    if (PwSmem(G, 4, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 4>(m, c, bsrc, bsum, PwSmem(G, 4, BITS).total, filter, s);
+    if constexpr (BITS == 4) {
+        if (PwSmem(G, 4, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 4>(m, c, bsrc, bsum, PwSmem(G, 4, BITS).total, filter, s);
+    }
     if (PwSmem(G, 2, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 2>(m, c, bsrc, bsum, PwSmem(G, 2, BITS).total, filter, s);
     return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
 }
@@ -983,12 +1017,12 @@ bool prefill_supported(const zc_moe_desc& d) {
 }
 
 // tile list -> FP16 activations -> gate/up (+SwiGLU) -> down. Routing must already be in place.
-int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s) {
+int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s, uint32_t skip_rows_upto) {
     int rc;
     const bool wide = m->prefill_wide;
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
-        pf_tiles_kernel<<<1, 1024, 0, s>>>(c.offsets, c.E, c.first_expert, c.local_experts, c.T, c.has_shared, wide ? PW_NMAX : PF_NMAX,
+        pf_tiles_kernel<<<1, 1024, 0, s>>>(c.offsets, c.E, c.first_expert, c.local_experts, c.T, c.has_shared, wide ? PW_NMAX : PF_NMAX, skip_rows_upto,
                                            static_cast<PfTile*>(m->pf_tiles), m->pf_ntiles);
         if ((rc = check_launch(m, "prefill tiles")) < 0) return rc;
     }
