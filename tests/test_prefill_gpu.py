@@ -154,3 +154,18 @@ def test_full_shape_token_order_invariance():
                             router_bias=bias)
     assert np.array_equal(want["ids"], ids[:check])
     assert util.rel_max_error(out[:check].float().cpu().numpy(), want["out"]) <= TOL
+
+
+@pytest.mark.parametrize("bits", [(4, 4, 4), (4, 4, 8)])
+def test_prefill_at_the_native_geometry(bits):
+    """hidden 2560 / ffn 640 (the reference's own layer shape): 40 groups per gate/up row and 10 per down row, so the
+    metadata tile and the group sums are padded to a multiple of eight groups, the down rows' metadata is read value by
+    value (20-byte rows) and the last 128-byte code line of a down row is half full. BF16 metadata and router."""
+    cfg = util.cfg0(arith=oracle.ARITH_FP32, act_dtype=BF16, experts=32, top_k=10,
+                    gate_bits=bits[0], up_bits=bits[1], down_bits=bits[2], max_tokens=512)
+    m, x, out, routing = run_prefill(cfg, 333)
+    err = check_against_oracle(cfg, x, out, routing)
+    dec = m.decode(0, device_x(m, x)).float().cpu().numpy()
+    assert m.status() == 0
+    assert util.rel_max_error(out, dec) <= TOL
+    print("native geometry", bits, "error", err)

@@ -217,7 +217,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     A(&c.hbuf, (T * K + T) * F * 4);
     if (prefill_supported(d) && T > 64) {
         A(&m->xp, T * H * 2); A(&m->hbuf16, (T * K + T) * F * 2);
-        A(&m->xsum, T * (H / 64) * 4 * 2); A(&m->hsum, (T * K + T) * (F / 64) * 4 * 2);
+        A(&m->xsum, T * prefill_sum_halves(d.hidden) * 2); A(&m->hsum, (T * K + T) * prefill_sum_halves(d.ffn) * 2);
         m->pf_max_tiles = uint32_t(prefill_tile_capacity(d));
         uint8_t* tl = nullptr; A(&tl, m->pf_max_tiles * prefill_tile_bytes()); m->pf_tiles = tl;
         A(&m->pf_ntiles, 16);

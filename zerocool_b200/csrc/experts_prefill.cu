@@ -221,12 +221,14 @@ __global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, _
 
 // Per row of an FP16 matrix [rows, K] and per 64-wide group g: S_g = sum of the row's values in the group (FP32 sum),
 // stored as the B' operand of the correction stages, [0 .. | hi_0.. | 0 .. | lo_0..] with hi = fp16(S),
-// lo = fp16(S - hi) (4 G halves per row; the zeros meet the scale half of the metadata tile). One warp per row.
+// lo = fp16(S - hi): 4 Gp halves per row, Gp = the group count rounded up to a multiple of eight (entries past G are
+// zero); the zeros of the first half meet the scale half of the metadata tile. One warp per row.
+__host__ __device__ inline uint32_t pf_padded_groups(uint32_t K) { return (K / 64 + 7) & ~7u; }
 __global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, uint32_t K, __half* __restrict__ sums, uint32_t* __restrict__ status) {
     const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
     if (row >= rows) return;
-    const uint32_t G = K / 64;
-    for (uint32_t g0 = 0; g0 < G; g0 += 4) {             // a lane adds one 16-byte piece; eight lanes cover a group
+    const uint32_t G = K / 64, Gp = pf_padded_groups(K);
+    for (uint32_t g0 = 0; g0 < Gp; g0 += 4) {            // a lane adds one 16-byte piece; eight lanes cover a group
         const uint32_t g = g0 + lane / 8;
         float sum = 0.0f;
         if (g < G) {
@@ -238,13 +240,13 @@ __global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, ui
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        if (g < G && lane % 8 == 0) {
+        if (g < Gp && lane % 8 == 0) {
             if (!(fabsf(sum) <= 65504.0f)) atomicOr(status, ZC_STATUS_RANGE);      // S (or an infinite input) leaves FP16
-            const __half hi = __float2half_rn(sum), lo = __float2half_rn(sum - __half2float(hi));
-            __half* dst = sums + size_t(row) * 4 * G;
+            const __half hi = __float2half_rn(sum), lo = __float2half_rn(sum - __half2float(hi));      // both zero for a padding group
+            __half* dst = sums + size_t(row) * 4 * Gp;
             const __half zero = __float2half_rn(0.0f);
-            dst[g] = zero; dst[G + g] = hi;
-            dst[2 * G + g] = zero; dst[3 * G + g] = lo;
+            dst[g] = zero; dst[Gp + g] = hi;
+            dst[2 * Gp + g] = zero; dst[3 * Gp + g] = lo;
         }
     }
 }
@@ -665,20 +667,21 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
 #ifdef ZC_PW_STAMPS
     if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) pw_stamps[1][2][0] = clock64();
 #endif
-    const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
+    const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64, Gp = pf_padded_groups(K);
     const uint32_t nmain = G;
-    const uint32_t kb = 2 * G < PW_K ? 2 * G : PW_K, nblk = 2 * G / kb, ncorr = 2 * nblk, nst = nmain + ncorr;
+    // correction stages: K' = 2 Gp metadata columns (scales, then biases, each padded to Gp) in blocks of kb
+    const uint32_t kb = (2 * Gp) % 64 == 0 ? 64u : (2 * Gp) % 32 == 0 ? 32u : 16u, nblk = 2 * Gp / kb, ncorr = 2 * nblk, nst = nmain + ncorr;
     const uint32_t N = uint32_t(tile.rows), Npad = (N + 15) & ~15u;
     const uint32_t NA = Npad > 64 ? 2u : 3u;               // A stages beside two accumulators of Npad columns
     const uint32_t NB = DR + NA;                           // token-row slots
     const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t r0 = blockIdx.x * (NMAT == 2 ? 128u : 256u);
-    const PwSmem L(G, DR, BITS);
+    const PwSmem L(Gp, DR, BITS);
     const uint32_t base = (pf_smem(pf_raw_smem) + 1023) & ~1023u;
     uint8_t* const sm = pf_raw_smem + (base - pf_smem(pf_raw_smem));
     auto at = [&](uint32_t shared_addr) { return sm + (shared_addr - base); };
     const uint32_t b_ring = base + L.b_ring, raw_base = base + L.raw, meta_base = base + L.meta;
-    const uint32_t meta_sbo = (2 * G / 8) * 128, meta_tile = 128 * 2 * G * 2;
+    const uint32_t meta_sbo = (2 * Gp / 8) * 128, meta_tile = 128 * 2 * Gp * 2;
     const uint8_t* record = tile.shared ? c.shared_record : c.records + size_t(uint32_t(tile.expert) - c.first_expert) * c.record_stride;
     uint32_t* status = c.status;
 
@@ -733,22 +736,37 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
             const uint8_t* sc = record + pr.scales + size_t(mrow) * G * 2;
             const uint8_t* bi = record + pr.biases + size_t(mrow) * G * 2;
             const uint32_t dst = meta_base + m * meta_tile + (r / 8) * meta_sbo + (r % 8) * 16;
-            for (uint32_t ch = 0; ch < G / 8; ++ch) {
-                if (c.meta_f16) {
-                    pf_cp16(dst + ch * 128, sc + ch * 16);
-                    pf_cp16(dst + (G / 8 + ch) * 128, bi + ch * 16);
-                } else {
-                    const uint4 a = *reinterpret_cast<const uint4*>(sc + ch * 16), b = *reinterpret_cast<const uint4*>(bi + ch * 16);
-                    const uint32_t ra[4] = {a.x, a.y, a.z, a.w}, rb[4] = {b.x, b.y, b.z, b.w};
-                    uint32_t ha[4], hb[4];
+            if (G % 8 == 0) {
+                for (uint32_t ch = 0; ch < G / 8; ++ch) {
+                    if (c.meta_f16) {
+                        pf_cp16(dst + ch * 128, sc + ch * 16);
+                        pf_cp16(dst + (G / 8 + ch) * 128, bi + ch * 16);
+                    } else {
+                        const uint4 a = *reinterpret_cast<const uint4*>(sc + ch * 16), b = *reinterpret_cast<const uint4*>(bi + ch * 16);
+                        const uint32_t ra[4] = {a.x, a.y, a.z, a.w}, rb[4] = {b.x, b.y, b.z, b.w};
+                        uint32_t ha[4], hb[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const __half2 x = __floats2half2_rn(__uint_as_float(ra[i] << 16), __uint_as_float(ra[i] & 0xffff0000u));
-                        const __half2 y = __floats2half2_rn(__uint_as_float(rb[i] << 16), __uint_as_float(rb[i] & 0xffff0000u));
-                        ha[i] = *reinterpret_cast<const uint32_t*>(&x); hb[i] = *reinterpret_cast<const uint32_t*>(&y);
+                        for (int i = 0; i < 4; ++i) {
+                            const __half2 x = __floats2half2_rn(__uint_as_float(ra[i] << 16), __uint_as_float(ra[i] & 0xffff0000u));
+                            const __half2 y = __floats2half2_rn(__uint_as_float(rb[i] << 16), __uint_as_float(rb[i] & 0xffff0000u));
+                            ha[i] = *reinterpret_cast<const uint32_t*>(&x); hb[i] = *reinterpret_cast<const uint32_t*>(&y);
+                        }
+                        *reinterpret_cast<uint4*>(at(dst + ch * 128)) = make_uint4(ha[0], ha[1], ha[2], ha[3]);
+                        *reinterpret_cast<uint4*>(at(dst + (G / 8 + ch) * 128)) = make_uint4(hb[0], hb[1], hb[2], hb[3]);
                     }
-                    *reinterpret_cast<uint4*>(at(dst + ch * 128)) = make_uint4(ha[0], ha[1], ha[2], ha[3]);
-                    *reinterpret_cast<uint4*>(at(dst + (G / 8 + ch) * 128)) = make_uint4(hb[0], hb[1], hb[2], hb[3]);
+                }
+            } else {
+                // a group count that is not a multiple of eight (ffn 640: ten groups): the row's metadata is not 16-byte
+                // aligned, so it is read value by value; the columns past G are zero
+                for (uint32_t g = 0; g < Gp; ++g) {
+                    __half sv = __float2half_rn(0.0f), bv = sv;
+                    if (g < G) {
+                        const uint16_t sr = *reinterpret_cast<const uint16_t*>(sc + g * 2), br = *reinterpret_cast<const uint16_t*>(bi + g * 2);
+                        sv = c.meta_f16 ? __ushort_as_half(sr) : __float2half_rn(bf_to_float(sr));
+                        bv = c.meta_f16 ? __ushort_as_half(br) : __float2half_rn(bf_to_float(br));
+                    }
+                    *reinterpret_cast<__half*>(at(dst + (g / 8) * 128 + (g % 8) * 2)) = sv;
+                    *reinterpret_cast<__half*>(at(dst + (Gp / 8 + g / 8) * 128 + (g % 8) * 2)) = bv;
                 }
             }
         }
@@ -781,7 +799,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                 const uint32_t chunks = kb / 8, term = (j - nmain) / nblk, blk = (j - nmain) % nblk;
                 for (uint32_t q = tid; q < N * chunks; q += 256) {
                     const uint32_t row = q / chunks, kc = q % chunks;
-                    pf_cp16(bs + (row / 8) * (chunks * 128) + kc * 128 + (row % 8) * 16, bsum + size_t(brow[row]) * 4 * G + term * 2 * G + blk * kb + kc * 8);
+                    pf_cp16(bs + (row / 8) * (chunks * 128) + kc * 128 + (row % 8) * 16, bsum + size_t(brow[row]) * 4 * Gp + term * 2 * Gp + blk * kb + kc * 8);
                 }
             }
         };
@@ -964,7 +982,7 @@ int launch_prefill_wide_d(zc_moe* m, const Call& c, const __half* bsrc, const __
 // Deepest weight prefetch that fits beside the metadata tiles.
 template <int NMAT, int BITS>
 int launch_prefill_wide(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, uint32_t filter, cudaStream_t s) {
-    const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
+    const uint32_t K = NMAT == 2 ? c.H : c.F, G = pf_padded_groups(K);
     const size_t limit = 227 * 1024 - 2048;             // dynamic shared memory beside the kernel's static arrays
     if constexpr (BITS == 4) {
         if (PwSmem(G, 4, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 4>(m, c, bsrc, bsum, PwSmem(G, 4, BITS).total, filter, s);
@@ -1012,9 +1030,11 @@ size_t prefill_tile_capacity(const zc_moe_desc& d) {
 size_t prefill_tile_bytes() { return sizeof(PfTile); }
 
 bool prefill_supported(const zc_moe_desc& d) {
-    // BF16 activations convert to FP16 exactly; an FP32 activation would need a second FP16 term.
-    return d.arith == ZC_ARITH_FP32 && d.act_dtype == ZC_BF16 && d.ffn % 512 == 0 && d.hidden % 512 == 0 && d.hidden <= 4096;
+    // BF16 activations convert to FP16 exactly; an FP32 activation would need a second FP16 term. Row tiles: 128 rows of
+    // gate/up, 256 of down. (The per-group-drain kernel behind the prefill_wide = 0 option needs multiples of 512.)
+    return d.arith == ZC_ARITH_FP32 && d.act_dtype == ZC_BF16 && d.ffn % 128 == 0 && d.hidden % 256 == 0 && d.hidden <= 4096;
 }
+size_t prefill_sum_halves(uint32_t K) { return size_t(4) * pf_padded_groups(K); }
 
 // tile list -> FP16 activations -> gate/up (+SwiGLU) -> down. Routing must already be in place.
 int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s, uint32_t skip_rows_upto) {
