@@ -323,6 +323,14 @@ int zc_moe_read_device(zc_moe* moe, void* host_dst, const void* device_src, uint
 /* Waits for the handle's work on `stream` and returns the device status word (then clears it). */
 int zc_moe_status(zc_moe* moe, void* stream, uint32_t* status);
 
+/* Runs the give-up path of the tensor-core kernels on its own (a diagnostic; nothing in the reference corresponds to it:
+ * its Metal command buffers have no device-side waits). One CTA allocates tensor memory, then two of its roles wait -
+ * with the bounded waits the kernels use - on an mbarrier that nothing arrives on: after `polls` attempts (1..100000,
+ * about a microsecond each) the wait gives up, raises the CTA's abort flag and ZC_STATUS_TIMEOUT in the handle's status
+ * word (read and cleared by zc_moe_status), the other role leaves on the flag, and the CTA returns its tensor memory.
+ * report[0..3] = {suspending wait's result, polling wait's result (0 = gave up), abort flag, TMEM base}. Synchronous. */
+int zc_moe_wait_selftest(zc_moe* moe, uint32_t polls, uint32_t report[4], void* stream);
+
 /* Number of kernel launches the handle has issued since creation (graph replays count their nodes). */
 uint64_t zc_moe_launch_count(const zc_moe* moe);
 

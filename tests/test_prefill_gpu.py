@@ -169,3 +169,19 @@ def test_prefill_at_the_native_geometry(bits):
     assert m.status() == 0
     assert util.rel_max_error(out, dec) <= TOL
     print("native geometry", bits, "error", err)
+
+
+def test_bounded_waits_give_up_and_leave_the_context_usable():
+    """The give-up path of the tensor-core kernels on its own: both kinds of bounded wait face a barrier that nothing
+    arrives on, run out (about 2 ms), raise the time-out bit, the CTA returns its tensor memory, and the next layer on
+    the same handle runs and matches the checker - no fault, no hang, no lost context."""
+    from zerocool_b200.moe import STATUS_TIMEOUT
+    cfg = util.cfg2(experts=32, top_k=4, max_tokens=256)
+    m, x, out, routing = run_prefill(cfg, 150)
+    waited, polled, abort_flag, _ = m.wait_selftest(polls=2000)
+    assert waited == 0 and polled == 0 and abort_flag == 1
+    assert m.status() & STATUS_TIMEOUT                      # read and cleared
+    again = m.prefill(0, device_x(m, x)).float().cpu().numpy()
+    assert m.status() == 0
+    assert np.array_equal(again, out)
+    check_against_oracle(cfg, x, again, routing)

@@ -854,6 +854,25 @@ int zc_moe_status(zc_moe* m, void* stream, uint32_t* status) {
     return ZC_OK;
 }
 
+int zc_moe_wait_selftest(zc_moe* m, uint32_t polls, uint32_t* report, void* stream) {
+    if (!m || !report) return fail(m, ZC_EINVAL, "null handle or report");
+    if (polls == 0 || polls > 100000) return fail(m, ZC_EINVAL, "wait self-test: polls must be in 1..100000");
+    DeviceGuard guard(m->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint32_t* dev = nullptr;
+    cudaError_t e = cudaMalloc(&dev, 16);
+    if (e != cudaSuccess) return cuda_fail(m, e, "wait self-test scratch");
+    e = cudaMemsetAsync(dev, 0xff, 16, s);
+    int rc = e == cudaSuccess ? launch_wait_selftest(m, polls, dev, s) : cuda_fail(m, e, "wait self-test scratch");
+    if (rc >= 0) {
+        if ((e = cudaStreamSynchronize(s)) == cudaSuccess) e = cudaMemcpy(report, dev, 16, cudaMemcpyDeviceToHost);
+        rc = e == cudaSuccess ? ZC_OK : cuda_fail(m, e, "wait self-test");
+    }
+    cudaFree(dev);
+    if (rc == ZC_OK) ++m->launches;
+    return rc;
+}
+
 int zc_moe_stack_eager(zc_moe* m, const void* x, uint32_t tokens, void* out, void* stream) {
     int rc = check_call(m, 0, x, tokens, out);
     if (rc != ZC_OK) return rc;

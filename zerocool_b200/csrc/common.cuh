@@ -209,6 +209,7 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s, uint32_t sk
 bool prefill_supported(const zc_moe_desc& d);
 size_t prefill_tile_capacity(const zc_moe_desc& d);
 size_t prefill_tile_bytes();
+int launch_wait_selftest(zc_moe* m, uint32_t polls, uint32_t* report, cudaStream_t s);
 size_t prefill_sum_halves(uint32_t K);      // group-sum halves per row the tensor-core family keeps for a projection with this K
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_ep_gather(zc_moe* m, const Call& c, void* rows, int32_t* row_experts, cudaStream_t s);

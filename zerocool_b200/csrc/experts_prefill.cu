@@ -79,9 +79,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {     
                  : "=r"(ok) : "r"(pf_smem(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status, uint32_t limit = PF_POLL_LIMIT) {
     if (mbar_test(bar, parity)) return true;          // the common case in a pipeline that runs ahead
-    for (uint32_t i = 0; i < PF_POLL_LIMIT; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
     }
@@ -92,8 +92,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 
 // The same for the lane that feeds the tensor cores: it has nothing else to do, and the wake-up of a suspended wait
 // (a few hundred clocks) is idle tensor time, so it polls without suspending. Still bounded.
-__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
-    for (uint32_t i = 0; i < (PF_POLL_LIMIT << 4); ++i) {
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status, uint32_t limit = PF_POLL_LIMIT) {
+    for (uint32_t i = 0; i < (limit << 4); ++i) {
         if (mbar_test(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
@@ -1017,7 +1017,37 @@ int launch_prefill(zc_moe* m, const Call& c, const __half* bsrc, const __half* b
     return fail(m, ZC_EINVAL, "prefill kernel: shape needs too much shared memory");
 }
 
+// The give-up path of the tensor-core kernels, run on its own: the roles of a CTA wait, with the kernels' own bounded
+// waits, on an mbarrier that nothing ever arrives on. The suspending wait runs out after `polls` attempts (about a
+// microsecond each), raises the abort flag and ZC_STATUS_TIMEOUT; the polling wait of the issuing role sees the flag (or
+// runs out itself); then the CTA meets at its barrier and returns the tensor memory it had allocated, as the kernels do.
+// report: {suspending wait returned, polling wait returned, abort flag, TMEM base} (a wait returns 0 when it gave up).
+__global__ void __launch_bounds__(96) pf_wait_selftest_kernel(uint32_t polls, uint32_t* status, uint32_t* report) {
+    __shared__ uint64_t never;
+    __shared__ volatile uint32_t abort_flag;
+    __shared__ uint32_t tmem_slot;
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (threadIdx.x == 0) { mbar_init(&never, 1); abort_flag = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pf_smem(&tmem_slot)), "r"(32u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 1 && lane == 0) report[0] = mbar_wait(&never, 0, &abort_flag, status, polls) ? 1u : 0u;
+    if (warp == 2 && lane == 0) report[1] = mbar_spin(&never, 0, &abort_flag, status, polls) ? 1u : 0u;
+    __syncthreads();
+    if (threadIdx.x == 0) { report[2] = abort_flag; report[3] = tmem_slot; }
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_slot), "r"(32u) : "memory");
+}
+
 }  // namespace
+
+int launch_wait_selftest(zc_moe* m, uint32_t polls, uint32_t* report, cudaStream_t s) {
+    pf_wait_selftest_kernel<<<1, 96, 0, s>>>(polls, m->scratch.status, report);
+    return check_launch(m, "wait self-test");
+}
 
 #ifdef ZC_PW_STAMPS
 extern "C" int zc_dbg_prefill_stamps(void* host) { return cudaMemcpyFromSymbol(host, pw_stamps, sizeof(pw_stamps)) == cudaSuccess ? 0 : -1; }

@@ -32,7 +32,7 @@ EXPORTS = [
     "zc_moe_ep_export", "zc_moe_ep_attach", "zc_moe_ep_layer", "zc_moe_ep_send", "zc_moe_ep_process", "zc_moe_ep_finish", "zc_moe_ep_stack", "zc_moe_ep_stack_eager",
     "zc_moe_forward_host", "zc_moe_forward_host_async", "zc_moe_set_cancel", "zc_moe_stack",
     "zc_moe_stack_host", "zc_moe_set_option", "zc_moe_stack_eager", "zc_moe_profile_begin", "zc_moe_profile_end", "zc_moe_kernel_name",
-    "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_ep_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_launch_count", "zc_synth_fill_layer",
+    "zc_moe_last_routing", "zc_moe_active_counts", "zc_moe_ep_active_counts", "zc_moe_read_device", "zc_moe_status", "zc_moe_wait_selftest", "zc_moe_launch_count", "zc_synth_fill_layer",
 ]
 
 
@@ -112,6 +112,7 @@ def load_library():
     lib.zc_moe_last_routing.argtypes = [vp] + [ctypes.POINTER(vp)] * 5
     lib.zc_moe_read_device.argtypes = [vp, vp, vp, u64]
     lib.zc_moe_status.argtypes = [vp, vp, ctypes.POINTER(u32)]
+    lib.zc_moe_wait_selftest.argtypes = [vp, u32, ctypes.POINTER(u32), vp]
     lib.zc_moe_launch_count.argtypes = [vp]
     lib.zc_moe_launch_count.restype = u64
     lib.zc_synth_fill_layer.argtypes = [vp, u32, u64, vp]
@@ -490,6 +491,13 @@ class Moe:
         word = ctypes.c_uint32()
         self._check(self.lib.zc_moe_status(self._h, self._stream(), ctypes.byref(word)))
         return word.value
+
+    def wait_selftest(self, polls=2000):
+        """Runs the bounded waits of the tensor-core kernels against a barrier nothing arrives on; -> the four report
+        words (suspending wait, polling wait, abort flag, TMEM base). ZC_STATUS_TIMEOUT is then set in the status word."""
+        report = (ctypes.c_uint32 * 4)()
+        self._check(self.lib.zc_moe_wait_selftest(self._h, ctypes.c_uint32(polls), report, self._stream()))
+        return list(report)
 
     def check_status(self):
         """Raises like Model::moe ("invalid router output", src/engine/model.cpp:459)."""
