@@ -40,6 +40,7 @@ from zerocool_b200.records import BF16, F16, F32, MoeConfig  # noqa: E402
 METRIC = "MoE-layer tokens/s at Qwen3-Next shape (decode, 48-layer MoE stack)"
 SEED = 20261125
 BATCHES = (1, 4, 16, 64)
+EXTRA_OPTIONS = []    # (name, value) pairs from --opt, applied to the long-batch handle (tuning sweeps)
 SMALL_ROWS = 16       # long batches: experts with at most this many rows take the streaming kernels (option prefill_small_rows)
 TOL = 2e-3            # max-abs error / output RMS, fp32 accumulation (the tolerance of the benchmark specification)
 
@@ -332,6 +333,8 @@ def measure_long_batch(torch, m, cfg, tokens, steps, warmup, kind, biases, skip_
     x_np, _, x_dev = make_inputs(torch, cfg, tokens, 0)
     out_dev = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device="cuda")
     m.set_option("prefill_small_rows", SMALL_ROWS)
+    for name, value in EXTRA_OPTIONS:
+        m.set_option(name, value)
     parity = None
     if not skip_parity:
         got16 = m.moe(0, x_dev).float().cpu().numpy()
@@ -788,11 +791,15 @@ def main():
     ap.add_argument("--skip-batches", action="store_true")
     ap.add_argument("--skip-extras", action="store_true", help="leave out the prefill and mixed sub-records (one-GPU runs)")
     ap.add_argument("--skip-ep", action="store_true", help="leave out the configuration-5 sub-record")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="library option for the long-batch handle (zc_moe_set_option), repeatable")
     ap.add_argument("--small-rows", type=int, default=SMALL_ROWS, help="long batches: experts with at most this many rows take the streaming kernels (0: none)")
     ap.add_argument("--record-routes", default="", help="write the expert selections of one decode pass as a route trace (JSON lines) and exit")
     ap.add_argument("--replay-routes", default="", help="time the decode stack with the expert selections of a recorded route trace forced into every layer")
     args = ap.parse_args()
     globals()["SMALL_ROWS"] = args.small_rows
+    for item in args.opt:
+        name, _, value = item.partition("=")
+        EXTRA_OPTIONS.append((name, int(value)))
     if args.warmup < 3:
         args.warmup = 3
     if not args.tokens:

@@ -290,6 +290,8 @@ int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* ou
  *   0 selects the earlier per-group-drain kernel.
  *   "prefill_small_rows" (default 16, 0..64): in a long batch, experts with at most this many rows run on the streaming
  *   kernels and the grouped GEMM takes the others (0: the grouped GEMM takes every expert).
+ *   "few_tiles_gate_up" (default 1), "few_tiles_down" (default 2), 1..4: 16-row tiles per warp of those streaming
+ *   launches (few experts have work there: fewer tiles per warp mean more, shorter CTAs per expert).
  * Changing an option drops the cached graphs of zc_moe_stack. */
 int zc_moe_set_option(zc_moe* moe, const char* name, int value);
 

@@ -117,7 +117,7 @@ def test_forward_picks_the_family_by_token_count():
     a = m.moe(0, x)
     used = m.launches - before
     b = m.prefill(0, x)
-    assert torch.equal(a, b) and used == 11             # router, route, gate/up + down for few-row experts, tiles, activations, sums, gate/up, sums, down, combine
+    assert torch.equal(a, b) and used == 10             # router, route, gate/up + down for few-row experts, tiles, activations + sums, gate/up, sums, down, combine
     small = device_x(m, synth.activations(cfg, SEED, 0, 8))
     before = m.launches
     m.moe(0, small)

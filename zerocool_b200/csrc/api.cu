@@ -191,7 +191,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     if (prop.major < 10) return fail(nullptr, ZC_EEXEC, "this library is built for sm_100a (B200) only");
 
     zc_moe* m = new zc_moe();
-    m->d = d; m->device = device;
+    m->d = d; m->device = device; m->sms = prop.multiProcessorCount > 0 ? uint32_t(prop.multiProcessorCount) : 148u;
     if (const char* v = std::getenv("ZC_MOE_PDL")) m->pdl = uint32_t(std::strtoul(v, nullptr, 0)) ? (std::strtoul(v, nullptr, 0) == 1 ? 0xffffffffu : uint32_t(std::strtoul(v, nullptr, 0))) : 0u;   // 0 off, 1 on, else a mask of kernel kinds
     m->layers.resize(d.layers);
     const size_t T = d.max_tokens, H = d.hidden, F = d.ffn, E = d.experts, K = d.top_k;
@@ -210,6 +210,7 @@ int zc_moe_create(const zc_moe_desc* desc, int device, zc_moe** out) {
     Call& c = m->scratch;
     A(&c.logits, T * E * 4); A(&c.gate_logit, T * 4); A(&c.ids, T * K * 4); A(&c.weights, T * K * 4);
     A(&c.offsets, (E + 1) * 4); A(&c.perm, T * K * 4); A(&c.active, E * 4); A(&c.items, E * 16); A(&c.counters, (16 + size_t(d.layers)) * 4);
+    if (T * K > 4096) A(&m->permute_blocks, permute_block_count(T * K) * E * 4);
     A(&m->router_partial, 16 * T * size_t(router_rows_padded(d)) * 4);
     const size_t done_n = size_t(router_rows_padded(d) / 32) * ((T + 7) / 8);
     A(&m->router_done, done_n * 4);
@@ -892,6 +893,13 @@ int zc_moe_set_option(zc_moe* m, const char* name, int value) {
         DeviceGuard guard(m->device);
         drop_graphs(m);
         m->prefill_small_rows = uint32_t(value);
+        return ZC_OK;
+    }
+    if (!std::strcmp(name, "few_tiles_gate_up") || !std::strcmp(name, "few_tiles_down")) {
+        if (value < 1 || value > 4) return fail(m, ZC_EINVAL, "few_tiles_* must be 1..4");
+        DeviceGuard guard(m->device);
+        drop_graphs(m);
+        (name[10] == 'g' ? m->few_tiles_gate_up : m->few_tiles_down) = uint32_t(value);
         return ZC_OK;
     }
     if (!std::strcmp(name, "ep_wait_ms")) {

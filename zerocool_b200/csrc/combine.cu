@@ -7,6 +7,8 @@
 // first, then the eight partials in order, without fused multiply-add contraction. For a top_k other
 // than 10 the same rule reads: partial_i = sum over j = i, i+8, ...; (partial_0 + partial_1), then
 // + partial_2 ... + partial_7.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace zc {
@@ -24,15 +26,22 @@ __device__ __forceinline__ float4 add4(float4 a, float4 b) {
 // compile-time slot count: every slot's 16 bytes (and the shared expert's) are requested before the first is
 // used, so that a thread waits for one memory round trip, not one per slot. A slot whose id is invalid is read
 // too (the buffer always holds T x K rows) and replaced by zero.
-template <int KMAX>
-__device__ __forceinline__ void combine_columns(const Call& c, uint32_t t, uint32_t col, float (&r)[4]) {
-    const float4* base = reinterpret_cast<const float4*>(c.expert_out + size_t(t) * c.K * c.H + col);
+// NV: four-column vectors per thread, at col and col + vstride (a long batch takes two, so that twice the bytes are in
+// flight per thread and the slot weights, ids and the gate are fetched once for both); a vector past the row's end is
+// skipped. The arithmetic of every element is the same for any NV.
+template <int KMAX, int NV>
+__device__ __forceinline__ void combine_columns_n(const Call& c, uint32_t t, uint32_t col, uint32_t vstride, float (&r)[NV][4]) {
     const uint32_t stride = c.H / 4;
-    float4 y[KMAX];
+    float4 y[NV][KMAX];
 #pragma unroll
-    for (int j = 0; j < KMAX; ++j) {
-        y[j] = make_float4(0, 0, 0, 0);
-        if (uint32_t(j) < c.K) y[j] = __ldcg(base + size_t(j) * stride);
+    for (int v = 0; v < NV; ++v) {
+        const bool on = col + v * vstride < c.H;
+        const float4* base = reinterpret_cast<const float4*>(c.expert_out + size_t(t) * c.K * c.H + col + v * vstride);
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) {
+            y[v][j] = make_float4(0, 0, 0, 0);
+            if (on && uint32_t(j) < c.K) y[v][j] = __ldcg(base + size_t(j) * stride);
+        }
     }
     // Router weight and validity of every slot: the same addresses for the whole CTA (one broadcast transaction
     // per warp), requested together with the rows instead of through a staged copy and a barrier.
@@ -43,41 +52,53 @@ __device__ __forceinline__ void combine_columns(const Call& c, uint32_t t, uint3
         w[j] = 0.0f; id[j] = -1;
         if (uint32_t(j) < c.K) { w[j] = __ldcg(c.weights + size_t(t) * c.K + j); id[j] = __ldcg(c.ids + size_t(t) * c.K + j); }
     }
-    float4 sh = make_float4(0, 0, 0, 0);
+    float4 sh[NV];
     float gate_logit = 0.0f;
-    if (c.has_shared) {
-        sh = __ldcg(reinterpret_cast<const float4*>(c.shared_out + size_t(t) * c.H + col));
-        gate_logit = __ldcg(c.gate_logit + t);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        sh[v] = make_float4(0, 0, 0, 0);
+        if (c.has_shared && col + v * vstride < c.H) sh[v] = __ldcg(reinterpret_cast<const float4*>(c.shared_out + size_t(t) * c.H + col + v * vstride));
     }
+    if (c.has_shared) gate_logit = __ldcg(c.gate_logit + t);
+    float gate = 0.0f;
+    if (c.has_shared) gate = c.ref ? bf_round(sigmoid_bf(bf_round(gate_logit))) : sigmoid_f(gate_logit);
 #pragma unroll
-    for (int j = 0; j < KMAX; ++j) {
-        if (uint32_t(j) < c.K) y[j] = mul4(id[j] >= 0 ? y[j] : make_float4(0, 0, 0, 0), w[j]);
-    }
-    // partial_i = sum over j = i, i+8, ... in ascending j; then (partial_0 + partial_1) + partial_2 ...
+    for (int v = 0; v < NV; ++v) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-#pragma unroll
-        for (int j = i + 8; j < KMAX; j += 8) if (uint32_t(j) < c.K) y[i] = add4(y[i], y[j]);
-    }
-    float4 total = y[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i) if (uint32_t(i) < c.K) total = add4(total, y[i]);
-    r[0] = total.x; r[1] = total.y; r[2] = total.z; r[3] = total.w;
-    if (c.has_shared) {
-        const float s[4] = {sh.x, sh.y, sh.z, sh.w};
-        if (c.ref) {
-            const float gate = bf_round(sigmoid_bf(bf_round(gate_logit)));
-#pragma unroll
-            for (int i = 0; i < 4; ++i) r[i] = bf_round(__fadd_rn(bf_round(r[i]), bf_round(__fmul_rn(gate, s[i]))));
-        } else {
-            const float gate = sigmoid_f(gate_logit);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) r[i] = __fadd_rn(r[i], __fmul_rn(gate, s[i]));
+        for (int j = 0; j < KMAX; ++j) {
+            if (uint32_t(j) < c.K) y[v][j] = mul4(id[j] >= 0 ? y[v][j] : make_float4(0, 0, 0, 0), w[j]);
         }
-    } else if (c.ref) {
+        // partial_i = sum over j = i, i+8, ... in ascending j; then (partial_0 + partial_1) + partial_2 ...
 #pragma unroll
-        for (int i = 0; i < 4; ++i) r[i] = bf_round(r[i]);
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int j = i + 8; j < KMAX; j += 8) if (uint32_t(j) < c.K) y[v][i] = add4(y[v][i], y[v][j]);
+        }
+        float4 total = y[v][0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) if (uint32_t(i) < c.K) total = add4(total, y[v][i]);
+        r[v][0] = total.x; r[v][1] = total.y; r[v][2] = total.z; r[v][3] = total.w;
+        if (c.has_shared) {
+            const float s4[4] = {sh[v].x, sh[v].y, sh[v].z, sh[v].w};
+            if (c.ref) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) r[v][i] = bf_round(__fadd_rn(bf_round(r[v][i]), bf_round(__fmul_rn(gate, s4[i]))));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) r[v][i] = __fadd_rn(r[v][i], __fmul_rn(gate, s4[i]));
+            }
+        } else if (c.ref) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r[v][i] = bf_round(r[v][i]);
+        }
     }
+}
+template <int KMAX>
+__device__ __forceinline__ void combine_columns(const Call& c, uint32_t t, uint32_t col, float (&r)[4]) {
+    float one[1][4];
+    combine_columns_n<KMAX, 1>(c, t, col, 0, one);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r[i] = one[0][i];
 }
 __device__ __forceinline__ void store4(void* base, int dtype, size_t index, const float (&r)[4]) {
     if (dtype == ZC_F32) {
@@ -89,16 +110,35 @@ __device__ __forceinline__ void store4(void* base, int dtype, size_t index, cons
     }
 }
 
+// Grid: (column blocks, tokens or fewer); a CTA walks the tokens blockIdx.y, blockIdx.y + gridDim.y, ... so that a long
+// batch runs as a few resident waves instead of thousands of one-shot CTAs.
 template <int KMAX>
 __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(Call c) {
-    const uint32_t t = blockIdx.y;
     const uint32_t col = (blockIdx.x * COMBINE_THREADS + threadIdx.x) * 4;
     pdl_wait();
     pdl_launch_dependents();
     if (col >= c.H) return;
-    float r[4];
-    combine_columns<KMAX>(c, t, col, r);
-    store4(c.out, c.out_dtype, size_t(t) * c.H + col, r);
+    for (uint32_t t = blockIdx.y; t < c.T; t += gridDim.y) {
+        float r[4];
+        combine_columns<KMAX>(c, t, col, r);
+        store4(c.out, c.out_dtype, size_t(t) * c.H + col, r);
+    }
+}
+
+// The same for a long batch: every thread takes two vectors of a token row, COMBINE_THREADS x 4 columns apart, and a
+// CTA walks the tokens blockIdx.x, blockIdx.x + gridDim.x, ... (the grid is one resident wave).
+template <int KMAX>
+__global__ void __launch_bounds__(COMBINE_THREADS, 2) combine_long_kernel(Call c) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (uint32_t t = blockIdx.x; t < c.T; t += gridDim.x) {
+        for (uint32_t col = threadIdx.x * 4; col < c.H; col += COMBINE_THREADS * 8) {
+            float r[2][4];
+            combine_columns_n<KMAX, 2>(c, t, col, COMBINE_THREADS * 4, r);
+            store4(c.out, c.out_dtype, size_t(t) * c.H + col, r[0]);
+            if (col + COMBINE_THREADS * 4 < c.H) store4(c.out, c.out_dtype, size_t(t) * c.H + col + COMBINE_THREADS * 4, r[1]);
+        }
+    }
 }
 
 // combine + the inter-layer stand-in of the chained stack in one launch: one CTA per token computes the
@@ -108,20 +148,28 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(Call c) {
 // synthetic weights have a non-zero mean (codes 0..15 with bias -8 scale): without centring, that common
 // component is amplified layer after layer until every token carries the same vector and routes to the same
 // ten experts, which a real model's hidden states do not do.
-constexpr int CN_THREADS = 512;
-template <int KMAX>
+// CN_THREADS: 512 for short batches (one pass over a 2048-wide row, the latency of a decode step), 256 for long ones
+// (several CTAs per SM, so that the loads of one overlap the reductions of another); a CTA walks the tokens
+// blockIdx.x, blockIdx.x + gridDim.x, ...
+template <int KMAX, int CN_THREADS>
 __global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(Call c, void* next, int next_dtype) {
     extern __shared__ float row[];          // [H]
     __shared__ float partial[CN_THREADS / 32];
-    const uint32_t t = blockIdx.x;
     pdl_wait();
     pdl_launch_dependents();
+    for (uint32_t t = blockIdx.x; t < c.T; t += gridDim.x) {
     float sum = 0.0f;
-    for (uint32_t col = threadIdx.x * 4; col < c.H; col += CN_THREADS * 4) {
-        float r[4];
-        combine_columns<KMAX>(c, t, col, r);
+    constexpr int NV = CN_THREADS == 256 ? 2 : 1;          // the long-batch form keeps two vectors per thread in flight
+    for (uint32_t col = threadIdx.x * 4; col < c.H; col += CN_THREADS * 4 * NV) {
+        float r[NV][4];
+        combine_columns_n<KMAX, NV>(c, t, col, CN_THREADS * 4, r);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { if (c.out_dtype != ZC_F32) r[i] = bf_round(r[i]); row[col + i] = r[i]; sum += r[i]; }
+        for (int v = 0; v < NV; ++v) {
+            const uint32_t cv = col + v * CN_THREADS * 4;
+            if (cv >= c.H) break;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { if (c.out_dtype != ZC_F32) r[v][i] = bf_round(r[v][i]); row[cv + i] = r[v][i]; sum += r[v][i]; }
+        }
     }
     auto block_total = [&](float v) {
 #pragma unroll
@@ -146,6 +194,8 @@ __global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(Call c, void* 
 #pragma unroll
         for (int i = 0; i < 4; ++i) r[i] = __fmul_rn(row[col + i] - mean, scale);
         store4(next, next_dtype, size_t(t) * c.H + col, r);
+    }
+    __syncthreads();                        // the row is rewritten for the CTA's next token
     }
 }
 
@@ -241,10 +291,16 @@ int launch_combine_hc(zc_moe* m, const Call& c, const float* hyper, const float*
 
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s) {
     if (c.K > MAX_K) return fail(m, ZC_EINVAL, "top_k above 32");
-    const dim3 grid((c.H / 4 + COMBINE_THREADS - 1) / COMBINE_THREADS, c.T);
     int rc;
-    { Timed t(m, s, KERNEL_COMBINE); auto k = c.K <= 8 ? combine_kernel<8> : c.K <= 16 ? combine_kernel<16> : combine_kernel<32>;
-      launch_chained(m, KERNEL_COMBINE, k, grid, dim3(COMBINE_THREADS), 0, s, nullptr, 0, c);
+    { Timed t(m, s, KERNEL_COMBINE);
+      if (c.T > 128 && c.K <= 10) {          // two vectors of sixteen slots per thread do not fit the registers of two CTAs per SM
+          auto k = c.K <= 8 ? combine_long_kernel<8> : combine_long_kernel<10>;
+          launch_chained(m, KERNEL_COMBINE, k, dim3(std::min<uint32_t>(c.T, 2 * sm_count(m))), dim3(COMBINE_THREADS), 0, s, nullptr, 0, c);
+      } else {
+          const dim3 grid((c.H / 4 + COMBINE_THREADS - 1) / COMBINE_THREADS, c.T);
+          auto k = c.K <= 8 ? combine_kernel<8> : c.K <= 10 ? combine_kernel<10> : c.K <= 16 ? combine_kernel<16> : combine_kernel<32>;
+          launch_chained(m, KERNEL_COMBINE, k, grid, dim3(COMBINE_THREADS), 0, s, nullptr, 0, c);
+      }
       rc = check_launch(m, "combine"); }
     return rc < 0 ? rc : 1;
 }
@@ -253,8 +309,13 @@ int launch_combine_norm(zc_moe* m, const Call& c, void* next, int next_dtype, cu
     if (c.K > MAX_K) return fail(m, ZC_EINVAL, "top_k above 32");
     int rc;
     { Timed t(m, s, KERNEL_COMBINE); const size_t smem = c.H * sizeof(float);
-      auto k = c.K <= 8 ? combine_norm_kernel<8> : c.K <= 16 ? combine_norm_kernel<16> : combine_norm_kernel<32>;
-      launch_chained(m, KERNEL_COMBINE, k, dim3(c.T), dim3(CN_THREADS), smem, s, nullptr, 0, c, next, next_dtype);
+      if (c.T <= 128 || c.K > 10) {
+          auto k = c.K <= 8 ? combine_norm_kernel<8, 512> : c.K <= 10 ? combine_norm_kernel<10, 512> : c.K <= 16 ? combine_norm_kernel<16, 512> : combine_norm_kernel<32, 512>;
+          launch_chained(m, KERNEL_COMBINE, k, dim3(c.T), dim3(512), smem, s, nullptr, 0, c, next, next_dtype);
+      } else {
+          auto k = c.K <= 8 ? combine_norm_kernel<8, 256> : combine_norm_kernel<10, 256>;
+          launch_chained(m, KERNEL_COMBINE, k, dim3(std::min<uint32_t>(c.T, 2 * sm_count(m))), dim3(256), smem, s, nullptr, 0, c, next, next_dtype);
+      }
       rc = check_launch(m, "combine_norm"); }
     return rc < 0 ? rc : 1;
 }

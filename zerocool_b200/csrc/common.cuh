@@ -144,6 +144,7 @@ EpWindow ep_window_layout(const zc_moe_desc& d);
 struct zc_moe {
     zc_moe_desc d{};
     int device = 0;
+    uint32_t sms = 148;                  // SMs of the device (grids of the persistent-style kernels are sized in resident waves)
     std::vector<zc::LayerMem> layers;
     std::vector<void*> allocations;
     zc::Call scratch{};           // scratch pointers (x/out/layer fields filled per call)
@@ -153,6 +154,7 @@ struct zc_moe {
     __half* hbuf16 = nullptr;            // [max_tokens*K + max_tokens, F] FP16 SwiGLU outputs (prefill)
     void* pf_tiles = nullptr;            // tile list of the prefill launches
     int32_t* pf_ntiles = nullptr;
+    int32_t* permute_blocks = nullptr;   // [ceil(max slots / 2048)][E]: per-CTA expert counts of the multi-CTA permutation
     uint32_t pf_max_tiles = 0;
     uint32_t* router_done = nullptr;     // arrival counters of the router's (row tile, token tile) pairs
     zc::Call ep{};                       // second scratch set: the experts step of expert parallelism (rows from all ranks)
@@ -189,6 +191,7 @@ struct zc_moe {
     // Optional per-kernel timing (zc_moe_profile_begin/end): one event pair per launch.
     uint32_t pdl = 0xffffffffu;   // bit per KernelKind: that kernel launches with programmatic stream serialization (see launch_chained)
     bool exact_h = false;         // down reads the FP32 SwiGLU rows as two FP16 terms instead of one
+    uint32_t few_tiles_gate_up = 1, few_tiles_down = 2;      // 16-row tiles per warp of the streaming launches for those experts (few items: more, shorter CTAs)
     uint32_t prefill_small_rows = 16;   // long batches: experts with at most this many rows run on the streaming kernels (0 = none)
     bool prefill_wide = true;     // long batches: wide-tile kernel with accumulators resident in TMEM (false: per-group drain kernel)
     bool fold_q4 = true;          // Q4 codes enter the MMA with their 1024 offset (removed from the FP32 group sum)
@@ -209,6 +212,7 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s, uint32_t sk
 bool prefill_supported(const zc_moe_desc& d);
 size_t prefill_tile_capacity(const zc_moe_desc& d);
 size_t prefill_tile_bytes();
+size_t permute_block_count(size_t slots);   // CTAs of the multi-CTA permutation for this many slots
 int launch_wait_selftest(zc_moe* m, uint32_t polls, uint32_t* report, cudaStream_t s);
 size_t prefill_sum_halves(uint32_t K);      // group-sum halves per row the tensor-core family keeps for a projection with this K
 int launch_combine(zc_moe* m, const Call& c, cudaStream_t s);
@@ -254,6 +258,8 @@ inline cudaError_t opt_in_smem(Kernel kernel, SmemOptIn& state, int device, size
 }
 
 // Makes the handle's device current for the duration of an entry point and restores the caller's device.
+inline uint32_t sm_count(const zc_moe* m) { return m ? m->sms : 148u; }
+
 struct DeviceGuard {
     int previous = -1;
     bool changed = false;

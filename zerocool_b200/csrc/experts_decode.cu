@@ -620,10 +620,12 @@ static int launch_experts_decode_one(zc_moe* m, const Call& c, cudaStream_t s) {
 #ifndef ZC_TPW_DN
 #define ZC_TPW_DN 4
 #endif
-    else rc = dispatch_expert<2, 1>(m, c, items, ZC_TPW_GU, split_x, c.gate.bits, fold, s);
+    // As the few-row side of a long batch only a fraction of the items has work (the others leave at once): fewer
+    // tiles per warp, i.e. more and shorter CTAs per item, keep the SMs filled.
+    else rc = dispatch_expert<2, 1>(m, c, items, c.item_rows_max ? m->few_tiles_gate_up : ZC_TPW_GU, split_x, c.gate.bits, fold, s);
     if (rc < 0) return rc;
     if (small) rc = dispatch_expert<1, 2>(m, c, items, 1, split_h, c.down.bits, fold, s);
-    else rc = dispatch_expert<1, 1>(m, c, items, ZC_TPW_DN, split_h, c.down.bits, fold, s);
+    else rc = dispatch_expert<1, 1>(m, c, items, c.item_rows_max ? m->few_tiles_down : ZC_TPW_DN, split_h, c.down.bits, fold, s);
     if (rc < 0) return rc;
     return 2;
 }

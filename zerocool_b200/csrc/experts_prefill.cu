@@ -195,30 +195,6 @@ __global__ void __launch_bounds__(1024) pf_tiles_kernel(const int32_t* __restric
     if (threadIdx.x == 0) *ntiles = int(shared_tiles) + warp_totals[32];
 }
 
-// x [T, H] (bf16 or fp32) -> FP16 [T, H] with every block of eight k values stored in pf_pos8 order: the
-// B operand of the gate/up launch, copied into shared memory with plain 16-byte cp.async.
-__global__ void pf_prepare_x_kernel(const void* __restrict__ x, int act_dtype, __half* __restrict__ xp, size_t blocks, uint32_t* __restrict__ status) {
-    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= blocks) return;
-    float v[8];
-    if (act_dtype == ZC_F32) {
-        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + i * 8);
-        const float4 a = p[0], b = p[1];
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    } else {
-        const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + i * 8);
-        const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(r[j] << 16); v[2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u); }
-    }
-    __half h[8];
-    bool out_of_range = false;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { out_of_range |= fabsf(v[j]) > 65504.0f; h[pf_pos8(j)] = __float2half_rn(v[j]); }
-    *reinterpret_cast<uint4*>(xp + i * 8) = *reinterpret_cast<uint4*>(h);
-    if (out_of_range) atomicOr(status, ZC_STATUS_RANGE);
-}
-
 // Per row of an FP16 matrix [rows, K] and per 64-wide group g: S_g = sum of the row's values in the group (FP32 sum),
 // stored as the B' operand of the correction stages, [0 .. | hi_0.. | 0 .. | lo_0..] with hi = fp16(S),
 // lo = fp16(S - hi): 4 Gp halves per row, Gp = the group count rounded up to a multiple of eight (entries past G are
@@ -249,6 +225,53 @@ __global__ void pf_sums_kernel(const __half* __restrict__ src, uint32_t rows, ui
             dst[2 * Gp + g] = zero; dst[3 * Gp + g] = lo;
         }
     }
+}
+
+// The layer's input x [T, H] (bf16 or fp32) -> FP16 [T, H] with every block of eight k values stored in pf_pos8 order
+// (the B operand of the gate/up launch, copied into shared memory with plain 16-byte cp.async), and its group sums in
+// the same pass: one warp per token row, the same piece per lane and the same order of additions as pf_sums_kernel.
+__global__ void pf_prepare_x_sums_kernel(const void* __restrict__ x, int act_dtype, __half* __restrict__ xp, uint32_t rows, uint32_t K,
+                                         __half* __restrict__ sums, uint32_t* __restrict__ status) {
+    const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
+    if (row >= rows) return;
+    const uint32_t G = K / 64, Gp = pf_padded_groups(K);
+    bool out_of_range = false;
+    for (uint32_t g0 = 0; g0 < Gp; g0 += 4) {
+        const uint32_t g = g0 + lane / 8;
+        float sum = 0.0f;
+        if (g < G) {
+            const size_t at = size_t(row) * K + g * 64 + (lane % 8) * 8;
+            float v[8];
+            if (act_dtype == ZC_F32) {
+                const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + at);
+                const float4 a = p[0], b = p[1];
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            } else {
+                const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + at);
+                const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(r[j] << 16); v[2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u); }
+            }
+            __half h[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { out_of_range |= fabsf(v[j]) > 65504.0f; h[pf_pos8(j)] = __float2half_rn(v[j]); }
+            *reinterpret_cast<uint4*>(xp + at) = *reinterpret_cast<uint4*>(h);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += __half2float(h[j]);
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (g < Gp && lane % 8 == 0) {
+            if (!(fabsf(sum) <= 65504.0f)) out_of_range = true;
+            const __half hi = __float2half_rn(sum), lo = __float2half_rn(sum - __half2float(hi));
+            __half* dst = sums + size_t(row) * 4 * Gp;
+            const __half zero = __float2half_rn(0.0f);
+            dst[g] = zero; dst[Gp + g] = hi;
+            dst[2 * Gp + g] = zero; dst[3 * Gp + g] = lo;
+        }
+    }
+    if (out_of_range) atomicOr(status, ZC_STATUS_RANGE);
 }
 
 __device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src) {
@@ -979,12 +1002,19 @@ int launch_prefill_wide_d(zc_moe* m, const Call& c, const __half* bsrc, const __
     return check_launch(m, NMAT == 2 ? "prefill gate_up" : "prefill down");
 }
 
-// Deepest weight prefetch that fits beside the metadata tiles.
+// Token-row prefetch depth: two stages ahead measured slightly faster than four (a shorter set-up per CTA: the first
+// stages of a tile arrive at the SM's share of the memory bandwidth, about 25 bytes per clock).
 template <int NMAT, int BITS>
 int launch_prefill_wide(zc_moe* m, const Call& c, const __half* bsrc, const __half* bsum, uint32_t filter, cudaStream_t s) {
     const uint32_t K = NMAT == 2 ? c.H : c.F, G = pf_padded_groups(K);
     const size_t limit = 227 * 1024 - 2048;             // dynamic shared memory beside the kernel's static arrays
-    if constexpr (BITS == 4) {
+#ifndef ZC_PW_DR_GU
+#define ZC_PW_DR_GU 2
+#endif
+#ifndef ZC_PW_DR_DN
+#define ZC_PW_DR_DN 2
+#endif
+    if constexpr (BITS == 4 && (NMAT == 2 ? ZC_PW_DR_GU : ZC_PW_DR_DN) == 4) {
         if (PwSmem(G, 4, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 4>(m, c, bsrc, bsum, PwSmem(G, 4, BITS).total, filter, s);
     }
     if (PwSmem(G, 2, BITS).total <= limit) return launch_prefill_wide_d<NMAT, BITS, 2>(m, c, bsrc, bsum, PwSmem(G, 2, BITS).total, filter, s);
@@ -1078,14 +1108,8 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s, uint32_t sk
     }
     {
         Timed t(m, s, KERNEL_PREFILL_PREP);
-        const size_t blocks = size_t(c.T) * c.H / 8;
-        pf_prepare_x_kernel<<<unsigned((blocks + 255) / 256), 256, 0, s>>>(c.x, c.act_dtype, m->xp, blocks, c.status);
-        if ((rc = check_launch(m, "prefill activations")) < 0) return rc;
-    }
-    {
-        Timed t(m, s, KERNEL_PREFILL_PREP);
-        pf_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(m->xp, c.T, c.H, m->xsum, c.status);
-        if ((rc = check_launch(m, "prefill activation sums")) < 0) return rc;
+        pf_prepare_x_sums_kernel<<<(c.T * 32 + 255) / 256, 256, 0, s>>>(c.x, c.act_dtype, m->xp, c.T, c.H, m->xsum, c.status);
+        if ((rc = check_launch(m, "prefill activations and sums")) < 0) return rc;
     }
     // The code width is a template parameter: a shared expert with other bit widths than the routed experts' takes the
     // shared tiles in launches of its own (filter 2) while the routed launch skips them (filter 1).
@@ -1111,7 +1135,7 @@ int launch_experts_prefill(zc_moe* m, const Call& c, cudaStream_t s, uint32_t sk
     rc = gemm(std::integral_constant<int, 1>{}, c, c.down.bits, m->hbuf16, m->hsum, split ? 1u : 0u);
     if (rc >= 0 && split) { rc = gemm(std::integral_constant<int, 1>{}, shared, shared.down.bits, m->hbuf16, m->hsum, 2u); ++extra; }
     if (rc < 0) return rc;
-    return 6 + extra;
+    return 5 + extra;
 }
 
 }  // namespace zc

@@ -321,6 +321,128 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const int32_t*
     permute_any<PERMUTE_THREADS>(ids, slots, E, first_expert, local_experts, offsets, perm, active, items, counters, layer, status, hist);
 }
 
+// Long batches (tens of thousands of slots): the same stable counting sort by many CTAs, in three launches.
+//   permute_count_kernel: CTA b counts the experts of its PERMUTE_BLOCK consecutive slots      -> blocks[b][e]
+//   permute_scan_kernel:  one CTA turns each expert's column into an exclusive running count over the CTAs
+//                         (blocks[b][e] = slots of e before CTA b), scans the expert totals (offsets), and writes
+//                         the list of experts with work, as the one-CTA form does
+//   permute_place_kernel: CTA b ranks its own slots (per-warp counts, ids kept in registers between the passes) on
+//                         top of offsets[e] + blocks[b][e] and writes perm
+constexpr uint32_t PERMUTE_BLOCK = 2048;          // slots per CTA: 64 per warp of 1024 threads
+
+__global__ void __launch_bounds__(PERMUTE_THREADS) permute_count_kernel(const int32_t* __restrict__ ids, uint32_t slots, uint32_t E,
+                                                                         int32_t* __restrict__ blocks, uint32_t* status) {
+    extern __shared__ int32_t hist[];
+    for (uint32_t e = threadIdx.x; e < E; e += PERMUTE_THREADS) hist[e] = 0;
+    __syncthreads();
+    bool bad = false;
+    for (uint32_t i = threadIdx.x; i < PERMUTE_BLOCK; i += PERMUTE_THREADS) {
+        const uint32_t p = blockIdx.x * PERMUTE_BLOCK + i;
+        if (p >= slots) break;
+        const int32_t id = __ldcg(ids + p);
+        if (id >= 0 && uint32_t(id) < E) atomicAdd(&hist[id], 1);
+        else bad = true;
+    }
+    if (bad && status) atomicOr(status, ZC_STATUS_INVALID_ROUTE);
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < E; e += PERMUTE_THREADS) blocks[size_t(blockIdx.x) * E + e] = hist[e];
+}
+
+__global__ void __launch_bounds__(PERMUTE_THREADS) permute_scan_kernel(int32_t* __restrict__ blocks, uint32_t nblocks, uint32_t E,
+                                                                        uint32_t first_expert, uint32_t local_experts,
+                                                                        int32_t* __restrict__ offsets, int32_t* __restrict__ active, int4* __restrict__ items,
+                                                                        int32_t* __restrict__ counters, uint32_t layer) {
+    __shared__ unsigned long long warp_totals[33];
+    for (uint32_t i = threadIdx.x; i < E; i += PERMUTE_THREADS) items[i].x = -1;        // entries past the end of the new list
+    __syncthreads();
+    const uint32_t own = (E + PERMUTE_THREADS - 1) / PERMUTE_THREADS;      // <= PERMUTE_OWN, checked at launch
+    // Thread i owns experts i, i + NT, ... for the column sums (coalesced) ...
+    for (uint32_t q = 0; q < own; ++q) {
+        const uint32_t e = q * PERMUTE_THREADS + threadIdx.x;
+        if (e >= E) break;
+        int running = 0;
+        for (uint32_t b = 0; b < nblocks; ++b) { const int n = blocks[size_t(b) * E + e]; blocks[size_t(b) * E + e] = running; running += n; }
+        offsets[e] = running;                   // the expert's total for now; becomes its first position below
+    }
+    __syncthreads();
+    // ... and `own` consecutive experts for the scan, as the one-CTA form.
+    const uint32_t e_first = threadIdx.x * own;
+    int count[PERMUTE_OWN];
+    unsigned long long packed = 0;
+#pragma unroll
+    for (int q = 0; q < PERMUTE_OWN; ++q) {
+        const uint32_t e = e_first + q;
+        count[q] = 0;
+        if (uint32_t(q) < own && e < E) {
+            count[q] = offsets[e];
+            const bool has_work = count[q] > 0 && e >= first_expert && e < first_expert + local_experts;
+            packed += (unsigned long long)(count[q]) | ((unsigned long long)(has_work ? 1 : 0) << 32);
+        }
+    }
+    __syncthreads();
+    unsigned long long total;
+    const unsigned long long before = block_exclusive_scan<PERMUTE_THREADS>(packed, warp_totals, total);
+    int offset = int(uint32_t(before)), slot = int(before >> 32);
+#pragma unroll
+    for (int q = 0; q < PERMUTE_OWN; ++q) {
+        const uint32_t e = e_first + q;
+        if (uint32_t(q) < own && e < E) {
+            offsets[e] = offset;
+            if (count[q] > 0 && e >= first_expert && e < first_expert + local_experts) {
+                active[slot] = int32_t(e);
+                items[slot] = make_int4(int(e), offset, count[q], 0);
+                ++slot;
+            }
+            offset += count[q];
+        }
+    }
+    if (threadIdx.x == 0) { offsets[E] = int(uint32_t(total)); counters[0] = int(total >> 32); counters[16 + layer] = int(total >> 32); }
+}
+
+__global__ void __launch_bounds__(PERMUTE_THREADS) permute_place_kernel(const int32_t* __restrict__ ids, uint32_t slots, uint32_t E,
+                                                                         const int32_t* __restrict__ blocks, const int32_t* __restrict__ offsets,
+                                                                         int32_t* __restrict__ perm) {
+    extern __shared__ int32_t hist[];            // [32 warps][E]
+    constexpr uint32_t NW = PERMUTE_THREADS / 32, CHUNKS = PERMUTE_BLOCK / PERMUTE_THREADS;
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t begin = blockIdx.x * PERMUTE_BLOCK + warp * (32 * CHUNKS);
+    int32_t* mine = hist + warp * E;
+    for (uint32_t i = threadIdx.x; i < NW * E; i += PERMUTE_THREADS) hist[i] = 0;
+    int32_t cached[CHUNKS];
+#pragma unroll
+    for (uint32_t q = 0; q < CHUNKS; ++q) { const uint32_t p = begin + 32 * q + lane; cached[q] = p < slots ? __ldcg(ids + p) : -1; }
+    __syncthreads();
+#pragma unroll
+    for (uint32_t q = 0; q < CHUNKS; ++q) {
+        const int32_t id = cached[q];
+        const bool valid = id >= 0 && uint32_t(id) < E;
+        const uint32_t peers = __match_any_sync(0xffffffffu, valid ? uint32_t(id) : E + lane);
+        if (valid && (peers & ((1u << lane) - 1)) == 0) mine[id] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < E; e += PERMUTE_THREADS) {
+        int running = offsets[e] + blocks[size_t(blockIdx.x) * E + e];
+        for (uint32_t w = 0; w < NW; ++w) { const int n = hist[w * E + e]; hist[w * E + e] = running; running += n; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (uint32_t q = 0; q < CHUNKS; ++q) {
+        const int32_t id = cached[q];
+        const bool valid = id >= 0 && uint32_t(id) < E;
+        const uint32_t peers = __match_any_sync(0xffffffffu, valid ? uint32_t(id) : E + lane);
+        const uint32_t before_me = peers & ((1u << lane) - 1);
+        int cursor = 0;
+        if (valid) cursor = mine[id];
+        __syncwarp();
+        if (valid) {
+            perm[cursor + __popc(before_me)] = int32_t(begin + 32 * q + lane);
+            if (before_me == 0) mine[id] = cursor + __popc(peers);
+        }
+        __syncwarp();
+    }
+}
+
 // Route (one warp per token, eight tokens per CTA) and, when asked, the permutation as the tail of the
 // last CTA to finish, so that a layer needs one launch for both. Dynamic shared memory: the eight score rows
 // [8][E] floats, reused as the [8][E] histogram of the permutation.
@@ -351,6 +473,8 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
 }
 
 }  // namespace
+
+size_t permute_block_count(size_t slots) { return (slots + PERMUTE_BLOCK - 1) / PERMUTE_BLOCK; }
 
 int launch_forced_weights(zc_moe* m, const Call& c, const int32_t* forced, cudaStream_t s) {
     if (c.K > 32) return fail(m, ZC_EINVAL, "route: top_k above 32");
@@ -395,7 +519,21 @@ int launch_route_permute(zc_moe* m, const Call& c, cudaStream_t s, bool do_route
         if (rc < 0) return rc;
         ++launched;
     }
-    if (separate || (!do_route && do_permute)) {
+    if ((separate || (!do_route && do_permute)) && size_t(c.T) * c.K > 4096 && m->permute_blocks) {
+        const uint32_t slots = c.T * c.K, nblocks = uint32_t(permute_block_count(slots));
+        static SmemOptIn configured;
+        if (opt_in_smem(permute_place_kernel, configured, m->device, 160 * 1024) != cudaSuccess) return check_launch(m, "permute attribute");
+        int rc;
+        {
+            Timed t(m, s, KERNEL_PERMUTE);
+            permute_count_kernel<<<nblocks, PERMUTE_THREADS, c.E * sizeof(int32_t), s>>>(c.ids, slots, c.E, m->permute_blocks, c.quiet_drop ? nullptr : c.status);
+            permute_scan_kernel<<<1, PERMUTE_THREADS, 0, s>>>(m->permute_blocks, nblocks, c.E, c.first_expert, c.local_experts, c.offsets, c.active, c.items, c.counters, c.layer);
+            permute_place_kernel<<<nblocks, PERMUTE_THREADS, hist_bytes, s>>>(c.ids, slots, c.E, m->permute_blocks, c.offsets, c.perm);
+            rc = check_launch(m, "permute");
+        }
+        if (rc < 0) return rc;
+        launched += 3;
+    } else if (separate || (!do_route && do_permute)) {
         static SmemOptIn configured;
         if (opt_in_smem(permute_kernel, configured, m->device, 160 * 1024) != cudaSuccess) return check_launch(m, "permute attribute");
         int rc;

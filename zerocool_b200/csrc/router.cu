@@ -426,77 +426,120 @@ int launch_router_cluster(zc_moe* m, const Call& c, cudaStream_t s) {
 // kernel bound by the FP32 pipe and not by shared memory. Tiles keep the row-major [row][k] layout (leading
 // dimension part + 4 floats), so FP32 router rows are copied with 16-byte cp.async.
 constexpr int LONG_TT = 64, LONG_RT = 64;
-__global__ void __launch_bounds__(ROUTER_THREADS, 3) router_long_kernel(Call c) {
+#ifndef ZC_RL_ROWS
+#define ZC_RL_ROWS 4          // rows x tokens per thread: 4 x 4 chains, 256 threads (8 x 4 with 128 threads measured 20 % slower)
+#endif
+#ifndef ZC_RL_UNROLL
+#define ZC_RL_UNROLL 2
+#endif
+#ifndef ZC_RL_BLOCKS
+#define ZC_RL_BLOCKS 2
+#endif
+#define ZC_PRAGMA(x) _Pragma(#x)
+#define ZC_UNROLL(n) ZC_PRAGMA(unroll n)
+constexpr int LONG_RI = ZC_RL_ROWS, LONG_TJ = 4;
+constexpr int LONG_TXN = LONG_RT / LONG_RI, LONG_TYN = LONG_TT / LONG_TJ, LONG_THREADS = LONG_TXN * LONG_TYN;
+// Thread (tx, ty) owns rows tx + TXN i and tokens ty + TYN j: the lanes of a warp read consecutive rows of either tile,
+// which the row pitch of part + 4 floats spreads over all banks (one wavefront per 128 distinct bytes).
+__global__ void __launch_bounds__(LONG_THREADS, ZC_RL_BLOCKS) router_long_kernel(Call c) {
     extern __shared__ __align__(16) float smem[];
     const uint32_t H = c.H, part = H / 16, LD = part + 4;
     float* ws = smem;                       // [LONG_RT][LD]
     float* xs = ws + LONG_RT * LD;          // [LONG_TT][LD]
     const uint32_t e0 = blockIdx.x * LONG_RT, t0 = blockIdx.y * LONG_TT;
     const uint32_t rows_total = c.E + (c.has_shared ? 1u : 0u);
-    const uint32_t tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+    const uint32_t tid = threadIdx.x, tx = tid % LONG_TXN, ty = tid / LONG_TXN, warp = tid / 32, lane = tid % 32;
     const bool x32 = c.act_dtype == ZC_F32, w32 = c.router_dtype == ZC_F32;
-    float total[4][4];
+    const uint32_t rows_here = min(uint32_t(LONG_RT), rows_total - e0);
+    const bool narrow = rows_here <= LONG_THREADS / LONG_TT;
+    float total[LONG_RI][LONG_TJ];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < LONG_RI; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) total[i][j] = 0.0f;
+        for (int j = 0; j < LONG_TJ; ++j) total[i][j] = 0.0f;
     pdl_wait();
     for (uint32_t p = 0; p < 16; ++p) {
         const uint32_t k0 = p * part;
         __syncthreads();                     // the previous partition's tiles have been consumed
-        for (uint32_t task = tid; task < LONG_RT * (part / 4); task += ROUTER_THREADS) {
-            const uint32_t el = task / (part / 4), kq = task % (part / 4), e = e0 + el;
-            float* dst = ws + el * LD + kq * 4;
-            if (e >= rows_total) { *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0); continue; }
-            if (w32) {
-                const float* base = e < c.E ? static_cast<const float*>(c.router_w) + size_t(e) * H : static_cast<const float*>(c.shared_gate_w);
-                cp_async16(dst, base + k0 + kq * 4);
+        // Staging without divisions: warp w copies rows w, w + warps, ... of both tiles, its lanes walk the row.
+        for (uint32_t el = warp; el < (narrow ? rows_here : uint32_t(LONG_RT)); el += LONG_THREADS / 32) {
+            const uint32_t e = e0 + el;
+            float* dst = ws + el * LD;
+            if (e >= rows_total) {
+                for (uint32_t kq = lane; kq < part / 4; kq += 32) *reinterpret_cast<float4*>(dst + kq * 4) = make_float4(0, 0, 0, 0);
+            } else if (w32) {
+                const float* base = (e < c.E ? static_cast<const float*>(c.router_w) + size_t(e) * H : static_cast<const float*>(c.shared_gate_w)) + k0;
+                for (uint32_t kq = lane; kq < part / 4; kq += 32) cp_async16(dst + kq * 4, base + kq * 4);
             } else {
-                const uint16_t* base = e < c.E ? static_cast<const uint16_t*>(c.router_w) + size_t(e) * H : static_cast<const uint16_t*>(c.shared_gate_w);
-                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(base + k0 + kq * 4));
-                *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                                                              __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                const uint16_t* base = (e < c.E ? static_cast<const uint16_t*>(c.router_w) + size_t(e) * H : static_cast<const uint16_t*>(c.shared_gate_w)) + k0;
+                for (uint32_t kq = lane; kq < part / 4; kq += 32) {
+                    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(base + kq * 4));
+                    *reinterpret_cast<float4*>(dst + kq * 4) = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                                                           __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                }
             }
         }
         if (x32) {
-            for (uint32_t task = tid; task < LONG_TT * (part / 4); task += ROUTER_THREADS) {
-                const uint32_t tt = task / (part / 4), kq = task % (part / 4), t = t0 + tt;
-                float* dst = xs + tt * LD + kq * 4;
-                if (t < c.T) cp_async16(dst, static_cast<const float*>(c.x) + size_t(t) * H + k0 + kq * 4);
-                else *reinterpret_cast<float4*>(dst) = make_float4(0, 0, 0, 0);
+            for (uint32_t tt = warp; tt < LONG_TT; tt += LONG_THREADS / 32) {
+                const uint32_t t = t0 + tt;
+                float* dst = xs + tt * LD;
+                if (t < c.T) { const float* base = static_cast<const float*>(c.x) + size_t(t) * H + k0; for (uint32_t kq = lane; kq < part / 4; kq += 32) cp_async16(dst + kq * 4, base + kq * 4); }
+                else for (uint32_t kq = lane; kq < part / 4; kq += 32) *reinterpret_cast<float4*>(dst + kq * 4) = make_float4(0, 0, 0, 0);
             }
         } else {
-            for (uint32_t task = tid; task < LONG_TT * (part / 8); task += ROUTER_THREADS) {
-                const uint32_t tt = task / (part / 8), kb = task % (part / 8), t = t0 + tt;
-                uint4 raw = make_uint4(0, 0, 0, 0);
-                if (t < c.T) raw = __ldcg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(c.x) + size_t(t) * H + k0 + kb * 8));
-                const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
-                float4* dst = reinterpret_cast<float4*>(xs + tt * LD + kb * 8);
-                dst[0] = make_float4(__uint_as_float(r[0] << 16), __uint_as_float(r[0] & 0xffff0000u), __uint_as_float(r[1] << 16), __uint_as_float(r[1] & 0xffff0000u));
-                dst[1] = make_float4(__uint_as_float(r[2] << 16), __uint_as_float(r[2] & 0xffff0000u), __uint_as_float(r[3] << 16), __uint_as_float(r[3] & 0xffff0000u));
+            // BF16 rows: 16 bytes = eight values per lane; a half-warp takes a row (two rows per pass of the warp)
+            for (uint32_t tt = warp * 2 + lane / 16; tt < LONG_TT; tt += LONG_THREADS / 16) {
+                const uint32_t t = t0 + tt;
+                const uint16_t* base = static_cast<const uint16_t*>(c.x) + size_t(t) * H + k0;
+                for (uint32_t kb = lane % 16; kb < part / 8; kb += 16) {
+                    uint4 raw = make_uint4(0, 0, 0, 0);
+                    if (t < c.T) raw = __ldcg(reinterpret_cast<const uint4*>(base + kb * 8));
+                    float4* dst = reinterpret_cast<float4*>(xs + tt * LD + kb * 8);
+                    dst[0] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                    dst[1] = make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u), __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
+                }
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        float acc[4][4];
+        if (narrow) {
+            // A row tile with one or two rows (the shared gate's row after 512 experts): one chain per thread,
+            // thread = (token, row), the same k-ascending chain and the same ordered sum of partials.
+            const uint32_t tt = tid % LONG_TT, rr = tid / LONG_TT;
+            float a = 0.0f;
+            if (rr < rows_here) {
+                const float* wr = ws + rr * LD;
+                const float* xr = xs + tt * LD;
+                for (uint32_t k = 0; k < part; k += 4) {
+                    const float4 wv = *reinterpret_cast<const float4*>(wr + k), xv = *reinterpret_cast<const float4*>(xr + k);
+                    a = __fmaf_rn(xv.x, wv.x, a);
+                    a = __fmaf_rn(xv.y, wv.y, a);
+                    a = __fmaf_rn(xv.z, wv.z, a);
+                    a = __fmaf_rn(xv.w, wv.w, a);
+                }
+            }
+            total[0][0] = __fadd_rn(total[0][0], a);
+            continue;
+        }
+        float acc[LONG_RI][LONG_TJ];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < LONG_RI; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+            for (int j = 0; j < LONG_TJ; ++j) acc[i][j] = 0.0f;
         const float* wrow = ws + tx * LD;
-        const float* xrow = xs + ty * 4 * LD;
-#pragma unroll 2
+        const float* xrow = xs + ty * LD;
+ZC_UNROLL(ZC_RL_UNROLL)
         for (uint32_t k = 0; k < part; k += 4) {
-            float4 wv[4], xv[4];
+            float4 wv[LONG_RI], xv[LONG_TJ];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) wv[i] = *reinterpret_cast<const float4*>(wrow + i * 16 * LD + k);
+            for (int i = 0; i < LONG_RI; ++i) wv[i] = *reinterpret_cast<const float4*>(wrow + i * LONG_TXN * LD + k);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) xv[j] = *reinterpret_cast<const float4*>(xrow + j * LD + k);
+            for (int j = 0; j < LONG_TJ; ++j) xv[j] = *reinterpret_cast<const float4*>(xrow + j * LONG_TYN * LD + k);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < LONG_RI; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < LONG_TJ; ++j) {
                     float a = acc[i][j];
                     a = __fmaf_rn(xv[j].x, wv[i].x, a);
                     a = __fmaf_rn(xv[j].y, wv[i].y, a);
@@ -506,18 +549,26 @@ __global__ void __launch_bounds__(ROUTER_THREADS, 3) router_long_kernel(Call c) 
                 }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < LONG_RI; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) total[i][j] = __fadd_rn(total[i][j], acc[i][j]);      // partial p joins the ordered sum
+            for (int j = 0; j < LONG_TJ; ++j) total[i][j] = __fadd_rn(total[i][j], acc[i][j]);      // partial p joins the ordered sum
     }
     pdl_launch_dependents();
+    if (narrow) {
+        const uint32_t tt = tid % LONG_TT, rr = tid / LONG_TT, e = e0 + rr, t = t0 + tt;
+        if (rr < rows_here && t < c.T) {
+            if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(total[0][0], c.router_bias[e]) : total[0][0];
+            else c.gate_logit[t] = total[0][0];
+        }
+        return;
+    }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t e = e0 + tx + 16 * i;
+    for (int i = 0; i < LONG_RI; ++i) {
+        const uint32_t e = e0 + tx + LONG_TXN * i;
         if (e >= rows_total) continue;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t t = t0 + ty * 4 + j;
+        for (int j = 0; j < LONG_TJ; ++j) {
+            const uint32_t t = t0 + ty + LONG_TYN * j;
             if (t >= c.T) continue;
             if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(total[i][j], c.router_bias[e]) : total[i][j];
             else c.gate_logit[t] = total[i][j];
@@ -536,7 +587,7 @@ int launch_router_long(zc_moe* m, const Call& c, cudaStream_t s) {
     int rc;
     {
         Timed t(m, s, KERNEL_ROUTER);
-        const cudaError_t e = launch_chained(m, -1, router_long_kernel, grid, dim3(ROUTER_THREADS), smem, s, nullptr, 0, c);
+        const cudaError_t e = launch_chained(m, -1, router_long_kernel, grid, dim3(LONG_THREADS), smem, s, nullptr, 0, c);
         if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("router (long) launch: ") + cudaGetErrorString(e));
         rc = check_launch(m, "router");
     }
