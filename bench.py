@@ -388,6 +388,8 @@ def measure_ep(torch, dist, rank, world, local, layers, total_tokens, steps, war
     t_local = total_tokens // world
     cfg = config5(layers, t_local, rank, world)
     m = Moe(cfg, local)
+    for name, value in EXTRA_OPTIONS:
+        m.set_option(name, value)
     fill(m, cfg)
     x_np, _, x_dev = make_inputs(torch, cfg, t_local, rank)
     out_dev = torch.empty((t_local, cfg.hidden), dtype=torch.bfloat16, device="cuda")
@@ -619,6 +621,8 @@ def run_ours(args):
     extras = world == 1 and not args.skip_extras
     cfg = config(args.layers, max(BATCHES + (args.tokens,) + ((8192,) if extras else ())))
     m = Moe(cfg, local)
+    for name, value in EXTRA_OPTIONS:
+        m.set_option(name, value)
     fill(m, cfg)
 
     def inputs(tokens):

@@ -485,3 +485,25 @@ def test_few_row_experts_take_the_streaming_kernels_in_a_long_batch():
         assert err <= TOL, (small, err)
     with pytest.raises(ValueError):
         m.set_option("prefill_small_rows", 65)
+
+
+@pytest.mark.parametrize("tokens", [5, 40])
+def test_metadata_blocks_give_the_same_bits(tokens):
+    """hidden 4096 (config 5's geometry): scales and biases fetched eight groups at a time (default) or per ring stage
+    (option meta_blocks = 0) feed the same arithmetic: identical bits, and within tolerance of the CPU checker."""
+    import torch
+    cfg = util.cfg2(hidden=4096, experts=32, top_k=4, max_tokens=64)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    x = synth.activations(cfg, SEED, 0, tokens)
+    blocks = m.decode(0, device_x(m, x)).clone()
+    m.set_option("meta_blocks", 0)
+    stages = m.decode(0, device_x(m, x)).clone()
+    assert m.status() == 0
+    assert torch.equal(blocks, stages)
+    routing = m.last_routing(tokens)
+    records = util.selected_records(cfg, SEED, 0, routing["ids"])
+    want = oracle.moe_layer(cfg.as_dict(), records, synth.router(cfg, SEED, 0), x,
+                            shared_record=synth.record(cfg, SEED, 0, synth.SHARED_EXPERT), shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    assert np.array_equal(routing["ids"], want["ids"])
+    assert util.rel_max_error(blocks.float().cpu().numpy(), want["out"]) <= TOL

@@ -902,6 +902,13 @@ int zc_moe_set_option(zc_moe* m, const char* name, int value) {
         (name[10] == 'g' ? m->few_tiles_gate_up : m->few_tiles_down) = uint32_t(value);
         return ZC_OK;
     }
+    if (!std::strcmp(name, "meta_blocks")) {
+        if (value < 0 || value > 2) return fail(m, ZC_EINVAL, "meta_blocks must be 0, 1 or 2");
+        DeviceGuard guard(m->device);
+        drop_graphs(m);
+        m->meta_blocks = uint32_t(value);
+        return ZC_OK;
+    }
     if (!std::strcmp(name, "ep_wait_ms")) {
         if (value < 1 || value > 60000) return fail(m, ZC_EINVAL, "ep_wait_ms must be 1..60000");
         DeviceGuard guard(m->device);

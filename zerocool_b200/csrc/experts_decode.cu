@@ -55,7 +55,7 @@ constexpr int ROW_PAD = 8;            // halves added to each staged row (keeps 
 #endif
 
 // One ring stage of one matrix holds CHT quantisation groups of 16 rows: for every row one LINE of CHT x ROWB
-// contiguous code bytes (a full 128-byte line for Q4 with four groups and for Q8 with two), then the metadata.
+// contiguous code bytes (a full 128-byte line for Q4 with four groups and for Q8 with two).
 template <int BITS, int CHT> struct Fmt {
     static constexpr int ROWB = BITS * 8;                 // code bytes of one row of one group (64 weights)
     static constexpr int LINE = CHT * ROWB;               // code bytes of one row in one stage
@@ -63,8 +63,10 @@ template <int BITS, int CHT> struct Fmt {
     static constexpr int ROWS_PER_PASS = 32 / PIECES;
     static constexpr int PASSES = 16 / ROWS_PER_PASS;
     static constexpr int CODES = 16 * LINE;
-    static constexpr int META = 16 * 2 * CHT * 2;         // [row][scale, bias][CHT] halves
-    static constexpr int MATRIX = CODES + META;
+    static constexpr int MATRIX = CODES;                  // a ring stage holds the codes only
+    // Metadata of a matrix, beside the ring: [buffer][row][scale, bias][MG halves]. MG = 8 groups per block (one 16-byte
+    // copy per (row, kind), two buffers) where a warp walks K in order, else MG = CHT (one block per ring stage).
+    __host__ __device__ static constexpr int meta_area(bool mb8, int stages) { return mb8 ? 2 * 32 * 16 : stages * 32 * CHT * 2; }     // bytes per matrix per warp
     // Rows whose lines fall into the same 128-byte bank window are ROWS_PER_WINDOW apart; the block index of a row is
     // xor-ed with swizzle(row) so that rows read together by one MMA fragment load use different banks.
     static constexpr int ROWS_PER_WINDOW = LINE >= 128 ? 1 : 128 / LINE;
@@ -211,7 +213,7 @@ struct LaneSource {
     using F = Fmt<BITS, CHT>;
     const uint8_t* codes;      // record + codes offset + (row in pass) * row_bytes + piece * 16
     const uint8_t* meta;       // record + scales or biases offset (by kind) + row * G * 2
-    uint32_t row_bytes, dst0, meta_dst;
+    uint32_t row_bytes, dst0, meta_pair;      // meta_pair: this lane's (row, kind) index in a metadata block
     const uint8_t* tile_codes; // set per tile
     const uint8_t* tile_meta;
     __device__ __forceinline__ void init(const uint8_t* record, const Projection& pr, uint32_t lane, uint32_t G) {
@@ -221,7 +223,7 @@ struct LaneSource {
         dst0 = rip * F::LINE + ((block ^ F::swizzle(rip)) * F::ROWB) + within;      // swizzle(rip) == swizzle(row): passes add multiples of 4 rows
         codes = record + pr.codes + size_t(rip) * row_bytes + piece * 16;
         meta = record + (lane / 16 ? pr.biases : pr.scales) + size_t(lane % 16) * G * 2;
-        meta_dst = F::CODES + ((lane % 16) * 2 + lane / 16) * CHT * 2;
+        meta_pair = (lane % 16) * 2 + lane / 16;
     }
     __device__ __forceinline__ void set_tile(uint32_t row0, uint32_t G) {
         tile_codes = codes + size_t(row0) * row_bytes;
@@ -229,17 +231,25 @@ struct LaneSource {
     }
 };
 
-// Issue the cp.async copies of one chunk (CHT groups starting at grp0) of one matrix into a ring stage.
-template <int BITS, int CHT>
-__device__ __forceinline__ void issue_matrix(uint32_t stage, const LaneSource<BITS, CHT>& src, uint32_t grp0) {
+// Issue the cp.async copies of one chunk (CHT groups starting at grp0) of one matrix into a ring stage, and the
+// metadata that goes with it. MB8: one 16-byte copy per (row, kind) every eight groups, into buffer meta_buf of two (a
+// 4-byte copy per chunk moves a whole 32-byte sector for it and costs as many shared-memory wavefronts as a code copy);
+// otherwise the chunk's own scale and bias halves, into the buffer of its ring slot.
+template <int BITS, int CHT, bool MB8>
+__device__ __forceinline__ void issue_matrix(uint32_t stage, uint32_t meta_area, const LaneSource<BITS, CHT>& src, uint32_t grp0, uint32_t meta_buf, bool meta_now) {
     using F = Fmt<BITS, CHT>;
     const uint8_t* g0 = src.tile_codes + grp0 * F::ROWB;
 #pragma unroll
     for (int p = 0; p < F::PASSES; ++p)
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + src.dst0 + p * F::ROWS_PER_PASS * F::LINE),
                      "l"(g0 + size_t(p * F::ROWS_PER_PASS) * src.row_bytes) : "memory");
-    if constexpr (CHT == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(stage + src.meta_dst), "l"(src.tile_meta + grp0 * 2) : "memory");
-    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(stage + src.meta_dst), "l"(src.tile_meta + grp0 * 2) : "memory");
+    if constexpr (MB8) {
+        if (meta_now) asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(meta_area + meta_buf * 512 + src.meta_pair * 16), "l"(src.tile_meta + grp0 * 2) : "memory");
+    } else if constexpr (CHT == 4) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(meta_area + meta_buf * (32 * CHT * 2) + src.meta_pair * CHT * 2), "l"(src.tile_meta + grp0 * 2) : "memory");
+    } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(meta_area + meta_buf * (32 * CHT * 2) + src.meta_pair * CHT * 2), "l"(src.tile_meta + grp0 * 2) : "memory");
+    }
 }
 
 // (a & b) | c in one logic instruction.
@@ -325,13 +335,15 @@ __device__ __forceinline__ void group_mma(float (&d)[4], float c0, float c1, con
 //       go to two different warps, which halves the registers and ring of a warp (three CTAs per SM instead
 //       of two) at the price of meeting in shared memory for the SwiGLU.
 //   CH: quantisation groups per ring stage (4 when K is a multiple of 256, else 2; Q8 always 2).
-template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH>
+//   MB8: scales and biases arrive eight groups at a time (needs KS = 1 and a group count that is a multiple of eight).
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH, bool MB8>
 __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN : (MW == 2 ? 3 : ZC_MIN_BLOCKS)) expert_kernel(Call c, uint32_t tiles_per_warp) {
     using F = Fmt<BITS, CH>;
     constexpr int STAGES = stages_for(NMAT / MW, CH);
     constexpr int WM = NMAT / MW;                    // matrices per warp
     constexpr int RT = WARPS / (KS * MW);
     constexpr int STAGE = WM * F::MATRIX;
+    constexpr int META_AREA = F::meta_area(MB8, STAGES);
     constexpr bool VIA_SMEM = KS > 1 || MW > 1;
     constexpr int WORDS = F::ROWB / 16;              // 32-bit words per lane per row per group: 2 (Q4) / 4 (Q8)
     constexpr bool FOLDQ = FOLD && BITS == 4;
@@ -347,7 +359,8 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
     __half* xlo = xhi + (SPLIT ? NTOK * RS : 0);
     float* sums = reinterpret_cast<float*>(xhi + (SPLIT ? 2 : 1) * NTOK * RS);       // [G][NTOK][2]
     uint8_t* ring = reinterpret_cast<uint8_t*>(sums + G * NTOK * 2);                  // [WARPS][STAGES][STAGE]
-    float* red = reinterpret_cast<float*>(ring + WARPS * STAGES * STAGE);             // [KS][NMAT][RT*16][NTOK] when VIA_SMEM
+    uint8_t* meta_all = ring + WARPS * STAGES * STAGE;                                // [WARPS][WM][META_AREA]
+    float* red = reinterpret_cast<float*>(meta_all + WARPS * WM * META_AREA);      // [KS][NMAT][RT*16][NTOK] when VIA_SMEM
     __shared__ int rows[NTOK];
     __shared__ long long dest[NTOK];
 
@@ -355,6 +368,7 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
     const uint32_t mw = warp % MW, ks = (warp / MW) % KS, rt = warp / (MW * KS);
     const uint32_t first_tile = (blockIdx.x * RT + rt) * tiles_per_warp;
     uint8_t* my_ring = ring + warp * STAGES * STAGE;
+    uint8_t* my_meta = meta_all + warp * WM * META_AREA;
     const uint32_t nchunks = G / CH;                 // G is a multiple of CH
     const uint32_t my_n = ks < nchunks ? (nchunks - ks + KS - 1) / KS : 0;
     const uint32_t my_tiles = my_n ? tiles_per_warp : 0;
@@ -370,14 +384,18 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
     for (uint32_t pass = 0; pass * NTOK < it.count; ++pass) {
         const uint32_t nvalid = min(uint32_t(NTOK), it.count - pass * NTOK);
         uint32_t is_tile = 0, is_chunk = 0, is_slot = 0;        // producer position in the flattened (tile, chunk) sequence
-        const uint32_t ring_base = smem_u32(my_ring);
+        uint32_t is_mblk = 0;                  // MB8: metadata blocks issued so far; the next one goes to buffer is_mblk & 1
+        const uint32_t ring_base = smem_u32(my_ring), meta_base = smem_u32(my_meta);
 #pragma unroll
         for (int m = 0; m < WM; ++m) src[m].set_tile(first_tile * 16, G);
         auto issue = [&]() {
             if (is_tile < my_tiles) {
                 const uint32_t stage = ring_base + is_slot * STAGE, grp0 = (ks + is_chunk * KS) * CH;
+                const bool meta_now = MB8 && (is_chunk * CH) % 8 == 0;
+                const uint32_t meta_buf = MB8 ? (is_mblk & 1) : is_slot;
 #pragma unroll
-                for (int m = 0; m < WM; ++m) issue_matrix<BITS, CH>(stage + m * F::MATRIX, src[m], grp0);
+                for (int m = 0; m < WM; ++m) issue_matrix<BITS, CH, MB8>(stage + m * F::MATRIX, meta_base + m * META_AREA, src[m], grp0, meta_buf, meta_now);
+                if (meta_now) ++is_mblk;
                 if (++is_chunk == my_n) {
                     is_chunk = 0; ++is_tile;
 #pragma unroll
@@ -424,7 +442,7 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
             }
         };
 
-        uint32_t slot = 0;
+        uint32_t slot = 0, mblk = 0;           // mblk: metadata blocks the consumer has begun (MB8)
         for (uint32_t tile = 0; tile < tiles_per_warp; ++tile) {
             float acc[WM][4];
 #pragma unroll
@@ -433,6 +451,10 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
                 cp_async_wait<STAGES - 2>();
                 __syncwarp();
                 const uint8_t* stage = my_ring + slot * STAGE;
+                // this chunk's scale and bias halves: at its place in the current 8-group block (MB8), or in the buffer of its slot
+                if (MB8 && (i * CH) % 8 == 0) ++mblk;
+                constexpr uint32_t PAIR = MB8 ? 16u : uint32_t(CH * 2);          // bytes of one (row, kind) entry
+                const uint8_t* mbase = MB8 ? my_meta + ((mblk - 1) & 1) * 512 + ((i * CH) % 8) * 2 : my_meta + slot * (32 * CH * 2);
                 slot = slot + 1 == STAGES ? 0 : slot + 1;
                 issue();          // refills the slot consumed by the previous iteration while this chunk is multiplied
                 const uint32_t grp0 = (ks + i * KS) * CH;
@@ -441,10 +463,12 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
                 for (int m = 0; m < WM; ++m) {
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
-                        const uint8_t* mp = stage + m * F::MATRIX + F::CODES + (g + 8 * r) * (4 * CH);
+                        const uint8_t* mp = mbase + m * META_AREA + (g + 8 * r) * 2 * PAIR;
                         if constexpr (CH == 4) {
-                            const uint4 v = *reinterpret_cast<const uint4*>(mp);
-                            mraw[m][r][0] = v.x; mraw[m][r][1] = v.y; mraw[m][r][2] = v.z; mraw[m][r][3] = v.w;
+                            const uint2 sc = *reinterpret_cast<const uint2*>(mp), bi = *reinterpret_cast<const uint2*>(mp + PAIR);
+                            mraw[m][r][0] = sc.x; mraw[m][r][1] = sc.y; mraw[m][r][2] = bi.x; mraw[m][r][3] = bi.y;
+                        } else if constexpr (MB8) {
+                            mraw[m][r][0] = *reinterpret_cast<const uint32_t*>(mp); mraw[m][r][1] = *reinterpret_cast<const uint32_t*>(mp + PAIR);
                         } else {
                             const uint2 v = *reinterpret_cast<const uint2*>(mp);
                             mraw[m][r][0] = v.x; mraw[m][r][1] = v.y;
@@ -530,23 +554,39 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
     }
 }
 
-template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH>
-int launch_expert_ch(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH, bool MB8>
+int launch_expert_mb(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
     constexpr int RT = WARPS / (KS * MW);
     constexpr int STAGES = stages_for(NMAT / MW, CH);
     const uint32_t K = NMAT == 2 ? c.H : c.F, N = NMAT == 2 ? c.F : c.H, G = K / 64;
     const size_t smem = size_t(SPLIT ? 2 : 1) * NTOK * (K + ROW_PAD) * 2 + size_t(G) * NTOK * 2 * 4 +
-                        size_t(WARPS) * STAGES * (NMAT / MW) * Fmt<BITS, CH>::MATRIX + ((KS > 1 || MW > 1) ? size_t(KS) * NMAT * RT * 16 * NTOK * 4 : 0);
+                        size_t(WARPS) * (NMAT / MW) * (STAGES * Fmt<BITS, CH>::MATRIX + Fmt<BITS, CH>::meta_area(MB8, STAGES)) + ((KS > 1 || MW > 1) ? size_t(KS) * NMAT * RT * 16 * NTOK * 4 : 0);
     if (smem > 220 * 1024) return fail(m, ZC_EINVAL, "expert kernel: shape needs too much shared memory");
     while (tiles_per_warp > 1 && N % (16 * RT * tiles_per_warp)) --tiles_per_warp;
     if (N % (16 * RT * tiles_per_warp)) return fail(m, ZC_EINVAL, "expert kernel: rows not a multiple of the CTA tile");
-    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH>;
+    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, MB8>;
     static SmemOptIn configured;        // one per instantiation of this function template
     if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) return check_launch(m, "expert kernel attribute");
     Timed t(m, s, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN);
     const cudaError_t e = launch_chained(m, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN, kernel, dim3(N / (16 * RT * tiles_per_warp), items), dim3(EXPERT_THREADS), smem, s, nullptr, 0, c, tiles_per_warp);
     if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("expert kernel launch: ") + cudaGetErrorString(e));
     return check_launch(m, NMAT == 2 ? "gate_up" : "down");
+}
+
+// Metadata in 8-group blocks: possible where a warp walks K in order (KS = 1) and every block of a row's metadata is
+// 16-byte aligned; used for gate/up with long rows (hidden 4096: 423 -> 368 us at 512 experts x 5 rows). With short rows
+// the extra kilobyte per warp pushes two CTAs per SM over a shared-memory carve-out step, which costs the L1 that serves
+// the small copies (97 -> 104 us at hidden 2048), and down's short K does not gain (56 -> 58 us): those keep one block per
+// ring stage. Option meta_blocks: 0 never, 1 by this rule, 2 wherever possible.
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH>
+int launch_expert_ch(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
+    if constexpr (KS == 1) {
+        const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
+        const bool long_rows = NMAT == 2 && K >= 4096;
+        if (G % 8 == 0 && (m->meta_blocks == 2 || (m->meta_blocks == 1 && long_rows)))
+            return launch_expert_mb<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, true>(m, c, items, tiles_per_warp, s);
+    }
+    return launch_expert_mb<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, false>(m, c, items, tiles_per_warp, s);
 }
 
 // Two groups per ring stage for gate/up: four groups per stage (a full 128-byte line per Q4 row) leave room for
