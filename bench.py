@@ -369,7 +369,8 @@ def measure_long_batch(torch, m, cfg, tokens, steps, warmup, kind, biases, skip_
         "rows_last_layer": {"tensor_core_family": rows_big, "streaming_family": rows_small},
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst,
                      "frac_of_sustained": tf / sustained, "peak_source": tsource, "algorithmic_flops_per_launch": flops[dominant],
-                     "avg_launch_us": kernels[dominant]["avg_us"], "traffic": None,
+                     "avg_launch_us": kernels[dominant]["avg_us"],
+                     "traffic": ncu_traffic().get(dominant) if (kind == "prefill" and tokens == 2048) else None,      # the capture was taken at 2048 tokens
                      "definition": "2 x rows this kernel family processed (last layer's routing) x output columns x K of this launch (useful flops; "
                                    "padded token columns, the second FP16 term of the exact weights and the bias-correction stages are not counted)"},
         "roofline_step": {"tensor_tflops": step_flops / (ms * 1e-3) / 1e12, "frac_of_tensor_peak": step_flops / (ms * 1e-3) / 1e12 / burst,
