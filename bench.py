@@ -574,7 +574,9 @@ def run_ours(args):
     dist = None
     if world > 1:
         import torch.distributed as d
-        d.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a rank that fails inside a sub-record must not leave the others waiting for ten minutes
+        d.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=240))
         dist = d
     from zerocool_b200.moe import Moe
     hbm_peak, peak_source = peaks()
@@ -759,7 +761,10 @@ def run_ours(args):
         m4.close()
         del m4
     if not args.skip_ep:
-        ep = measure_ep(torch, dist, rank, world, local, args.layers, 256, 10 if world > 1 else 5, 3, args.skip_parity)
+        try:
+            ep = measure_ep(torch, dist, rank, world, local, args.layers, 256, 10 if world > 1 else 5, 3, args.skip_parity)
+        except Exception as exc:      # the headline measured above is still reported; the failure is part of the line
+            ep = {"error": f"{type(exc).__name__}: {exc}"[:400]}
 
     if rank == 0:
         line = {
