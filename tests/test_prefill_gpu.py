@@ -185,3 +185,30 @@ def test_bounded_waits_give_up_and_leave_the_context_usable():
     assert m.status() == 0
     assert np.array_equal(again, out)
     check_against_oracle(cfg, x, again, routing)
+
+
+def test_bf16_scale_below_fp16_range_raises_the_range_bit():
+    """BF16 metadata reaches far below FP16: a scale of 2e-6 would lose bits (FP16 subnormal) as the factor of the
+    two-term weights, so the tensor-core family reports it in the status word instead of rounding it silently."""
+    from zerocool_b200.moe import STATUS_RANGE
+    from zerocool_b200.records import build_record, float_to_meta
+    cfg = util.cfg2(experts=32, top_k=4, max_tokens=256, meta_dtype=BF16)
+    tiny = None
+    records = []
+    for e in range(cfg.experts):
+        parts = []
+        for p in range(3):
+            codes, sbits, bbits = synth.projection_parts(cfg, SEED, 0, e, p)
+            if p == 0:
+                sbits = sbits.copy()
+                sbits.reshape(-1)[5] = float_to_meta(np.array([2e-6], np.float32), BF16)[0]
+                tiny = sbits
+            parts.append((codes, sbits, bbits))
+        records.append(build_record(cfg, parts))
+    m = make(cfg)
+    m.load_layer(0, records=np.stack(records), router_w=synth.router(cfg, SEED, 0), shared_record=synth.record(cfg, SEED, 0, synth.SHARED_EXPERT),
+                 shared_gate_w=synth.shared_gate(cfg, SEED, 0))
+    x = synth.activations(cfg, SEED, 0, 200)
+    m.prefill(0, device_x(m, x))
+    assert m.status() & STATUS_RANGE
+    assert tiny is not None

@@ -649,6 +649,10 @@ __device__ unsigned long long pw_stamps[4][96][8];
 #define PW_STAMP(role, stage, slot) do {} while (0)
 #endif
 
+// A BF16 scale or bias must survive the conversion to FP16 (the A' operand of the correction stages and the factor of the
+// two-term weights): zero, or a magnitude in [2^-14, 65504]. Anything else is reported, not silently rounded.
+__device__ __forceinline__ bool pw_meta_fits_f16(float v) { const float a = fabsf(v); return a == 0.0f || (a >= 6.103515625e-5f && a <= 65504.0f); }
+
 struct PwSmem {
     uint32_t b_ring, raw, meta, total;
     __host__ __device__ PwSmem(uint32_t G, uint32_t DR, uint32_t bits) {
@@ -755,6 +759,7 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
         const uint32_t lane_base = (quad * 32) << 16;
         // metadata of the row -> A' tile [s_0..s_G-1 | b_0..b_G-1] as FP16 (the correction stages' A operand, and where
         // this thread reads its scales)
+        bool meta_bad = false;
         {
             const uint8_t* sc = record + pr.scales + size_t(mrow) * G * 2;
             const uint8_t* bi = record + pr.biases + size_t(mrow) * G * 2;
@@ -770,8 +775,11 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                         uint32_t ha[4], hb[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const __half2 x = __floats2half2_rn(__uint_as_float(ra[i] << 16), __uint_as_float(ra[i] & 0xffff0000u));
-                            const __half2 y = __floats2half2_rn(__uint_as_float(rb[i] << 16), __uint_as_float(rb[i] & 0xffff0000u));
+                            const float s0 = __uint_as_float(ra[i] << 16), s1 = __uint_as_float(ra[i] & 0xffff0000u);
+                            const float b0 = __uint_as_float(rb[i] << 16), b1 = __uint_as_float(rb[i] & 0xffff0000u);
+                            meta_bad |= !(pw_meta_fits_f16(s0) && pw_meta_fits_f16(s1) && pw_meta_fits_f16(b0) && pw_meta_fits_f16(b1));
+                            const __half2 x = __floats2half2_rn(s0, s1);
+                            const __half2 y = __floats2half2_rn(b0, b1);
                             ha[i] = *reinterpret_cast<const uint32_t*>(&x); hb[i] = *reinterpret_cast<const uint32_t*>(&y);
                         }
                         *reinterpret_cast<uint4*>(at(dst + ch * 128)) = make_uint4(ha[0], ha[1], ha[2], ha[3]);
@@ -787,12 +795,14 @@ __global__ void __launch_bounds__(PW_THREADS, 1) prefill_wide_kernel(Call c, con
                         const uint16_t sr = *reinterpret_cast<const uint16_t*>(sc + g * 2), br = *reinterpret_cast<const uint16_t*>(bi + g * 2);
                         sv = c.meta_f16 ? __ushort_as_half(sr) : __float2half_rn(bf_to_float(sr));
                         bv = c.meta_f16 ? __ushort_as_half(br) : __float2half_rn(bf_to_float(br));
+                        if (!c.meta_f16) meta_bad |= !(pw_meta_fits_f16(bf_to_float(sr)) && pw_meta_fits_f16(bf_to_float(br)));
                     }
                     *reinterpret_cast<__half*>(at(dst + (g / 8) * 128 + (g % 8) * 2)) = sv;
                     *reinterpret_cast<__half*>(at(dst + (Gp / 8 + g / 8) * 128 + (g % 8) * 2)) = bv;
                 }
             }
         }
+        if (meta_bad) atomicOr(status, ZC_STATUS_RANGE);
         PW_STAMP(1, 0, 1);
         // Token rows of a main stage: 128 bytes per row = 8 pieces; thread t copies piece (row t / 8 + 32 i, chunk t mod 8)
         // for i < 4. The row pointers are prepared once; a stage adds 128 bytes.
