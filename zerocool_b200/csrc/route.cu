@@ -446,11 +446,116 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_place_kernel(const in
 // Route (one warp per token, eight tokens per CTA) and, when asked, the permutation as the tail of the
 // last CTA to finish, so that a layer needs one launch for both. Dynamic shared memory: the eight score rows
 // [8][E] floats, reused as the [8][E] histogram of the permutation.
+// The permutation of a batch that one routing CTA covers (at most eight tokens, so at most 256 slots): the selections
+// are still in shared memory, so each slot finds its place by counting - its expert's first position is the number of
+// slots with a smaller expert id, its rank the number of earlier slots with the same id - and each expert's first slot
+// writes the expert's entry of the work list. No histogram, no scan, no re-read of the ids from global memory, and no
+// arrival counter; the result is the same stable counting sort.
+__device__ __forceinline__ void permute_small(const RouteArgs& a, const int32_t (*selected)[32], int32_t* flat, int32_t* opens /* [256] shared each */) {
+    const uint32_t slots = a.T * a.K, E = a.E, tid = threadIdx.x;
+    for (uint32_t i = tid; i < E; i += ROUTE_THREADS) a.items[i].x = -1;         // entries past the end of the new list
+    if (tid < slots) {                      // slot p = t K + j in one flat array; anything that is not an expert id becomes -1
+        const int32_t id = selected[tid / a.K][tid % a.K];
+        flat[tid] = (id >= 0 && uint32_t(id) < E) ? id : -1;
+    }
+    __syncthreads();
+    int32_t mine = -1, before = 0, rank = 0, count = 0;
+    bool opener = false;
+    if (tid < slots) {
+        mine = flat[tid];
+        if (mine >= 0) {
+            for (uint32_t q = 0; q < slots; ++q) {
+                const int32_t other = flat[q];
+                before += other >= 0 && other < mine;
+                count += other == mine;
+                rank += (other == mine) && q < tid;
+            }
+            a.perm[before + rank] = int32_t(tid);
+            opener = rank == 0 && uint32_t(mine) >= a.first_expert && uint32_t(mine) < a.first_expert + a.local_experts;
+        }
+    }
+    if (tid < 256) opens[tid] = opener ? mine : -1;                             // the expert ids that open a work-list entry
+    for (uint32_t e = tid; e <= E; e += ROUTE_THREADS) {                        // offsets[e] = slots routed to experts below e
+        int32_t below = 0;
+        for (uint32_t q = 0; q < slots; ++q) below += flat[q] >= 0 && uint32_t(flat[q]) < e;
+        a.offsets[e] = below;
+    }
+    __syncthreads();
+    if (opener) {
+        int32_t entry = 0;
+        for (uint32_t q = 0; q < slots; ++q) entry += opens[q] >= 0 && opens[q] < mine;
+        a.active[entry] = mine;
+        a.items[entry] = make_int4(mine, before, count, 0);
+    }
+    if (tid == 0) {
+        int32_t entries = 0;
+        for (uint32_t q = 0; q < slots; ++q) entries += opens[q] >= 0;
+        a.counters[0] = entries; a.counters[16 + a.layer] = entries;
+    }
+}
+
+// Route (one warp per token, eight tokens per CTA) and, when asked, the permutation as the tail of the
+// last CTA to finish, so that a layer needs one launch for both. Dynamic shared memory: the eight score rows
+// [8][E] floats, reused as the [8][E] histogram of the permutation.
+// The permutation of a batch that one routing CTA covers (at most eight tokens, so at most 256 slots): the selections
+// are still in shared memory, so each slot finds its place by counting - its expert's first position is the number of
+// slots with a smaller expert id, its rank the number of earlier slots with the same id - and each expert's first slot
+// writes the expert's entry of the work list. No histogram, no scan, no re-read of the ids from global memory, and no
+// arrival counter; the result is the same stable counting sort.
+__device__ __forceinline__ void permute_small(const RouteArgs& a, const int32_t (*selected)[32], int32_t* flags /* [256] shared */) {
+    const uint32_t slots = a.T * a.K, E = a.E, tid = threadIdx.x;
+    auto id_of = [&](uint32_t p) { return selected[p / a.K][p % a.K]; };
+    for (uint32_t i = tid; i < E; i += ROUTE_THREADS) a.items[i].x = -1;         // entries past the end of the new list
+    int32_t mine = -1, before = 0, rank = 0, count = 0;
+    bool first = false, local = false;
+    if (tid < slots) {
+        mine = id_of(tid);
+        if (mine >= 0 && uint32_t(mine) < E) {
+            for (uint32_t q = 0; q < slots; ++q) {
+                const int32_t other = id_of(q);
+                if (other < 0 || uint32_t(other) >= E) continue;
+                before += other < mine;
+                count += other == mine;
+                rank += (other == mine) && q < tid;
+            }
+            first = rank == 0;
+            local = uint32_t(mine) >= a.first_expert && uint32_t(mine) < a.first_expert + a.local_experts;
+            a.perm[before + rank] = int32_t(tid);
+        }
+    }
+    if (tid < 256) flags[tid] = (first && local) ? mine : -1;                   // the expert ids that open a work-list entry
+    // offsets[e] = slots routed to experts below e
+    uint32_t valid = 0;
+    for (uint32_t e = tid; e <= E; e += ROUTE_THREADS) {
+        int32_t below = 0;
+        for (uint32_t q = 0; q < slots; ++q) { const int32_t other = id_of(q); below += other >= 0 && uint32_t(other) < E && uint32_t(other) < e; }
+        a.offsets[e] = below;
+        if (e == E) valid = uint32_t(below);
+    }
+    (void)valid;
+    __syncthreads();
+    if (first && local) {
+        int32_t entry = 0;
+        for (uint32_t q = 0; q < slots; ++q) entry += flags[q] >= 0 && flags[q] < mine;
+        a.active[entry] = mine;
+        a.items[entry] = make_int4(mine, before, count, 0);
+    }
+    if (tid == 0) {
+        int32_t entries = 0;
+        for (uint32_t q = 0; q < slots; ++q) entries += flags[q] >= 0;
+        a.counters[0] = entries; a.counters[16 + a.layer] = entries;
+    }
+}
+
+// Route (one warp per token, eight tokens per CTA) and, when asked, the permutation as the tail of the
+// last CTA to finish, so that a layer needs one launch for both. Dynamic shared memory: the eight score rows
+// [8][E] floats, reused as the [8][E] histogram of the permutation.
 template <int MAXC>
 __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
     extern __shared__ int32_t hist[];
     __shared__ float scores[ROUTE_WARPS][32];
     __shared__ int32_t selected[ROUTE_WARPS][32];
+    __shared__ int32_t flat[256], opens[256];
     __shared__ bool last;
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t t = blockIdx.x * ROUTE_WARPS + warp;
@@ -458,6 +563,11 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
     pdl_launch_dependents();
     if (t < a.T) route_token<MAXC>(a, t, lane, reinterpret_cast<float*>(hist) + warp * a.E, scores[warp], selected[warp]);
     if (!a.do_permute) return;
+    if (gridDim.x == 1) {                   // this CTA routed every token: ROUTE_WARPS x K <= 256 slots
+        __syncthreads();
+        permute_small(a, selected, flat, opens);
+        return;
+    }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) last = atomicAdd(a.done, 1u) == gridDim.x - 1;
