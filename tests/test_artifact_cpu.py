@@ -93,3 +93,32 @@ def test_manifest_checks(tmp_path):
     os.truncate(os.path.join(str(tmp_path), artifact.layer_file(0)), cfg.record_stride * 7)
     with pytest.raises(RuntimeError, match="invalid prepared expert length"):
         artifact.PreparedExperts(str(tmp_path), cfg)
+
+
+def test_repack_of_stacked_checkpoint_tensors_is_lossless(tmp_path):
+    """The nine stacked tensors of a checkpoint layer (switch_mlp.<proj>.<piece>[expert]) become the records byte for
+    byte (scripts/qwen/prepare_storage.py:133-152), for 4- and 8-bit projections; wrong shapes are refused."""
+    cfg = tiny(down_bits=8)
+    stacks = {name: [] for name in artifact.PIECES}
+    for e in range(cfg.experts):
+        for p, proj in enumerate(("gate_proj", "up_proj", "down_proj")):
+            codes, scales, biases = synth.projection_parts(cfg, SEED, 1, e, p)
+            lay = cfg.projection_layout(p)
+            stacks[proj + ".weight"].append(np.ascontiguousarray(codes, dtype=np.uint8).reshape(lay["N"], -1).view(np.uint32))
+            stacks[proj + ".scales"].append(scales)
+            stacks[proj + ".biases"].append(biases)
+    tensors = {name: np.stack(v) for name, v in stacks.items()}
+    records = list(artifact.repack_switch_mlp(cfg, tensors))
+    assert len(records) == cfg.experts
+    for e, record in enumerate(records):
+        assert np.array_equal(record, synth.record(cfg, SEED, 1, e))
+    artifact.write_artifact(str(tmp_path), tiny(down_bits=8, layers=1), lambda layer: artifact.repack_switch_mlp(cfg, tensors))
+    prepared = artifact.PreparedExperts(str(tmp_path), tiny(down_bits=8, layers=1))
+    got = np.concatenate([block.copy() for _, block in prepared.runs(0, run_experts=3)])      # the staging buffer is reused between runs
+    assert np.array_equal(got, np.stack(records))
+    bad = dict(tensors)
+    bad["up_proj.scales"] = tensors["up_proj.scales"][:, :, :-1]
+    with pytest.raises(ValueError):
+        list(artifact.repack_switch_mlp(cfg, bad))
+    with pytest.raises(ValueError):
+        list(artifact.repack_switch_mlp(cfg, {k: v for k, v in tensors.items() if k != "down_proj.biases"}))

@@ -11,7 +11,9 @@ is handed to ``zc_moe_load_layer`` (one host-to-device copy per run), and the SH
 the manifest's on the way. 8-bit projections and FP16 metadata (``dtype: "F16"``) are admitted next to the
 reference's Q4 / BF16.
 
-``write_artifact`` produces such a directory from records in memory (tests, synthetic checkpoints).
+``write_artifact`` produces such a directory from records in memory (tests, synthetic checkpoints);
+``repack_switch_mlp`` turns a checkpoint layer's nine stacked tensors into those records, the lossless repack of
+prepare_storage.py:133-152 for a parametric geometry.
 """
 import hashlib
 import json
@@ -41,6 +43,39 @@ def expert_layout(cfg: MoeConfig):
         out.append(dict(name=PIECES[3 * p + 2], offset=lay["biases"], length=lay["meta_bytes"], shape=[n, k // cfg.group],
                         dtype=meta, bits=bits, group_size=cfg.group))
     return out
+
+
+def repack_switch_mlp(cfg: MoeConfig, tensors):
+    """The records of one layer from the checkpoint's stacked expert tensors.
+
+    tensors maps the nine piece names (``gate_proj.weight`` ... ``down_proj.biases``, the suffix of the checkpoint's
+    ``...mlp.switch_mlp.<piece>`` keys) to arrays whose first axis is the expert: weights ``[E, N, K*bits/32]`` uint32
+    (or the same bytes as uint8), scales and biases ``[E, N, K/group]`` as 16-bit patterns in the metadata dtype. Yields
+    cfg.experts records of record_stride bytes: for every expert its nine slices back to back in that order, padded to
+    the stride - bytes are moved, never re-encoded. Shapes and sizes are checked against the geometry first (the
+    reference's writer refuses a checkpoint whose pieces do not add up to the record length, prepare_storage.py:143-144)."""
+    layout = expert_layout(cfg)
+    pieces = []
+    for entry in layout:
+        if entry["name"] not in tensors:
+            raise ValueError(f"missing tensor {entry['name']}")
+        t = np.ascontiguousarray(tensors[entry["name"]])
+        if t.shape[0] != cfg.experts:
+            raise ValueError(f"{entry['name']}: {t.shape[0]} experts, geometry has {cfg.experts}")
+        width = 4 if entry["dtype"] == "U32" else 2
+        if t.dtype.itemsize not in (1, width) or t.dtype.kind not in "ui":
+            raise ValueError(f"{entry['name']}: expected {entry['dtype']} bit patterns (or bytes), got {t.dtype}")
+        per_expert = t.reshape(cfg.experts, -1).view(np.uint8)
+        if per_expert.shape[1] != entry["length"]:
+            raise ValueError(f"{entry['name']}: {per_expert.shape[1]} bytes per expert, layout has {entry['length']} (shape {entry['shape']})")
+        pieces.append((entry["offset"], per_expert))
+    if sum(p.shape[1] for _, p in pieces) != cfg.record_bytes:
+        raise ValueError("unsupported expert format: the pieces do not add up to the record length")
+    for e in range(cfg.experts):
+        record = np.zeros(cfg.record_stride, np.uint8)
+        for offset, per_expert in pieces:
+            record[offset:offset + per_expert.shape[1]] = per_expert[e]
+        yield record
 
 
 def layer_file(layer):
