@@ -381,7 +381,9 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
         src[j].init(it.record, NMAT == 1 ? c.down : (mi == 0 ? c.gate : c.up), lane, G);
     }
 
-    for (uint32_t pass = 0; pass * NTOK < it.count; ++pass) {
+    // An item with more than eight rows takes several passes; with gridDim.z > 1 they are spread over that many CTAs
+    // (a pass is independent of the others), so that one long item does not set the duration of a launch.
+    for (uint32_t pass = blockIdx.z; pass * NTOK < it.count; pass += gridDim.z) {
         const uint32_t nvalid = min(uint32_t(NTOK), it.count - pass * NTOK);
         uint32_t is_tile = 0, is_chunk = 0, is_slot = 0;        // producer position in the flattened (tile, chunk) sequence
         uint32_t is_mblk = 0;                  // MB8: metadata blocks issued so far; the next one goes to buffer is_mblk & 1
@@ -564,11 +566,14 @@ int launch_expert_mb(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_pe
     if (smem > 220 * 1024) return fail(m, ZC_EINVAL, "expert kernel: shape needs too much shared memory");
     while (tiles_per_warp > 1 && N % (16 * RT * tiles_per_warp)) --tiles_per_warp;
     if (N % (16 * RT * tiles_per_warp)) return fail(m, ZC_EINVAL, "expert kernel: rows not a multiple of the CTA tile");
+    // Items that can have more than eight rows (two or more rows per expert on average, or the few-row side of a long
+    // batch with its limit above eight): their passes run as separate CTAs.
+    const uint32_t pass_ctas = (KS == 1 && (c.item_rows_max > NTOK || uint64_t(c.T) * c.K >= 2ull * c.local_experts)) ? 2u : 1u;
     auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, MB8>;
     static SmemOptIn configured;        // one per instantiation of this function template
     if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) return check_launch(m, "expert kernel attribute");
     Timed t(m, s, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN);
-    const cudaError_t e = launch_chained(m, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN, kernel, dim3(N / (16 * RT * tiles_per_warp), items), dim3(EXPERT_THREADS), smem, s, nullptr, 0, c, tiles_per_warp);
+    const cudaError_t e = launch_chained(m, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN, kernel, dim3(N / (16 * RT * tiles_per_warp), items, pass_ctas), dim3(EXPERT_THREADS), smem, s, nullptr, 0, c, tiles_per_warp);
     if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("expert kernel launch: ") + cudaGetErrorString(e));
     return check_launch(m, NMAT == 2 ? "gate_up" : "down");
 }
