@@ -495,8 +495,8 @@ def measure_ep(torch, dist, rank, world, local, layers, total_tokens, steps, war
         "nvlink": {"remote_rows_per_layer_all_ranks": remote_sum, "bytes_per_layer_all_ranks": remote_sum * (row_bytes + cfg.hidden * 4 + 8),
                    "definition": "rows whose expert lives on another rank (last layer's routing): bf16 row + 8-byte tag out, fp32 result row back"},
         "kernels_rank0": kernels, "exchange_share_rank0": sum(v["share"] for v in ep_kinds.values()) if kernels else None,
-        "exchange_note": "kind 'ep' = send, receive (includes the wait for the slowest sender), return and the wait for results; event-timed "
-                         "eager launches on rank 0" if kernels else None,
+        "exchange_note": "kind 'ep' = send, receive + sort of the received rows (includes the wait for the slowest sender) and return; the wait for "
+                         "the owners' results is inside the combine kernel; event-timed eager launches on rank 0" if kernels else None,
         "parity": parity,
     }
 

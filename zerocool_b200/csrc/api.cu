@@ -564,12 +564,16 @@ int ep_send_phase(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, cud
 // into the senders' windows and publish the return flags.
 int ep_process_phase(zc_moe* m, uint32_t layer, cudaStream_t s) {
     int n, total = 0;
-    if ((n = launch_ep_receive(m, s)) < 0) return n; total += n;
     Call q = m->ep;
     const LayerMem& L = m->layers[layer];
     q.x = m->ep_window + m->ep_layout.rows; q.records = L.records; q.ids = m->ep_row_ids;
     q.T = m->ep_world * m->ep_layout.cap; q.layer = layer; q.status = m->scratch.status; q.quiet_drop = 1;
-    if ((n = launch_route_permute(m, q, s, false, true)) < 0) return n; total += n;
+    if ((n = launch_ep_receive_permute(m, q, s)) < 0) return n;
+    if (n == 0) {                           // a receive area too large for one sorting CTA: two launches
+        if ((n = launch_ep_receive(m, s)) < 0) return n; total += n;
+        if ((n = launch_route_permute(m, q, s, false, true)) < 0) return n;
+    }
+    total += n;
     if ((n = launch_experts_decode(m, q, s)) < 0) return n; total += n;
     if ((n = launch_ep_return(m, s)) < 0) return n; total += n;
     return total;
@@ -579,9 +583,11 @@ int ep_process_phase(zc_moe* m, uint32_t layer, cudaStream_t s) {
 // window), then the fixed-order combine; with `next` also the normalised input of the following layer.
 int ep_finish_phase(zc_moe* m, uint32_t layer, const void* x, uint32_t tokens, void* out, cudaStream_t s, void* next) {
     int n, total = 0;
-    if ((n = launch_ep_returned(m, s)) < 0) return n; total += n;
     Call c = make_call(m, layer, x, tokens, out);
     c.expert_out = reinterpret_cast<float*>(m->ep_window + m->ep_layout.out);
+    // the combine's CTAs wait themselves for the owners' return flags (no launch that only waits)
+    c.ep_ret_flags = reinterpret_cast<const unsigned long long*>(m->ep_window + m->ep_layout.ret_flags);
+    c.ep_ctl = m->ep_ctl; c.ep_world = m->ep_world; c.ep_wait_ns = (unsigned long long)(m->ep_wait_ms) * 1000000ull;
     n = next ? launch_combine_norm(m, c, next, m->d.act_dtype, s) : launch_combine(m, c, s);
     if (n < 0) return n; total += n;
     return total;

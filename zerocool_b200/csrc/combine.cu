@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(Call c) {
     const uint32_t col = (blockIdx.x * COMBINE_THREADS + threadIdx.x) * 4;
     pdl_wait();
     pdl_launch_dependents();
+    ep_wait_results(c);
     if (col >= c.H) return;
     for (uint32_t t = blockIdx.y; t < c.T; t += gridDim.y) {
         float r[4];
@@ -131,6 +132,7 @@ template <int KMAX>
 __global__ void __launch_bounds__(COMBINE_THREADS, 2) combine_long_kernel(Call c) {
     pdl_wait();
     pdl_launch_dependents();
+    ep_wait_results(c);
     for (uint32_t t = blockIdx.x; t < c.T; t += gridDim.x) {
         for (uint32_t col = threadIdx.x * 4; col < c.H; col += COMBINE_THREADS * 8) {
             float r[2][4];
@@ -157,6 +159,7 @@ __global__ void __launch_bounds__(CN_THREADS) combine_norm_kernel(Call c, void* 
     __shared__ float partial[CN_THREADS / 32];
     pdl_wait();
     pdl_launch_dependents();
+    ep_wait_results(c);
     for (uint32_t t = blockIdx.x; t < c.T; t += gridDim.x) {
     float sum = 0.0f;
     constexpr int NV = CN_THREADS == 256 ? 2 : 1;          // the long-batch form keeps two vectors per thread in flight
@@ -233,6 +236,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_hc_kernel(Call c, con
     const uint32_t col = (blockIdx.x * COMBINE_THREADS + threadIdx.x) * 4;
     pdl_wait();
     pdl_launch_dependents();
+    ep_wait_results(c);
     if (col >= c.H) return;
     float m[4];
     combine_columns<KMAX>(c, t, col, m);

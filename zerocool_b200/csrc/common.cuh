@@ -122,6 +122,11 @@ struct Call {
     uint8_t act_dtype, out_dtype, meta_f16, router_dtype, has_shared, ref, q8_signed;
     uint32_t item_rows_max;   // decode family: items with more rows than this are left to the tensor-core family (0 = no limit)
     uint8_t quiet_drop;       // the permutation drops ids outside [0, E) without raising the status bit (unused row slots of a receive area)
+    // expert parallelism, sender side: the combine waits (bounded) for every owner's return flag of the current epoch
+    const unsigned long long* ep_ret_flags;   // [ep_world] in this rank's window; null outside expert parallelism
+    const uint32_t* ep_ctl;                   // [0] = epoch
+    uint32_t ep_world;
+    unsigned long long ep_wait_ns;
 };
 
 // Expert parallelism over peer memory (csrc/ep.cu). Every rank owns one window with this layout (byte offsets).
@@ -138,6 +143,78 @@ struct EpWindow {
 };
 struct EpPeers { uint8_t* base[EP_MAX_RANKS]; };
 EpWindow ep_window_layout(const zc_moe_desc& d);
+
+struct EpArgs {
+    EpPeers peers;
+    EpWindow win;
+    uint32_t me, world, per;          // this rank, ranks, experts per rank
+    uint32_t* ctl;                    // [0] epoch, [1] send arrivals, [2] return arrivals
+    uint32_t* status;
+    unsigned long long wait_ns;
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait of one thread for flag word `p` to carry an epoch >= `epoch`. Returns the word, or 0 after
+// the limit (the caller then treats the source as having sent nothing). Once the status word carries the
+// time-out bit, later waits give up at once, so a stack of layers does not wait the limit again per layer.
+__device__ __forceinline__ unsigned long long ep_wait(const unsigned long long* p, uint32_t epoch, uint32_t* status, unsigned long long limit_ns) {
+    unsigned long long v = ld_acquire_sys(p);
+    if (uint32_t(v >> 32) >= epoch) return v;
+    if (*reinterpret_cast<volatile uint32_t*>(status) & ZC_STATUS_TIMEOUT) return 0;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        __nanosleep(200);
+        v = ld_acquire_sys(p);
+        if (uint32_t(v >> 32) >= epoch) return v;
+        if (global_ns() - t0 > limit_ns) break;
+    }
+    atomicOr(status, ZC_STATUS_TIMEOUT);
+    return 0;
+}
+// Owner side of the peer transport: wait for every source's flag of the current epoch, then write the expert id of every
+// row slot of the receive area (-1 for slots beyond a source's count, and for ids outside this rank's range). One CTA.
+__device__ __forceinline__ void ep_receive_body(const EpArgs& a, int32_t* __restrict__ row_ids, uint32_t* __restrict__ counts, uint32_t* count_s /* shared [EP_MAX_RANKS] */) {
+    const uint8_t* mine = a.peers.base[a.me];
+    const uint32_t epoch = a.ctl[0];
+    if (threadIdx.x < a.world) {
+        const unsigned long long v = ep_wait(reinterpret_cast<const unsigned long long*>(mine + a.win.in_flags) + threadIdx.x, epoch, a.status, a.wait_ns);
+        const uint32_t n = uint32_t(v >> 32) >= epoch && epoch ? min(uint32_t(v), a.win.cap) : 0u;
+        count_s[threadIdx.x] = n;
+        counts[threadIdx.x] = n;
+    }
+    __syncthreads();
+    const int2* tags = reinterpret_cast<const int2*>(mine + a.win.tags);
+    const uint32_t first = a.me * a.per;
+    for (uint32_t i = threadIdx.x; i < a.world * a.win.cap; i += blockDim.x) {
+        const uint32_t src = i / a.win.cap, j = i % a.win.cap;
+        int32_t id = -1;
+        if (j < count_s[src]) {
+            id = __ldcg(&tags[i].x);
+            if (id < int32_t(first) || id >= int32_t(first + a.per)) id = -1;
+        }
+        row_ids[i] = id;
+    }
+}
+// Sender side, inside the combine kernels: every CTA waits for the owners' return flags before it reads the results.
+__device__ __forceinline__ void ep_wait_results(const Call& c) {
+    if (!c.ep_ret_flags) return;
+    if (threadIdx.x < c.ep_world) ep_wait(c.ep_ret_flags + threadIdx.x, c.ep_ctl[0], c.status, c.ep_wait_ns);
+    __syncthreads();
+}
+#endif
 
 }  // namespace zc
 
@@ -221,8 +298,9 @@ int launch_ep_gather(zc_moe* m, const Call& c, void* rows, int32_t* row_experts,
 int launch_ep_scatter(zc_moe* m, const Call& c, const float* y, cudaStream_t s);
 int launch_ep_send(zc_moe* m, const Call& c, cudaStream_t s);
 int launch_ep_receive(zc_moe* m, cudaStream_t s);
+int launch_ep_receive_permute(zc_moe* m, const Call& q, cudaStream_t s);   // both in one launch (route.cu); 0 = not applicable
+EpArgs ep_args(const zc_moe* m);
 int launch_ep_return(zc_moe* m, cudaStream_t s);
-int launch_ep_returned(zc_moe* m, cudaStream_t s);
 int launch_hc_mix(zc_moe* m, const float* n, const float* mix, uint32_t T, uint32_t H, void* x, int x_dtype, cudaStream_t s);
 int launch_combine_hc(zc_moe* m, const Call& c, const float* hyper, const float* inject, float* out, cudaStream_t s);
 int launch_activation_table(const float* x, uint32_t n, float* sigmoid_out, float* silu_out, cudaStream_t s);

@@ -54,47 +54,6 @@ namespace {
 
 constexpr int EP_THREADS = 128;
 
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-struct EpArgs {
-    EpPeers peers;
-    EpWindow win;
-    uint32_t me, world, per;          // this rank, ranks, experts per rank
-    uint32_t* ctl;                    // [0] epoch, [1] send arrivals, [2] return arrivals
-    uint32_t* status;
-    unsigned long long wait_ns;
-};
-
-// Bounded wait of one thread for flag word `p` to carry an epoch >= `epoch`. Returns the word, or 0 after
-// the limit (the caller then treats the source as having sent nothing). Once the status word carries the
-// time-out bit, later waits give up at once, so a stack of layers does not wait the limit again per layer.
-__device__ __forceinline__ unsigned long long ep_wait(const unsigned long long* p, uint32_t epoch, uint32_t* status, unsigned long long limit_ns) {
-    unsigned long long v = ld_acquire_sys(p);
-    if (uint32_t(v >> 32) >= epoch) return v;
-    if (*reinterpret_cast<volatile uint32_t*>(status) & ZC_STATUS_TIMEOUT) return 0;
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-        __nanosleep(200);
-        v = ld_acquire_sys(p);
-        if (uint32_t(v >> 32) >= epoch) return v;
-        if (global_ns() - t0 > limit_ns) break;
-    }
-    atomicOr(status, ZC_STATUS_TIMEOUT);
-    return 0;
-}
-
 // Last-block election: every thread's stores are fenced at system scope, then one arrival per block.
 __device__ __forceinline__ bool ep_last_block(uint32_t* counter) {
     __shared__ bool last;
@@ -142,26 +101,7 @@ __global__ void __launch_bounds__(EP_THREADS) ep_send_kernel(EpArgs a, const voi
 // of the receive area (-1 for slots beyond a source's count, and for ids outside this rank's range).
 __global__ void __launch_bounds__(1024) ep_receive_kernel(EpArgs a, int32_t* __restrict__ row_ids, uint32_t* __restrict__ counts) {
     __shared__ uint32_t count_s[EP_MAX_RANKS];
-    const uint8_t* mine = a.peers.base[a.me];
-    const uint32_t epoch = a.ctl[0];
-    if (threadIdx.x < a.world) {
-        const unsigned long long v = ep_wait(reinterpret_cast<const unsigned long long*>(mine + a.win.in_flags) + threadIdx.x, epoch, a.status, a.wait_ns);
-        const uint32_t n = uint32_t(v >> 32) >= epoch && epoch ? min(uint32_t(v), a.win.cap) : 0u;
-        count_s[threadIdx.x] = n;
-        counts[threadIdx.x] = n;
-    }
-    __syncthreads();
-    const int2* tags = reinterpret_cast<const int2*>(mine + a.win.tags);
-    const uint32_t first = a.me * a.per;
-    for (uint32_t i = threadIdx.x; i < a.world * a.win.cap; i += 1024) {
-        const uint32_t src = i / a.win.cap, j = i % a.win.cap;
-        int32_t id = -1;
-        if (j < count_s[src]) {
-            id = __ldcg(&tags[i].x);
-            if (id < int32_t(first) || id >= int32_t(first + a.per)) id = -1;
-        }
-        row_ids[i] = id;
-    }
+    ep_receive_body(a, row_ids, counts, count_s);
 }
 
 // Owner side: result row i of the receive area -> the sender's window at the row's router slot. The last block
@@ -183,12 +123,6 @@ __global__ void __launch_bounds__(EP_THREADS) ep_return_kernel(EpArgs a, const f
         __threadfence_system();
         st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.base[threadIdx.x] + a.win.ret_flags) + a.me, (unsigned long long)(a.ctl[0]) << 32);
     }
-}
-
-// Sender side: waits until every owner has returned the results of the current epoch.
-__global__ void ep_returned_kernel(EpArgs a) {
-    const uint8_t* mine = a.peers.base[a.me];
-    if (threadIdx.x < a.world) ep_wait(reinterpret_cast<const unsigned long long*>(mine + a.win.ret_flags) + threadIdx.x, a.ctl[0], a.status, a.wait_ns);
 }
 
 // rows[i, :] = x[perm[i] / K, :] (16-byte pieces), row_experts[i] = ids[perm[i]], for i < offsets[E].
@@ -213,14 +147,14 @@ __global__ void ep_scatter_kernel(const float* __restrict__ y, const int32_t* __
     for (uint32_t j = threadIdx.x; j < H / 4; j += blockDim.x) dst[j] = src[j];
 }
 
+}  // namespace
+
 EpArgs ep_args(const zc_moe* m) {
     EpArgs a{};
     a.peers = m->ep_peers; a.win = m->ep_layout; a.me = m->ep_rank; a.world = m->ep_world; a.per = m->d.local_experts;
     a.ctl = m->ep_ctl; a.status = m->scratch.status; a.wait_ns = (unsigned long long)(m->ep_wait_ms) * 1000000ull;
     return a;
 }
-
-}  // namespace
 
 int launch_ep_gather(zc_moe* m, const Call& c, void* rows, int32_t* row_experts, cudaStream_t s) {
     const uint32_t row_bytes = c.H * (c.act_dtype == ZC_F32 ? 4 : 2);
@@ -256,13 +190,6 @@ int launch_ep_return(zc_moe* m, cudaStream_t s) {
     Timed t(m, s, KERNEL_EP);
     ep_return_kernel<<<m->ep_world * m->ep_layout.cap, EP_THREADS, 0, s>>>(ep_args(m), m->ep.expert_out, m->ep_counts, m->d.hidden);
     int rc = check_launch(m, "ep return");
-    return rc < 0 ? rc : 1;
-}
-
-int launch_ep_returned(zc_moe* m, cudaStream_t s) {
-    Timed t(m, s, KERNEL_EP);
-    ep_returned_kernel<<<1, 32, 0, s>>>(ep_args(m));
-    int rc = check_launch(m, "ep wait for results");
     return rc < 0 ? rc : 1;
 }
 

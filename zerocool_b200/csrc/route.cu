@@ -321,6 +321,21 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const int32_t*
     permute_any<PERMUTE_THREADS>(ids, slots, E, first_expert, local_experts, offsets, perm, active, items, counters, layer, status, hist);
 }
 
+// Expert-parallel owner: wait for the sources' rows, write the expert id of every row slot, and sort the slots, in one
+// launch of one CTA (the two steps were separate launches of the same shape; one of them is a wait).
+__global__ void __launch_bounds__(PERMUTE_THREADS) ep_receive_permute_kernel(EpArgs a, int32_t* __restrict__ row_ids, uint32_t* __restrict__ counts,
+                                                                              uint32_t slots, uint32_t E, uint32_t first_expert, uint32_t local_experts,
+                                                                              int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
+                                                                              int32_t* __restrict__ active, int4* __restrict__ items, int32_t* __restrict__ counters, uint32_t layer) {
+    extern __shared__ int32_t hist[];
+    __shared__ uint32_t count_s[EP_MAX_RANKS];
+    const uint32_t used = min(uint32_t(PERMUTE_THREADS / 32), (slots + permute_range(slots, PERMUTE_THREADS / 32) - 1) / max(permute_range(slots, PERMUTE_THREADS / 32), 1u));
+    for (uint32_t i = threadIdx.x; i < used * E; i += PERMUTE_THREADS) hist[i] = 0;
+    ep_receive_body(a, row_ids, counts, count_s);
+    __syncthreads();                        // the ids written above are read back by other threads of this CTA
+    permute_any<PERMUTE_THREADS>(row_ids, slots, E, first_expert, local_experts, offsets, perm, active, items, counters, layer, nullptr, hist);
+}
+
 // Long batches (tens of thousands of slots): the same stable counting sort by many CTAs, in three launches.
 //   permute_count_kernel: CTA b counts the experts of its PERMUTE_BLOCK consecutive slots      -> blocks[b][e]
 //   permute_scan_kernel:  one CTA turns each expert's column into an exclusive running count over the CTAs
@@ -585,6 +600,19 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(RouteArgs a) {
 }  // namespace
 
 size_t permute_block_count(size_t slots) { return (slots + PERMUTE_BLOCK - 1) / PERMUTE_BLOCK; }
+
+int launch_ep_receive_permute(zc_moe* m, const Call& q, cudaStream_t s) {
+    const size_t slots = size_t(q.T) * q.K;
+    if (slots > 4096 || q.E % 32 || q.E > 1024 || slots != size_t(m->ep_world) * m->ep_layout.cap) return 0;       // the caller issues the two launches
+    static SmemOptIn configured;
+    if (opt_in_smem(ep_receive_permute_kernel, configured, m->device, 160 * 1024) != cudaSuccess) return check_launch(m, "permute attribute");
+    const size_t hist_bytes = size_t(PERMUTE_THREADS / 32) * q.E * sizeof(int32_t);
+    Timed t(m, s, KERNEL_EP);
+    ep_receive_permute_kernel<<<1, PERMUTE_THREADS, hist_bytes, s>>>(ep_args(m), m->ep_row_ids, m->ep_counts, uint32_t(slots), q.E, q.first_expert, q.local_experts,
+                                                                    q.offsets, q.perm, q.active, q.items, q.counters, q.layer);
+    const int rc = check_launch(m, "ep receive + permute");
+    return rc < 0 ? rc : 1;
+}
 
 int launch_forced_weights(zc_moe* m, const Call& c, const int32_t* forced, cudaStream_t s) {
     if (c.K > 32) return fail(m, ZC_EINVAL, "route: top_k above 32");
