@@ -33,18 +33,28 @@ def build(force=False, verbose=False, ptxas_info=False):
     env = dict(os.environ)
     env.pop("CXX", None)
     env.pop("CC", None)
+    jobs = []
     for name in SOURCES:
         src = os.path.join(CSRC, name)
         obj = os.path.join(CSRC, name[:-3] + ".o")
         objects.append(obj)
         if force or _stale(obj, [src] + headers):
             extra = os.environ.get("ZC_NVCC_FLAGS", "").split()
-            cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
-            r = subprocess.run(cmd, capture_output=True, text=True, env=env)
-            if verbose or ptxas_info or r.returncode:
-                sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
-            if r.returncode:
-                raise RuntimeError("nvcc failed on " + name)
+            jobs.append((name, [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]))
+
+    def compile_one(job):
+        name, cmd = job
+        return name, cmd, subprocess.run(cmd, capture_output=True, text=True, env=env)
+
+    # the translation units are independent: compile them side by side (the largest one takes minutes)
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
+        results = list(pool.map(compile_one, jobs))
+    for name, cmd, r in results:
+        if verbose or ptxas_info or r.returncode:
+            sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+        if r.returncode:
+            raise RuntimeError("nvcc failed on " + name)
     if force or _stale(LIB, objects):
         cmd = [_nvcc(), "-shared", "-o", LIB] + objects + ["-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, capture_output=True, text=True, env=env)
