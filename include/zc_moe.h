@@ -293,8 +293,8 @@ int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* ou
  *   "few_tiles_gate_up" (default 1), "few_tiles_down" (default 2), 1..4: 16-row tiles per warp of those streaming
  *   launches (few experts have work there: fewer tiles per warp mean more, shorter CTAs per expert).
  *   "meta_blocks" (default 1): the streaming kernels fetch scales and biases eight groups at a time (16-byte copies)
- *   for gate/up at hidden >= 4096; 2 does so wherever the layout allows, 0 never (each ring stage's own halves, 4- or
- *   8-byte copies). Results are identical.
+ *   for gate/up at hidden >= 4096; 2 does so wherever the layout allows, 3 uses four-group blocks for gate/up, 0 never
+ *   (each ring stage's own halves, 4- or 8-byte copies). Results are identical.
  * Changing an option drops the cached graphs of zc_moe_stack. */
 int zc_moe_set_option(zc_moe* moe, const char* name, int value);
 

@@ -909,7 +909,7 @@ int zc_moe_set_option(zc_moe* m, const char* name, int value) {
         return ZC_OK;
     }
     if (!std::strcmp(name, "meta_blocks")) {
-        if (value < 0 || value > 2) return fail(m, ZC_EINVAL, "meta_blocks must be 0, 1 or 2");
+        if (value < 0 || value > 3) return fail(m, ZC_EINVAL, "meta_blocks must be 0..3");
         DeviceGuard guard(m->device);
         drop_graphs(m);
         m->meta_blocks = uint32_t(value);

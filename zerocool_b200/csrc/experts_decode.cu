@@ -66,7 +66,7 @@ template <int BITS, int CHT> struct Fmt {
     static constexpr int MATRIX = CODES;                  // a ring stage holds the codes only
     // Metadata of a matrix, beside the ring: [buffer][row][scale, bias][MG halves]. MG = 8 groups per block (one 16-byte
     // copy per (row, kind), two buffers) where a warp walks K in order, else MG = CHT (one block per ring stage).
-    __host__ __device__ static constexpr int meta_area(bool mb8, int stages) { return mb8 ? 2 * 32 * 16 : stages * 32 * CHT * 2; }     // bytes per matrix per warp
+    __host__ __device__ static constexpr int meta_area(int mbg, int stages) { return mbg ? 2 * 32 * mbg * 2 : stages * 32 * CHT * 2; }     // bytes per matrix per warp (mbg: groups per block, 0 = per stage)
     // Rows whose lines fall into the same 128-byte bank window are ROWS_PER_WINDOW apart; the block index of a row is
     // xor-ed with swizzle(row) so that rows read together by one MMA fragment load use different banks.
     static constexpr int ROWS_PER_WINDOW = LINE >= 128 ? 1 : 128 / LINE;
@@ -235,7 +235,7 @@ struct LaneSource {
 // metadata that goes with it. MB8: one 16-byte copy per (row, kind) every eight groups, into buffer meta_buf of two (a
 // 4-byte copy per chunk moves a whole 32-byte sector for it and costs as many shared-memory wavefronts as a code copy);
 // otherwise the chunk's own scale and bias halves, into the buffer of its ring slot.
-template <int BITS, int CHT, bool MB8>
+template <int BITS, int CHT, int MBG>
 __device__ __forceinline__ void issue_matrix(uint32_t stage, uint32_t meta_area, const LaneSource<BITS, CHT>& src, uint32_t grp0, uint32_t meta_buf, bool meta_now) {
     using F = Fmt<BITS, CHT>;
     const uint8_t* g0 = src.tile_codes + grp0 * F::ROWB;
@@ -243,8 +243,10 @@ __device__ __forceinline__ void issue_matrix(uint32_t stage, uint32_t meta_area,
     for (int p = 0; p < F::PASSES; ++p)
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + src.dst0 + p * F::ROWS_PER_PASS * F::LINE),
                      "l"(g0 + size_t(p * F::ROWS_PER_PASS) * src.row_bytes) : "memory");
-    if constexpr (MB8) {
+    if constexpr (MBG == 8) {
         if (meta_now) asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(meta_area + meta_buf * 512 + src.meta_pair * 16), "l"(src.tile_meta + grp0 * 2) : "memory");
+    } else if constexpr (MBG == 4) {
+        if (meta_now) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(meta_area + meta_buf * 256 + src.meta_pair * 8), "l"(src.tile_meta + grp0 * 2) : "memory");
     } else if constexpr (CHT == 4) {
         asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(meta_area + meta_buf * (32 * CHT * 2) + src.meta_pair * CHT * 2), "l"(src.tile_meta + grp0 * 2) : "memory");
     } else {
@@ -335,15 +337,17 @@ __device__ __forceinline__ void group_mma(float (&d)[4], float c0, float c1, con
 //       go to two different warps, which halves the registers and ring of a warp (three CTAs per SM instead
 //       of two) at the price of meeting in shared memory for the SwiGLU.
 //   CH: quantisation groups per ring stage (4 when K is a multiple of 256, else 2; Q8 always 2).
-//   MB8: scales and biases arrive eight groups at a time (needs KS = 1 and a group count that is a multiple of eight).
-template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH, bool MB8>
+//   MBG: scales and biases arrive MBG = 8 or 4 groups at a time (needs KS = 1 and a group count that is a multiple of MBG); 0: with every ring stage.
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH, int MBG>
 __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN : (MW == 2 ? 3 : ZC_MIN_BLOCKS)) expert_kernel(Call c, uint32_t tiles_per_warp) {
     using F = Fmt<BITS, CH>;
     constexpr int STAGES = stages_for(NMAT / MW, CH);
     constexpr int WM = NMAT / MW;                    // matrices per warp
     constexpr int RT = WARPS / (KS * MW);
     constexpr int STAGE = WM * F::MATRIX;
-    constexpr int META_AREA = F::meta_area(MB8, STAGES);
+    constexpr int META_AREA = F::meta_area(MBG, STAGES);
+    constexpr bool MB8 = MBG != 0;                   // metadata in blocks of MBG groups
+    constexpr int MBLOCK = MBG ? MBG : 8;
     constexpr bool VIA_SMEM = KS > 1 || MW > 1;
     constexpr int WORDS = F::ROWB / 16;              // 32-bit words per lane per row per group: 2 (Q4) / 4 (Q8)
     constexpr bool FOLDQ = FOLD && BITS == 4;
@@ -393,10 +397,10 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
         auto issue = [&]() {
             if (is_tile < my_tiles) {
                 const uint32_t stage = ring_base + is_slot * STAGE, grp0 = (ks + is_chunk * KS) * CH;
-                const bool meta_now = MB8 && (is_chunk * CH) % 8 == 0;
+                const bool meta_now = MB8 && (is_chunk * CH) % MBLOCK == 0;
                 const uint32_t meta_buf = MB8 ? (is_mblk & 1) : is_slot;
 #pragma unroll
-                for (int m = 0; m < WM; ++m) issue_matrix<BITS, CH, MB8>(stage + m * F::MATRIX, meta_base + m * META_AREA, src[m], grp0, meta_buf, meta_now);
+                for (int m = 0; m < WM; ++m) issue_matrix<BITS, CH, MBG>(stage + m * F::MATRIX, meta_base + m * META_AREA, src[m], grp0, meta_buf, meta_now);
                 if (meta_now) ++is_mblk;
                 if (++is_chunk == my_n) {
                     is_chunk = 0; ++is_tile;
@@ -454,9 +458,9 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
                 __syncwarp();
                 const uint8_t* stage = my_ring + slot * STAGE;
                 // this chunk's scale and bias halves: at its place in the current 8-group block (MB8), or in the buffer of its slot
-                if (MB8 && (i * CH) % 8 == 0) ++mblk;
-                constexpr uint32_t PAIR = MB8 ? 16u : uint32_t(CH * 2);          // bytes of one (row, kind) entry
-                const uint8_t* mbase = MB8 ? my_meta + ((mblk - 1) & 1) * 512 + ((i * CH) % 8) * 2 : my_meta + slot * (32 * CH * 2);
+                if (MB8 && (i * CH) % MBLOCK == 0) ++mblk;
+                constexpr uint32_t PAIR = MB8 ? uint32_t(MBLOCK * 2) : uint32_t(CH * 2);          // bytes of one (row, kind) entry
+                const uint8_t* mbase = MB8 ? my_meta + ((mblk - 1) & 1) * (32 * PAIR) + ((i * CH) % MBLOCK) * 2 : my_meta + slot * (32 * CH * 2);
                 slot = slot + 1 == STAGES ? 0 : slot + 1;
                 issue();          // refills the slot consumed by the previous iteration while this chunk is multiplied
                 const uint32_t grp0 = (ks + i * KS) * CH;
@@ -556,20 +560,20 @@ __global__ void __launch_bounds__(EXPERT_THREADS, NMAT == 1 ? ZC_MIN_BLOCKS_DOWN
     }
 }
 
-template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH, bool MB8>
+template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH, int MBG>
 int launch_expert_mb(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
     constexpr int RT = WARPS / (KS * MW);
     constexpr int STAGES = stages_for(NMAT / MW, CH);
     const uint32_t K = NMAT == 2 ? c.H : c.F, N = NMAT == 2 ? c.F : c.H, G = K / 64;
     const size_t smem = size_t(SPLIT ? 2 : 1) * NTOK * (K + ROW_PAD) * 2 + size_t(G) * NTOK * 2 * 4 +
-                        size_t(WARPS) * (NMAT / MW) * (STAGES * Fmt<BITS, CH>::MATRIX + Fmt<BITS, CH>::meta_area(MB8, STAGES)) + ((KS > 1 || MW > 1) ? size_t(KS) * NMAT * RT * 16 * NTOK * 4 : 0);
+                        size_t(WARPS) * (NMAT / MW) * (STAGES * Fmt<BITS, CH>::MATRIX + Fmt<BITS, CH>::meta_area(MBG, STAGES)) + ((KS > 1 || MW > 1) ? size_t(KS) * NMAT * RT * 16 * NTOK * 4 : 0);
     if (smem > 220 * 1024) return fail(m, ZC_EINVAL, "expert kernel: shape needs too much shared memory");
     while (tiles_per_warp > 1 && N % (16 * RT * tiles_per_warp)) --tiles_per_warp;
     if (N % (16 * RT * tiles_per_warp)) return fail(m, ZC_EINVAL, "expert kernel: rows not a multiple of the CTA tile");
     // Items that can have more than eight rows (two or more rows per expert on average, or the few-row side of a long
     // batch with its limit above eight): their passes run as separate CTAs.
     const uint32_t pass_ctas = (KS == 1 && (c.item_rows_max > NTOK || uint64_t(c.T) * c.K >= 2ull * c.local_experts)) ? 2u : 1u;
-    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, MB8>;
+    auto kernel = expert_kernel<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, MBG>;
     static SmemOptIn configured;        // one per instantiation of this function template
     if (opt_in_smem(kernel, configured, m->device, smem) != cudaSuccess) return check_launch(m, "expert kernel attribute");
     Timed t(m, s, NMAT == 2 ? KERNEL_GATE_UP : KERNEL_DOWN);
@@ -582,16 +586,20 @@ int launch_expert_mb(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_pe
 // 16-byte aligned; used for gate/up with long rows (hidden 4096: 423 -> 368 us at 512 experts x 5 rows). With short rows
 // the extra kilobyte per warp pushes two CTAs per SM over a shared-memory carve-out step, which costs the L1 that serves
 // the small copies (97 -> 104 us at hidden 2048), and down's short K does not gain (56 -> 58 us): those keep one block per
-// ring stage. Option meta_blocks: 0 never, 1 by this rule, 2 wherever possible.
+// ring stage. Option meta_blocks: 0 never, 1 by this rule, 2 wherever possible, 3 four-group blocks for gate/up.
 template <int BITS, bool SPLIT, int NMAT, int KS, bool FOLD, bool META_F16, int MW, int CH>
 int launch_expert_ch(zc_moe* m, const Call& c, uint32_t items, uint32_t tiles_per_warp, cudaStream_t s) {
     if constexpr (KS == 1) {
         const uint32_t K = NMAT == 2 ? c.H : c.F, G = K / 64;
         const bool long_rows = NMAT == 2 && K >= 4096;
         if (G % 8 == 0 && (m->meta_blocks == 2 || (m->meta_blocks == 1 && long_rows)))
-            return launch_expert_mb<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, true>(m, c, items, tiles_per_warp, s);
+            return launch_expert_mb<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, 8>(m, c, items, tiles_per_warp, s);
+        if constexpr (CH == 2 && NMAT == 2) {       // 4-group blocks (8-byte copies every second stage; stays inside the carve-out): 99.7 against 98.1 us at hidden 2048, so only on request
+            if (G % 4 == 0 && m->meta_blocks == 3)
+                return launch_expert_mb<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, 4>(m, c, items, tiles_per_warp, s);
+        }
     }
-    return launch_expert_mb<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, false>(m, c, items, tiles_per_warp, s);
+    return launch_expert_mb<BITS, SPLIT, NMAT, KS, FOLD, META_F16, MW, CH, 0>(m, c, items, tiles_per_warp, s);
 }
 
 // Two groups per ring stage for gate/up: four groups per stage (a full 128-byte line per Q4 row) leave room for
