@@ -295,6 +295,8 @@ int zc_moe_stack_host(zc_moe* moe, const void* x_host, uint32_t tokens, void* ou
  *   "meta_blocks" (default 1): the streaming kernels fetch scales and biases eight groups at a time (16-byte copies)
  *   for gate/up at hidden >= 4096; 2 does so wherever the layout allows, 3 uses four-group blocks for gate/up, 0 never
  *   (each ring stage's own halves, 4- or 8-byte copies). Results are identical.
+ *   "router_db" (default 1): long batches with FP32 router rows and BF16 activations use the double-buffered router
+ *   tiles; 0 selects the single-buffer form. Results are identical.
  * Changing an option drops the cached graphs of zc_moe_stack. */
 int zc_moe_set_option(zc_moe* moe, const char* name, int value);
 

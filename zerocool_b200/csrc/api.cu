@@ -908,6 +908,13 @@ int zc_moe_set_option(zc_moe* m, const char* name, int value) {
         (name[10] == 'g' ? m->few_tiles_gate_up : m->few_tiles_down) = uint32_t(value);
         return ZC_OK;
     }
+    if (!std::strcmp(name, "router_db")) {
+        if (value != 0 && value != 1) return fail(m, ZC_EINVAL, "router_db must be 0 or 1");
+        DeviceGuard guard(m->device);
+        drop_graphs(m);
+        m->router_db = uint32_t(value);
+        return ZC_OK;
+    }
     if (!std::strcmp(name, "meta_blocks")) {
         if (value < 0 || value > 3) return fail(m, ZC_EINVAL, "meta_blocks must be 0..3");
         DeviceGuard guard(m->device);

@@ -269,6 +269,7 @@ struct zc_moe {
     uint32_t pdl = 0xffffffffu;   // bit per KernelKind: that kernel launches with programmatic stream serialization (see launch_chained)
     bool exact_h = false;         // down reads the FP32 SwiGLU rows as two FP16 terms instead of one
     uint32_t few_tiles_gate_up = 1, few_tiles_down = 2;      // 16-row tiles per warp of the streaming launches for those experts (few items: more, shorter CTAs)
+    uint32_t router_db = 1;              // long batches: double-buffered whole-K router tiles (FP32 router rows, BF16 activations)
     uint32_t meta_blocks = 1;            // streaming kernels fetch scales and biases eight groups at a time: 0 never, 1 for gate/up with long rows, 2 wherever possible
     uint32_t prefill_small_rows = 16;   // long batches: experts with at most this many rows run on the streaming kernels (0 = none)
     bool prefill_wide = true;     // long batches: wide-tile kernel with accumulators resident in TMEM (false: per-group drain kernel)

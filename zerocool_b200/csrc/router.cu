@@ -576,7 +576,146 @@ ZC_UNROLL(ZC_RL_UNROLL)
     }
 }
 
+// The same whole-K tile for the common format - FP32 router rows, BF16 activations - with the two tiles double-buffered:
+// the activations stay BF16 in shared memory (they become FP32 in registers, the same values), so both tiles are plain
+// 16-byte cp.async copies, and partition p + 1 is fetched while partition p is multiplied. With one buffer the two CTAs
+// of an SM start together and stay in step, so the FMA pipe idles through every staging phase (ncu: FMA pipe 41 %).
+__global__ void __launch_bounds__(LONG_THREADS, 2) router_long_db_kernel(Call c) {
+    extern __shared__ __align__(16) float smem[];
+    const uint32_t H = c.H, part = H / 16, LD = part + 4, LDH = part + 8;
+    const uint32_t w_floats = LONG_RT * LD, stage_bytes = w_floats * 4 + LONG_TT * LDH * 2;       // one stage: [64][LD] floats, then [64][LDH] halves
+    const uint32_t e0 = blockIdx.x * LONG_RT, t0 = blockIdx.y * LONG_TT;
+    const uint32_t rows_total = c.E + (c.has_shared ? 1u : 0u);
+    const uint32_t tid = threadIdx.x, tx = tid % LONG_TXN, ty = tid / LONG_TXN, warp = tid / 32, lane = tid % 32;
+    const uint32_t rows_here = min(uint32_t(LONG_RT), rows_total - e0);
+    const bool narrow = rows_here <= LONG_THREADS / LONG_TT;
+    auto ws_of = [&](uint32_t stage) { return reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(smem) + stage * stage_bytes); };
+    auto xh_of = [&](uint32_t stage) { return reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(smem) + stage * stage_bytes + w_floats * 4); };
+    auto issue = [&](uint32_t p) {
+        const uint32_t k0 = p * part;
+        float* ws = ws_of(p & 1);
+        uint16_t* xh = xh_of(p & 1);
+        for (uint32_t el = warp; el < (narrow ? rows_here : uint32_t(LONG_RT)); el += LONG_THREADS / 32) {
+            const uint32_t e = e0 + el;
+            float* dst = ws + el * LD;
+            if (e >= rows_total) {
+                for (uint32_t kq = lane; kq < part / 4; kq += 32) *reinterpret_cast<float4*>(dst + kq * 4) = make_float4(0, 0, 0, 0);
+            } else {
+                const float* base = (e < c.E ? static_cast<const float*>(c.router_w) + size_t(e) * H : static_cast<const float*>(c.shared_gate_w)) + k0;
+                for (uint32_t kq = lane; kq < part / 4; kq += 32) cp_async16(dst + kq * 4, base + kq * 4);
+            }
+        }
+        for (uint32_t tt = warp * 2 + lane / 16; tt < LONG_TT; tt += LONG_THREADS / 16) {      // a half-warp takes a row of 16-byte pieces
+            const uint32_t t = t0 + tt;
+            const uint16_t* base = static_cast<const uint16_t*>(c.x) + size_t(t) * H + k0;
+            for (uint32_t kb = lane % 16; kb < part / 8; kb += 16) {
+                if (t < c.T) cp_async16(xh + tt * LDH + kb * 8, base + kb * 8);
+                else *reinterpret_cast<uint4*>(xh + tt * LDH + kb * 8) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto x4 = [](uint2 raw) { return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u)); };
+    float total[LONG_RI][LONG_TJ];
+#pragma unroll
+    for (int i = 0; i < LONG_RI; ++i)
+#pragma unroll
+        for (int j = 0; j < LONG_TJ; ++j) total[i][j] = 0.0f;
+    pdl_wait();
+    issue(0);
+    for (uint32_t p = 0; p < 16; ++p) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                     // partition p has landed for everyone, and partition p - 1 has been consumed
+        if (p + 1 < 16) issue(p + 1);        // into the buffer partition p - 1 used
+        const float* ws = ws_of(p & 1);
+        const uint16_t* xh = xh_of(p & 1);
+        if (narrow) {
+            const uint32_t tt = tid % LONG_TT, rr = tid / LONG_TT;
+            float a = 0.0f;
+            if (rr < rows_here) {
+                const float* wr = ws + rr * LD;
+                for (uint32_t k = 0; k < part; k += 4) {
+                    const float4 wv = *reinterpret_cast<const float4*>(wr + k), xv = x4(*reinterpret_cast<const uint2*>(xh + tt * LDH + k));
+                    a = __fmaf_rn(xv.x, wv.x, a);
+                    a = __fmaf_rn(xv.y, wv.y, a);
+                    a = __fmaf_rn(xv.z, wv.z, a);
+                    a = __fmaf_rn(xv.w, wv.w, a);
+                }
+            }
+            total[0][0] = __fadd_rn(total[0][0], a);
+            continue;
+        }
+        float acc[LONG_RI][LONG_TJ];
+#pragma unroll
+        for (int i = 0; i < LONG_RI; ++i)
+#pragma unroll
+            for (int j = 0; j < LONG_TJ; ++j) acc[i][j] = 0.0f;
+        const float* wrow = ws + tx * LD;
+#pragma unroll 2
+        for (uint32_t k = 0; k < part; k += 4) {
+            float4 wv[LONG_RI], xv[LONG_TJ];
+#pragma unroll
+            for (int i = 0; i < LONG_RI; ++i) wv[i] = *reinterpret_cast<const float4*>(wrow + i * LONG_TXN * LD + k);
+#pragma unroll
+            for (int j = 0; j < LONG_TJ; ++j) xv[j] = x4(*reinterpret_cast<const uint2*>(xh + (ty + j * LONG_TYN) * LDH + k));
+#pragma unroll
+            for (int i = 0; i < LONG_RI; ++i)
+#pragma unroll
+                for (int j = 0; j < LONG_TJ; ++j) {
+                    float a = acc[i][j];
+                    a = __fmaf_rn(xv[j].x, wv[i].x, a);
+                    a = __fmaf_rn(xv[j].y, wv[i].y, a);
+                    a = __fmaf_rn(xv[j].z, wv[i].z, a);
+                    a = __fmaf_rn(xv[j].w, wv[i].w, a);
+                    acc[i][j] = a;
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < LONG_RI; ++i)
+#pragma unroll
+            for (int j = 0; j < LONG_TJ; ++j) total[i][j] = __fadd_rn(total[i][j], acc[i][j]);      // partial p joins the ordered sum
+    }
+    pdl_launch_dependents();
+    if (narrow) {
+        const uint32_t tt = tid % LONG_TT, rr = tid / LONG_TT, e = e0 + rr, t = t0 + tt;
+        if (rr < rows_here && t < c.T) {
+            if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(total[0][0], c.router_bias[e]) : total[0][0];
+            else c.gate_logit[t] = total[0][0];
+        }
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < LONG_RI; ++i) {
+        const uint32_t e = e0 + tx + LONG_TXN * i;
+        if (e >= rows_total) continue;
+#pragma unroll
+        for (int j = 0; j < LONG_TJ; ++j) {
+            const uint32_t t = t0 + ty + LONG_TYN * j;
+            if (t >= c.T) continue;
+            if (e < c.E) c.logits[size_t(t) * c.E + e] = c.router_bias ? __fadd_rn(total[i][j], c.router_bias[e]) : total[i][j];
+            else c.gate_logit[t] = total[i][j];
+        }
+    }
+}
+
 int launch_router_long(zc_moe* m, const Call& c, cudaStream_t s) {
+    if (c.router_dtype == ZC_F32 && c.act_dtype != ZC_F32 && m->router_db) {       // the double-buffered form
+        const uint32_t partd = c.H / 16;
+        const size_t bytes = 2 * (size_t(LONG_RT) * (partd + 4) * 4 + size_t(LONG_TT) * (partd + 8) * 2);
+        static SmemOptIn configured_db;
+        if (bytes <= 110 * 1024 && opt_in_smem(router_long_db_kernel, configured_db, m->device, bytes) == cudaSuccess) {
+            const uint32_t rows = c.E + (c.has_shared ? 1 : 0);
+            int rcd;
+            {
+                Timed t(m, s, KERNEL_ROUTER);
+                const cudaError_t e = launch_chained(m, -1, router_long_db_kernel, dim3((rows + LONG_RT - 1) / LONG_RT, (c.T + LONG_TT - 1) / LONG_TT), dim3(LONG_THREADS), bytes, s, nullptr, 0, c);
+                if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("router (long, double-buffered) launch: ") + cudaGetErrorString(e));
+                rcd = check_launch(m, "router");
+            }
+            return rcd < 0 ? rcd : 1;
+        }
+        cudaGetLastError();
+    }
     const uint32_t part = c.H / 16, LD = part + 4;
     const size_t smem = size_t(LONG_RT + LONG_TT) * LD * sizeof(float);
     if (smem > 200 * 1024) return 0;
