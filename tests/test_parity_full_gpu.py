@@ -507,3 +507,30 @@ def test_metadata_blocks_give_the_same_bits(tokens):
                             shared_record=synth.record(cfg, SEED, 0, synth.SHARED_EXPERT), shared_gate_w=synth.shared_gate(cfg, SEED, 0))
     assert np.array_equal(routing["ids"], want["ids"])
     assert util.rel_max_error(blocks.float().cpu().numpy(), want["out"]) <= TOL
+
+
+def test_tuning_switches_do_not_change_a_bit():
+    """Every switch that only moves work around (copy sizes of the metadata, CTAs per few-row expert, router tile
+    buffering, prefetch form, dependent launches) must leave a long batch and a short batch bit-identical."""
+    import torch
+    cfg = util.cfg2(max_tokens=1280)
+    m = make(cfg)
+    m.synth_fill_layer(0, SEED)
+    m.set_router_bias(0, synth.zipf_router_bias(cfg, SEED, 0))
+    long_x = device_x(m, synth.activations(cfg, SEED, 0, 1200))          # whole-K router tiles, hybrid dispatch, many-CTA permutation
+    short_x = device_x(m, synth.activations(cfg, SEED, 1, 24))
+    base_long, base_short = m.moe(0, long_x).clone(), m.moe(0, short_x).clone()
+    ids_long = m.last_routing(24)["ids"].copy()
+    for name, value, restore in (("meta_blocks", 0, 1), ("meta_blocks", 2, 1), ("meta_blocks", 3, 1), ("few_tiles_gate_up", 2, 1),
+                                 ("few_tiles_down", 4, 2), ("router_db", 0, 1), ("pdl", 0, 1)):
+        m.set_option(name, value)
+        assert torch.equal(m.moe(0, long_x), base_long), (name, value)
+        assert torch.equal(m.moe(0, short_x), base_short), (name, value)
+        assert np.array_equal(m.last_routing(24)["ids"], ids_long)
+        m.set_option(name, restore)
+    assert m.status() == 0
+    # fold_q4 is not in that list: removing the 1024 offset in FP16 before the product instead of from the FP32 group sum
+    # changes the rounding of the group sums (both forms are inside the tolerance, the folded one is the default)
+    m.set_option("fold_q4", 0)
+    unfolded = m.moe(0, short_x)
+    assert util.rel_max_error(unfolded.float().cpu().numpy(), base_short.float().cpu().numpy()) <= TOL
