@@ -68,6 +68,8 @@ __device__ __forceinline__ bool ep_last_block(uint32_t* counter) {
 // block to finish publishes {epoch, rows for that owner} to every owner.
 __global__ void __launch_bounds__(EP_THREADS) ep_send_kernel(EpArgs a, const void* __restrict__ x, uint32_t row_bytes, const int32_t* __restrict__ perm,
                                                              const int32_t* __restrict__ ids, const int32_t* __restrict__ offsets, uint32_t E, uint32_t K) {
+    pdl_wait();                             // the routing kernel's lists
+    pdl_launch_dependents();
     const uint32_t i = blockIdx.x, total = uint32_t(offsets[E]);
     if (i < total) {
         const uint32_t slot = uint32_t(perm[i]);
@@ -107,6 +109,8 @@ __global__ void __launch_bounds__(1024) ep_receive_kernel(EpArgs a, int32_t* __r
 // Owner side: result row i of the receive area -> the sender's window at the row's router slot. The last block
 // publishes the return flag to every sender.
 __global__ void __launch_bounds__(EP_THREADS) ep_return_kernel(EpArgs a, const float* __restrict__ y, const uint32_t* __restrict__ counts, uint32_t H) {
+    pdl_wait();                             // the down kernel's result rows
+    pdl_launch_dependents();
     const uint32_t i = blockIdx.x, src = i / a.win.cap, j = i % a.win.cap;
     const uint8_t* mine = a.peers.base[a.me];
     if (src < a.world && j < counts[src]) {
@@ -174,7 +178,11 @@ int launch_ep_scatter(zc_moe* m, const Call& c, const float* y, cudaStream_t s) 
 int launch_ep_send(zc_moe* m, const Call& c, cudaStream_t s) {
     const uint32_t row_bytes = c.H * (c.act_dtype == ZC_F32 ? 4 : 2);
     Timed t(m, s, KERNEL_EP);
-    ep_send_kernel<<<c.T * c.K, EP_THREADS, 0, s>>>(ep_args(m), c.x, row_bytes, c.perm, c.ids, c.offsets, c.E, c.K);
+    // The exchange kernels are links of the layer's launch chain like the others (see launch_chained): set-up overlaps the
+    // tail of the kernel before, and a kernel that waits for a peer does so after its own grid-dependency wait.
+    const cudaError_t e = launch_chained(m, KERNEL_EP, ep_send_kernel, dim3(c.T * c.K), dim3(EP_THREADS), 0, s, nullptr, 0,
+                                         ep_args(m), c.x, row_bytes, c.perm, c.ids, c.offsets, c.E, c.K);
+    if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("ep send launch: ") + cudaGetErrorString(e));
     int rc = check_launch(m, "ep send");
     return rc < 0 ? rc : 1;
 }
@@ -188,7 +196,9 @@ int launch_ep_receive(zc_moe* m, cudaStream_t s) {
 
 int launch_ep_return(zc_moe* m, cudaStream_t s) {
     Timed t(m, s, KERNEL_EP);
-    ep_return_kernel<<<m->ep_world * m->ep_layout.cap, EP_THREADS, 0, s>>>(ep_args(m), m->ep.expert_out, m->ep_counts, m->d.hidden);
+    const cudaError_t e = launch_chained(m, KERNEL_EP, ep_return_kernel, dim3(m->ep_world * m->ep_layout.cap), dim3(EP_THREADS), 0, s, nullptr, 0,
+                                         ep_args(m), static_cast<const float*>(m->ep.expert_out), static_cast<const uint32_t*>(m->ep_counts), m->d.hidden);
+    if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("ep return launch: ") + cudaGetErrorString(e));
     int rc = check_launch(m, "ep return");
     return rc < 0 ? rc : 1;
 }

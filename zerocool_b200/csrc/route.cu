@@ -331,6 +331,8 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) ep_receive_permute_kernel(EpA
     __shared__ uint32_t count_s[EP_MAX_RANKS];
     const uint32_t used = min(uint32_t(PERMUTE_THREADS / 32), (slots + permute_range(slots, PERMUTE_THREADS / 32) - 1) / max(permute_range(slots, PERMUTE_THREADS / 32), 1u));
     for (uint32_t i = threadIdx.x; i < used * E; i += PERMUTE_THREADS) hist[i] = 0;
+    pdl_wait();                             // the send kernel of this rank (its local rows and flag) has completed
+    pdl_launch_dependents();
     ep_receive_body(a, row_ids, counts, count_s);
     __syncthreads();                        // the ids written above are read back by other threads of this CTA
     permute_any<PERMUTE_THREADS>(row_ids, slots, E, first_expert, local_experts, offsets, perm, active, items, counters, layer, nullptr, hist);
@@ -608,8 +610,10 @@ int launch_ep_receive_permute(zc_moe* m, const Call& q, cudaStream_t s) {
     if (opt_in_smem(ep_receive_permute_kernel, configured, m->device, 160 * 1024) != cudaSuccess) return check_launch(m, "permute attribute");
     const size_t hist_bytes = size_t(PERMUTE_THREADS / 32) * q.E * sizeof(int32_t);
     Timed t(m, s, KERNEL_EP);
-    ep_receive_permute_kernel<<<1, PERMUTE_THREADS, hist_bytes, s>>>(ep_args(m), m->ep_row_ids, m->ep_counts, uint32_t(slots), q.E, q.first_expert, q.local_experts,
-                                                                    q.offsets, q.perm, q.active, q.items, q.counters, q.layer);
+    const cudaError_t e = launch_chained(m, KERNEL_EP, ep_receive_permute_kernel, dim3(1), dim3(PERMUTE_THREADS), hist_bytes, s, nullptr, 0,
+                                         ep_args(m), m->ep_row_ids, static_cast<uint32_t*>(m->ep_counts), uint32_t(slots), q.E, q.first_expert, q.local_experts,
+                                         q.offsets, q.perm, q.active, q.items, q.counters, q.layer);
+    if (e != cudaSuccess) return fail(m, ZC_EEXEC, std::string("ep receive launch: ") + cudaGetErrorString(e));
     const int rc = check_launch(m, "ep receive + permute");
     return rc < 0 ? rc : 1;
 }
